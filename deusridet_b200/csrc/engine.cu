@@ -1,0 +1,615 @@
+// engine.cu — the C ABI (include/drkv.h): owns the pool slab, the device block tables and
+// the split-KV scratch, keeps the host bookkeeping (page_book.hpp) and launches the kernels.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/drkv.h"
+#include "kernels.hpp"
+#include "page_book.hpp"
+
+using namespace drkv;
+
+namespace {
+
+thread_local std::string g_err;
+
+int set_err(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+bool geometry_ok(const drkv_geometry& g, std::string* why) {
+    auto bad = [&](const char* m) {
+        *why = m;
+        return false;
+    };
+    if (g.num_layers <= 0 || g.num_q_heads <= 0 || g.num_kv_heads <= 0) return bad("layer/head counts must be positive");
+    if (g.num_q_heads % g.num_kv_heads != 0) return bad("num_q_heads must be a multiple of num_kv_heads");
+    if (g.num_q_heads / g.num_kv_heads > 16) return bad("GQA group larger than 16 is not supported");
+    if (g.head_dim != 64 && g.head_dim != 128 && g.head_dim != 256) return bad("head_dim must be 64, 128 or 256");
+    if (g.page_size <= 0 || g.page_size % 16 != 0) return bad("page_size must be a positive multiple of 16");
+    if (g.dtype != DRKV_DTYPE_F16 && g.dtype != DRKV_DTYPE_BF16) return bad("dtype must be f16 or bf16");
+    if (g.rotary_dim < 0 || g.rotary_dim > g.head_dim || g.rotary_dim % 16 != 0)
+        return bad("rotary_dim must be a multiple of 16 within head_dim");
+    if (g.rotary_dim > 0 && !(g.rope_theta > 0.f)) return bad("rope_theta must be positive");
+    return true;
+}
+
+// freq_i = 1 / theta^(2i / rot) in fp32, the reference's expression
+// (src/machina/layer_attention.cu:45) evaluated once on the host.
+void fill_inv_freq(float theta, int rot, std::vector<float>* out) {
+    out->resize(rot / 2);
+    for (int i = 0; i < rot / 2; i++) (*out)[i] = 1.0f / powf(theta, (2.0f * (float)i) / (float)rot);
+}
+
+size_t page_bytes_all_layers(const drkv_geometry& g) {
+    return (size_t)g.num_layers * 2 * g.num_kv_heads * g.page_size * g.head_dim * 2;
+}
+
+int pick_chunk(int n_seq, int hkv, int max_kv_span) {
+    // Enough CTAs to fill 148 SMs x 2 resident CTAs a few times over, but not so many
+    // chunks that the partials become a visible share of the traffic.
+    const long target_lo = 592, target_hi = 4736;
+    int chunk = 512;
+    auto ctas = [&](int c) { return (long)n_seq * hkv * ((max_kv_span + c - 1) / c); };
+    while (chunk > 64 && ctas(chunk) < target_lo) chunk >>= 1;
+    while (chunk < 4096 && ctas(chunk) > target_hi) chunk <<= 1;
+    return chunk;
+}
+
+}  // namespace
+
+struct drkv_engine {
+    drkv_geometry geom{};
+    drkv_config cfg{};
+    PageBook book;
+    std::mutex mu;  // the reference guards the pool and ensure_blocks_for the same way
+
+    bool has_device = false;
+    int device = -1;
+    void* pool = nullptr;
+    size_t pool_bytes = 0;
+    int32_t* d_tables = nullptr;
+    float* d_inv_freq = nullptr;
+    int* d_error = nullptr;
+    float* d_scratch = nullptr;
+    size_t scratch_bytes = 0;
+    CUtensorMap tmap{};
+    PoolLayout layout{};
+    int forced_chunk = 0;
+
+    // staging for table updates: two pinned buffers used alternately
+    int32_t* h_stage[2] = {nullptr, nullptr};
+    cudaEvent_t stage_done[2] = {nullptr, nullptr};
+    bool stage_busy[2] = {false, false};
+    int stage_next = 0;
+    size_t stage_ints = 0;
+    int64_t sync_bytes = 0, syncs = 0, cow_bytes = 0;
+};
+
+#define LOCK(e) std::lock_guard<std::mutex> lock_((e)->mu)
+#define NEED(e)                                                        \
+    if ((e) == nullptr) return set_err(DRKV_ERR_INVALID, "null engine")
+#define NEED_DEVICE(e)                                                                           \
+    if (!(e)->has_device) return set_err(DRKV_ERR_NO_DEVICE, "engine was created without a device")
+#define CUDA_TRY(expr)                                                                             \
+    do {                                                                                           \
+        cudaError_t ce_ = (expr);                                                                  \
+        if (ce_ != cudaSuccess) return set_err(DRKV_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(ce_)); \
+    } while (0)
+
+static int book_err(drkv_engine* e, int rc) {
+    if (rc < 0) g_err = e->book.error();
+    return rc;
+}
+
+static int run_cow(drkv_engine* e, const std::vector<CowJob>& jobs, cudaStream_t stream) {
+    for (const CowJob& j : jobs) {
+        e->cow_bytes += (int64_t)j.n_slots * e->geom.head_dim * 2 * 2 * e->geom.num_kv_heads * e->geom.num_layers;
+        if (!e->has_device) continue;
+        CowParams cp;
+        cp.layout = e->layout;
+        cp.pool = e->pool;
+        cp.src_page = j.src_page;
+        cp.dst_page = j.dst_page;
+        cp.n_slots = j.n_slots;
+        CUDA_TRY(launch_cow_copy(cp, e->geom.num_layers, stream));
+    }
+    return DRKV_OK;
+}
+
+extern "C" {
+
+const char* drkv_last_error(void) { return g_err.c_str(); }
+
+int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine** out) {
+    if (!geom || !cfg || !out) return set_err(DRKV_ERR_INVALID, "null argument");
+    *out = nullptr;
+    std::string why;
+    if (!geometry_ok(*geom, &why)) return set_err(DRKV_ERR_INVALID, "geometry: %s", why.c_str());
+    if (cfg->max_seqs <= 0) return set_err(DRKV_ERR_INVALID, "max_seqs must be positive");
+
+    const size_t per_page = page_bytes_all_layers(*geom);
+    long max_pages = cfg->max_pages > 0 ? cfg->max_pages : (long)(cfg->budget_bytes / per_page);  // block_pool.cpp:30
+    if (max_pages > 0x7fffffffL) return set_err(DRKV_ERR_INVALID, "too many pages");
+
+    drkv_engine* e = new drkv_engine();
+    e->geom = *geom;
+    e->cfg = *cfg;
+    std::string err;
+    if (!e->book.init((int)max_pages, geom->page_size, cfg->max_seqs, cfg->max_pages_per_seq,
+                      cfg->stream_evict != 0, &err)) {
+        delete e;
+        return set_err(DRKV_ERR_INVALID, "%s (budget %.1f MB, %.1f MB per page)", err.c_str(),
+                       cfg->budget_bytes / 1048576.0, per_page / 1048576.0);
+    }
+    e->layout = PoolLayout::make(geom->num_kv_heads, geom->page_size, geom->head_dim, (int)max_pages);
+    e->pool_bytes = per_page * (size_t)max_pages;
+
+    if (cfg->device >= 0) {
+        auto fail = [&](int code, const char* what, cudaError_t ce) {
+            set_err(code, "%s: %s", what, cudaGetErrorString(ce));
+            drkv_destroy(e);
+            return code;
+        };
+        cudaError_t ce = cudaSetDevice(cfg->device);
+        if (ce != cudaSuccess) return fail(DRKV_ERR_NO_DEVICE, "cudaSetDevice", ce);
+        e->device = cfg->device;
+        e->has_device = true;
+        if ((ce = cudaMalloc(&e->pool, e->pool_bytes)) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(pool)", ce);
+        if ((ce = cudaMemset(e->pool, 0, e->pool_bytes)) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMemset(pool)", ce);
+        const size_t table_ints = (size_t)cfg->max_seqs * e->book.row_width();
+        if ((ce = cudaMalloc(&e->d_tables, table_ints * 4)) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(tables)", ce);
+        if ((ce = cudaMemset(e->d_tables, 0xFF, table_ints * 4)) != cudaSuccess)  // -1 = not resident (cache_manager.cpp:53)
+            return fail(DRKV_ERR_CUDA, "cudaMemset(tables)", ce);
+        e->stage_ints = table_ints;
+        for (int i = 0; i < 2; i++) {
+            if ((ce = cudaHostAlloc(&e->h_stage[i], table_ints * 4, cudaHostAllocDefault)) != cudaSuccess)
+                return fail(DRKV_ERR_CUDA, "cudaHostAlloc(stage)", ce);
+            if ((ce = cudaEventCreateWithFlags(&e->stage_done[i], cudaEventDisableTiming)) != cudaSuccess)
+                return fail(DRKV_ERR_CUDA, "cudaEventCreate", ce);
+        }
+        if ((ce = cudaMalloc(&e->d_error, sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(error)", ce);
+        if ((ce = cudaMemset(e->d_error, 0, sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMemset(error)", ce);
+        std::vector<float> inv;
+        fill_inv_freq(geom->rope_theta, geom->rotary_dim, &inv);
+        if ((ce = cudaMalloc(&e->d_inv_freq, sizeof(float) * (inv.size() + 1))) != cudaSuccess)
+            return fail(DRKV_ERR_CUDA, "cudaMalloc(inv_freq)", ce);
+        if (!inv.empty() &&
+            (ce = cudaMemcpy(e->d_inv_freq, inv.data(), sizeof(float) * inv.size(), cudaMemcpyHostToDevice)) != cudaSuccess)
+            return fail(DRKV_ERR_CUDA, "cudaMemcpy(inv_freq)", ce);
+        // split-KV scratch: every sequence at full table length in 512-key chunks, at least 64 MB
+        const size_t row_tokens = (size_t)e->book.row_width() * geom->page_size;
+        size_t need = (size_t)cfg->max_seqs * geom->num_q_heads * ((row_tokens + 511) / 512) * (geom->head_dim + 2) * 4;
+        e->scratch_bytes = need < (64u << 20) ? (64u << 20) : need;
+        if ((ce = cudaMalloc(&e->d_scratch, e->scratch_bytes)) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(scratch)", ce);
+        const char* terr = nullptr;
+        if (!make_pool_tensor_map(&e->tmap, e->pool, geom->num_layers, (int)max_pages, geom->num_kv_heads,
+                                  geom->page_size, geom->head_dim, &terr)) {
+            set_err(DRKV_ERR_CUDA, "%s", terr ? terr : "tensor map");
+            drkv_destroy(e);
+            return DRKV_ERR_CUDA;
+        }
+    }
+    *out = e;
+    return DRKV_OK;
+}
+
+void drkv_destroy(drkv_engine* e) {
+    if (!e) return;
+    if (e->has_device) {
+        cudaSetDevice(e->device);
+        cudaDeviceSynchronize();
+        cudaFree(e->pool);
+        cudaFree(e->d_tables);
+        cudaFree(e->d_inv_freq);
+        cudaFree(e->d_error);
+        cudaFree(e->d_scratch);
+        for (int i = 0; i < 2; i++) {
+            if (e->h_stage[i]) cudaFreeHost(e->h_stage[i]);
+            if (e->stage_done[i]) cudaEventDestroy(e->stage_done[i]);
+        }
+    }
+    delete e;
+}
+
+int drkv_get_geometry(const drkv_engine* e, drkv_geometry* out) {
+    NEED(e);
+    if (!out) return set_err(DRKV_ERR_INVALID, "null argument");
+    *out = e->geom;
+    return DRKV_OK;
+}
+
+int drkv_get_stats(const drkv_engine* ce, drkv_stats* out) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    NEED(e);
+    if (!out) return set_err(DRKV_ERR_INVALID, "null argument");
+    LOCK(e);
+    out->pages_total = e->book.max_pages();
+    out->pages_free = e->book.free_count();
+    out->pages_cached = (int64_t)e->book.cached_lru().size();
+    out->pages_active = out->pages_total - out->pages_free - out->pages_cached;
+    out->evictions_cached = e->book.n_evict_cached;
+    out->evictions_stream = e->book.n_evict_stream;
+    out->cow_copies = e->book.n_cow;
+    out->cow_bytes = e->cow_bytes;
+    out->table_sync_bytes = e->sync_bytes;
+    out->table_syncs = e->syncs;
+    out->live_seqs = e->book.live_seqs();
+    return DRKV_OK;
+}
+
+// ---- pool -------------------------------------------------------------------------------
+int drkv_pool_alloc(drkv_engine* e) {
+    if (!e) return -1;
+    LOCK(e);
+    return e->book.pool_alloc();
+}
+int drkv_pool_free(drkv_engine* e, int page) {
+    NEED(e);
+    LOCK(e);
+    return book_err(e, e->book.pool_free(page));
+}
+int drkv_pool_free_count(const drkv_engine* ce) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    if (!e) return 0;
+    LOCK(e);
+    return e->book.free_count();
+}
+int drkv_pool_max_pages(const drkv_engine* e) { return e ? e->book.max_pages() : 0; }
+int drkv_pool_page_size(const drkv_engine* e) { return e ? e->book.page_size() : 0; }
+void* drkv_pool_ptr(const drkv_engine* e) { return e ? e->pool : nullptr; }
+size_t drkv_pool_total_bytes(const drkv_engine* e) { return e ? e->pool_bytes : 0; }
+size_t drkv_pool_k_offset(const drkv_engine* e, int layer, int page) {
+    return e ? (size_t)e->layout.row(layer, page, 0, 0, 0) * 2 : 0;  // block_pool.cpp:89-91
+}
+size_t drkv_pool_v_offset(const drkv_engine* e, int layer, int page) {
+    return e ? (size_t)e->layout.row(layer, page, 1, 0, 0) * 2 : 0;  // block_pool.cpp:93-95
+}
+
+// ---- sequences --------------------------------------------------------------------------
+int drkv_seq_create(drkv_engine* e) {
+    NEED(e);
+    LOCK(e);
+    return book_err(e, e->book.seq_create());
+}
+int drkv_seq_release(drkv_engine* e, int seq, int discard) {
+    NEED(e);
+    LOCK(e);
+    return book_err(e, e->book.seq_release(seq, discard != 0));
+}
+int drkv_seq_fork(drkv_engine* e, int parent) {
+    NEED(e);
+    LOCK(e);
+    return book_err(e, e->book.seq_fork(parent));
+}
+int drkv_seq_ensure_pos(drkv_engine* e, int seq, int pos, void* stream) {
+    NEED(e);
+    LOCK(e);
+    std::vector<CowJob> jobs;
+    int rc = e->book.seq_ensure_pos(seq, pos, &jobs);
+    int rc2 = run_cow(e, jobs, (cudaStream_t)stream);
+    return rc < 0 ? book_err(e, rc) : rc2;
+}
+int drkv_seq_ensure_range(drkv_engine* e, int seq, int pos_start, int m, void* stream) {
+    NEED(e);
+    LOCK(e);
+    std::vector<CowJob> jobs;
+    int rc = e->book.seq_ensure_range(seq, pos_start, m, &jobs);
+    int rc2 = run_cow(e, jobs, (cudaStream_t)stream);
+    return rc < 0 ? book_err(e, rc) : rc2;
+}
+int drkv_seq_reserve(drkv_engine* e, int seq, int n_tokens, void* stream) {
+    NEED(e);
+    LOCK(e);
+    int len = e->book.seq_len(seq);
+    if (len < 0) return set_err(DRKV_ERR_STATE, "reserve: unknown sequence");
+    std::vector<CowJob> jobs;
+    int rc = e->book.seq_ensure_range(seq, len, n_tokens, &jobs);
+    int rc2 = run_cow(e, jobs, (cudaStream_t)stream);
+    return rc < 0 ? book_err(e, rc) : rc2;
+}
+int drkv_seq_set_len(drkv_engine* e, int seq, int len) {
+    NEED(e);
+    LOCK(e);
+    return book_err(e, e->book.seq_set_len(seq, len));
+}
+int drkv_seq_len(const drkv_engine* ce, int seq) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    NEED(e);
+    LOCK(e);
+    return e->book.seq_len(seq);
+}
+int drkv_seq_num_pages(const drkv_engine* ce, int seq) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    NEED(e);
+    LOCK(e);
+    return e->book.seq_num_pages(seq);
+}
+int drkv_seq_table(const drkv_engine* ce, int seq, int32_t* out, int cap) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    NEED(e);
+    LOCK(e);
+    const PageBook::Seq* s = e->book.seq(seq);
+    if (!s) return set_err(DRKV_ERR_STATE, "table: unknown sequence");
+    int n = (int)s->table.size() < cap ? (int)s->table.size() : cap;
+    if (n > 0) memcpy(out, s->table.data(), (size_t)n * 4);
+    return n;
+}
+int drkv_seq_adopt(drkv_engine* e, int seq, const int32_t* pages, int n_pages, int n_tokens) {
+    NEED(e);
+    LOCK(e);
+    return book_err(e, e->book.seq_adopt(seq, pages, n_pages, n_tokens));
+}
+
+// ---- eviction ---------------------------------------------------------------------------
+int drkv_seq_evict(drkv_engine* e, int seq, int n) {
+    NEED(e);
+    LOCK(e);
+    return book_err(e, e->book.seq_evict(seq, n));
+}
+int drkv_evict_cached(drkv_engine* e, int n) {
+    NEED(e);
+    LOCK(e);
+    return e->book.evict_cached(n);
+}
+int drkv_ensure_free(drkv_engine* e, int seq, int n_free) {
+    NEED(e);
+    LOCK(e);
+    return e->book.ensure_free(seq, n_free);
+}
+
+// ---- inspection -------------------------------------------------------------------------
+int drkv_refcounts(const drkv_engine* ce, int32_t* out, int cap) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    NEED(e);
+    LOCK(e);
+    const auto& v = e->book.refcounts();
+    int n = (int)v.size() < cap ? (int)v.size() : cap;
+    if (n > 0) memcpy(out, v.data(), (size_t)n * 4);
+    return n;
+}
+int drkv_free_stack(const drkv_engine* ce, int32_t* out, int cap) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    NEED(e);
+    LOCK(e);
+    const auto& v = e->book.free_stack();
+    int n = (int)v.size() < cap ? (int)v.size() : cap;
+    if (n > 0) memcpy(out, v.data(), (size_t)n * 4);
+    return n;
+}
+int drkv_cached_lru(const drkv_engine* ce, int32_t* out, int cap) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    NEED(e);
+    LOCK(e);
+    int n = 0;
+    for (int p : e->book.cached_lru()) {
+        if (n >= cap) break;
+        out[n++] = p;
+    }
+    return n;
+}
+int drkv_evict_log(drkv_engine* e, drkv_evict_record* out, int cap, int clear) {
+    NEED(e);
+    LOCK(e);
+    auto& log = e->book.evict_log();
+    int n = (int)log.size() < cap ? (int)log.size() : cap;
+    for (int i = 0; i < n; i++) out[i] = {log[i].kind, log[i].seq, log[i].logical, log[i].page};
+    int total = (int)log.size();
+    if (clear) log.clear();
+    return out ? n : total;
+}
+
+// ---- device tables ----------------------------------------------------------------------
+int drkv_sync_tables(drkv_engine* e, void* stream_) {
+    NEED(e);
+    NEED_DEVICE(e);
+    LOCK(e);
+    cudaStream_t stream = (cudaStream_t)stream_;
+    std::vector<DirtyRange> dirty;
+    e->book.take_dirty(&dirty);
+    if (dirty.empty()) return DRKV_OK;
+    const int b = e->stage_next;
+    if (e->stage_busy[b]) CUDA_TRY(cudaEventSynchronize(e->stage_done[b]));
+    int32_t* stage = e->h_stage[b];
+    size_t off = 0;
+    const int width = e->book.row_width();
+    for (const DirtyRange& r : dirty) {
+        // A released slot has no Seq to read from any more: its row is all -1.
+        const PageBook::Seq* s = e->book.seq(r.row);
+        const int n = r.hi - r.lo;
+        if (s)
+            memcpy(stage + off, s->table.data() + r.lo, (size_t)n * 4);
+        else
+            memset(stage + off, 0xFF, (size_t)n * 4);
+        CUDA_TRY(cudaMemcpyAsync(e->d_tables + (size_t)r.row * width + r.lo, stage + off, (size_t)n * 4,
+                                 cudaMemcpyHostToDevice, stream));
+        off += n;
+        e->sync_bytes += (int64_t)n * 4;
+    }
+    CUDA_TRY(cudaEventRecord(e->stage_done[b], stream));
+    e->stage_busy[b] = true;
+    e->stage_next ^= 1;
+    e->syncs++;
+    return DRKV_OK;
+}
+const int32_t* drkv_device_tables(const drkv_engine* e) { return e ? e->d_tables : nullptr; }
+int drkv_table_stride(const drkv_engine* e) { return e ? e->book.row_width() : 0; }
+
+int drkv_kernel_error(drkv_engine* e) {
+    NEED(e);
+    NEED_DEVICE(e);
+    int code = 0;
+    CUDA_TRY(cudaMemcpy(&code, e->d_error, sizeof(int), cudaMemcpyDeviceToHost));
+    if (code != 0) {
+        cudaMemset(e->d_error, 0, sizeof(int));
+        return set_err(DRKV_ERR_CUDA, "a kernel reported error code %d (1 = load wait, 2 = ring wait, 3 = page id)", code);
+    }
+    return DRKV_OK;
+}
+
+int drkv_set_chunk_tokens(drkv_engine* e, int chunk_tokens) {
+    NEED(e);
+    if (chunk_tokens != 0 && (chunk_tokens % 64 != 0 || chunk_tokens < 64 || chunk_tokens > 4096))
+        return set_err(DRKV_ERR_INVALID, "chunk_tokens must be 0 (automatic) or a multiple of 64 in [64, 4096]");
+    e->forced_chunk = chunk_tokens;
+    return DRKV_OK;
+}
+
+// ---- append -----------------------------------------------------------------------------
+static AppendParams append_params(drkv_engine* e, int layer) {
+    AppendParams p{};
+    p.layout = e->layout;
+    p.pool = e->pool;
+    p.tables = e->d_tables;
+    p.table_stride = e->book.row_width();
+    p.layer = layer;
+    p.rotary_dim = e->geom.rotary_dim;
+    p.inv_freq = e->d_inv_freq;
+    return p;
+}
+
+int drkv_append_rope(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows, const int32_t* d_pos,
+                     const void* k_src, const void* v_src, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (layer < 0 || layer >= e->geom.num_layers || n_seq < 0 || !d_rows || !d_pos || !k_src || !v_src)
+        return set_err(DRKV_ERR_INVALID, "append_rope: bad argument");
+    AppendParams p = append_params(e, layer);
+    p.rows = d_rows;
+    p.pos = d_pos;
+    p.k_src = k_src;
+    p.v_src = v_src;
+    CUDA_TRY(launch_append_rope(p, n_seq, e->geom.dtype, (cudaStream_t)stream));
+    return DRKV_OK;
+}
+
+int drkv_append_rope_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m, const void* k_src,
+                           const void* v_src, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (layer < 0 || layer >= e->geom.num_layers || m < 0 || pos_start < 0 || !k_src || !v_src || seq < 0 ||
+        seq >= e->book.max_seqs())
+        return set_err(DRKV_ERR_INVALID, "append_rope_chunk: bad argument");
+    AppendParams p = append_params(e, layer);
+    p.rows = nullptr;
+    p.pos = nullptr;
+    p.row = seq;
+    p.pos_start = pos_start;
+    p.k_src = k_src;
+    p.v_src = v_src;
+    CUDA_TRY(launch_append_rope(p, m, e->geom.dtype, (cudaStream_t)stream));
+    return DRKV_OK;
+}
+
+// ---- attention --------------------------------------------------------------------------
+static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows, const int32_t* d_kv_len,
+                         int row, int kv_begin, int kv_end, int max_span, const void* q, void* out,
+                         float* out_partial, float scale, cudaStream_t stream) {
+    const drkv_geometry& g = e->geom;
+    int chunk = e->forced_chunk ? e->forced_chunk : pick_chunk(n_seq, g.num_kv_heads, max_span);
+    auto need_bytes = [&](int c) {
+        return (size_t)n_seq * g.num_q_heads * ((max_span + c - 1) / c) * (g.head_dim + 2) * 4;
+    };
+    while (need_bytes(chunk) > e->scratch_bytes && chunk < 4096) chunk <<= 1;
+    if (need_bytes(chunk) > e->scratch_bytes)
+        return set_err(DRKV_ERR_CAPACITY, "attend: split-KV scratch too small for %d sequences x %d keys", n_seq, max_span);
+    const int max_chunks = (max_span + chunk - 1) / chunk;
+    const size_t n_slots = (size_t)n_seq * g.num_q_heads * max_chunks;
+
+    DecodeParams p{};
+    p.tables = e->d_tables;
+    p.table_stride = e->book.row_width();
+    p.rows = d_rows;
+    p.kv_len = d_kv_len;
+    p.row = row;
+    p.kv_begin = kv_begin;
+    p.kv_end = kv_end;
+    p.q = q;
+    p.part_o = e->d_scratch;
+    p.part_m = e->d_scratch + n_slots * g.head_dim;
+    p.part_l = p.part_m + n_slots;
+    p.layer = layer;
+    p.max_pages = e->book.max_pages();
+    p.num_q_heads = g.num_q_heads;
+    p.num_kv_heads = g.num_kv_heads;
+    p.group = g.num_q_heads / g.num_kv_heads;
+    p.page_size = g.page_size;
+    p.chunk_tokens = chunk;
+    p.max_chunks = max_chunks;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.error_word = e->d_error;
+    CUDA_TRY(launch_attend_decode(e->tmap, p, n_seq, g.head_dim, g.dtype, stream));
+
+    CombineParams c{};
+    c.part_o = p.part_o;
+    c.part_m = p.part_m;
+    c.part_l = p.part_l;
+    c.kv_len = d_kv_len;
+    c.kv_begin = kv_begin;
+    c.kv_end = kv_end;
+    c.num_q_heads = g.num_q_heads;
+    c.head_dim = g.head_dim;
+    c.chunk_tokens = chunk;
+    c.max_chunks = max_chunks;
+    c.out = out;
+    c.out_partial = out_partial;
+    CUDA_TRY(launch_combine(c, n_seq, g.dtype, stream));
+    return DRKV_OK;
+}
+
+int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows, const int32_t* d_kv_len,
+                       int max_kv_len, const void* q, void* out, float scale, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (layer < 0 || layer >= e->geom.num_layers || n_seq < 0 || !d_rows || !d_kv_len || !q || !out || max_kv_len < 0)
+        return set_err(DRKV_ERR_INVALID, "attend_decode: bad argument");
+    if (n_seq == 0 || max_kv_len == 0) return DRKV_OK;
+    return decode_common(e, layer, n_seq, d_rows, d_kv_len, 0, 0, 0, max_kv_len, q, out, nullptr, scale,
+                         (cudaStream_t)stream);
+}
+
+int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end, const void* q, float* part,
+                        float scale, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (layer < 0 || layer >= e->geom.num_layers || seq < 0 || seq >= e->book.max_seqs() || kv_begin < 0 || !q || !part)
+        return set_err(DRKV_ERR_INVALID, "attend_partial: bad argument");
+    int span = kv_end - (kv_begin / 16) * 16;
+    if (span < 1) span = 1;   // an empty range still has to produce the (-1e20, 0, 0) partial
+    return decode_common(e, layer, 1, nullptr, nullptr, seq, kv_begin, kv_end, span, q, nullptr, part, scale,
+                         (cudaStream_t)stream);
+}
+
+int drkv_combine_partials(drkv_engine* e, int n_parts, const float* parts, void* out, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (n_parts < 0 || !parts || !out) return set_err(DRKV_ERR_INVALID, "combine_partials: bad argument");
+    CUDA_TRY(launch_combine_external(n_parts, parts, e->geom.num_q_heads, e->geom.head_dim, out, e->geom.dtype,
+                                     (cudaStream_t)stream));
+    return DRKV_OK;
+}
+
+size_t drkv_partial_floats(const drkv_engine* e) {
+    return e ? (size_t)e->geom.num_q_heads * (e->geom.head_dim + 2) : 0;
+}
+
+int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m, const void* q, void* out,
+                              float scale, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    (void)layer; (void)seq; (void)pos_start; (void)m; (void)q; (void)out; (void)scale; (void)stream;
+    return set_err(DRKV_ERR_INVALID, "attend_prefill_chunk: not built yet");
+}
+
+}  // extern "C"

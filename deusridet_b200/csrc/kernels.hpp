@@ -1,0 +1,77 @@
+// kernels.hpp — parameter blocks and launchers of the paged-KV kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kv_common.cuh"
+
+namespace drkv {
+
+struct AppendParams {
+    PoolLayout layout;
+    void* pool;
+    const int32_t* tables;   // [rows][table_stride]
+    int table_stride;
+    const int32_t* rows;     // per token table row, or nullptr: all tokens use `row`
+    const int32_t* pos;      // per token position (rows != nullptr) or one device int (rows == nullptr)
+    int row, pos_start;      // used when rows == nullptr (pos_start only if pos == nullptr)
+    int layer;
+    int rotary_dim;          // 0 = plain copy
+    const float* inv_freq;   // [rotary_dim / 2] device
+    const void* k_src;
+    const void* v_src;
+};
+
+struct CowParams {
+    PoolLayout layout;
+    void* pool;
+    int src_page, dst_page, n_slots;
+};
+
+// Split-KV decode attention.  One CTA handles (chunk of keys, KV head, sequence).
+struct DecodeParams {
+    const int32_t* tables;
+    int table_stride;
+    const int32_t* rows;      // [n_seq] table row per batch entry, nullptr = `row` for all
+    const int32_t* kv_len;    // [n_seq] keys visible, nullptr = `kv_end`
+    int row, kv_begin, kv_end;
+    const void* q;            // [n_seq][Hq][D]
+    float* part_o;            // [n_seq][Hq][max_chunks][D]   un-normalised
+    float* part_m;            // [n_seq][Hq][max_chunks]      natural-log domain
+    float* part_l;            // [n_seq][Hq][max_chunks]
+    int layer, max_pages, num_q_heads, num_kv_heads, group, page_size;
+    int chunk_tokens, max_chunks;
+    float scale_log2;         // scale * log2(e)
+    int* error_word;
+};
+
+struct CombineParams {
+    const float* part_o;
+    const float* part_m;
+    const float* part_l;
+    const int32_t* kv_len;    // [n_seq] or nullptr
+    int kv_begin, kv_end;
+    int num_q_heads, head_dim, chunk_tokens, max_chunks;
+    void* out;                // storage type [n_seq][Hq][D] (normalised) ...
+    float* out_partial;       // ... or fp32 partial [Hq*D | Hq m | Hq l] when non-null
+};
+
+cudaError_t launch_append_rope(const AppendParams& p, int n_tokens, int dtype, cudaStream_t stream);
+cudaError_t launch_cow_copy(const CowParams& p, int num_layers, cudaStream_t stream);
+
+// Builds the TMA descriptor of a pool: a 2-D tensor [rows][head_dim] of 2-byte elements with
+// a {64 x 16} box and 128-byte swizzle.  Returns false if the driver entry point is missing.
+bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
+                          int num_kv_heads, int page_size, int head_dim, const char** err);
+
+cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int n_seq, int head_dim,
+                                 int dtype, cudaStream_t stream);
+cudaError_t launch_combine(const CombineParams& p, int n_seq, int dtype, cudaStream_t stream);
+
+// Merges partials that already sit in the external layout (drkv_attend_partial).
+cudaError_t launch_combine_external(int n_parts, const float* parts, int num_q_heads, int head_dim,
+                                    void* out, int dtype, cudaStream_t stream);
+
+}  // namespace drkv

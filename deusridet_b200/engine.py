@@ -1,0 +1,154 @@
+"""PagedKVEngine: Python host over the C ABI, mirroring the reference's call surface
+(BlockPool / CacheManager methods, src/memoria/block_pool.h:69-107 and
+src/memoria/cache_manager.h:67-125, plus the paged_* free functions,
+src/machina/paged_attention.h:27-71).  Device buffers are passed as raw pointers; torch
+tensors are accepted wherever a pointer is (their data_ptr() is used)."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import capi
+from .capi import Config, Geometry, check
+
+
+def _ptr(x) -> Optional[int]:
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()  # torch tensor
+
+
+def _stream(stream) -> Optional[int]:
+    if stream is None:
+        return None
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream  # torch.cuda.Stream
+
+
+class PagedKVEngine:
+    def __init__(self, *, num_layers: int, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                 dtype: str = "bf16", rotary_dim: Optional[int] = None, rope_theta: float = 10000.0,
+                 max_pages: int = 0, budget_bytes: int = 0, max_seqs: int = 1, max_pages_per_seq: int = 0,
+                 device: int = 0, stream_evict: bool = False):
+        self.lib = capi.load_library()
+        self.geom = Geometry(num_layers, num_q_heads, num_kv_heads, head_dim, page_size,
+                             capi.F16 if dtype in ("f16", "fp16") else capi.BF16,
+                             head_dim if rotary_dim is None else rotary_dim, rope_theta)
+        cfg = Config(budget_bytes, max_pages, max_seqs, max_pages_per_seq, device, 1 if stream_evict else 0)
+        h = C.c_void_p()
+        check(self.lib.drkv_create(C.byref(self.geom), C.byref(cfg), C.byref(h)))
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.drkv_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- BlockPool -------------------------------------------------------------------
+    def alloc_block(self) -> int: return self.lib.drkv_pool_alloc(self.h)
+    def free_block(self, page: int) -> None: check(self.lib.drkv_pool_free(self.h, page))
+    def free_count(self) -> int: return self.lib.drkv_pool_free_count(self.h)
+    def max_blocks(self) -> int: return self.lib.drkv_pool_max_pages(self.h)
+    def block_size(self) -> int: return self.lib.drkv_pool_page_size(self.h)
+    def pool_ptr(self) -> int: return self.lib.drkv_pool_ptr(self.h) or 0
+    def total_bytes(self) -> int: return self.lib.drkv_pool_total_bytes(self.h)
+    def k_offset(self, layer: int, page: int) -> int: return self.lib.drkv_pool_k_offset(self.h, layer, page)
+    def v_offset(self, layer: int, page: int) -> int: return self.lib.drkv_pool_v_offset(self.h, layer, page)
+
+    def pool_tensor(self):
+        """The pool slab as a flat int16 torch tensor aliasing the engine's device memory."""
+        import torch
+
+        class _Raw:
+            pass
+
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (self.total_bytes() // 2,), "typestr": "<i2",
+                                        "data": (self.pool_ptr(), False), "version": 2}
+        return torch.as_tensor(raw, device=f"cuda:{self.device}")
+
+    # ---- sequences (CacheManager, one row per sequence) ---------------------------------
+    def seq_create(self) -> int: return check(self.lib.drkv_seq_create(self.h))
+    def seq_release(self, seq: int, discard: bool = False) -> None:
+        check(self.lib.drkv_seq_release(self.h, seq, 1 if discard else 0))
+    def seq_fork(self, parent: int) -> int: return check(self.lib.drkv_seq_fork(self.h, parent))
+    def ensure_blocks_for(self, seq: int, pos: int, stream=None) -> bool:
+        return self.lib.drkv_seq_ensure_pos(self.h, seq, pos, _stream(stream)) == 0
+    def ensure_blocks_for_range(self, seq: int, pos_start: int, m: int, stream=None) -> bool:
+        return self.lib.drkv_seq_ensure_range(self.h, seq, pos_start, m, _stream(stream)) == 0
+    def reserve(self, seq: int, n_tokens: int, stream=None) -> None:
+        check(self.lib.drkv_seq_reserve(self.h, seq, n_tokens, _stream(stream)))
+    def set_seq_len(self, seq: int, n: int) -> None: check(self.lib.drkv_seq_set_len(self.h, seq, n))
+    def seq_len(self, seq: int) -> int: return check(self.lib.drkv_seq_len(self.h, seq))
+    def num_logical_blocks(self, seq: int) -> int: return check(self.lib.drkv_seq_num_pages(self.h, seq))
+    def adopt(self, seq: int, pages: Sequence[int], n_tokens: int) -> None:
+        arr = (C.c_int32 * len(pages))(*pages)
+        check(self.lib.drkv_seq_adopt(self.h, seq, arr, len(pages), n_tokens))
+    def table(self, seq: int, n: Optional[int] = None) -> np.ndarray:
+        n = self.table_stride() if n is None else n
+        out = np.empty(n, dtype=np.int32)
+        got = check(self.lib.drkv_seq_table(self.h, seq, out.ctypes.data_as(C.POINTER(C.c_int32)), n))
+        return out[:got]
+
+    # ---- eviction ----------------------------------------------------------------------
+    def evict_blocks(self, seq: int, n: int) -> int: return check(self.lib.drkv_seq_evict(self.h, seq, n))
+    def evict_cached(self, n: int) -> int: return check(self.lib.drkv_evict_cached(self.h, n))
+    def ensure_free_blocks(self, seq: int, n_free: int) -> bool:
+        return self.lib.drkv_ensure_free(self.h, seq, n_free) == 1
+
+    # ---- inspection ----------------------------------------------------------------------
+    def _ints(self, fn, cap: int) -> np.ndarray:
+        out = np.empty(max(cap, 1), dtype=np.int32)
+        n = check(fn(self.h, out.ctypes.data_as(C.POINTER(C.c_int32)), cap))
+        return out[:n].copy()
+    def refcounts(self) -> np.ndarray: return self._ints(self.lib.drkv_refcounts, self.max_blocks())
+    def free_stack(self) -> np.ndarray: return self._ints(self.lib.drkv_free_stack, self.max_blocks())
+    def cached_lru(self) -> np.ndarray: return self._ints(self.lib.drkv_cached_lru, self.max_blocks())
+    def evict_log(self, clear: bool = True):
+        cap = 1 << 16
+        buf = (capi.EvictRecord * cap)()
+        n = check(self.lib.drkv_evict_log(self.h, buf, cap, 1 if clear else 0))
+        return [(buf[i].kind, buf[i].seq, buf[i].logical, buf[i].page) for i in range(n)]
+    def stats(self) -> dict:
+        s = capi.Stats()
+        check(self.lib.drkv_get_stats(self.h, C.byref(s)))
+        return {n: getattr(s, n) for n, _ in capi.Stats._fields_}
+
+    # ---- device tables --------------------------------------------------------------------
+    def sync_block_table(self, stream=None) -> None: check(self.lib.drkv_sync_tables(self.h, _stream(stream)))
+    def d_block_table(self) -> int: return self.lib.drkv_device_tables(self.h) or 0
+    def table_stride(self) -> int: return self.lib.drkv_table_stride(self.h)
+    def check_kernels(self) -> None: check(self.lib.drkv_kernel_error(self.h))
+    def set_chunk_tokens(self, n: int) -> None: check(self.lib.drkv_set_chunk_tokens(self.h, n))
+
+    # ---- kernels ----------------------------------------------------------------------------
+    def append_rope(self, layer, n_seq, d_rows, d_pos, k_src, v_src, stream=None) -> None:
+        check(self.lib.drkv_append_rope(self.h, layer, n_seq, _ptr(d_rows), _ptr(d_pos), _ptr(k_src), _ptr(v_src),
+                                        _stream(stream)))
+    def append_rope_chunk(self, layer, seq, pos_start, m, k_src, v_src, stream=None) -> None:
+        check(self.lib.drkv_append_rope_chunk(self.h, layer, seq, pos_start, m, _ptr(k_src), _ptr(v_src),
+                                              _stream(stream)))
+    def attend_decode(self, layer, n_seq, d_rows, d_kv_len, max_kv_len, q, out, scale, stream=None) -> None:
+        check(self.lib.drkv_attend_decode(self.h, layer, n_seq, _ptr(d_rows), _ptr(d_kv_len), max_kv_len, _ptr(q),
+                                          _ptr(out), scale, _stream(stream)))
+    def attend_prefill_chunk(self, layer, seq, pos_start, m, q, out, scale, stream=None) -> None:
+        check(self.lib.drkv_attend_prefill_chunk(self.h, layer, seq, pos_start, m, _ptr(q), _ptr(out), scale,
+                                                 _stream(stream)))
+    def attend_partial(self, layer, seq, kv_begin, kv_end, q, part, scale, stream=None) -> None:
+        check(self.lib.drkv_attend_partial(self.h, layer, seq, kv_begin, kv_end, _ptr(q), _ptr(part), scale,
+                                           _stream(stream)))
+    def combine_partials(self, n_parts, parts, out, stream=None) -> None:
+        check(self.lib.drkv_combine_partials(self.h, n_parts, _ptr(parts), _ptr(out), _stream(stream)))
+    def partial_floats(self) -> int: return self.lib.drkv_partial_floats(self.h)

@@ -1,0 +1,230 @@
+/*
+ * drkv.h — C ABI of the B200 paged KV-cache engine.
+ *
+ * One shared library (libdrkv.so) exports everything below with C linkage, plain
+ * pointers and sizes.  It replaces, for the KV-cache hot path only, what the
+ * DeusRidet reference links statically from its `memoria` and `machina` libraries:
+ *
+ *   page pool            src/memoria/block_pool.h:58-123     (BlockPool)
+ *   block tables/evict   src/memoria/cache_manager.h:52-169  (CacheManager)
+ *   K/V append           src/machina/paged_attention.h:27-52 (paged_kv_cache_write[_batch])
+ *   RoPE on K            src/machina/layer.h:127-130, src/machina/layer_attention.cu:32-79
+ *   decode attention     src/machina/paged_attention.h:61-71 (paged_gqa_decode_attention)
+ *   prefill attention    src/machina/paged_attention.cu:465-554 (paged_prefill_attention_kernel)
+ *   split-KV merge       src/sensus/auditus/asr/asr_ops_attn.cu:88-108 (semantic analogue)
+ *
+ * Conventions: every call returns DRKV_OK (0) or a negative drkv_status; nothing throws
+ * across this boundary; kernels are enqueued on the caller's stream (a cudaStream_t
+ * passed as void*) and never synchronise; device memory is owned by the engine and
+ * released by drkv_destroy().  There is no CPU fallback: a compute entry point called
+ * on an engine without a device returns DRKV_ERR_NO_DEVICE.
+ *
+ * Pool layout, identical to the reference (src/machina/paged_attention.cu:13-18,
+ * src/memoria/block_pool.cpp:23-24,81-95), in elements of the storage type:
+ *   elem(layer, page, kv, head, slot, d) =
+ *       layer * layer_stride + page * block_stride + kv * kv_plane
+ *       + head * page_size * head_dim + slot * head_dim + d
+ *   kv_plane = num_kv_heads * page_size * head_dim, block_stride = 2 * kv_plane,
+ *   layer_stride = max_pages * block_stride.
+ */
+#ifndef DRKV_H_
+#define DRKV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DRKV_API __attribute__((visibility("default")))
+
+typedef enum drkv_status {
+    DRKV_OK = 0,
+    DRKV_ERR_INVALID = -1,     /* bad argument (range, alignment, unsupported geometry) */
+    DRKV_ERR_EXHAUSTED = -2,   /* no free page and nothing evictable */
+    DRKV_ERR_NO_DEVICE = -3,   /* compute call on a bookkeeping-only engine, or no GPU */
+    DRKV_ERR_CUDA = -4,        /* a CUDA runtime/driver call failed; see drkv_last_error */
+    DRKV_ERR_STATE = -5,       /* double free, unknown sequence, released sequence ... */
+    DRKV_ERR_CAPACITY = -6     /* position beyond the table, too many sequences, scratch too small */
+} drkv_status;
+
+enum { DRKV_DTYPE_F16 = 0, DRKV_DTYPE_BF16 = 1 };
+
+/* Runtime geometry.  The reference fixes these at compile time (PagedKVConfig,
+ * src/memoria/block_pool.h:34-52) or in process-wide statics (ModelConfig,
+ * src/machina/model.h:30-83). */
+typedef struct drkv_geometry {
+    int32_t num_layers;    /* full-attention layers sharing the pool (NUM_FA_LAYERS) */
+    int32_t num_q_heads;
+    int32_t num_kv_heads;
+    int32_t head_dim;      /* 64, 128 or 256 */
+    int32_t page_size;     /* tokens per page, a multiple of 16 */
+    int32_t dtype;         /* DRKV_DTYPE_* : storage type of Q, K, V, out and the pool */
+    int32_t rotary_dim;    /* leading dims of each K head that RoPE rotates (0 = none) */
+    float rope_theta;
+} drkv_geometry;
+
+typedef struct drkv_config {
+    size_t budget_bytes;        /* pool budget; used when max_pages == 0 (BlockPool::init) */
+    int32_t max_pages;          /* explicit page count (0 = derive from budget_bytes) */
+    int32_t max_seqs;           /* rows of the device table */
+    int32_t max_pages_per_seq;  /* row width; 0 = 2 * max_pages as in CacheManager::init */
+    int32_t device;             /* CUDA device ordinal; -1 = bookkeeping only, no device memory */
+    int32_t stream_evict;       /* 1 = a sequence that cannot get a page discards its own oldest
+                                   page (CacheManager behaviour); 0 = fail with DRKV_ERR_EXHAUSTED */
+} drkv_config;
+
+typedef struct drkv_stats {
+    int64_t pages_total, pages_free, pages_cached, pages_active;
+    int64_t evictions_cached, evictions_stream, cow_copies, cow_bytes;
+    int64_t table_sync_bytes, table_syncs;
+    int64_t live_seqs;
+} drkv_stats;
+
+/* One eviction, in the order it happened.  kind 0: an unreferenced cached page was
+ * reclaimed (seq = logical = -1).  kind 1: a sequence discarded one of its own pages. */
+typedef struct drkv_evict_record {
+    int32_t kind, seq, logical, page;
+} drkv_evict_record;
+
+typedef struct drkv_engine drkv_engine;
+
+/* ---- lifetime ------------------------------------------------------------------- */
+/* CacheManager::init + BlockPool::init (src/memoria/cache_manager.cpp:24-71,
+ * src/memoria/block_pool.cpp:18-61): page count = budget / bytes per page over all layers,
+ * fails below 4 pages, slab zero-filled, page ids pop 0,1,2,... */
+DRKV_API int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine** out);
+/* CacheManager::destroy / BlockPool::destroy (cache_manager.cpp:328-338, block_pool.cpp:97-105) */
+DRKV_API void drkv_destroy(drkv_engine* e);
+/* Text of the last failure on this thread (the reference logs with LOG_ERROR instead). */
+DRKV_API const char* drkv_last_error(void);
+DRKV_API int drkv_get_geometry(const drkv_engine* e, drkv_geometry* out);
+DRKV_API int drkv_get_stats(const drkv_engine* e, drkv_stats* out);
+
+/* ---- page pool: BlockPool (src/memoria/block_pool.h:69-107) --------------------- */
+DRKV_API int drkv_pool_alloc(drkv_engine* e);                 /* alloc_block: id or -1 */
+DRKV_API int drkv_pool_free(drkv_engine* e, int page);        /* free_block, with double-free/range check */
+DRKV_API int drkv_pool_free_count(const drkv_engine* e);      /* free_count */
+DRKV_API int drkv_pool_max_pages(const drkv_engine* e);       /* max_blocks */
+DRKV_API int drkv_pool_page_size(const drkv_engine* e);       /* block_size */
+DRKV_API void* drkv_pool_ptr(const drkv_engine* e);           /* pool_ptr (device) */
+DRKV_API size_t drkv_pool_total_bytes(const drkv_engine* e);  /* total_bytes */
+DRKV_API size_t drkv_pool_k_offset(const drkv_engine* e, int layer, int page);  /* k_offset (bytes) */
+DRKV_API size_t drkv_pool_v_offset(const drkv_engine* e, int layer, int page);  /* v_offset (bytes) */
+
+/* ---- sequences and block tables: CacheManager (src/memoria/cache_manager.h:67-125) */
+/* The reference has one implicit sequence; here each sequence owns one table row. */
+DRKV_API int drkv_seq_create(drkv_engine* e);                 /* new empty sequence: id (lowest free) */
+/* Drops the sequence.  Pages whose reference count reaches 0 keep their contents and
+ * join the tail of the evictable LRU list (discard = 0), or go straight back to the
+ * free stack (discard = 1), in ascending logical order. */
+DRKV_API int drkv_seq_release(drkv_engine* e, int seq, int discard);
+/* Decode branch: the child shares every page of the parent (reference count + 1).
+ * No counterpart in the reference code; intent in docs/en/architecture/02-memoria.md:25-26. */
+DRKV_API int drkv_seq_fork(drkv_engine* e, int parent);
+/* ensure_blocks_for(pos) (cache_manager.cpp:73-95): make the page holding `pos` resident
+ * and private to this sequence (copy-on-write when it is shared). */
+DRKV_API int drkv_seq_ensure_pos(drkv_engine* e, int seq, int pos, void* stream);
+/* ensure_blocks_for_range(pos_start, m) (cache_manager.cpp:97-106): stops at the first
+ * failure and keeps earlier allocations. */
+DRKV_API int drkv_seq_ensure_range(drkv_engine* e, int seq, int pos_start, int m, void* stream);
+/* ensure_blocks_for_range(seq_len, n): room for n more tokens after the current length. */
+DRKV_API int drkv_seq_reserve(drkv_engine* e, int seq, int n_tokens, void* stream);
+DRKV_API int drkv_seq_set_len(drkv_engine* e, int seq, int len);   /* set_seq_len */
+DRKV_API int drkv_seq_len(const drkv_engine* e, int seq);          /* seq_len */
+DRKV_API int drkv_seq_num_pages(const drkv_engine* e, int seq);    /* num_logical_blocks = ceil(len / page) */
+/* Host copy of the row (h_block_table_); returns entries written. */
+DRKV_API int drkv_seq_table(const drkv_engine* e, int seq, int32_t* out, int cap);
+/* Attach existing pages (active or cached) to an empty sequence as its first
+ * ceil(n_tokens / page) logical pages: prefix reuse after the owner was released. */
+DRKV_API int drkv_seq_adopt(drkv_engine* e, int seq, const int32_t* pages, int n_pages, int n_tokens);
+
+/* ---- eviction (src/memoria/cache_manager.cpp:118-205) ----------------------------- */
+/* evict_blocks(n) for one sequence: discard its n oldest-allocated resident pages that
+ * nobody else references; returns the number evicted. */
+DRKV_API int drkv_seq_evict(drkv_engine* e, int seq, int n);
+/* Reclaim up to n unreferenced cached pages, least recently released first. */
+DRKV_API int drkv_evict_cached(drkv_engine* e, int n);
+/* ensure_free_blocks(n_free): cached pages first, then (stream_evict) pages of `seq`
+ * (seq = -1: cached pages only).  Returns 1 if the target is met, 0 if not. */
+DRKV_API int drkv_ensure_free(drkv_engine* e, int seq, int n_free);
+
+/* ---- inspection (bit-exact bookkeeping artefacts) ---------------------------------- */
+DRKV_API int drkv_refcounts(const drkv_engine* e, int32_t* out, int cap);
+DRKV_API int drkv_free_stack(const drkv_engine* e, int32_t* out, int cap);   /* bottom..top */
+DRKV_API int drkv_cached_lru(const drkv_engine* e, int32_t* out, int cap);   /* head(oldest)..tail */
+DRKV_API int drkv_evict_log(drkv_engine* e, drkv_evict_record* out, int cap, int clear);
+
+/* ---- device block tables (src/memoria/cache_manager.cpp:108-112) ------------------- */
+/* sync_block_table: uploads only the entries changed since the last call. */
+DRKV_API int drkv_sync_tables(drkv_engine* e, void* stream);
+DRKV_API const int32_t* drkv_device_tables(const drkv_engine* e);  /* d_block_table: [max_seqs][stride] */
+DRKV_API int drkv_table_stride(const drkv_engine* e);
+/* Reads (and clears) the device error word that kernels set instead of trapping when a
+ * bounded wait gives up or a table holds an impossible page id.  Synchronises the device.
+ * The reference has no counterpart: its kernels index the pool unchecked. */
+DRKV_API int drkv_kernel_error(drkv_engine* e);
+/* Keys per split-KV chunk of the decode kernel: 0 = chosen per call from the batch shape,
+ * else a multiple of 64 in [64, 4096].  Tuning knob, no counterpart in the reference. */
+DRKV_API int drkv_set_chunk_tokens(drkv_engine* e, int chunk_tokens);
+
+/* ---- K/V append with RoPE on K ------------------------------------------------------ */
+/* paged_kv_cache_write + rope_kernel's K half (paged_attention.cu:73-115,
+ * layer_attention.cu:32-69), batched over sequences: sequence i of the batch uses table
+ * row d_rows[i] and writes its token at d_pos[i] (both device int32 arrays).
+ * k_src/v_src: [n_seq][num_kv_heads][head_dim] device, storage type. */
+DRKV_API int drkv_append_rope(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows,
+                              const int32_t* d_pos, const void* k_src, const void* v_src,
+                              void* stream);
+/* paged_kv_cache_write_batch + paged_rope_batch_kernel's K half (paged_attention.cu:123-167,
+ * 412-451): m consecutive tokens of one sequence from pos_start.
+ * k_src/v_src: [m][num_kv_heads][head_dim]. */
+DRKV_API int drkv_append_rope_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m,
+                                    const void* k_src, const void* v_src, void* stream);
+
+/* ---- attention ---------------------------------------------------------------------- */
+/* paged_gqa_decode_attention (paged_attention.cu:179-282), batched: q/out
+ * [n_seq][num_q_heads][head_dim]; sequence i attends to keys 0..d_kv_len[i]-1 of table row
+ * d_rows[i].  max_kv_len is a host-side upper bound of the d_kv_len values (it sizes the
+ * grid).  Table entries < 0 are skipped.  A sequence with no visible key leaves its output
+ * rows untouched (paged_attention.cu:266-268). */
+DRKV_API int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows,
+                                const int32_t* d_kv_len, int max_kv_len, const void* q, void* out,
+                                float scale, void* stream);
+/* paged_prefill_attention_kernel (paged_attention.cu:465-554): q/out
+ * [m][num_q_heads][head_dim]; token t attends keys 0..pos_start+t. */
+DRKV_API int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m,
+                                       const void* q, void* out, float scale, void* stream);
+/* One sequence whose pages are split across GPUs by contiguous key range: this rank
+ * attends keys [kv_begin, kv_end) of table row `seq` and returns the un-normalised partial
+ * (m, l, o) per query head in fp32: part[0 .. Hq*D) = o, then Hq values m, then Hq values l.
+ * Empty range: m = -1e20, l = 0, o = 0 (asr_ops_attn.cu:38-42). */
+DRKV_API int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end,
+                                 const void* q, float* part, float scale, void* stream);
+/* contiguous_split_k_merge_kernel (asr_ops_attn.cu:88-108): merges n_parts partials laid
+ * out as drkv_attend_partial writes them (parts[p] at p * (Hq*(D+2)) floats). */
+DRKV_API int drkv_combine_partials(drkv_engine* e, int n_parts, const float* parts, void* out,
+                                   void* stream);
+DRKV_API size_t drkv_partial_floats(const drkv_engine* e);   /* Hq * (D + 2) */
+
+/* ---- stateless kernel entry points: the reference's free functions -------------------
+ * Same argument meaning as src/machina/paged_attention.h:27-71 plus the geometry the
+ * reference reads from ModelConfig statics.  One sequence, one table. */
+DRKV_API int drkv_k_cache_write(const drkv_geometry* g, const void* src_k, const void* src_v,
+                                void* kv_pool, const int32_t* d_block_table, int layer,
+                                const int32_t* d_pos, int max_pages, void* stream);
+DRKV_API int drkv_k_cache_write_batch(const drkv_geometry* g, const void* src_k, const void* src_v,
+                                      void* kv_pool, const int32_t* d_block_table, int layer,
+                                      int pos_start, int m, int max_pages, void* stream);
+/* `scratch`: device memory of at least drkv_k_decode_scratch_bytes(g, seq_len) bytes. */
+DRKV_API int drkv_k_decode_attention(const drkv_geometry* g, const void* q, const void* kv_pool,
+                                     const int32_t* d_block_table, void* out, int layer,
+                                     int seq_len, int max_pages, float scale, void* scratch,
+                                     size_t scratch_bytes, void* stream);
+DRKV_API size_t drkv_k_decode_scratch_bytes(const drkv_geometry* g, int seq_len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DRKV_H_ */

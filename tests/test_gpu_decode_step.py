@@ -1,0 +1,142 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU checker on one decode step:
+block tables, appended K/V bytes and attention output."""
+import numpy as np
+import pytest
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3  # max-abs on attention outputs: fp16/bf16 out, fp32 accumulate
+
+
+def _decode_case(oracle, *, layers, hq, hkv, d, page, dtype, theta, lens, seed, pool_slack=1.1, rot=None,
+                 chunk=0, holes=0):
+    import torch
+    from deusridet_b200 import PagedKVEngine
+
+    ob = oracle
+    rng = np.random.default_rng(seed)
+    rot = d if rot is None else rot
+    lens = np.asarray(lens, dtype=np.int32)
+    n_seq = len(lens)
+    pages_needed = int(sum((int(n) + 1 + page - 1) // page for n in lens))
+    max_pages = max(4, int(np.ceil(pool_slack * pages_needed)))
+    width = int(max((int(n) + 1 + page - 1) // page for n in lens)) + 1
+    eng = PagedKVEngine(num_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page,
+                        dtype="f16" if dtype == ob.F16 else "bf16", rotary_dim=rot, rope_theta=theta,
+                        max_pages=max_pages, max_seqs=n_seq, max_pages_per_seq=width, device=0)
+    g = ob.geom(layers, hq, hkv, d, page, dtype, rot, theta)
+    try:
+        if chunk:
+            eng.set_chunk_tokens(chunk)
+        H.shuffled_free_stack(eng, rng)
+        seqs = [eng.seq_create() for _ in range(n_seq)]
+        # cached context, then room for the token being decoded
+        for s, n in zip(seqs, lens):
+            assert eng.ensure_blocks_for_range(s, 0, int(n))
+            eng.set_seq_len(s, int(n))
+        for s in seqs:
+            eng.reserve(s, 1)
+        tables = np.stack([eng.table(s) for s in seqs])
+        if holes:
+            # evicted pages: the table entry becomes -1 and attention must skip it
+            for s in seqs:
+                eng.evict_blocks(s, holes)
+            tables = np.stack([eng.table(s) for s in seqs])
+            assert (tables[:, :holes] == -1).all()
+        eng.sync_block_table()
+
+        # pool contents: N(0,1) everywhere (also in slots no sequence owns)
+        pool_host = H.randn_bits(rng, ob.pool_elems(g, max_pages), dtype)
+        eng.pool_tensor().copy_(torch.from_numpy(pool_host.view(np.int16)))
+
+        rows = np.asarray(seqs, dtype=np.int32)
+        pos = lens.copy()
+        d_rows = torch.from_numpy(rows).cuda()
+        d_pos = torch.from_numpy(pos).cuda()
+        d_len = torch.from_numpy(pos + 1).cuda()
+        scale = 1.0 / np.sqrt(d)
+        for layer in range(layers):
+            k_new = H.randn_bits(rng, (n_seq, hkv, d), dtype)
+            v_new = H.randn_bits(rng, (n_seq, hkv, d), dtype)
+            q = H.randn_bits(rng, (n_seq, hq, d), dtype)
+            out_dev = torch.full((n_seq, hq, d), 7.0, device="cuda",
+                                 dtype=torch.float16 if dtype == ob.F16 else torch.bfloat16)
+            eng.append_rope(layer, n_seq, d_rows, d_pos, H.to_dev(k_new, dtype), H.to_dev(v_new, dtype))
+            eng.attend_decode(layer, n_seq, d_rows, d_len, int(pos.max()) + 1, H.to_dev(q, dtype), out_dev, scale)
+            torch.cuda.synchronize()
+            eng.check_kernels()
+
+            # checker on the host copy
+            for i in range(n_seq):
+                ob.append(g, pool_host, max_pages, tables[i], layer, int(pos[i]), 1, k_new[i], v_new[i], rope=True)
+            want = H.torch_bits(torch.full((n_seq, hq, d), 7.0,
+                                           dtype=torch.float16 if dtype == ob.F16 else torch.bfloat16))
+            want = want.copy()
+            ob.attend_decode(g, pool_host, max_pages, tables, np.arange(n_seq), pos + 1, layer, q, want, scale)
+
+            got_pool = eng.pool_tensor().cpu().numpy().view(np.uint16)
+            assert np.array_equal(got_pool, pool_host), f"layer {layer}: pool bytes differ after append"
+            got = ob.to_float(H.torch_bits(out_dev), dtype)
+            ref = ob.to_float(want, dtype)
+            # 2e-3 max-abs; where one unit in the last place of the storage type is itself larger
+            # than that (|out| >= 0.25 in bf16, >= 2 in fp16: only the very short sequences here),
+            # a one-unit rounding flip is the most two correct fp32 results can differ by.
+            tol = np.maximum(TOL, H.ulp(ref, dtype))
+            err = np.abs(got - ref)
+            exact = ob.attend_decode_f64(g, pool_host, max_pages, tables, np.arange(n_seq), pos + 1, layer, q, scale)
+            err64 = np.abs(got - exact).max()
+            assert (err <= tol).all(), f"layer {layer}: max-abs {err.max()} vs checker (vs fp64 {err64})"
+            long_ctx = pos + 1 >= 512
+            if long_ctx.any():
+                assert err[long_ctx].max() <= TOL
+        return eng.stats()
+    finally:
+        eng.close()
+
+
+def test_toy_decode_step_fp16(drkv_lib, oracle):
+    """1 layer, 16/4 heads, head_dim 128, fp16, page 16, 512 cached tokens on a seeded page
+    permutation of a 64-page pool; append one token (RoPE base 1e4), attend over 513."""
+    _decode_case(oracle, layers=1, hq=16, hkv=4, d=128, page=16, dtype=oracle.F16, theta=1e4, lens=[512], seed=1,
+                 pool_slack=64 / 33)
+
+
+def test_batched_decode_bf16_ragged(drkv_lib, oracle):
+    """Qwen3-8B-shaped heads (32/8, bf16, page 16, RoPE base 1e6), 2 layers, ragged lengths."""
+    _decode_case(oracle, layers=2, hq=32, hkv=8, d=128, page=16, dtype=oracle.BF16, theta=1e6,
+                 lens=[1024, 1531, 4097, 2048, 777, 3000, 1, 15, 16, 17], seed=2)
+
+
+@pytest.mark.parametrize("chunk", [64, 256, 2048])
+def test_decode_chunk_sizes(drkv_lib, oracle, chunk):
+    _decode_case(oracle, layers=1, hq=32, hkv=8, d=128, page=16, dtype=oracle.BF16, theta=1e6,
+                 lens=[1200, 63, 64, 65, 2500], seed=3, chunk=chunk)
+
+
+def test_decode_group8_page64(drkv_lib, oracle):
+    """64/8 heads (GQA 8), page 64: the long-context configuration's head shape."""
+    _decode_case(oracle, layers=1, hq=64, hkv=8, d=128, page=64, dtype=oracle.BF16, theta=1e6, lens=[3000, 64, 129],
+                 seed=4)
+
+
+def test_decode_group16(drkv_lib, oracle):
+    _decode_case(oracle, layers=1, hq=32, hkv=2, d=128, page=16, dtype=oracle.F16, theta=1e4, lens=[700, 33], seed=5)
+
+
+def test_decode_reference_model_shape(drkv_lib, oracle):
+    """The reference's own geometry: 24/4 heads, head_dim 256, page 256, partial rotary 64, fp16
+    (src/memoria/block_pool.h:34-40, src/machina/model.h)."""
+    _decode_case(oracle, layers=1, hq=24, hkv=4, d=256, page=256, dtype=oracle.F16, theta=1e7, lens=[1000, 300],
+                 seed=6, rot=64)
+
+
+def test_decode_head_dim_64(drkv_lib, oracle):
+    _decode_case(oracle, layers=1, hq=8, hkv=2, d=64, page=32, dtype=oracle.BF16, theta=1e4, lens=[500, 100], seed=7)
+
+
+def test_decode_with_evicted_pages(drkv_lib, oracle):
+    """Holes in the table (evicted pages) contribute nothing."""
+    _decode_case(oracle, layers=1, hq=16, hkv=4, d=128, page=16, dtype=oracle.BF16, theta=1e4, lens=[600, 900],
+                 seed=8, holes=3)
