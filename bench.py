@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark of the paged KV-cache decode step (fused RoPE + K/V append, then paged GQA decode
+attention, every layer) on B200, through the C ABI of libdrkv.so.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --gpus N --steps K ...  # the reference semantics on host cores
+
+Default workload (`c2`): Qwen3-8B-shaped batched decode — 36 layers, 32 query / 8 KV heads,
+head_dim 128, bf16, page 16, 64 sequences with context lengths uniform in [1024, 8192], block
+tables a seeded shuffle of a pool of 1.1x the pages in use, Q/K/V ~ N(0,1), RoPE base 1e6.
+With N > 1 every rank runs its own 64-sequence batch (independent sequences shard with no
+collective); the reported value is the tokens all ranks decoded per second.
+
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: layers, hq, hkv, d, page, n_seq, ctx_lo, ctx_hi, theta
+    "c2": dict(layers=36, hq=32, hkv=8, d=128, page=16, n_seq=64, lo=1024, hi=8192, theta=1e6,
+               desc="Qwen3-8B-shaped batched decode: 36 layers, 32/8 heads, head_dim 128, bf16, page 16, "
+                    "64 sequences, ctx U[1024,8192]"),
+    "c5b": dict(layers=32, hq=32, hkv=8, d=128, page=16, n_seq=128, lo=4096, hi=4096, theta=1e6,
+                desc="independent 4096-token sequences, 32 layers, 32/8 heads, 128 per GPU (1024 over 8 GPUs)"),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_lens(w, seed, n_seq):
+    rng = np.random.default_rng(seed)
+    return rng.integers(w["lo"], w["hi"] + 1, size=n_seq).astype(np.int32)
+
+
+def algorithmic_bytes_per_layer(w, lens):
+    """KV read once per sequence and KV head + append write + Q read / O write + table."""
+    e = 2
+    kv_tok = 2 * w["hkv"] * w["d"] * e
+    n = len(lens)
+    kv = float((lens.astype(np.int64) + 1).sum()) * kv_tok
+    app = n * kv_tok
+    qo = n * 2 * w["hq"] * w["d"] * e
+    tab = 4 * float(sum((int(x) + 1 + w["page"] - 1) // w["page"] for x in lens))
+    return kv, kv + app + qo + tab
+
+
+# --------------------------------------------------------------------------------------------
+# this repository's CUDA path
+# --------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from deusridet_b200 import PagedKVEngine, build
+    build.build()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+
+    w = dict(WORKLOADS[args.workload])
+    if args.layers:
+        w["layers"] = args.layers
+    n_seq = args.seqs or w["n_seq"]
+    L, hq, hkv, d, page = w["layers"], w["hq"], w["hkv"], w["d"], w["page"]
+    lens = make_lens(w, 1234 + rank, n_seq)
+    K, W = args.steps, args.warmup
+    room = K + W + 8                                   # tokens each sequence may grow in the e2e pass
+    pages_needed = int(sum((int(n) + room + page - 1) // page for n in lens))
+    max_pages = int(np.ceil(1.1 * pages_needed))
+    width = int(max((int(n) + room + page - 1) // page for n in lens)) + 1
+    eng = PagedKVEngine(num_layers=L, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
+                        rope_theta=w["theta"], max_pages=max_pages, max_seqs=n_seq, max_pages_per_seq=width,
+                        device=local)
+    rng = np.random.default_rng(99 + rank)
+    # seeded shuffle of the pool through the public pool calls
+    pages = [eng.alloc_block() for _ in range(max_pages)]
+    for p in rng.permutation(max_pages):
+        eng.free_block(int(p))
+    seqs = [eng.seq_create() for _ in range(n_seq)]
+    for s, n in zip(seqs, lens):
+        assert eng.ensure_blocks_for_range(s, 0, int(n) + 1)
+        eng.set_seq_len(s, int(n))
+    stream = torch.cuda.current_stream()
+    eng.sync_block_table(stream)
+    torch.manual_seed(7 + rank)
+    pool = eng.pool_tensor().view(torch.bfloat16)
+    step_elems = 1 << 28
+    for off in range(0, pool.numel(), step_elems):     # N(0,1) cache contents, in slices to bound temporaries
+        pool[off:off + step_elems].normal_()
+    if args.chunk:
+        eng.set_chunk_tokens(args.chunk)
+
+    d_rows = torch.tensor(seqs, dtype=torch.int32, device=dev)
+    d_pos = torch.from_numpy(lens).to(dev)
+    d_len = d_pos + 1
+    q = torch.randn(L, n_seq, hq, d, device=dev, dtype=torch.bfloat16)
+    kn = torch.randn(L, n_seq, hkv, d, device=dev, dtype=torch.bfloat16)
+    vn = torch.randn(L, n_seq, hkv, d, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(L, n_seq, hq, d, device=dev, dtype=torch.bfloat16)
+    scale = 1.0 / float(np.sqrt(d))
+    max_kv = int(lens.max()) + 1
+
+    def device_step():
+        for l in range(L):
+            eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
+            eng.attend_decode(l, n_seq, d_rows, d_len, max_kv, q[l], out[l], scale, stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: `value` ----
+    for _ in range(W):
+        device_step()
+    barrier()
+    eng.check_kernels()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(K):
+        device_step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / K
+    launches = K * L * 3                               # append, attention, combine per layer
+
+    # ---- dominant kernel: per-launch duration from events around each launch ----
+    eng.kernel_timing(True)
+    for _ in range(min(K, 3)):
+        device_step()
+    kms, kn_launch = eng.kernel_timing(False, read=True)
+    kv_bytes, all_bytes = algorithmic_bytes_per_layer(w, lens)
+    peak, peak_kind = peaks()
+    achieved = kv_bytes / (kms / kn_launch * 1e-3) / 1e9 if kn_launch else None
+
+    # ---- end to end through the public API with host buffers ----
+    e2e = None
+    if not args.no_e2e:
+        hq_, hk_, hv_ = (torch.randn(x.shape, dtype=torch.bfloat16).pin_memory() for x in (q, kn, vn))
+        h_out = torch.empty(out.shape, dtype=torch.bfloat16).pin_memory()
+        h_pos = torch.empty(n_seq, dtype=torch.int32).pin_memory()
+        cur = lens.copy()
+
+        def e2e_step():
+            for s in seqs:                              # allocate (copy-on-write aware) room for one token
+                eng.reserve(s, 1, stream)
+            eng.sync_block_table(stream)
+            h_pos.copy_(torch.from_numpy(cur))
+            d_pos.copy_(h_pos, non_blocking=True)
+            torch.add(d_pos, 1, out=d_len)
+            q.copy_(hq_, non_blocking=True)
+            kn.copy_(hk_, non_blocking=True)
+            vn.copy_(hv_, non_blocking=True)
+            mk = int(cur.max()) + 1
+            for l in range(L):
+                eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
+                eng.attend_decode(l, n_seq, d_rows, d_len, mk, q[l], out[l], scale, stream)
+            h_out.copy_(out, non_blocking=True)
+            stream.synchronize()                        # the caller samples from `out` before the next token
+            for i, s in enumerate(seqs):
+                cur[i] += 1
+                eng.set_seq_len(s, int(cur[i]))
+
+        for _ in range(W):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for _ in range(K):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+        wall = (time.perf_counter() - t0) * 1e3
+        t = torch.tensor([max(e0.elapsed_time(e1), wall)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item()) / K
+        h2d = hq_.numel() * 2 + hk_.numel() * 2 + hv_.numel() * 2 + n_seq * 4
+        e2e = {"value": world * n_seq / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(h_out.numel() * 2)}
+    eng.check_kernels()
+    stats = eng.stats()
+    eng.close()
+
+    result = None
+    if rank == 0:
+        result = {
+            "metric": "decode tokens/s/GPU + achieved HBM GB/s (% of peak) for paged attn+append",
+            "value": world * n_seq / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['desc']}", "layers": L, "seqs_per_gpu": n_seq,
+                       "sum_ctx": int(lens.sum()), "page": page, "pool_pages": max_pages,
+                       "pool_gb": round(eng_bytes(max_pages, w) / 1e9, 2), "parallelism": f"dp{world}",
+                       "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer" % (kv_bytes / 1e9)},
+            "tokens_per_s_per_gpu": n_seq / (ms_step * 1e-3),
+            "hbm_gbs_step": all_bytes * L / (ms_step * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
+                         "traffic": None, "bytes_per_launch": kv_bytes,
+                         "us_per_launch": kms / kn_launch * 1e3 if kn_launch else None},
+            "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
+            "cow_copies": stats["cow_copies"],
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result, (w, lens)
+
+
+def eng_bytes(max_pages, w):
+    return max_pages * w["layers"] * 2 * w["hkv"] * w["page"] * w["d"] * 2
+
+
+# --------------------------------------------------------------------------------------------
+# the reference semantics on the host cores (CPU restatement in oracle/, OpenMP over (seq, head))
+# --------------------------------------------------------------------------------------------
+def cpu_pass(w, lens, repeats, seed=5):
+    """One layer x all sequences of the workload on the host: append then attention, repeated;
+    returns seconds per layer-pass and the thread count."""
+    from oracle import cbind as ob
+    ob.lib()
+    hq, hkv, d, page = w["hq"], w["hkv"], w["d"], w["page"]
+    n_seq = len(lens)
+    g = ob.geom(1, hq, hkv, d, page, ob.BF16, d, w["theta"])
+    rng = np.random.default_rng(seed)
+    pages = [(int(n) + 1 + page - 1) // page for n in lens]
+    max_pages = int(np.ceil(1.1 * sum(pages)))
+    perm = rng.permutation(max_pages).astype(np.int32)
+    width = max(pages)
+    tables = np.full((n_seq, width), -1, dtype=np.int32)
+    off = 0
+    for i, n in enumerate(pages):
+        tables[i, :n] = perm[off:off + n]
+        off += n
+    # finite bf16 patterns in +-[0.5, 1): the values do not change the work done
+    pool = (rng.integers(0, 1 << 16, ob.pool_elems(g, max_pages), dtype=np.uint16) & np.uint16(0x807F)) | np.uint16(0x3F00)
+    mk = lambda shape: ob.from_float(rng.standard_normal(shape, dtype=np.float32), ob.BF16)
+    q, k, v = mk((n_seq, hq, d)), mk((n_seq, hkv, d)), mk((n_seq, hkv, d))
+    out = np.zeros((n_seq, hq, d), dtype=np.uint16)
+    rows = np.arange(n_seq, dtype=np.int32)
+    scale = 1.0 / float(np.sqrt(d))
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for i in range(n_seq):
+            ob.append(g, pool, max_pages, tables[i], 0, int(lens[i]), 1, k[i], v[i], rope=True)
+        ob.attend_decode(g, pool, max_pages, tables, rows, lens + 1, 0, q, out, scale)
+        times.append(time.perf_counter() - t0)
+    return times, ob.num_threads()
+
+
+def cpu_baseline(w, lens):
+    times, threads = cpu_pass(w, lens, repeats=1)
+    reps = int(min(100, max(1, 12.0 / max(times[0], 1e-3))))
+    if reps > 1:
+        more, _ = cpu_pass(w, lens, repeats=reps)
+        times = more
+    t_layer = float(np.median(times))
+    return {"value": len(lens) / (t_layer * w["layers"]), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"1 of {w['layers']} layers x all {len(lens)} sequences, {len(times)} passes, median "
+                      f"{t_layer:.3f} s/layer, scaled by the layer count"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    w = dict(WORKLOADS[args.workload])
+    if args.layers:
+        w["layers"] = args.layers
+    lens = make_lens(w, 1234, args.seqs or w["n_seq"])
+    times, threads = cpu_pass(w, lens, repeats=args.warmup + args.steps)
+    times = times[args.warmup:]
+    t_layer = float(np.mean(times))
+    ms_step = t_layer * w["layers"] * 1e3
+    val = len(lens) / (ms_step * 1e-3)
+    sample = (f"each step = 1 of {w['layers']} layers x all {len(lens)} sequences (append + attention), "
+              f"scaled by the layer count")
+    return {
+        "impl": "reference",
+        "metric": "decode tokens/s/GPU + achieved HBM GB/s (% of peak) for paged attn+append",
+        "value": val, "unit": "tokens/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {w['desc']}", "layers": w["layers"], "seqs_per_gpu": len(lens)},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling a small case)")
+    ap.add_argument("--seqs", type=int, default=0, help="override sequences per GPU (profiling a small case)")
+    ap.add_argument("--chunk", type=int, default=0, help="keys per split-KV chunk (0 = automatic)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and not (args.layers or args.seqs):
+        args.warmup = 3
+    if args.impl == "reference":
+        res = run_reference(args)
+        if res is not None:
+            print(json.dumps(res), flush=True)
+        return
+    res, (w, lens) = run_ours(args)
+    if res is not None:
+        if args.gpus == 1 and not args.no_cpu_baseline:
+            res["cpu_baseline"] = cpu_baseline(w, lens)
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

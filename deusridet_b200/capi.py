@@ -81,6 +81,7 @@ SIGNATURES = {
     "drkv_table_stride": (_i, [_vp]),
     "drkv_kernel_error": (_i, [_vp]),
     "drkv_set_chunk_tokens": (_i, [_vp, _i]),
+    "drkv_kernel_timing": (_i, [_vp, _i, C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "drkv_append_rope": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "drkv_append_rope_chunk": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp]),
     "drkv_attend_decode": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _vp]),

@@ -21,6 +21,8 @@ template <typename T>
 __global__ void __launch_bounds__(kAppendThreads)
 append_rope_kernel(AppendParams p) {
     const int tok = blockIdx.x;
+    pdl_wait();                     // positions, sources and the pool may come from the preceding kernel
+    pdl_launch_dependents();
     int row, pos;
     if (p.rows != nullptr) {
         row = p.rows[tok];
@@ -98,6 +100,8 @@ append_rope_kernel(AppendParams p) {
 __global__ void __launch_bounds__(128) cow_copy_kernel(CowParams p) {
     const int head = blockIdx.x, kv = blockIdx.y, layer = blockIdx.z;
     const int D = p.layout.head_dim;
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t esize = 2;
     const char* src = reinterpret_cast<const char*>(p.pool) + p.layout.row(layer, p.src_page, kv, head, 0) * esize;
     char* dst = reinterpret_cast<char*>(p.pool) + p.layout.row(layer, p.dst_page, kv, head, 0) * esize;
@@ -110,17 +114,14 @@ __global__ void __launch_bounds__(128) cow_copy_kernel(CowParams p) {
 cudaError_t launch_append_rope(const AppendParams& p, int n_tokens, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return cudaSuccess;
     if (dtype == DRKV_DTYPE_F16)
-        append_rope_kernel<__half><<<n_tokens, kAppendThreads, 0, stream>>>(p);
-    else
-        append_rope_kernel<__nv_bfloat16><<<n_tokens, kAppendThreads, 0, stream>>>(p);
-    return cudaGetLastError();
+        return launch_pdl(append_rope_kernel<__half>, dim3(n_tokens), dim3(kAppendThreads), 0, stream, p);
+    return launch_pdl(append_rope_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(kAppendThreads), 0, stream, p);
 }
 
 cudaError_t launch_cow_copy(const CowParams& p, int num_layers, cudaStream_t stream) {
     if (p.n_slots <= 0) return cudaSuccess;
     dim3 grid(p.layout.num_kv_heads, 2, num_layers);
-    cow_copy_kernel<<<grid, 128, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(cow_copy_kernel, grid, dim3(128), 0, stream, p);
 }
 
 }  // namespace drkv

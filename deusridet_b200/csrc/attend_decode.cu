@@ -2,15 +2,16 @@
 //
 // Replaces paged_gqa_decode_attention_kernel (src/machina/paged_attention.cu:179-269): one
 // CTA per query head walking every key with two block barriers per key.  Here:
-//   * grid = (key chunks, KV heads, sequences): the keys of one sequence are split into
-//     chunks, each CTA produces an un-normalised partial (m, l, o) per query head of the
-//     GQA group, a second small kernel merges the partials (same arithmetic as
-//     contiguous_split_k_merge_kernel, src/sensus/auditus/asr/asr_ops_attn.cu:88-108);
+//   * the keys of one sequence are split into chunks; (sequence, KV head, chunk) work items
+//     are pulled from an atomic queue by a persistent grid of one CTA per SM; every item
+//     yields an un-normalised partial (m, l, o) per query head of the GQA group, a second
+//     small kernel merges the partials (same arithmetic as contiguous_split_k_merge_kernel,
+//     src/sensus/auditus/asr/asr_ops_attn.cu:88-108);
 //   * every K/V byte is read from HBM once per KV head: the query heads of a group share
 //     the tile (the reference re-reads it once per query head);
 //   * pages are gathered by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
-//     into a 3-stage shared-memory ring guarded by mbarriers, issued by a producer warp
-//     from a shared-memory copy of the block-table slice;
+//     into per-warp shared-memory rings guarded by mbarriers (192 KB in flight per SM),
+//     issued by a producer warp that walks the block table;
 //   * QK^T and PV run as m16n8k16 tensor-core tiles with fp32 accumulation: the 4..16
 //     query rows of a GQA group are far from a dense contraction (the tensor pipe stays
 //     under 10 % busy), they only keep the SM's issue slots free so that the kernel stays
@@ -25,14 +26,24 @@ namespace drkv {
 
 namespace {
 
-constexpr int kConsumerWarps = 4;
-constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kGroupTokens = 16;                               // keys per warp per stage
-constexpr int kStageTokens = kConsumerWarps * kGroupTokens;    // 64
-constexpr int kStages = 3;
-constexpr int kMaxChunkGroups = 256;                           // chunk_tokens <= 4096
+constexpr int kGroupTokens = 16;                               // keys per ring slot
 constexpr float kNegBig = -1.0e30f;                            // "no key seen yet" in the log2 domain
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;     // 2 s
+
+// Ring geometry per head_dim: consumer warps per CTA and slots per warp ring, sized so that
+// warps * depth * (K tile + V tile) = 192 KB of loads can be in flight per SM.
+template <int D> struct RingShape;
+template <> struct RingShape<64>  { static constexpr int kWarps = 8, kDepth = 6; };
+template <> struct RingShape<128> { static constexpr int kWarps = 8, kDepth = 3; };
+template <> struct RingShape<256> { static constexpr int kWarps = 4, kDepth = 3; };
+
+enum SlotFlags : int { SLOT_FIRST = 1, SLOT_LAST = 2, SLOT_SKIP = 4, SLOT_DONE = 8 };
+
+// What the producer tells a consumer warp about one ring slot.
+struct alignas(16) SlotMeta {
+    int b, kvh, part_slot, flags;   // part_slot: index of the partial of query row 0 of the group
+    int v_lo, v_hi, pad0, pad1;     // keys [v_lo, v_hi) of the 16 in the slot are visible
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -132,317 +143,431 @@ __device__ __forceinline__ void split_pack(float p0, float p1, uint32_t& hi, uin
     lo = Elem<T>::pack2(p0 - h.x, p1 - h.y);
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Prefix sums of per-sequence chunk counts live in shared memory: kMaxDecodeSeqs + 1 ints.
+
+// Persistent kernel, one CTA per SM, every warp on its own.  Work item = (sequence, KV head,
+// chunk of keys); a block-wide prefix sum of the per-sequence chunk counts turns the atomic
+// queue index into (sequence, head, chunk) without empty items.  A warp owns a private ring
+// of DEPTH slots (16 keys of K and V each), its 16-row query fragments and its (m, l, o)
+// state.  Its lane 0 issues the TMA gathers DEPTH - 1 groups ahead of the group being
+// computed, across item boundaries, and the next item (queue index, length, table row, first
+// page id) is fetched while the current one is processed, so that neither the atomic nor the
+// table look-ups sit on the critical path.  An item's partial goes straight from the
+// accumulators to global memory; there is no block-level barrier after start-up.
 // HI: the GQA group has more than 8 query heads, so rows 8..15 of the 16-row tile are live.
 template <typename T, int D, bool HI>
-__global__ void __launch_bounds__(kDecodeThreads, 2)
+__global__ void __launch_bounds__(RingShape<D>::kWarps * 32, 1)
 attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams p) {
+    constexpr int WARPS = RingShape<D>::kWarps, DEPTH = RingShape<D>::kDepth;
+    constexpr int THREADS = WARPS * 32;
     constexpr int NH = D / 64;                       // 128-byte sub-rows per head row
     constexpr int KSTEPS = D / 16;
     constexpr int NT = D / 8;
     constexpr int TILE_BYTES = NH * 2048;            // 16 keys of K (or V)
-    constexpr int STAGE_BYTES = 2 * kConsumerWarps * TILE_BYTES;
-    constexpr int OROW = D + 8;                      // padded fp32 row of the merge buffer
+    constexpr int SLOT_BYTES = 2 * TILE_BYTES;
     constexpr int NR = HI ? 2 : 1;
-
-    const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int trow = p.rows != nullptr ? p.rows[b] : p.row;
-    const int kv_end = p.kv_len != nullptr ? p.kv_len[b] : p.kv_end;
-    const int kv_begin = p.kv_begin;
-    const int tok_lo = (kv_begin / kGroupTokens) * kGroupTokens + chunk * p.chunk_tokens;
-    if (tok_lo >= kv_end) return;                    // uniform over the CTA, before any barrier exists
-    const int tok_hi = min(tok_lo + p.chunk_tokens, kv_end);
-    const int n_groups = (tok_hi - tok_lo + kGroupTokens - 1) / kGroupTokens;
-    const int n_iters = (n_groups + kConsumerWarps - 1) / kConsumerWarps;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* q_tile = smem + kStages * STAGE_BYTES;
-    int* s_pages = reinterpret_cast<int*>(q_tile + TILE_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_pages + kMaxChunkGroups);
-    __shared__ int s_dead;
+    SlotMeta* metas = reinterpret_cast<SlotMeta*>(smem + WARPS * DEPTH * SLOT_BYTES);   // [WARPS][DEPTH]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(metas + WARPS * DEPTH);               // full[WARPS][DEPTH]
+    int* cum = reinterpret_cast<int*>(bars + WARPS * DEPTH);                           // [n_seq + 1]
+    __shared__ int s_warp_tot[WARPS];
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages);
+    const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+    const uint32_t bar_full = smem_u32(bars);
+    const int base_tok = (p.kv_begin / kGroupTokens) * kGroupTokens;
+    const int CT = p.chunk_tokens;
 
     if (tid == 0) {
-        s_dead = 0;
-        for (int s = 0; s < kStages; s++) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, kConsumerWarps);
-        }
+        for (int i = 0; i < WARPS * DEPTH; i++) mbar_init(bar_full + 8 * i, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
     }
-    // Block-table slice of this chunk: one page id per 16-key group.
-    for (int gi = tid; gi < n_groups; gi += kDecodeThreads) {
-        const int logical = (tok_lo + gi * kGroupTokens) / p.page_size;
-        int page = -1;
-        if (logical < p.table_stride) page = p.tables[(int64_t)trow * p.table_stride + logical];
-        if (page >= p.max_pages) {
-            page = -1;
-            atomicExch(p.error_word, (int)KERR_BAD_PAGE);
-        }
-        s_pages[gi] = page;
-    }
-    // Query rows of the group, swizzled like a K tile; rows beyond the group are zero.
+    // Only the barrier set-up overlaps the preceding kernel: lengths, tables, the pool, the
+    // queue head and the scratch may all have been written by it.
+    pdl_wait();
+    pdl_launch_dependents();
+    // ---- items per sequence, exclusive prefix sum into cum[] ----
     {
-        const T* qb = reinterpret_cast<const T*>(p.q) + ((int64_t)b * p.num_q_heads + (int64_t)kvh * p.group) * D;
-        for (int i = tid; i < 16 * (D / 8); i += kDecodeThreads) {
-            const int r = i / (D / 8), c = i - r * (D / 8);
-            Vec16 v = {{0u, 0u, 0u, 0u}};
-            if (r < p.group) v = ldg16(qb + (int64_t)r * D + c * 8);
-            *reinterpret_cast<Vec16*>(q_tile + (c >> 3) * 2048 + swz(r, c & 7)) = v;
+        const int per = (p.n_seq + THREADS - 1) / THREADS;
+        const int lo = min(tid * per, p.n_seq), hi = min(lo + per, p.n_seq);
+        int local = 0;
+        for (int b = lo; b < hi; b++) {
+            const int kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + b) : p.kv_end;
+            int nch = kv_end > base_tok ? (kv_end - base_tok + CT - 1) / CT : 0;
+            nch = min(nch, p.max_chunks);
+            local += nch * p.num_kv_heads;
         }
+        int incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) s_warp_tot[w] = incl;
+        __syncthreads();
+        int offset = 0;
+        for (int i = 0; i < w; i++) offset += s_warp_tot[i];
+        int run = offset + incl - local;
+        for (int b = lo; b < hi; b++) {
+            cum[b] = run;
+            const int kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + b) : p.kv_end;
+            int nch = kv_end > base_tok ? (kv_end - base_tok + CT - 1) / CT : 0;
+            nch = min(nch, p.max_chunks);
+            run += nch * p.num_kv_heads;
+        }
+        if (tid == THREADS - 1) cum[p.n_seq] = offset + incl;
     }
     __syncthreads();
+    const int total_items = cum[p.n_seq];
+
+    // ---- next-item prefetch state (warp-uniform except raw_next, which lane 0 owns) ----
+    int raw_next = 0;
+    bool n_valid = false, n_page_loaded = false;
+    int n_b = 0, n_kvh = 0, n_chunk = 0, n_trow = 0, n_kv_end = 0, n_page = -1;
+    // ---- issue cursor ----
+    bool c_valid = false;
+    int c_b = 0, c_kvh = 0, c_chunk = 0, c_trow = 0, c_kv_end = 0, c_tok_lo = 0, c_ngroups = 0, c_gi = 0, c_page = -1;
+    int i_slot = 0, outstanding = 0;
+    // ---- compute cursor ----
+    int slot = 0, phase = 0;
+    const int64_t rows_per_plane = (int64_t)p.num_kv_heads * p.page_size;
+
+    auto fetch_raw = [&]() {
+        if (lane == 0) raw_next = atomicAdd(p.work_counter, 1);
+    };
+    // queue index -> (sequence, head, chunk); requests the sequence's length and table row
+    auto decode_next = [&]() {
+        const int raw = __shfl_sync(0xffffffffu, raw_next, 0);
+        fetch_raw();                                   // the one after, consumed an item later
+        if (raw >= total_items) {
+            n_valid = false;
+            return;
+        }
+        int lo = 0, hi = p.n_seq;                      // largest b with cum[b] <= raw
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (cum[mid] <= raw) lo = mid; else hi = mid;
+        }
+        n_b = lo;
+        const int nch = (cum[lo + 1] - cum[lo]) / p.num_kv_heads;
+        const int j = raw - cum[lo];
+        n_kvh = j / nch;
+        n_chunk = j - n_kvh * nch;
+        n_kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + lo) : p.kv_end;
+        n_trow = p.rows != nullptr ? __ldg(p.rows + lo) : p.row;
+        n_valid = true;
+        n_page_loaded = false;
+    };
+    auto load_page = [&](int trow, int tok) -> int {
+        const int logical = tok / p.page_size;
+        return logical < p.table_stride ? __ldg(p.tables + (int64_t)trow * p.table_stride + logical) : -1;
+    };
+
+    fetch_raw();
+    decode_next();
 
     float m2[2] = {kNegBig, kNegBig};
     float lsum[2] = {0.f, 0.f};
     float o[NT][2 * NR];
-#pragma unroll
-    for (int i = 0; i < NT; i++)
-#pragma unroll
-        for (int j = 0; j < 2 * NR; j++) o[i][j] = 0.f;
+    uint32_t qf[KSTEPS][4];
+    const int col = (lane & 3) * 2;
+    const int qrow = lane >> 2;
 
-    if (warp == kConsumerWarps) {
-        // ---------------- producer: one lane issues the TMA gathers ----------------
-        if (lane == 0) {
-            const int64_t rows_per_plane = (int64_t)p.num_kv_heads * p.page_size;
-            for (int it = 0; it < n_iters; it++) {
-                const int s = it % kStages, u = it / kStages;
-                if (!mbar_wait(bar_empty + 8 * s, (u & 1) ^ 1)) {
-                    atomicExch(p.error_word, (int)KERR_WAIT_EMPTY);
-                    s_dead = 1;
-                    break;
-                }
-                uint32_t bytes = 0;
-#pragma unroll
-                for (int g = 0; g < kConsumerWarps; g++) {
-                    const int gi = it * kConsumerWarps + g;
-                    if (gi < n_groups && s_pages[gi] >= 0) bytes += 2 * TILE_BYTES;
-                }
-                mbar_arrive_expect_tx(bar_full + 8 * s, bytes);
-                const uint32_t stage = smem_u32(smem + s * STAGE_BYTES);
-#pragma unroll
-                for (int g = 0; g < kConsumerWarps; g++) {
-                    const int gi = it * kConsumerWarps + g;
-                    if (gi >= n_groups) break;
-                    const int page = s_pages[gi];
-                    if (page < 0) continue;
-                    const int tok = tok_lo + gi * kGroupTokens;
-                    const int slot = tok % p.page_size;
+    while (true) {
+        // ------------- issue: keep DEPTH groups in flight, across item boundaries -------------
+        while (outstanding < DEPTH) {
+            if (!c_valid) {
+                if (!n_valid) break;
+                c_b = n_b; c_kvh = n_kvh; c_chunk = n_chunk; c_trow = n_trow; c_kv_end = n_kv_end;
+                c_tok_lo = base_tok + c_chunk * CT;
+                c_ngroups = (min(c_tok_lo + CT, c_kv_end) - c_tok_lo + kGroupTokens - 1) / kGroupTokens;
+                c_gi = 0;
+                c_page = n_page_loaded ? n_page : load_page(c_trow, c_tok_lo);
+                c_valid = true;
+                decode_next();
+            }
+            const int ring = w * DEPTH + i_slot;
+            const int tok0 = c_tok_lo + c_gi * kGroupTokens;
+            int page = c_page;
+            if (page >= p.max_pages) {
+                page = -1;
+                if (lane == 0) atomicExch(p.error_word, (int)KERR_BAD_PAGE);
+            }
+            const bool last = (c_gi == c_ngroups - 1);
+            if (lane == 0) {
+                SlotMeta m;
+                m.b = c_b;
+                m.kvh = c_kvh;
+                m.part_slot = (c_b * p.num_q_heads + c_kvh * p.group) * p.max_chunks + c_chunk;
+                m.flags = (c_gi == 0 ? SLOT_FIRST : 0) | (last ? SLOT_LAST : 0) | (page < 0 ? SLOT_SKIP : 0);
+                m.v_lo = max(0, p.kv_begin - tok0);
+                m.v_hi = min(kGroupTokens, c_kv_end - tok0);
+                m.pad0 = m.pad1 = 0;
+                metas[ring] = m;
+                // earlier generic-proxy accesses to this slot (ldmatrix reads, zero fill) are ordered
+                // before the async-proxy writes of the new gather
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive_expect_tx(bar_full + 8 * ring, page >= 0 ? SLOT_BYTES : 0);
+                if (page >= 0) {
+                    const uint32_t dst = smem_u32(smem + ring * SLOT_BYTES);
                     const int64_t rk = (((int64_t)p.layer * p.max_pages + page) * 2) * rows_per_plane +
-                                       (int64_t)kvh * p.page_size + slot;
+                                       (int64_t)c_kvh * p.page_size + (tok0 % p.page_size);
                     const int64_t rv = rk + rows_per_plane;
 #pragma unroll
                     for (int h = 0; h < NH; h++) {
-                        tma_load_2d(stage + g * TILE_BYTES + h * 2048, &tmap, h * 64, (int)rk, bar_full + 8 * s);
-                        tma_load_2d(stage + (kConsumerWarps + g) * TILE_BYTES + h * 2048, &tmap, h * 64, (int)rv,
-                                    bar_full + 8 * s);
+                        tma_load_2d(dst + h * 2048, &tmap, h * 64, (int)rk, bar_full + 8 * ring);
+                        tma_load_2d(dst + TILE_BYTES + h * 2048, &tmap, h * 64, (int)rv, bar_full + 8 * ring);
                     }
                 }
             }
+            if (++i_slot == DEPTH) i_slot = 0;
+            outstanding++;
+            if (last) {
+                c_valid = false;
+            } else {
+                c_gi++;
+                // page id of the next group: same table entry while inside one page
+                if ((tok0 + kGroupTokens) % p.page_size == 0) c_page = load_page(c_trow, tok0 + kGroupTokens);
+            }
+            // first page id of the prefetched item, once its table row has arrived
+            if (n_valid && !n_page_loaded) {
+                n_page = load_page(n_trow, base_tok + n_chunk * CT);
+                n_page_loaded = true;
+            }
         }
-    } else {
-        // ---------------- consumers: warp w owns key group w of every stage ----------------
-        uint32_t qf[KSTEPS][4];
-        {
-            const int mi = lane >> 3;
-            const int r = (mi & 1) * 8 + (lane & 7);
-            const uint32_t qbase = smem_u32(q_tile);
+        if (outstanding == 0) break;                   // queue drained and every group consumed
+
+        // ------------- compute the oldest group in flight -------------
+        const int ring = w * DEPTH + slot;
+        if (!mbar_wait(bar_full + 8 * ring, phase)) {
+            if (lane == 0) atomicExch(p.error_word, (int)KERR_WAIT_FULL);
+            break;
+        }
+        __syncwarp();
+        const SlotMeta meta = metas[ring];
+        if (meta.flags & SLOT_FIRST) {
+            // query rows of the group straight into m16k16 A fragments; rows beyond the group are zero
+            const T* qb = reinterpret_cast<const T*>(p.q) + ((int64_t)meta.b * p.num_q_heads + (int64_t)meta.kvh * p.group) * D;
+            const bool r0 = qrow < p.group, r1 = HI && (qrow + 8 < p.group);
+            const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qb + (int64_t)qrow * D + col);
+            const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qb + (int64_t)(qrow + 8) * D + col);
 #pragma unroll
             for (int kk = 0; kk < KSTEPS; kk++) {
-                const int c = 2 * kk + (mi >> 1);
-                ldmatrix_x4(qf[kk], qbase + (c >> 3) * 2048 + swz(r, c & 7));
-                if (!HI) { qf[kk][1] = 0u; qf[kk][3] = 0u; }
+                qf[kk][0] = r0 ? __ldg(q0 + 8 * kk) : 0u;
+                qf[kk][2] = r0 ? __ldg(q0 + 8 * kk + 4) : 0u;
+                qf[kk][1] = r1 ? __ldg(q1 + 8 * kk) : 0u;
+                qf[kk][3] = r1 ? __ldg(q1 + 8 * kk + 4) : 0u;
             }
-        }
-        const int col = (lane & 3) * 2;
-        for (int it = 0; it < n_iters; it++) {
-            const int s = it % kStages, u = it / kStages;
-            if (!mbar_wait(bar_full + 8 * s, u & 1)) {
-                atomicExch(p.error_word, (int)KERR_WAIT_FULL);
-                s_dead = 1;
-                break;
-            }
-            const int gi = it * kConsumerWarps + warp;
-            if (gi < n_groups && s_pages[gi] >= 0) {
-                const int tok0 = tok_lo + gi * kGroupTokens;
-                const int v_hi = min(kGroupTokens, kv_end - tok0);   // keys [v_lo, v_hi) of the group are visible
-                const int v_lo = max(0, kv_begin - tok0);
-                uint8_t* kt = smem + s * STAGE_BYTES + warp * TILE_BYTES;
-                uint8_t* vt = kt + kConsumerWarps * TILE_BYTES;
-                if (v_hi < kGroupTokens || v_lo > 0) {
-                    // Slots outside the visible range may hold anything (stale pages): give the
-                    // PV product zeros there so that 0 * garbage cannot produce a NaN.
-                    for (int i = lane; i < kGroupTokens * NH * 8; i += 32) {
-                        const int r = i / (NH * 8), c = i - r * (NH * 8);
-                        if (r >= v_hi || r < v_lo)
-                            *reinterpret_cast<Vec16*>(vt + (c >> 3) * 2048 + swz(r, c & 7)) = Vec16{{0u, 0u, 0u, 0u}};
-                    }
-                    __syncwarp();
-                }
-                // ---- S = Q K^T : 16 rows x 16 keys ----
-                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-                {
-                    const int mi = lane >> 3;
-                    const int key = (mi >> 1) * 8 + (lane & 7);
-                    const uint32_t kbase = smem_u32(kt);
-#pragma unroll
-                    for (int kk = 0; kk < KSTEPS; kk++) {
-                        const int c = 2 * kk + (mi & 1);
-                        uint32_t kb[4];
-                        ldmatrix_x4(kb, kbase + (c >> 3) * 2048 + swz(key, c & 7));
-                        Mma<T>::run(s0[0], s0[1], s0[2], s0[3], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], kb[0], kb[1]);
-                        Mma<T>::run(s1[0], s1[1], s1[2], s1[3], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], kb[2], kb[3]);
-                    }
-                }
-                // ---- online softmax in the log2 domain ----
-                const bool k0 = (col >= v_lo) && (col < v_hi), k1 = (col + 1 >= v_lo) && (col + 1 < v_hi);
-                const bool k8 = (col + 8 >= v_lo) && (col + 8 < v_hi), k9 = (col + 9 >= v_lo) && (col + 9 < v_hi);
-                uint32_t phi[4], plo[4];
-                float alpha[2] = {1.f, 1.f};
-#pragma unroll
-                for (int r = 0; r < NR; r++) {
-                    float x0 = k0 ? s0[2 * r] * p.scale_log2 : -INFINITY;
-                    float x1 = k1 ? s0[2 * r + 1] * p.scale_log2 : -INFINITY;
-                    float x8 = k8 ? s1[2 * r] * p.scale_log2 : -INFINITY;
-                    float x9 = k9 ? s1[2 * r + 1] * p.scale_log2 : -INFINITY;
-                    float mx = fmaxf(fmaxf(x0, x1), fmaxf(x8, x9));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    const float mnew = fmaxf(m2[r], mx);
-                    alpha[r] = fast_exp2(m2[r] - mnew);
-                    m2[r] = mnew;
-                    const float p0 = fast_exp2(x0 - mnew), p1 = fast_exp2(x1 - mnew);
-                    const float p8 = fast_exp2(x8 - mnew), p9 = fast_exp2(x9 - mnew);
-                    lsum[r] = lsum[r] * alpha[r] + ((p0 + p1) + (p8 + p9));
-                    split_pack<T>(p0, p1, phi[r], plo[r]);          // a0 (r=0) / a1 (r=1)
-                    split_pack<T>(p8, p9, phi[2 + r], plo[2 + r]);  // a2 / a3
-                }
-                if (!HI) { phi[1] = phi[3] = plo[1] = plo[3] = 0u; }
-                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
-#pragma unroll
-                    for (int i = 0; i < NT; i++) {
-                        o[i][0] *= alpha[0];
-                        o[i][1] *= alpha[0];
-                        if (HI) { o[i][2 * NR - 2] *= alpha[1]; o[i][2 * NR - 1] *= alpha[1]; }
-                    }
-                }
-                // ---- O += P V : 16 rows x D ----
-                {
-                    const int mi = lane >> 3;
-                    const int key = (mi & 1) * 8 + (lane & 7);
-                    const uint32_t vbase = smem_u32(vt);
-#pragma unroll
-                    for (int j = 0; j < NT; j += 2) {
-                        const int c = j + (mi >> 1);
-                        uint32_t vb[4];
-                        ldmatrix_x4_trans(vb, vbase + (c >> 3) * 2048 + swz(key, c & 7));
-                        if (HI) {
-                            Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], phi[0], phi[1], phi[2], phi[3], vb[0], vb[1]);
-                            Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[0], vb[1]);
-                            Mma<T>::run(o[j + 1][0], o[j + 1][1], o[j + 1][2 * NR - 2], o[j + 1][2 * NR - 1], phi[0], phi[1], phi[2], phi[3], vb[2], vb[3]);
-                            Mma<T>::run(o[j + 1][0], o[j + 1][1], o[j + 1][2 * NR - 2], o[j + 1][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[2], vb[3]);
-                        } else {
-                            float z0 = 0.f, z1 = 0.f;   // rows 8..15 are padding: their sums are discarded
-                            Mma<T>::run(o[j][0], o[j][1], z0, z1, phi[0], 0u, phi[2], 0u, vb[0], vb[1]);
-                            Mma<T>::run(o[j][0], o[j][1], z0, z1, plo[0], 0u, plo[2], 0u, vb[0], vb[1]);
-                            Mma<T>::run(o[j + 1][0], o[j + 1][1], z0, z1, phi[0], 0u, phi[2], 0u, vb[2], vb[3]);
-                            Mma<T>::run(o[j + 1][0], o[j + 1][1], z0, z1, plo[0], 0u, plo[2], 0u, vb[2], vb[3]);
-                        }
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
-        }
-        // row sums live split over the 4 lanes of a quad
-#pragma unroll
-        for (int r = 0; r < NR; r++) {
-            lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 1);
-            lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 2);
-        }
-    }
-
-    // ---------------- merge the four warps' partials, write the chunk partial ----------------
-    __syncthreads();   // every issued TMA has been waited for by every consumer: the ring is quiescent
-    if (s_dead) return;
-    float* mo = reinterpret_cast<float*>(smem);                       // [4][16][OROW]
-    float* mm = mo + kConsumerWarps * 16 * OROW;                      // [4][16]
-    float* ml = mm + kConsumerWarps * 16;                             // [4][16]
-    if (warp < kConsumerWarps) {
-        const int r0 = lane >> 2;
-#pragma unroll
-        for (int r = 0; r < NR; r++) {
-            const int row = r0 + 8 * r;
-            float* dst = mo + (warp * 16 + row) * OROW + (lane & 3) * 2;
+            m2[0] = m2[1] = kNegBig;
+            lsum[0] = lsum[1] = 0.f;
 #pragma unroll
             for (int i = 0; i < NT; i++)
-                *reinterpret_cast<float2*>(dst + 8 * i) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
-            if ((lane & 3) == 0) {
-                mm[warp * 16 + row] = m2[r];
-                ml[warp * 16 + row] = lsum[r];
+#pragma unroll
+                for (int j = 0; j < 2 * NR; j++) o[i][j] = 0.f;
+        }
+        if (!(meta.flags & SLOT_SKIP)) {
+            const int v_lo = meta.v_lo, v_hi = meta.v_hi;
+            uint8_t* kt = smem + ring * SLOT_BYTES;
+            uint8_t* vt = kt + TILE_BYTES;
+            if (v_hi < kGroupTokens || v_lo > 0) {
+                // Slots outside the visible range may hold anything (stale pages): give the
+                // PV product zeros there so that 0 * garbage cannot produce a NaN.
+                for (int i = lane; i < kGroupTokens * NH * 8; i += 32) {
+                    const int r = i / (NH * 8), c = i - r * (NH * 8);
+                    if (r >= v_hi || r < v_lo)
+                        *reinterpret_cast<Vec16*>(vt + (c >> 3) * 2048 + swz(r, c & 7)) = Vec16{{0u, 0u, 0u, 0u}};
+                }
+                __syncwarp();
+            }
+            // ---- S = Q K^T : 16 rows x 16 keys ----
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                const int mi = lane >> 3;
+                const int key = (mi >> 1) * 8 + (lane & 7);
+                const uint32_t kbase = smem_u32(kt);
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; kk++) {
+                    const int c = 2 * kk + (mi & 1);
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, kbase + (c >> 3) * 2048 + swz(key, c & 7));
+                    Mma<T>::run(s0[0], s0[1], s0[2], s0[3], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], kb[0], kb[1]);
+                    Mma<T>::run(s1[0], s1[1], s1[2], s1[3], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], kb[2], kb[3]);
+                }
+            }
+            // ---- online softmax in the log2 domain ----
+            const bool k0 = (col >= v_lo) && (col < v_hi), k1 = (col + 1 >= v_lo) && (col + 1 < v_hi);
+            const bool k8 = (col + 8 >= v_lo) && (col + 8 < v_hi), k9 = (col + 9 >= v_lo) && (col + 9 < v_hi);
+            uint32_t phi[4], plo[4];
+            float alpha[2] = {1.f, 1.f};
+#pragma unroll
+            for (int r = 0; r < NR; r++) {
+                float x0 = k0 ? s0[2 * r] * p.scale_log2 : -INFINITY;
+                float x1 = k1 ? s0[2 * r + 1] * p.scale_log2 : -INFINITY;
+                float x8 = k8 ? s1[2 * r] * p.scale_log2 : -INFINITY;
+                float x9 = k9 ? s1[2 * r + 1] * p.scale_log2 : -INFINITY;
+                float mx = fmaxf(fmaxf(x0, x1), fmaxf(x8, x9));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float mnew = fmaxf(m2[r], mx);
+                alpha[r] = fast_exp2(m2[r] - mnew);
+                m2[r] = mnew;
+                const float p0 = fast_exp2(x0 - mnew), p1 = fast_exp2(x1 - mnew);
+                const float p8 = fast_exp2(x8 - mnew), p9 = fast_exp2(x9 - mnew);
+                lsum[r] = lsum[r] * alpha[r] + ((p0 + p1) + (p8 + p9));
+                split_pack<T>(p0, p1, phi[r], plo[r]);          // a0 (r=0) / a1 (r=1)
+                split_pack<T>(p8, p9, phi[2 + r], plo[2 + r]);  // a2 / a3
+            }
+            if (!HI) { phi[1] = phi[3] = plo[1] = plo[3] = 0u; }
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+                for (int i = 0; i < NT; i++) {
+                    o[i][0] *= alpha[0];
+                    o[i][1] *= alpha[0];
+                    if (HI) { o[i][2 * NR - 2] *= alpha[1]; o[i][2 * NR - 1] *= alpha[1]; }
+                }
+            }
+            // ---- O += P V : 16 rows x D ----
+            {
+                const int mi = lane >> 3;
+                const int key = (mi & 1) * 8 + (lane & 7);
+                const uint32_t vbase = smem_u32(vt);
+#pragma unroll
+                for (int j = 0; j < NT; j += 2) {
+                    const int c = j + (mi >> 1);
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, vbase + (c >> 3) * 2048 + swz(key, c & 7));
+                    if (HI) {
+                        Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], phi[0], phi[1], phi[2], phi[3], vb[0], vb[1]);
+                        Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[0], vb[1]);
+                        Mma<T>::run(o[j + 1][0], o[j + 1][1], o[j + 1][2 * NR - 2], o[j + 1][2 * NR - 1], phi[0], phi[1], phi[2], phi[3], vb[2], vb[3]);
+                        Mma<T>::run(o[j + 1][0], o[j + 1][1], o[j + 1][2 * NR - 2], o[j + 1][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[2], vb[3]);
+                    } else {
+                        float z0 = 0.f, z1 = 0.f;   // rows 8..15 are padding: their sums are discarded
+                        Mma<T>::run(o[j][0], o[j][1], z0, z1, phi[0], 0u, phi[2], 0u, vb[0], vb[1]);
+                        Mma<T>::run(o[j][0], o[j][1], z0, z1, plo[0], 0u, plo[2], 0u, vb[0], vb[1]);
+                        Mma<T>::run(o[j + 1][0], o[j + 1][1], z0, z1, phi[0], 0u, phi[2], 0u, vb[2], vb[3]);
+                        Mma<T>::run(o[j + 1][0], o[j + 1][1], z0, z1, plo[0], 0u, plo[2], 0u, vb[2], vb[3]);
+                    }
+                }
             }
         }
-    }
-    __syncthreads();
-    const float kLn2 = 0.6931471805599453f;
-    for (int i = tid; i < p.group * D; i += kDecodeThreads) {
-        const int row = i / D, d = i - row * D;
-        float mmax = kNegBig;
+        __syncwarp();                                  // every lane is done with the slot's shared memory
+        outstanding--;
+        if (++slot == DEPTH) { slot = 0; phase ^= 1; }
+
+        if (meta.flags & SLOT_LAST) {
+            // the item's partial (m, l, o), un-normalised, straight from the accumulators
+            const float kLn2 = 0.6931471805599453f;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; w++) mmax = fmaxf(mmax, mm[w * 16 + row]);
-        float acc = 0.f, l = 0.f;
+            for (int r = 0; r < NR; r++) {
+                float l = lsum[r];
+                l += __shfl_xor_sync(0xffffffffu, l, 1);
+                l += __shfl_xor_sync(0xffffffffu, l, 2);
+                const int row = qrow + 8 * r;
+                if (row < p.group) {
+                    const int64_t ps = (int64_t)meta.part_slot + (int64_t)row * p.max_chunks;
+                    const bool empty = !(l > 0.f);
+                    float* dst = p.part_o + ps * D + col;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; w++) {
-            const float f = fast_exp2(mm[w * 16 + row] - mmax);
-            acc += f * mo[(w * 16 + row) * OROW + d];
-            l += f * ml[w * 16 + row];
-        }
-        const int64_t slot = ((int64_t)b * p.num_q_heads + (int64_t)kvh * p.group + row) * p.max_chunks + chunk;
-        const bool empty = !(l > 0.f);
-        p.part_o[slot * D + d] = empty ? 0.f : acc;
-        if (d == 0) {
-            p.part_m[slot] = empty ? -1.0e20f : mmax * kLn2;
-            p.part_l[slot] = empty ? 0.f : l;
+                    for (int i = 0; i < NT; i++)
+                        *reinterpret_cast<float2*>(dst + 8 * i) =
+                            empty ? make_float2(0.f, 0.f) : make_float2(o[i][2 * r], o[i][2 * r + 1]);
+                    if ((lane & 3) == 0) {
+                        p.part_m[ps] = empty ? -1.0e20f : m2[r] * kLn2;
+                        p.part_l[ps] = empty ? 0.f : l;
+                    }
+                }
+            }
         }
     }
 }
 
 // Merge of chunk partials: m = max m_c, weights exp(m_c - m); out = sum w_c o_c / sum w_c l_c.
-// Left unwritten when no key was visible (paged_attention.cu:266-268).
+// Left unwritten when no key was visible (paged_attention.cu:266-268).  One CTA per (query
+// head, sequence); its 8 warps take the chunks round-robin, each lane owning 4 (or 8)
+// consecutive dims as float4, and a shared-memory pass adds the 8 partial sums.
+constexpr int kCombineWarps = 8;
 template <typename T>
-__global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
+__global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const CombineParams p) {
     const int h = blockIdx.x, b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int D = p.head_dim;
+    const float kLog2e = 1.4426950408889634f;
+    __shared__ float s_m[kCombineWarps], s_l[kCombineWarps];
+    __shared__ float4 s_acc[kCombineWarps][64];         // D <= 256 -> at most 64 float4 per row
+
+    pdl_wait();                                          // partials come from the preceding kernel
+    pdl_launch_dependents();
     const int kv_end = p.kv_len != nullptr ? p.kv_len[b] : p.kv_end;
     const int base = (p.kv_begin / kGroupTokens) * kGroupTokens;
     int nchunks = kv_end > base ? (kv_end - base + p.chunk_tokens - 1) / p.chunk_tokens : 0;
     nchunks = min(nchunks, p.max_chunks);
     const int64_t slot0 = ((int64_t)b * p.num_q_heads + h) * p.max_chunks;
-    const int D = p.head_dim;
-    const float kLog2e = 1.4426950408889634f;
 
-    float mmax = -1.0e20f;
-    for (int c = 0; c < nchunks; c++) mmax = fmaxf(mmax, p.part_m[slot0 + c]);
+    float mloc = -1.0e20f;
+    for (int c = threadIdx.x; c < nchunks; c += kCombineWarps * 32) mloc = fmaxf(mloc, p.part_m[slot0 + c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+    if (lane == 0) s_m[warp] = mloc;
+    __syncthreads();
+    float mmax = s_m[0];
+#pragma unroll
+    for (int i = 1; i < kCombineWarps; i++) mmax = fmaxf(mmax, s_m[i]);
+
+    const int nq = D / 4;                                // float4 per row
+    float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
     float l = 0.f;
-    for (int c = 0; c < nchunks; c++)
-        l += p.part_l[slot0 + c] * fast_exp2((p.part_m[slot0 + c] - mmax) * kLog2e);
-
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    for (int c = warp; c < nchunks; c += kCombineWarps) {
+        const float wgt = fast_exp2((p.part_m[slot0 + c] - mmax) * kLog2e);
+        l += wgt * p.part_l[slot0 + c];
+        const float4* row = reinterpret_cast<const float4*>(p.part_o + (slot0 + c) * D);
+        if (lane < nq) {
+            const float4 v = row[lane];
+            acc0.x += wgt * v.x; acc0.y += wgt * v.y; acc0.z += wgt * v.z; acc0.w += wgt * v.w;
+        }
+        if (lane + 32 < nq) {
+            const float4 v = row[lane + 32];
+            acc1.x += wgt * v.x; acc1.y += wgt * v.y; acc1.z += wgt * v.z; acc1.w += wgt * v.w;
+        }
+    }
+    s_acc[warp][lane] = acc0;
+    s_acc[warp][lane + 32] = acc1;
+    if (lane == 0) s_l[warp] = l;
+    __syncthreads();
+    float lt = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCombineWarps; i++) lt += s_l[i];
+    for (int d = threadIdx.x; d < D; d += kCombineWarps * 32) {
         float acc = 0.f;
-        for (int c = 0; c < nchunks; c++)
-            acc += p.part_o[(slot0 + c) * D + d] * fast_exp2((p.part_m[slot0 + c] - mmax) * kLog2e);
+#pragma unroll
+        for (int i = 0; i < kCombineWarps; i++) acc += reinterpret_cast<const float*>(&s_acc[i][0])[d];
         if (p.out_partial != nullptr) {
-            p.out_partial[(int64_t)h * D + d] = l > 0.f ? acc : 0.f;
-        } else if (l > 0.f) {
-            reinterpret_cast<T*>(p.out)[((int64_t)b * p.num_q_heads + h) * D + d] = Elem<T>::from_f(acc / l);
+            p.out_partial[(int64_t)h * D + d] = lt > 0.f ? acc : 0.f;
+        } else if (lt > 0.f) {
+            reinterpret_cast<T*>(p.out)[((int64_t)b * p.num_q_heads + h) * D + d] = Elem<T>::from_f(acc / lt);
         }
     }
     if (p.out_partial != nullptr && threadIdx.x == 0) {
-        p.out_partial[(int64_t)p.num_q_heads * D + h] = l > 0.f ? mmax : -1.0e20f;
-        p.out_partial[(int64_t)p.num_q_heads * (D + 1) + h] = l > 0.f ? l : 0.f;
+        p.out_partial[(int64_t)p.num_q_heads * D + h] = lt > 0.f ? mmax : -1.0e20f;
+        p.out_partial[(int64_t)p.num_q_heads * (D + 1) + h] = lt > 0.f ? lt : 0.f;
     }
+    // The attention kernel that filled these partials is complete: rewind its work queue for
+    // the next launch on this stream.
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *p.work_counter = 0;
 }
 
 // Merge of whole-range partials in the external layout [Hq*D o | Hq m | Hq l] per part, in the
@@ -474,23 +599,26 @@ combine_external_kernel(int n_parts, const float* parts, int hq, int D, void* ou
     }
 }
 
-template <typename T, int D>
-cudaError_t launch_decode_t(const CUtensorMap& tmap, const DecodeParams& p, int n_seq, cudaStream_t stream) {
-    constexpr int NH = D / 64;
-    constexpr size_t smem = 1024 + (size_t)kStages * 2 * kConsumerWarps * NH * 2048 + NH * 2048 +
-                            kMaxChunkGroups * sizeof(int) + 2 * kStages * sizeof(uint64_t);
-    dim3 grid(p.max_chunks, p.num_kv_heads, n_seq);
-    cudaError_t e;
-    if (p.group > 8) {
-        e = cudaFuncSetAttribute(attend_decode_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+template <typename T, int D, bool HI>
+cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
+    constexpr int WARPS = RingShape<D>::kWarps, DEPTH = RingShape<D>::kDepth, NH = D / 64;
+    constexpr size_t smem = 1024 + (size_t)WARPS * DEPTH * (2 * NH * 2048 + sizeof(SlotMeta) + sizeof(uint64_t)) +
+                            (kMaxDecodeSeqs + 1) * sizeof(int);
+    static bool configured = false;   // per instantiation
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attend_decode_kernel<T, D, HI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        attend_decode_kernel<T, D, true><<<grid, kDecodeThreads, smem, stream>>>(tmap, p);
-    } else {
-        e = cudaFuncSetAttribute(attend_decode_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        attend_decode_kernel<T, D, false><<<grid, kDecodeThreads, smem, stream>>>(tmap, p);
+        configured = true;
     }
-    return cudaGetLastError();
+    int grid = (p.total_items + WARPS - 1) / WARPS;
+    if (grid > num_sms) grid = num_sms;
+    return launch_pdl(attend_decode_kernel<T, D, HI>, dim3(grid), dim3(WARPS * 32), smem, stream, tmap, p);
+}
+
+template <typename T, int D>
+cudaError_t launch_decode_t(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
+    return p.group > 8 ? launch_decode_hi<T, D, true>(tmap, p, num_sms, stream)
+                       : launch_decode_hi<T, D, false>(tmap, p, num_sms, stream);
 }
 
 }  // namespace
@@ -530,23 +658,23 @@ bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, in
     return true;
 }
 
-cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int n_seq, int head_dim, int dtype,
-                                 cudaStream_t stream) {
-    if (n_seq <= 0 || p.max_chunks <= 0) return cudaSuccess;
-    if (p.chunk_tokens % kStageTokens != 0 || p.chunk_tokens / kGroupTokens > kMaxChunkGroups || p.group > 16 ||
-        p.page_size % kGroupTokens != 0)
+cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,
+                                 int dtype, cudaStream_t stream) {
+    if (p.total_items <= 0) return cudaSuccess;
+    if (p.n_seq > kMaxDecodeSeqs) return cudaErrorInvalidValue;
+    if (p.chunk_tokens % kGroupTokens != 0 || p.chunk_tokens <= 0 || p.group > 16 || p.page_size % kGroupTokens != 0)
         return cudaErrorInvalidValue;
     const bool f16 = dtype == DRKV_DTYPE_F16;
     switch (head_dim) {
         case 64:
-            return f16 ? launch_decode_t<__half, 64>(tmap, p, n_seq, stream)
-                       : launch_decode_t<__nv_bfloat16, 64>(tmap, p, n_seq, stream);
+            return f16 ? launch_decode_t<__half, 64>(tmap, p, num_sms, stream)
+                       : launch_decode_t<__nv_bfloat16, 64>(tmap, p, num_sms, stream);
         case 128:
-            return f16 ? launch_decode_t<__half, 128>(tmap, p, n_seq, stream)
-                       : launch_decode_t<__nv_bfloat16, 128>(tmap, p, n_seq, stream);
+            return f16 ? launch_decode_t<__half, 128>(tmap, p, num_sms, stream)
+                       : launch_decode_t<__nv_bfloat16, 128>(tmap, p, num_sms, stream);
         case 256:
-            return f16 ? launch_decode_t<__half, 256>(tmap, p, n_seq, stream)
-                       : launch_decode_t<__nv_bfloat16, 256>(tmap, p, n_seq, stream);
+            return f16 ? launch_decode_t<__half, 256>(tmap, p, num_sms, stream)
+                       : launch_decode_t<__nv_bfloat16, 256>(tmap, p, num_sms, stream);
         default:
             return cudaErrorInvalidValue;
     }
@@ -555,11 +683,8 @@ cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p,
 cudaError_t launch_combine(const CombineParams& p, int n_seq, int dtype, cudaStream_t stream) {
     if (n_seq <= 0) return cudaSuccess;
     dim3 grid(p.num_q_heads, n_seq);
-    if (dtype == DRKV_DTYPE_F16)
-        combine_kernel<__half><<<grid, 128, 0, stream>>>(p);
-    else
-        combine_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(p);
-    return cudaGetLastError();
+    if (dtype == DRKV_DTYPE_F16) return launch_pdl(combine_kernel<__half>, grid, dim3(kCombineWarps * 32), 0, stream, p);
+    return launch_pdl(combine_kernel<__nv_bfloat16>, grid, dim3(kCombineWarps * 32), 0, stream, p);
 }
 
 cudaError_t launch_combine_external(int n_parts, const float* parts, int num_q_heads, int head_dim, void* out,

@@ -56,14 +56,15 @@ size_t page_bytes_all_layers(const drkv_geometry& g) {
     return (size_t)g.num_layers * 2 * g.num_kv_heads * g.page_size * g.head_dim * 2;
 }
 
-int pick_chunk(int n_seq, int hkv, int max_kv_span) {
-    // Enough CTAs to fill 148 SMs x 2 resident CTAs a few times over, but not so many
-    // chunks that the partials become a visible share of the traffic.
-    const long target_lo = 592, target_hi = 4736;
-    int chunk = 512;
-    auto ctas = [&](int c) { return (long)n_seq * hkv * ((max_kv_span + c - 1) / c); };
-    while (chunk > 64 && ctas(chunk) < target_lo) chunk >>= 1;
-    while (chunk < 4096 && ctas(chunk) > target_hi) chunk <<= 1;
+int pick_chunk(int n_seq, int hkv, int group, int max_kv_span, int num_sms) {
+    // Keys per work item.  Each item writes one fp32 partial per query head of the group
+    // (group * (D + 2) * 4 bytes against chunk * 2 * D * 2 bytes of K/V read), so the chunk
+    // stays large enough to keep that a few percent, and shrinks only when there would be
+    // fewer items than consumer warps on the GPU.
+    int chunk = group > 4 ? 512 : 256;
+    const long warps = (long)num_sms * 8;
+    auto items = [&](int c) { return (long)n_seq * hkv * ((max_kv_span + c - 1) / c); };
+    while (chunk > 64 && items(chunk) < warps) chunk >>= 1;
     return chunk;
 }
 
@@ -87,6 +88,13 @@ struct drkv_engine {
     CUtensorMap tmap{};
     PoolLayout layout{};
     int forced_chunk = 0;
+    int num_sms = 148;
+    int* d_work = nullptr;   // decode kernel's work-queue head
+
+    // optional per-launch timing of the decode attention kernel (events on the launch stream)
+    bool timing = false;
+    std::vector<cudaEvent_t> tev;   // pairs: start, stop
+    size_t tev_used = 0;
 
     // staging for table updates: two pinned buffers used alternately
     int32_t* h_stage[2] = {nullptr, nullptr};
@@ -179,8 +187,11 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
             if ((ce = cudaEventCreateWithFlags(&e->stage_done[i], cudaEventDisableTiming)) != cudaSuccess)
                 return fail(DRKV_ERR_CUDA, "cudaEventCreate", ce);
         }
-        if ((ce = cudaMalloc(&e->d_error, sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(error)", ce);
-        if ((ce = cudaMemset(e->d_error, 0, sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMemset(error)", ce);
+        if ((ce = cudaMalloc(&e->d_error, 2 * sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(error)", ce);
+        if ((ce = cudaMemset(e->d_error, 0, 2 * sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMemset(error)", ce);
+        e->d_work = e->d_error + 1;
+        if ((ce = cudaDeviceGetAttribute(&e->num_sms, cudaDevAttrMultiProcessorCount, cfg->device)) != cudaSuccess)
+            return fail(DRKV_ERR_CUDA, "cudaDeviceGetAttribute", ce);
         std::vector<float> inv;
         fill_inv_freq(geom->rope_theta, geom->rotary_dim, &inv);
         if ((ce = cudaMalloc(&e->d_inv_freq, sizeof(float) * (inv.size() + 1))) != cudaSuccess)
@@ -188,9 +199,9 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
         if (!inv.empty() &&
             (ce = cudaMemcpy(e->d_inv_freq, inv.data(), sizeof(float) * inv.size(), cudaMemcpyHostToDevice)) != cudaSuccess)
             return fail(DRKV_ERR_CUDA, "cudaMemcpy(inv_freq)", ce);
-        // split-KV scratch: every sequence at full table length in 512-key chunks, at least 64 MB
+        // split-KV scratch: every sequence at full table length in 256-key chunks, at least 64 MB
         const size_t row_tokens = (size_t)e->book.row_width() * geom->page_size;
-        size_t need = (size_t)cfg->max_seqs * geom->num_q_heads * ((row_tokens + 511) / 512) * (geom->head_dim + 2) * 4;
+        size_t need = (size_t)cfg->max_seqs * geom->num_q_heads * ((row_tokens + 255) / 256) * (geom->head_dim + 2) * 4;
         e->scratch_bytes = need < (64u << 20) ? (64u << 20) : need;
         if ((ce = cudaMalloc(&e->d_scratch, e->scratch_bytes)) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(scratch)", ce);
         const char* terr = nullptr;
@@ -215,6 +226,7 @@ void drkv_destroy(drkv_engine* e) {
         cudaFree(e->d_inv_freq);
         cudaFree(e->d_error);
         cudaFree(e->d_scratch);
+        for (auto& ev : e->tev) cudaEventDestroy(ev);
         for (int i = 0; i < 2; i++) {
             if (e->h_stage[i]) cudaFreeHost(e->h_stage[i]);
             if (e->stage_done[i]) cudaEventDestroy(e->stage_done[i]);
@@ -460,9 +472,32 @@ int drkv_kernel_error(drkv_engine* e) {
 
 int drkv_set_chunk_tokens(drkv_engine* e, int chunk_tokens) {
     NEED(e);
-    if (chunk_tokens != 0 && (chunk_tokens % 64 != 0 || chunk_tokens < 64 || chunk_tokens > 4096))
-        return set_err(DRKV_ERR_INVALID, "chunk_tokens must be 0 (automatic) or a multiple of 64 in [64, 4096]");
+    if (chunk_tokens != 0 && (chunk_tokens % 16 != 0 || chunk_tokens < 16))
+        return set_err(DRKV_ERR_INVALID, "chunk_tokens must be 0 (automatic) or a positive multiple of 16");
     e->forced_chunk = chunk_tokens;
+    return DRKV_OK;
+}
+
+int drkv_kernel_timing(drkv_engine* e, int enable, double* total_ms, int* launches) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (total_ms || launches) {
+        double sum = 0;
+        CUDA_TRY(cudaDeviceSynchronize());
+        for (size_t i = 0; i + 1 < e->tev_used; i += 2) {
+            float ms = 0;
+            CUDA_TRY(cudaEventElapsedTime(&ms, e->tev[i], e->tev[i + 1]));
+            sum += ms;
+        }
+        if (total_ms) *total_ms = sum;
+        if (launches) *launches = (int)(e->tev_used / 2);
+    }
+    e->tev_used = 0;
+    e->timing = enable != 0;
+    if (e->timing && e->tev.empty()) {
+        e->tev.resize(2 * 512);
+        for (auto& ev : e->tev) CUDA_TRY(cudaEventCreate(&ev));
+    }
     return DRKV_OK;
 }
 
@@ -517,11 +552,12 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
                          int row, int kv_begin, int kv_end, int max_span, const void* q, void* out,
                          float* out_partial, float scale, cudaStream_t stream) {
     const drkv_geometry& g = e->geom;
-    int chunk = e->forced_chunk ? e->forced_chunk : pick_chunk(n_seq, g.num_kv_heads, max_span);
+    int chunk = e->forced_chunk ? e->forced_chunk
+                                : pick_chunk(n_seq, g.num_kv_heads, g.num_q_heads / g.num_kv_heads, max_span, e->num_sms);
     auto need_bytes = [&](int c) {
         return (size_t)n_seq * g.num_q_heads * ((max_span + c - 1) / c) * (g.head_dim + 2) * 4;
     };
-    while (need_bytes(chunk) > e->scratch_bytes && chunk < 4096) chunk <<= 1;
+    while (need_bytes(chunk) > e->scratch_bytes && chunk < (1 << 24)) chunk <<= 1;
     if (need_bytes(chunk) > e->scratch_bytes)
         return set_err(DRKV_ERR_CAPACITY, "attend: split-KV scratch too small for %d sequences x %d keys", n_seq, max_span);
     const int max_chunks = (max_span + chunk - 1) / chunk;
@@ -547,9 +583,18 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     p.page_size = g.page_size;
     p.chunk_tokens = chunk;
     p.max_chunks = max_chunks;
+    p.n_seq = n_seq;
+    p.total_items = n_seq * g.num_kv_heads * max_chunks;
+    p.work_counter = e->d_work;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.error_word = e->d_error;
-    CUDA_TRY(launch_attend_decode(e->tmap, p, n_seq, g.head_dim, g.dtype, stream));
+    const bool timed = e->timing && e->tev_used + 2 <= e->tev.size();
+    if (timed) CUDA_TRY(cudaEventRecord(e->tev[e->tev_used], stream));
+    CUDA_TRY(launch_attend_decode(e->tmap, p, e->num_sms, g.head_dim, g.dtype, stream));
+    if (timed) {
+        CUDA_TRY(cudaEventRecord(e->tev[e->tev_used + 1], stream));
+        e->tev_used += 2;
+    }
 
     CombineParams c{};
     c.part_o = p.part_o;
@@ -564,6 +609,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     c.max_chunks = max_chunks;
     c.out = out;
     c.out_partial = out_partial;
+    c.work_counter = e->d_work;
     CUDA_TRY(launch_combine(c, n_seq, g.dtype, stream));
     return DRKV_OK;
 }
@@ -575,8 +621,16 @@ int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_ro
     if (layer < 0 || layer >= e->geom.num_layers || n_seq < 0 || !d_rows || !d_kv_len || !q || !out || max_kv_len < 0)
         return set_err(DRKV_ERR_INVALID, "attend_decode: bad argument");
     if (n_seq == 0 || max_kv_len == 0) return DRKV_OK;
-    return decode_common(e, layer, n_seq, d_rows, d_kv_len, 0, 0, 0, max_kv_len, q, out, nullptr, scale,
-                         (cudaStream_t)stream);
+    // one launch takes up to kMaxDecodeSeqs sequences; larger batches go in slices
+    const size_t row_bytes = (size_t)e->geom.num_q_heads * e->geom.head_dim * 2;
+    for (int s0 = 0; s0 < n_seq; s0 += kMaxDecodeSeqs) {
+        const int n = n_seq - s0 < kMaxDecodeSeqs ? n_seq - s0 : kMaxDecodeSeqs;
+        int rc = decode_common(e, layer, n, d_rows + s0, d_kv_len + s0, 0, 0, 0, max_kv_len,
+                               (const char*)q + s0 * row_bytes, (char*)out + s0 * row_bytes, nullptr, scale,
+                               (cudaStream_t)stream);
+        if (rc != DRKV_OK) return rc;
+    }
+    return DRKV_OK;
 }
 
 int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end, const void* q, float* part,

@@ -43,6 +43,9 @@ struct DecodeParams {
     float* part_l;            // [n_seq][Hq][max_chunks]
     int layer, max_pages, num_q_heads, num_kv_heads, group, page_size;
     int chunk_tokens, max_chunks;
+    int n_seq;
+    int total_items;          // upper bound n_seq * num_kv_heads * max_chunks (sizes the grid)
+    int* work_counter;        // device int, 0 at launch; the combine kernel rewinds it
     float scale_log2;         // scale * log2(e)
     int* error_word;
 };
@@ -56,6 +59,7 @@ struct CombineParams {
     int num_q_heads, head_dim, chunk_tokens, max_chunks;
     void* out;                // storage type [n_seq][Hq][D] (normalised) ...
     float* out_partial;       // ... or fp32 partial [Hq*D | Hq m | Hq l] when non-null
+    int* work_counter;        // the attention kernel's queue head, reset to 0 here
 };
 
 cudaError_t launch_append_rope(const AppendParams& p, int n_tokens, int dtype, cudaStream_t stream);
@@ -66,8 +70,9 @@ cudaError_t launch_cow_copy(const CowParams& p, int num_layers, cudaStream_t str
 bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
                           int num_kv_heads, int page_size, int head_dim, const char** err);
 
-cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int n_seq, int head_dim,
+cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,
                                  int dtype, cudaStream_t stream);
+constexpr int kMaxDecodeSeqs = 2048;   // sequences one decode-attention launch can take
 cudaError_t launch_combine(const CombineParams& p, int n_seq, int dtype, cudaStream_t stream);
 
 // Merges partials that already sit in the external layout (drkv_attend_partial).

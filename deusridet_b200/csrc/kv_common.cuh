@@ -133,6 +133,31 @@ __device__ __forceinline__ void stg16(void* p, const Vec16& v) {
                  : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with launch_pdl() may start while its
+// predecessor in the stream is still running.  pdl_wait() returns once the predecessor has
+// completed and its writes are visible; everything that touches memory shared with earlier
+// kernels comes after it.  pdl_launch_dependents() lets the successor's CTAs be scheduled
+// as soon as this grid leaves room.  Every kernel of the engine waits, so completion stays
+// chained in stream order.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Error word shared by all kernels of one engine: 0 = fine.  A kernel that gives up on a
 // bounded wait stores a code here instead of trapping, so the context stays usable.
 enum KernelError : int { KERR_NONE = 0, KERR_WAIT_FULL = 1, KERR_WAIT_EMPTY = 2, KERR_BAD_PAGE = 3 };

@@ -133,6 +133,16 @@ class PagedKVEngine:
     def check_kernels(self) -> None: check(self.lib.drkv_kernel_error(self.h))
     def set_chunk_tokens(self, n: int) -> None: check(self.lib.drkv_set_chunk_tokens(self.h, n))
 
+    def kernel_timing(self, enable: bool, read: bool = False):
+        """Switches per-launch event timing of the decode kernel; with read=True returns
+        (total_ms, launches) accumulated since the previous call."""
+        if read:
+            ms, n = C.c_double(), C.c_int()
+            check(self.lib.drkv_kernel_timing(self.h, 1 if enable else 0, C.byref(ms), C.byref(n)))
+            return ms.value, n.value
+        check(self.lib.drkv_kernel_timing(self.h, 1 if enable else 0, None, None))
+        return None
+
     # ---- kernels ----------------------------------------------------------------------------
     def append_rope(self, layer, n_seq, d_rows, d_pos, k_src, v_src, stream=None) -> None:
         check(self.lib.drkv_append_rope(self.h, layer, n_seq, _ptr(d_rows), _ptr(d_pos), _ptr(k_src), _ptr(v_src),

@@ -166,8 +166,14 @@ DRKV_API int drkv_table_stride(const drkv_engine* e);
  * The reference has no counterpart: its kernels index the pool unchecked. */
 DRKV_API int drkv_kernel_error(drkv_engine* e);
 /* Keys per split-KV chunk of the decode kernel: 0 = chosen per call from the batch shape,
- * else a multiple of 64 in [64, 4096].  Tuning knob, no counterpart in the reference. */
+ * else a positive multiple of 16.  Tuning knob, no counterpart in the reference. */
 DRKV_API int drkv_set_chunk_tokens(drkv_engine* e, int chunk_tokens);
+/* Measurement aid (the reference brackets its kernels with cudaEvents the same way,
+ * src/machina/forward.cu:265-275): while enabled, every launch of the decode attention kernel
+ * is bracketed by CUDA events on its own stream (up to 512 launches).  A call first returns,
+ * if the pointers are non-null, the summed duration and the count since the last call
+ * (synchronises the device), then sets the new mode. */
+DRKV_API int drkv_kernel_timing(drkv_engine* e, int enable, double* total_ms, int* launches);
 
 /* ---- K/V append with RoPE on K ------------------------------------------------------ */
 /* paged_kv_cache_write + rope_kernel's K half (paged_attention.cu:73-115,
