@@ -89,6 +89,10 @@ SIGNATURES = {
     "drkv_attend_partial": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_combine_partials": (_i, [_vp, _i, _vp, _vp, _vp]),
     "drkv_partial_floats": (_sz, [_vp]),
+    "drkv_k_cache_write": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
+    "drkv_k_cache_write_batch": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "drkv_k_decode_attention": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _sz, _vp]),
+    "drkv_k_decode_scratch_bytes": (_sz, [C.POINTER(Geometry), _i]),
 }
 
 _lib = None

@@ -604,11 +604,14 @@ cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int
     constexpr int WARPS = RingShape<D>::kWarps, DEPTH = RingShape<D>::kDepth, NH = D / 64;
     constexpr size_t smem = 1024 + (size_t)WARPS * DEPTH * (2 * NH * 2048 + sizeof(SlotMeta) + sizeof(uint64_t)) +
                             (kMaxDecodeSeqs + 1) * sizeof(int);
-    static bool configured = false;   // per instantiation
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attend_decode_kernel<T, D, HI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static bool configured[64] = {};  // per instantiation and device: the attribute belongs to the context
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        e = cudaFuncSetAttribute(attend_decode_kernel<T, D, HI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     int grid = (p.total_items + WARPS - 1) / WARPS;
     if (grid > num_sms) grid = num_sms;

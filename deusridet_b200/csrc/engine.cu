@@ -11,6 +11,7 @@
 #include "../../include/drkv.h"
 #include "kernels.hpp"
 #include "page_book.hpp"
+#include "stateless.hpp"
 
 using namespace drkv;
 
@@ -69,6 +70,10 @@ int pick_chunk(int n_seq, int hkv, int group, int max_kv_span, int num_sms) {
 }
 
 }  // namespace
+
+namespace drkv {
+void set_last_error(const char* msg) { g_err = msg ? msg : ""; }
+}  // namespace drkv
 
 struct drkv_engine {
     drkv_geometry geom{};

@@ -1,0 +1,211 @@
+// deusridet_shim.hpp — the reference's C++ call surface on top of the C ABI (drkv.h).
+//
+// Header-only.  A DeusRidet build that includes this instead of memoria/block_pool.h,
+// memoria/cache_manager.h and machina/paged_attention.h, and links libdrkv.so instead of
+// compiling block_pool.cpp / cache_manager.cpp / paged_attention.cu, keeps its callers
+// (src/conscientia/stream.cpp:145-255, 261-401; src/actus/awaken_consciousness.cpp:82-100)
+// unchanged: same class names, method names, argument meaning, bool / -1 failure convention.
+//
+//   BlockPool      src/memoria/block_pool.h:58-123
+//   CacheManager   src/memoria/cache_manager.h:52-169 (SSD tier and importance scorer: not
+//                  carried over; the pointers are accepted and ignored, which is also what the
+//                  reference does in production, src/actus/awaken_consciousness.cpp:91)
+//   paged_kv_cache_write / _batch, paged_gqa_decode_attention
+//                  src/machina/paged_attention.h:27-71
+//
+// The reference reads head counts and dims from process-wide ModelConfig statics
+// (src/machina/paged_attention.cu:110-114); here the integrator fills shim_geometry() once,
+// before the first init(), from the same statics.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <string>
+
+#include "drkv.h"
+
+namespace deusridet {
+
+// Defaults are the reference's compile-time PagedKVConfig (src/memoria/block_pool.h:34-40) and
+// Qwen3.5-27B's attention shape; set every field from ModelConfig in a real build.
+inline drkv_geometry& shim_geometry() {
+    static drkv_geometry g = {16, 24, 4, 256, 256, DRKV_DTYPE_F16, 64, 10000000.0f};
+    return g;
+}
+// CUDA device the pool lives on; -1 keeps bookkeeping only (host-side tests).
+inline int& shim_device() {
+    static int d = [] {
+        const char* s = std::getenv("DRKV_SHIM_DEVICE");
+        return s ? std::atoi(s) : 0;
+    }();
+    return d;
+}
+
+struct PagedKVConfig {
+    static constexpr int BLOCK_SIZE = 256;
+};
+
+class KVSwapper;         // accepted and ignored, see the header comment
+class ImportanceScorer;
+
+class BlockPool {
+public:
+    BlockPool() = default;
+    ~BlockPool() { destroy(); }
+    BlockPool(const BlockPool&) = delete;
+    BlockPool& operator=(const BlockPool&) = delete;
+
+    bool init(size_t budget_bytes, int block_size = PagedKVConfig::BLOCK_SIZE) {
+        return init_rows(budget_bytes, block_size, 1, 0, 0);
+    }
+    int alloc_block() { return e_ ? drkv_pool_alloc(e_) : -1; }
+    void free_block(int id) {
+        if (e_ && drkv_pool_free(e_, id) != DRKV_OK)
+            std::fprintf(stderr, "[Memoria] free_block(%d): %s\n", id, drkv_last_error());
+    }
+    int free_count() const { return e_ ? drkv_pool_free_count(e_) : 0; }
+    int max_blocks() const { return e_ ? drkv_pool_max_pages(e_) : 0; }
+    int block_size() const { return e_ ? drkv_pool_page_size(e_) : block_size_; }
+    __half* pool_ptr() const { return e_ ? static_cast<__half*>(drkv_pool_ptr(e_)) : nullptr; }
+    __half* k_ptr(int layer, int id) const {
+        return reinterpret_cast<__half*>(reinterpret_cast<char*>(pool_ptr()) + k_offset(layer, id));
+    }
+    __half* v_ptr(int layer, int id) const {
+        return reinterpret_cast<__half*>(reinterpret_cast<char*>(pool_ptr()) + v_offset(layer, id));
+    }
+    size_t k_offset(int layer, int id) const { return e_ ? drkv_pool_k_offset(e_, layer, id) : 0; }
+    size_t v_offset(int layer, int id) const { return e_ ? drkv_pool_v_offset(e_, layer, id) : 0; }
+    size_t total_bytes() const { return e_ ? drkv_pool_total_bytes(e_) : 0; }
+    void destroy() {
+        if (e_) drkv_destroy(e_);
+        e_ = nullptr;
+    }
+
+    drkv_engine* engine() const { return e_; }
+
+private:
+    friend class CacheManager;
+    bool init_rows(size_t budget_bytes, int block_size, int max_seqs, int row_width, int stream_evict) {
+        destroy();
+        block_size_ = block_size;
+        drkv_geometry g = shim_geometry();
+        g.page_size = block_size;
+        drkv_config c = {};
+        c.budget_bytes = budget_bytes;
+        c.max_seqs = max_seqs;
+        c.max_pages_per_seq = row_width;   // 0 = 2 x physical pages, CacheManager's logical space
+        c.device = shim_device();
+        c.stream_evict = stream_evict;
+        if (drkv_create(&g, &c, &e_) != DRKV_OK) {
+            std::fprintf(stderr, "[Memoria] BlockPool: %s\n", drkv_last_error());
+            e_ = nullptr;
+            return false;
+        }
+        return true;
+    }
+    drkv_engine* e_ = nullptr;
+    int block_size_ = PagedKVConfig::BLOCK_SIZE;
+};
+
+class CacheManager {
+public:
+    CacheManager() = default;
+    ~CacheManager() { destroy(); }
+    CacheManager(const CacheManager&) = delete;
+    CacheManager& operator=(const CacheManager&) = delete;
+
+    bool init(size_t kv_budget_bytes, const std::string& cache_dir = "",
+              int block_size = PagedKVConfig::BLOCK_SIZE, KVSwapper* = nullptr, ImportanceScorer* = nullptr) {
+        (void)cache_dir;
+        if (!pool_.init_rows(kv_budget_bytes, block_size, 1, 0, 1)) return false;
+        seq_ = drkv_seq_create(pool_.e_);
+        return seq_ >= 0;
+    }
+    bool ensure_blocks_for(int pos) { return ok(drkv_seq_ensure_pos(pool_.e_, seq_, pos, nullptr)); }
+    bool ensure_blocks_for_range(int pos_start, int m) {
+        return ok(drkv_seq_ensure_range(pool_.e_, seq_, pos_start, m, nullptr));
+    }
+    const int* d_block_table() const { return pool_.e_ ? drkv_device_tables(pool_.e_) : nullptr; }
+    void sync_block_table(cudaStream_t stream = 0) {
+        if (pool_.e_) drkv_sync_tables(pool_.e_, stream);
+    }
+    int seq_len() const { return pool_.e_ ? drkv_seq_len(pool_.e_, seq_) : 0; }
+    void set_seq_len(int n) {
+        if (pool_.e_) drkv_seq_set_len(pool_.e_, seq_, n);
+    }
+    int num_logical_blocks() const { return pool_.e_ ? drkv_seq_num_pages(pool_.e_, seq_) : 0; }
+    int evict_blocks(int n) { return pool_.e_ ? drkv_seq_evict(pool_.e_, seq_, n) : 0; }
+    bool ensure_free_blocks(int n_free) { return pool_.e_ && drkv_ensure_free(pool_.e_, seq_, n_free) == 1; }
+    void prefetch_block(int) {}
+    BlockPool& block_pool() { return pool_; }
+    const BlockPool& block_pool() const { return pool_; }
+    int gpu_blocks_used() const { return pool_.max_blocks() - pool_.free_count(); }
+    int ssd_blocks_used() const { return 0; }
+    int free_blocks() const { return pool_.free_count(); }
+    void destroy() {
+        pool_.destroy();
+        seq_ = -1;
+    }
+    // Host copy of the table, for tests.
+    int host_table(int* out, int cap) const { return pool_.e_ ? drkv_seq_table(pool_.e_, seq_, out, cap) : 0; }
+
+private:
+    bool ok(int rc) {
+        if (rc == DRKV_OK) return true;
+        std::fprintf(stderr, "[Memoria] %s\n", drkv_last_error());
+        return false;
+    }
+    BlockPool pool_;
+    int seq_ = -1;
+};
+
+// ---- src/machina/paged_attention.h:27-71 -------------------------------------------------------
+inline void paged_kv_cache_write(const __half* src_k, const __half* src_v, __half* kv_pool,
+                                 const int* d_block_table, int fa_layer_idx, const int* d_pos,
+                                 int max_phys_blocks, int block_size, cudaStream_t stream = 0) {
+    drkv_geometry g = shim_geometry();
+    g.page_size = block_size;
+    if (drkv_k_cache_write(&g, src_k, src_v, kv_pool, d_block_table, fa_layer_idx, d_pos, max_phys_blocks, stream) !=
+        DRKV_OK)
+        std::fprintf(stderr, "[Machina] paged_kv_cache_write: %s\n", drkv_last_error());
+}
+
+inline void paged_kv_cache_write_batch(const __half* src_k, const __half* src_v, __half* kv_pool,
+                                       const int* d_block_table, int fa_layer_idx, int pos_start, int M,
+                                       int max_phys_blocks, int block_size, cudaStream_t stream = 0) {
+    drkv_geometry g = shim_geometry();
+    g.page_size = block_size;
+    if (drkv_k_cache_write_batch(&g, src_k, src_v, kv_pool, d_block_table, fa_layer_idx, pos_start, M,
+                                 max_phys_blocks, stream) != DRKV_OK)
+        std::fprintf(stderr, "[Machina] paged_kv_cache_write_batch: %s\n", drkv_last_error());
+}
+
+// The reference signature has no workspace argument; the shim keeps one device buffer per
+// process, grown on demand (growth synchronises the device, as any cudaMalloc does).
+inline void paged_gqa_decode_attention(const __half* Q, __half* kv_pool, const int* d_block_table, __half* out,
+                                       int fa_layer_idx, int seq_len, int max_phys_blocks, int block_size,
+                                       float scale, cudaStream_t stream = 0) {
+    static void* scratch = nullptr;
+    static size_t scratch_bytes = 0;
+    drkv_geometry g = shim_geometry();
+    g.page_size = block_size;
+    const size_t need = drkv_k_decode_scratch_bytes(&g, seq_len > 0 ? seq_len : 1);
+    if (need > scratch_bytes) {
+        if (scratch) cudaFree(scratch);
+        scratch_bytes = need * 2;
+        if (cudaMalloc(&scratch, scratch_bytes) != cudaSuccess) {
+            std::fprintf(stderr, "[Machina] paged_gqa_decode_attention: scratch allocation failed\n");
+            scratch = nullptr;
+            scratch_bytes = 0;
+            return;
+        }
+    }
+    if (drkv_k_decode_attention(&g, Q, kv_pool, d_block_table, out, fa_layer_idx, seq_len, max_phys_blocks, scale,
+                                scratch, scratch_bytes, stream) != DRKV_OK)
+        std::fprintf(stderr, "[Machina] paged_gqa_decode_attention: %s\n", drkv_last_error());
+}
+
+}  // namespace deusridet

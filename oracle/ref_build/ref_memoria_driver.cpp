@@ -12,19 +12,6 @@
 #include <cstdlib>
 #include <cstring>
 
-namespace deusridet {
-// The pool sizes itself from this process-wide static (block_pool.cpp:27).
-int ModelConfig::NUM_FA_LAYERS = 1;
-
-// importance_scorer.cu is CUDA; only the host arg-min is reachable from
-// cache_manager.cpp and only when a scorer is attached, which this driver never does.
-ImportanceScorer::~ImportanceScorer() {}
-int ImportanceScorer::least_important(const int*, int) const {
-    fprintf(stderr, "ref driver: ImportanceScorer is not linked\n");
-    abort();
-}
-}  // namespace deusridet
-
 using namespace deusridet;
 
 static size_t budget_for(int num_fa_layers, int n_pages, int block_size) {
