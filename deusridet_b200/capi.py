@@ -93,7 +93,9 @@ SIGNATURES = {
     "drkv_k_cache_write_batch": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "drkv_k_decode_attention": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _sz, _vp]),
     "drkv_k_decode_scratch_bytes": (_sz, [C.POINTER(Geometry), _i]),
+    "drkv_k_decode_attention_noalloc": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
 }
+NOALLOC_SCRATCH_BYTES = 4 << 20
 
 _lib = None
 

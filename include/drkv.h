@@ -230,6 +230,25 @@ DRKV_API int drkv_k_decode_attention(const drkv_geometry* g, const void* q, cons
                                      size_t scratch_bytes, void* stream);
 DRKV_API size_t drkv_k_decode_scratch_bytes(const drkv_geometry* g, int seq_len);
 
+/* No counterpart in the reference.  drkv_k_decode_attention for callers that cannot get
+ * device memory at all: hosts that own the whole GPU through their own allocator, threads that
+ * must not take cudaMalloc's device-wide synchronisation, processes that have filled HBM with
+ * KV pages.  The split-KV partials go to a scratch area built into the library
+ * (DRKV_NOALLOC_SCRATCH_BYTES, resident on every GPU that loads the library until the process
+ * exits); the call itself allocates and frees nothing, on the host side of CUDA or the device.
+ *   - Limit: num_q_heads * ceil(seq_len / 4096) * (head_dim + 2) * 4 + 256 bytes must fit in the
+ *     scratch (e.g. 32 heads, head_dim 128: about one million keys); beyond that the call
+ *     returns DRKV_ERR_CAPACITY and launches nothing.
+ *   - The first call on each device looks the scratch address up and configures the kernel;
+ *     make that call before any stream capture begins.
+ *   - All calls in the process share the one scratch area per GPU: two calls whose kernels can
+ *     overlap on the GPU (different streams, no ordering between them) race on it.  Calls
+ *     ordered on one stream are safe; each call re-initialises what it needs. */
+#define DRKV_NOALLOC_SCRATCH_BYTES (4u << 20)
+DRKV_API int drkv_k_decode_attention_noalloc(const drkv_geometry* g, const void* q, const void* kv_pool,
+                                             const int32_t* d_block_table, void* out, int layer,
+                                             int seq_len, int max_pages, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
