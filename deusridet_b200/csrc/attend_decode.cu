@@ -21,6 +21,7 @@
 // up records a code in the engine's error word and the CTA retires without trapping.
 #include "kernels.hpp"
 #include "kv_common.cuh"
+#include "sm100_primitives.cuh"
 
 namespace drkv {
 
@@ -28,7 +29,6 @@ namespace {
 
 constexpr int kGroupTokens = 16;                               // keys per ring slot
 constexpr float kNegBig = -1.0e30f;                            // "no key seen yet" in the log2 domain
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;     // 2 s
 
 // Ring geometry per head_dim: consumer warps per CTA and slots per warp ring, sized so that
 // warps * depth * (K tile + V tile) = 192 KB of loads can be in flight per SM.
@@ -44,61 +44,6 @@ struct alignas(16) SlotMeta {
     int b, kvh, part_slot, flags;   // part_slot: index of the partial of query row 0 of the group
     int v_lo, v_hi, pad0, pad1;     // keys [v_lo, v_hi) of the 16 in the slot are visible
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ unsigned long long global_timer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false after kWaitLimitNs without completion.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_timer();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 255u) == 0 && global_timer() - t0 > kWaitLimitNs) return false;
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
 
 template <typename T>
 struct Mma;
@@ -123,36 +68,12 @@ struct Mma<__nv_bfloat16> {
     }
 };
 
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// Byte offset inside a 16-row x 128-byte sub-tile written by TMA with 128-byte swizzle:
-// the 16-byte chunk index is XORed with the row index modulo 8 (tile base 1024-aligned).
-__device__ __forceinline__ uint32_t swz(int row, int chunk16) {
-    return (uint32_t)(row * 128 + ((chunk16 ^ (row & 7)) << 4));
-}
-
 // Two-term split of a pair of probabilities into the storage type: hi = rn(p), lo = rn(p - hi).
 template <typename T>
 __device__ __forceinline__ void split_pack(float p0, float p1, uint32_t& hi, uint32_t& lo) {
     hi = Elem<T>::pack2(p0, p1);
     float2 h = Elem<T>::unpack2(hi);
     lo = Elem<T>::pack2(p0 - h.x, p1 - h.y);
-}
-
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
 }
 
 // Prefix sums of per-sequence chunk counts live in shared memory: kMaxDecodeSeqs + 1 ints.

@@ -1,0 +1,416 @@
+// attend_prefill.cu — chunked-prefill paged attention on the 5th-generation tensor cores.
+//
+// Replaces paged_prefill_attention_kernel (src/machina/paged_attention.cu:465-554): one CTA per
+// (query head, query token), each re-streaming every earlier key with scalar loads.  Here the
+// m tokens of a chunk times the g query heads of a GQA group form the rows of 128-row tiles; a
+// CTA owns two such tiles of one KV head and walks the keys 0 .. pos_start + t in blocks of 64:
+//     S = Q K^T   tcgen05.mma  M128 x N64  x K128   (A = Q tile, B = K block, both K-major in smem)
+//     P = softmax piece (fp32 in registers, one row per thread, read from TMEM with tcgen05.ld)
+//     O += P V    tcgen05.mma  M128 x N128 x K64    (A = P in tensor memory, B = V block, MN-major)
+// with the S and O accumulators and P in tensor memory (2 x (64 + 128 + 64) = all 512 columns).
+// P is stored as a two-term split (hi + lo, 32 packed columns each); the lo term is multiplied in
+// only by CTAs whose rows see at most 1024 keys, where single-term 16-bit weights would cost more
+// than the 2e-3 bound on rows dominated by a handful of keys.  One thread
+// issues all MMAs; while the tensor pipe works on one tile, the four softmax warps of the other
+// tile run (ping-pong), so the K/V block fetched by TMA is used by 256 query rows.  O stays in
+// TMEM across key blocks and is rescaled there only when a row's running maximum has grown by
+// more than 2^8 since the scale in use was chosen; the final division by l undoes the stale
+// scale.  Same recurrence and mask as the reference: token t sees keys [0, pos_start + t],
+// fp32 accumulation, out = o / l, rows without a visible key are left unwritten.
+// Block-table holes contribute nothing.  Waits are bounded; a give-up sets the engine's error
+// word, and the CTA still frees its tensor memory before it returns.
+#include "kernels.hpp"
+#include "kv_common.cuh"
+#include "sm100_primitives.cuh"
+
+namespace drkv {
+
+namespace {
+
+constexpr int kPfD = 128;                      // head_dim handled by this kernel
+constexpr int kPfBlockN = 64;                  // keys per block
+constexpr int kPfStages = 4;                   // K/V blocks in flight
+constexpr int kPfSoftmaxWarps = 8;             // 4 per tile
+constexpr int kPfProducerWarp = 8;
+constexpr int kPfMmaWarp = 9;
+constexpr int kPfThreads = 10 * 32;
+constexpr int kPfTmemCols = 512;
+constexpr int kPfQBytes = 128 * kPfD * 2;      // one Q tile: [2 halves][128 rows][128 B]
+constexpr int kPfKBytes = kPfBlockN * kPfD * 2;   // K (or V) of one block: [2 halves][64 keys][128 B]
+constexpr int kPfLoTermMaxKeys = 1024;         // CTAs that see at most this many keys add the lo term of P
+constexpr int kPfMaxTableSlice = 4096;         // block-table entries staged in shared memory
+constexpr float kPfRescaleThreshold = 8.0f;    // log2 units
+constexpr float kNegBigPf = -1.0e30f;          // "no key seen yet"
+
+struct PfSmem {
+    // byte offsets from the 1024-aligned base
+    static constexpr int q = 0;                                        // 2 tiles
+    static constexpr int kv = q + 2 * kPfQBytes;                       // stages x (K | V)
+    static constexpr int pages = kv + kPfStages * 2 * kPfKBytes;       // int[kPfMaxTableSlice]
+    static constexpr int holes = pages + kPfMaxTableSlice * 4;         // int[kPfStages]
+    static constexpr int bars = holes + 16;                            // uint64[...]
+    static constexpr int n_bars = 2 * kPfStages + 8;
+    static constexpr int tmem = bars + n_bars * 8;                     // uint32 holder
+    static constexpr int total = tmem + 16;
+};
+
+// barrier indices
+enum { BAR_KV_FULL = 0, BAR_KV_EMPTY = kPfStages, BAR_S_READY = 2 * kPfStages, BAR_S_FREE = BAR_S_READY + 2,
+       BAR_P_READY = BAR_S_FREE + 2, BAR_O_READY = BAR_P_READY + 2 };
+
+template <typename T>
+__global__ void __launch_bounds__(kPfThreads, 1)
+attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t sbase = smem_u32(smem);
+    int* s_pages = reinterpret_cast<int*>(smem + PfSmem::pages);
+    volatile int* s_holes = reinterpret_cast<volatile int*>(smem + PfSmem::holes);
+    const uint32_t bars = sbase + PfSmem::bars;
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + PfSmem::tmem);
+    __shared__ int s_dead;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = p.group, kvh = blockIdx.y;
+    const int tok_per_tile = 128 / g;
+    const int rows_used = tok_per_tile * g;
+    const int t0 = blockIdx.x * 2 * tok_per_tile;                       // first chunk token of tile A
+    const int t_end = min(t0 + 2 * tok_per_tile, p.m);                  // one past the last token of the CTA
+    const bool tile_b_active = t0 + tok_per_tile < p.m;
+    const int kv_hi = p.pos_start + t_end;                              // keys any row of this CTA may see
+    const int n_blocks = (kv_hi + kPfBlockN - 1) / kPfBlockN;
+    const int n_groups = (kv_hi + 15) / 16;
+    constexpr int fmt = Elem<T>::kUmmaFormat;
+    const bool use_lo = kv_hi <= kPfLoTermMaxKeys;
+    // tensor-memory columns: S of both tiles, O of both tiles, P (hi | lo) of both tiles
+    constexpr uint32_t kPfColS = 0, kPfColO = 2 * kPfBlockN, kPfColP = 2 * kPfBlockN + 2 * kPfD;
+
+    if (tid == 0) {
+        s_dead = 0;
+        for (int s = 0; s < kPfStages; s++) {
+            mbar_init(bars + 8 * (BAR_KV_FULL + s), 1);
+            mbar_init(bars + 8 * (BAR_KV_EMPTY + s), 1);
+        }
+        for (int x = 0; x < 2; x++) {
+            mbar_init(bars + 8 * (BAR_S_READY + x), 1);
+            mbar_init(bars + 8 * (BAR_S_FREE + x), 128);
+            mbar_init(bars + 8 * (BAR_P_READY + x), 128);
+            mbar_init(bars + 8 * (BAR_O_READY + x), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
+    }
+    if (warp == kPfMmaWarp) tmem_alloc(sbase + PfSmem::tmem, kPfTmemCols);
+    pdl_wait();                                  // Q, the pool and the table may come from the preceding kernel
+    pdl_launch_dependents();
+
+    // block-table slice: one page id per 16 keys (staged when it fits)
+    const bool pages_staged = n_groups <= kPfMaxTableSlice;
+    if (pages_staged) {
+        for (int gi = tid; gi < n_groups; gi += kPfThreads) {
+            const int logical = (gi * 16) / p.page_size;
+            int page = logical < p.table_stride ? p.tables[(int64_t)p.row * p.table_stride + logical] : -1;
+            if (page >= p.max_pages) {
+                page = -1;
+                atomicExch(p.error_word, (int)KERR_BAD_PAGE);
+            }
+            s_pages[gi] = page;
+        }
+    }
+    // Q tiles: row r = (token t0 + X * tok_per_tile + r / g, query head kvh * g + r % g), written in the
+    // K-major 128-byte-swizzled layout the MMA descriptor expects; unused rows are zero.
+    if (warp < kPfSoftmaxWarps) {
+        const int x = warp >> 2, r = (warp & 3) * 32 + lane;
+        const int t = t0 + x * tok_per_tile + r / g;
+        const bool valid = r < rows_used && t < p.m;
+        const T* src = reinterpret_cast<const T*>(p.q) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * kPfD;
+        uint8_t* dst = smem + PfSmem::q + x * kPfQBytes;
+#pragma unroll
+        for (int c = 0; c < kPfD / 8; c++) {
+            Vec16 v = {{0u, 0u, 0u, 0u}};
+            if (valid) v = ldg16(src + 8 * c);
+            *reinterpret_cast<Vec16*>(dst + (c >> 3) * (128 * 128) + swz(r, c & 7)) = v;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp == kPfProducerWarp) {
+        // ------------------------------- TMA producer -------------------------------
+        const int64_t rows_per_plane = (int64_t)p.num_kv_heads * p.page_size;
+        for (int j = 0; j < n_blocks; j++) {
+            const int s = j % kPfStages, u = j / kPfStages;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(bars + 8 * (BAR_KV_EMPTY + s), (u & 1) ^ 1);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (lane == 0) { atomicExch(p.error_word, (int)KERR_WAIT_EMPTY); s_dead = 1; }
+                break;
+            }
+            uint8_t* kdst = smem + PfSmem::kv + s * 2 * kPfKBytes;
+            uint8_t* vdst = kdst + kPfKBytes;
+            int holes = 0;
+            uint32_t bytes = 0;
+            int pg[4];
+#pragma unroll
+            for (int gi = 0; gi < 4; gi++) {
+                const int grp = j * 4 + gi;
+                int page = -1;
+                if (grp < n_groups) {
+                    if (pages_staged) page = s_pages[grp];
+                    else {
+                        const int logical = (grp * 16) / p.page_size;
+                        page = logical < p.table_stride ? __ldg(p.tables + (int64_t)p.row * p.table_stride + logical) : -1;
+                        if (page >= p.max_pages) page = -1;
+                    }
+                }
+                pg[gi] = page;
+                if (page < 0) {
+                    holes |= 1 << gi;
+                    // nothing will be loaded: give the MMAs zeros instead of stale shared memory
+                    for (int i = lane; i < 2 * 2 * 16 * 8; i += 32) {       // K and V, 2 halves, 16 rows, 8 chunks
+                        const int kvsel = i >> 8, h = (i >> 7) & 1, r = (i >> 3) & 15, c = i & 7;
+                        uint8_t* base = (kvsel ? vdst : kdst) + h * (kPfBlockN * 128) + (gi * 16 + r) * 128 + c * 16;
+                        *reinterpret_cast<Vec16*>(base) = Vec16{{0u, 0u, 0u, 0u}};
+                    }
+                } else {
+                    bytes += 2 * 2 * 2048;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                s_holes[s] = holes;
+                mbar_arrive_expect_tx(bars + 8 * (BAR_KV_FULL + s), bytes);
+#pragma unroll
+                for (int gi = 0; gi < 4; gi++) {
+                    if (pg[gi] < 0) continue;
+                    const int tok = (j * 4 + gi) * 16;
+                    const int64_t rk = (((int64_t)p.layer * p.max_pages + pg[gi]) * 2) * rows_per_plane +
+                                       (int64_t)kvh * p.page_size + (tok % p.page_size);
+                    const int64_t rv = rk + rows_per_plane;
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        tma_load_2d(smem_u32(kdst) + h * (kPfBlockN * 128) + gi * 2048, &tmap, h * 64, (int)rk,
+                                    bars + 8 * (BAR_KV_FULL + s));
+                        tma_load_2d(smem_u32(vdst) + h * (kPfBlockN * 128) + gi * 2048, &tmap, h * 64, (int)rv,
+                                    bars + 8 * (BAR_KV_FULL + s));
+                    }
+                }
+            }
+        }
+    } else if (warp == kPfMmaWarp) {
+        // ------------------------------- MMA issuer -------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, 128, kPfBlockN, 0, 0);
+            constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 128, kPfD, 0, 1);
+            const int n_tiles = tile_b_active ? 2 : 1;
+            bool dead = false;
+            auto issue_qk = [&](int x, int s) {
+                const uint32_t qa = sbase + PfSmem::q + x * kPfQBytes;
+                const uint32_t kb = sbase + PfSmem::kv + s * 2 * kPfKBytes;
+#pragma unroll
+                for (int kk = 0; kk < kPfD / 16; kk++) {
+                    const uint32_t off_q = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+                    const uint32_t off_k = (kk >> 2) * (kPfBlockN * 128) + (kk & 3) * 32;
+                    umma_f16(tmem_base + kPfColS + x * kPfBlockN, umma_desc_sw128(qa + off_q, 16, 1024),
+                             umma_desc_sw128(kb + off_k, 16, 1024), idesc_qk, kk > 0);
+                }
+                umma_commit(bars + 8 * (BAR_S_READY + x));
+            };
+            auto issue_pv = [&](int x, int s, bool first_block) {
+                const uint32_t pa = tmem_base + kPfColP + x * 64;       // hi at +0, lo at +32; 8 columns per 16 keys
+                const uint32_t vb = sbase + PfSmem::kv + s * 2 * kPfKBytes + kPfKBytes;
+#pragma unroll
+                for (int kk = 0; kk < kPfBlockN / 16; kk++) {
+                    const uint64_t vdesc = umma_desc_sw128(vb + kk * 2048, kPfBlockN * 128, 1024);
+                    umma_f16_ts(tmem_base + kPfColO + x * kPfD, pa + kk * 8, vdesc, idesc_pv, !(first_block && kk == 0));
+                    if (use_lo) umma_f16_ts(tmem_base + kPfColO + x * kPfD, pa + 32 + kk * 8, vdesc, idesc_pv, true);
+                }
+                umma_commit(bars + 8 * (BAR_O_READY + x));
+            };
+            // S(0) for both tiles
+            if (!mbar_wait(bars + 8 * (BAR_KV_FULL + 0), 0)) dead = true;
+            if (!dead) {
+                tcgen05_fence_after();
+                for (int x = 0; x < n_tiles; x++) issue_qk(x, 0);
+            }
+            for (int j = 0; j < n_blocks && !dead; j++) {
+                const int s = j % kPfStages;
+                // S(j+1): as soon as the softmax warps have pulled S(j) out of tensor memory
+                if (j + 1 < n_blocks) {
+                    const int s1 = (j + 1) % kPfStages;
+                    if (!mbar_wait(bars + 8 * (BAR_KV_FULL + s1), ((j + 1) / kPfStages) & 1)) { dead = true; break; }
+                    for (int x = 0; x < n_tiles && !dead; x++) {
+                        if (!mbar_wait(bars + 8 * (BAR_S_FREE + x), j & 1)) { dead = true; break; }
+                        tcgen05_fence_after();
+                        issue_qk(x, s1);
+                    }
+                    if (dead) break;
+                }
+                // O += P(j) V(j)
+                for (int x = 0; x < n_tiles && !dead; x++) {
+                    if (!mbar_wait(bars + 8 * (BAR_P_READY + x), j & 1)) { dead = true; break; }
+                    tcgen05_fence_after();
+                    issue_pv(x, s, j == 0);
+                }
+                if (dead) break;
+                umma_commit(bars + 8 * (BAR_KV_EMPTY + s));        // both MMAs that read this stage are done
+            }
+            if (dead) {
+                atomicExch(p.error_word, (int)KERR_WAIT_FULL);
+                s_dead = 1;
+            }
+        }
+    } else {
+        // ------------------------------- softmax / correction / epilogue -------------------------------
+        const int x = warp >> 2;                                        // tile 0 / 1
+        const int r = (warp & 3) * 32 + lane;                           // tile row = TMEM lane
+        if (x == 0 || tile_b_active) {
+            const int t = t0 + x * tok_per_tile + r / g;
+            const bool valid = r < rows_used && t < p.m;
+            const int limit = valid ? p.pos_start + t + 1 : 0;          // keys [0, limit) are visible to this row
+            const int tile_min_limit = p.pos_start + t0 + x * tok_per_tile + 1;
+            const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+            const uint32_t t_s = tmem_base + lane_base + kPfColS + x * kPfBlockN;
+            const uint32_t t_o = tmem_base + lane_base + kPfColO + x * kPfD;
+            const uint32_t t_p = tmem_base + lane_base + kPfColP + x * 64;
+            float m_used = kNegBigPf, l = 0.f;
+            bool dead = false;
+            for (int j = 0; j < n_blocks; j++) {
+                if (!mbar_wait(bars + 8 * (BAR_S_READY + x), j & 1)) { dead = true; break; }
+                tcgen05_fence_after();
+                float sv[2][32];
+                tmem_ld32(t_s, sv[0]);
+                tmem_ld32(t_s + 32, sv[1]);
+                tmem_wait_ld();
+                tcgen05_fence_before();
+                mbar_arrive(bars + 8 * (BAR_S_FREE + x));               // S(j+1) may overwrite the columns now
+                const int key0 = j * kPfBlockN;
+                const int holes = s_holes[j % kPfStages];
+                const bool full = (key0 + kPfBlockN <= tile_min_limit) && holes == 0;
+                float mx = -INFINITY;
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int c = 0; c < 32; c++) {
+                        float v = sv[h][c] * p.scale_log2;
+                        if (!full) {
+                            const int k = h * 32 + c;
+                            if (key0 + k >= limit || ((holes >> (k >> 4)) & 1)) v = -INFINITY;
+                        }
+                        sv[h][c] = v;
+                        mx = fmaxf(mx, v);
+                    }
+                // Keep the scale in use unless the row maximum outgrew it by more than 2^8.
+                float factor = 1.f;
+                bool need = false;
+                if (mx > m_used + kPfRescaleThreshold) {
+                    factor = fast_exp2(m_used - mx);
+                    l *= factor;
+                    m_used = mx;
+                    need = j > 0;
+                }
+                float sum = 0.f;
+                uint32_t phi[32], plo[32];
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) {
+                        const float p0 = fast_exp2(sv[h][c] - m_used), p1 = fast_exp2(sv[h][c + 1] - m_used);
+                        sum += p0 + p1;
+                        const uint32_t hi = Elem<T>::pack2(p0, p1);
+                        phi[h * 16 + (c >> 1)] = hi;
+                        if (use_lo) {
+                            const float2 hf = Elem<T>::unpack2(hi);
+                            plo[h * 16 + (c >> 1)] = Elem<T>::pack2(p0 - hf.x, p1 - hf.y);
+                        }
+                    }
+                l += sum;
+                if (j > 0) {
+                    // PV(j-1) must have landed before O is touched or P is overwritten
+                    if (!mbar_wait(bars + 8 * (BAR_O_READY + x), (j - 1) & 1)) { dead = true; break; }
+                    tcgen05_fence_after();
+                    if (__any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+                        for (int c0 = 0; c0 < kPfD; c0 += 32) {
+                            float ov[32];
+                            tmem_ld32(t_o + c0, ov);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int c = 0; c < 32; c++) ov[c] *= factor;
+                            tmem_st32(t_o + c0, ov);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+                // P(j) into tensor memory: 64 keys = 32 packed columns (hi), then the lo term
+                tmem_st32(t_p, phi);
+                if (use_lo) tmem_st32(t_p + 32, plo);
+                tmem_wait_st();
+                tcgen05_fence_before();
+                mbar_arrive(bars + 8 * (BAR_P_READY + x));
+            }
+            if (!dead && !mbar_wait(bars + 8 * (BAR_O_READY + x), (n_blocks - 1) & 1)) dead = true;
+            if (dead) {
+                atomicExch(p.error_word, (int)KERR_WAIT_FULL);
+                s_dead = 1;
+            } else {
+                tcgen05_fence_after();
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                T* orow = reinterpret_cast<T*>(p.out) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * kPfD;
+#pragma unroll 1
+                for (int c0 = 0; c0 < kPfD; c0 += 32) {
+                    float ov[32];
+                    tmem_ld32(t_o + c0, ov);
+                    tmem_wait_ld();
+                    if (valid && l > 0.f) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 8) {
+                            Vec16 v;
+#pragma unroll
+                            for (int e = 0; e < 4; e++) v.w[e] = Elem<T>::pack2(ov[c + 2 * e] * inv, ov[c + 2 * e + 1] * inv);
+                            stg16(orow + c0 + c, v);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ------------------------------- teardown -------------------------------
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == kPfMmaWarp) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kPfTmemCols);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
+                                  cudaStream_t stream) {
+    if (p.m <= 0) return cudaSuccess;
+    if (head_dim != kPfD || p.group < 1 || p.group > 16 || p.page_size % 16 != 0) return cudaErrorInvalidValue;
+    constexpr size_t smem = 1024 + PfSmem::total;
+    const int tok_per_tile = 128 / p.group;
+    dim3 grid((p.m + 2 * tok_per_tile - 1) / (2 * tok_per_tile), p.num_kv_heads);
+    static bool configured[2][64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const int ti = dtype == DRKV_DTYPE_F16 ? 0 : 1;
+    if (dev < 0 || dev >= 64 || !configured[ti][dev]) {
+        e = ti == 0 ? cudaFuncSetAttribute(attend_prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                    : cudaFuncSetAttribute(attend_prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[ti][dev] = true;
+    }
+    if (ti == 0) return launch_pdl(attend_prefill_kernel<__half>, grid, dim3(kPfThreads), smem, stream, tmap, p);
+    return launch_pdl(attend_prefill_kernel<__nv_bfloat16>, grid, dim3(kPfThreads), smem, stream, tmap, p);
+}
+
+}  // namespace drkv

@@ -667,8 +667,30 @@ int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start,
                               float scale, void* stream) {
     NEED(e);
     NEED_DEVICE(e);
-    (void)layer; (void)seq; (void)pos_start; (void)m; (void)q; (void)out; (void)scale; (void)stream;
-    return set_err(DRKV_ERR_INVALID, "attend_prefill_chunk: not built yet");
+    const drkv_geometry& g = e->geom;
+    if (layer < 0 || layer >= g.num_layers || seq < 0 || seq >= e->book.max_seqs() || pos_start < 0 || m < 0 || !q || !out)
+        return set_err(DRKV_ERR_INVALID, "attend_prefill_chunk: bad argument");
+    if (g.head_dim != 128)
+        return set_err(DRKV_ERR_INVALID, "attend_prefill_chunk: the tensor-core prefill kernel is built for head_dim 128");
+    if (m == 0) return DRKV_OK;
+    PrefillParams p{};
+    p.tables = e->d_tables;
+    p.table_stride = e->book.row_width();
+    p.row = seq;
+    p.q = q;
+    p.out = out;
+    p.layer = layer;
+    p.max_pages = e->book.max_pages();
+    p.num_q_heads = g.num_q_heads;
+    p.num_kv_heads = g.num_kv_heads;
+    p.group = g.num_q_heads / g.num_kv_heads;
+    p.page_size = g.page_size;
+    p.pos_start = pos_start;
+    p.m = m;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.error_word = e->d_error;
+    CUDA_TRY(launch_attend_prefill(e->tmap, p, g.head_dim, g.dtype, (cudaStream_t)stream));
+    return DRKV_OK;
 }
 
 }  // extern "C"

@@ -50,6 +50,18 @@ struct DecodeParams {
     int* error_word;
 };
 
+// Chunked-prefill attention of one sequence: chunk tokens [0, m) at positions pos_start + t.
+struct PrefillParams {
+    const int32_t* tables;
+    int table_stride, row;
+    const void* q;            // [m][Hq][D]
+    void* out;                // [m][Hq][D]
+    int layer, max_pages, num_q_heads, num_kv_heads, group, page_size;
+    int pos_start, m;
+    float scale_log2;
+    int* error_word;
+};
+
 struct CombineParams {
     const float* part_o;
     const float* part_m;
@@ -73,6 +85,8 @@ bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, in
 cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,
                                  int dtype, cudaStream_t stream);
 constexpr int kMaxDecodeSeqs = 2048;   // sequences one decode-attention launch can take
+cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
+                                  cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, int n_seq, int dtype, cudaStream_t stream);
 
 // Merges partials that already sit in the external layout (drkv_attend_partial).

@@ -37,6 +37,7 @@ template <typename T>
 struct Elem;
 template <>
 struct Elem<__half> {
+    static constexpr int kUmmaFormat = 0;   // tcgen05 kind::f16 operand format: 0 = f16, 1 = bf16
     static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
     static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
     static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -49,6 +50,7 @@ struct Elem<__half> {
 };
 template <>
 struct Elem<__nv_bfloat16> {
+    static constexpr int kUmmaFormat = 1;
     static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
     static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
     static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {

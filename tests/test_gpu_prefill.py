@@ -1,0 +1,94 @@
+"""Chunked prefill into the paged cache on the device: RoPE + scatter of a chunk's K/V into newly
+allocated pages, then causal attention of the chunk over everything cached so far through the
+block table (tcgen05 kernel), against the CPU checker."""
+import numpy as np
+import pytest
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+
+
+def _prefill_case(oracle, *, layers, hq, hkv, page, dtype, theta, chunks, seed, d=128, holes=0):
+    """chunks: list of chunk lengths processed in order from position 0."""
+    import torch
+    from deusridet_b200 import PagedKVEngine
+
+    ob = oracle
+    rng = np.random.default_rng(seed)
+    total = int(sum(chunks))
+    n_pages = (total + page - 1) // page
+    max_pages = n_pages + 7
+    eng = PagedKVEngine(num_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page,
+                        dtype="f16" if dtype == ob.F16 else "bf16", rope_theta=theta, max_pages=max_pages,
+                        max_seqs=2, max_pages_per_seq=n_pages + 2, device=0)
+    g = ob.geom(layers, hq, hkv, d, page, dtype, d, theta)
+    tdt = torch.float16 if dtype == ob.F16 else torch.bfloat16
+    try:
+        H.shuffled_free_stack(eng, rng)
+        filler = eng.seq_create()            # so that the sequence under test is not table row 0
+        seq = eng.seq_create()
+        pool_host = H.randn_bits(rng, ob.pool_elems(g, max_pages), dtype)   # stale contents everywhere
+        eng.pool_tensor().copy_(torch.from_numpy(pool_host.view(np.int16)))
+        scale = 1.0 / np.sqrt(d)
+        pos = 0
+        for ci, m in enumerate(chunks):
+            assert eng.ensure_blocks_for_range(seq, pos, m)
+            if holes and ci == len(chunks) - 1:
+                assert eng.evict_blocks(seq, holes) == holes
+            eng.sync_block_table()
+            table = eng.table(seq)
+            for layer in range(layers):
+                k = H.randn_bits(rng, (m, hkv, d), dtype)
+                v = H.randn_bits(rng, (m, hkv, d), dtype)
+                q = H.randn_bits(rng, (m, hq, d), dtype)
+                out = torch.full((m, hq, d), 5.0, dtype=tdt, device="cuda")
+                eng.append_rope_chunk(layer, seq, pos, m, H.to_dev(k, dtype), H.to_dev(v, dtype))
+                eng.attend_prefill_chunk(layer, seq, pos, m, H.to_dev(q, dtype), out, scale)
+                torch.cuda.synchronize()
+                eng.check_kernels()
+                ob.append(g, pool_host, max_pages, table, layer, pos, m, k, v, rope=True)
+                want = H.torch_bits(torch.full((m, hq, d), 5.0, dtype=tdt)).copy()
+                ob.attend_prefill(g, pool_host, max_pages, table, layer, pos, m, q, want, scale)
+                got_f, want_f = ob.to_float(H.torch_bits(out), dtype), ob.to_float(want, dtype)
+                tol = np.maximum(TOL, H.ulp(want_f, dtype))
+                err = np.abs(got_f - want_f)
+                bad = np.argwhere(err > tol)
+                assert bad.size == 0, (f"chunk {ci} layer {layer}: {len(bad)} elements off, worst {err.max():.4g} at "
+                                       f"{np.unravel_index(err.argmax(), err.shape)}")
+                # tokens that already see a few hundred keys must meet the plain 2e-3 bound
+                deep = np.arange(m) + pos >= 256
+                if deep.any():
+                    assert err[deep].max() <= TOL
+            got_pool = eng.pool_tensor().cpu().numpy().view(np.uint16)
+            assert np.array_equal(got_pool, pool_host), f"chunk {ci}: pool bytes differ after the chunk append"
+            pos += m
+            eng.set_seq_len(seq, pos)
+    finally:
+        eng.close()
+
+
+def test_prefill_group7_two_chunks_bf16(drkv_lib, oracle):
+    """28 query / 4 KV heads (GQA 7), head_dim 128, bf16, page 16, 2 layers, 2 chunks of 256."""
+    _prefill_case(oracle, layers=2, hq=28, hkv=4, page=16, dtype=oracle.BF16, theta=1e6, chunks=[256, 256], seed=21)
+
+
+def test_prefill_ragged_chunks_group4(drkv_lib, oracle):
+    _prefill_case(oracle, layers=1, hq=32, hkv=8, page=16, dtype=oracle.BF16, theta=1e6, chunks=[1, 37, 100, 333, 64],
+                  seed=22)
+
+
+def test_prefill_group8_page64_fp16(drkv_lib, oracle):
+    _prefill_case(oracle, layers=1, hq=64, hkv=8, page=64, dtype=oracle.F16, theta=1e4, chunks=[200, 130], seed=23)
+
+
+def test_prefill_deep_context(drkv_lib, oracle):
+    """A 128-token chunk on top of 3000 cached tokens (odd start position)."""
+    _prefill_case(oracle, layers=1, hq=28, hkv=4, page=16, dtype=oracle.BF16, theta=1e6, chunks=[3001, 128], seed=24)
+
+
+def test_prefill_with_evicted_pages(drkv_lib, oracle):
+    _prefill_case(oracle, layers=1, hq=16, hkv=4, page=16, dtype=oracle.BF16, theta=1e4, chunks=[300, 90], seed=25,
+                  holes=4)
