@@ -36,6 +36,14 @@ WORKLOADS = {
                     "64 sequences, ctx U[1024,8192]"),
     "c5b": dict(layers=32, hq=32, hkv=8, d=128, page=16, n_seq=128, lo=4096, hi=4096, theta=1e6,
                 desc="independent 4096-token sequences, 32 layers, 32/8 heads, 128 per GPU (1024 over 8 GPUs)"),
+    # one long sequence split by KV page range over the ranks (strong scaling, NCCL all-gather per layer)
+    "c5a": dict(layers=8, hq=64, hkv=8, d=128, page=64, seq_len=524288, theta=1e6,
+                desc="one 524288-token sequence, 8 layers, 64/8 heads, head_dim 128, bf16, page 64, KV pages split "
+                     "by contiguous range across GPUs, partial (m,l,o) all-gathered and LSE-combined"),
+    # chunked prefill into the paged cache (tensor-core bound)
+    "c4": dict(layers=28, hq=28, hkv=4, d=128, page=16, n_seq=4, seq_len=32768, chunk=2048, theta=1e6,
+               desc="chunked prefill: 28 layers, 28/4 heads, head_dim 128, bf16, page 16, 4 sequences x 32768 "
+                    "tokens in 2048-token chunks (RoPE + scatter, then causal attention over all prior pages)"),
 }
 
 
@@ -60,7 +68,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -215,6 +223,9 @@ def run_ours(args):
     kv_bytes, all_bytes = algorithmic_bytes_per_layer(w, lens)
     peak, peak_kind = peaks()
     achieved = kv_bytes / (kms / kn_launch * 1e-3) / 1e9 if kn_launch else None
+    # DRAM bytes per algorithmic K/V byte of attend_decode_kernel, from the ncu capture summarised in
+    # profiles/attend_decode_kernel_c2.md (small case; traffic grows in proportion to the keys processed)
+    traffic_ratio = 1.024
 
     # ---- end to end through the public API with host buffers ----
     e2e = None
@@ -280,7 +291,7 @@ def run_ours(args):
             "hbm_gbs_step": all_bytes * L / (ms_step * 1e-3) / 1e9,
             "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-                         "traffic": None, "bytes_per_launch": kv_bytes,
+                         "traffic": kv_bytes * traffic_ratio, "bytes_per_launch": kv_bytes,
                          "us_per_launch": kms / kn_launch * 1e3 if kn_launch else None},
             "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
             "cow_copies": stats["cow_copies"],
@@ -289,6 +300,214 @@ def run_ours(args):
         dist.barrier()
         dist.destroy_process_group()
     return result, (w, lens)
+
+
+def _dist_setup():
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    torch.cuda.set_device(local)
+    return world, rank, local
+
+
+def run_c5a(args):
+    """Single long sequence, KV pages split by contiguous range across the ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from deusridet_b200 import PagedKVEngine, build, sharding
+    build.build()
+    world, rank, local = _dist_setup()
+    dev = torch.device(f"cuda:{local}")
+    w = dict(WORKLOADS["c5a"])
+    if args.layers:
+        w["layers"] = args.layers
+    L, hq, hkv, d, page, S = w["layers"], w["hq"], w["hkv"], w["d"], w["page"], w["seq_len"]
+    K, W = args.steps, args.warmup
+    begin, end = sharding.key_range_for_rank(S, page, rank, world)
+    my_pages = (end - begin + page - 1) // page
+    width = (S + page - 1) // page + 2
+    eng = PagedKVEngine(num_layers=L, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
+                        rope_theta=w["theta"], max_pages=max(4, my_pages + 8), max_seqs=1, max_pages_per_seq=width,
+                        device=local)
+    rng = np.random.default_rng(5 + rank)
+    pages = [eng.alloc_block() for _ in range(eng.max_blocks())]
+    for p in rng.permutation(eng.max_blocks()):
+        eng.free_block(int(p))
+    s = eng.seq_create()
+    assert eng.ensure_blocks_for_range(s, begin, end - begin)       # only this rank's page range is resident
+    eng.set_seq_len(s, S)
+    stream = torch.cuda.current_stream()
+    eng.sync_block_table(stream)
+    torch.manual_seed(11 + rank)
+    pool = eng.pool_tensor().view(torch.bfloat16)
+    for off in range(0, pool.numel(), 1 << 28):
+        pool[off:off + (1 << 28)].normal_()
+    if args.chunk:
+        eng.set_chunk_tokens(args.chunk)
+    torch.manual_seed(3)                                             # the query is replicated
+    q = torch.randn(L, hq, d, device=dev, dtype=torch.bfloat16)
+    kn = torch.randn(L, 1, hkv, d, device=dev, dtype=torch.bfloat16)
+    vn = torch.randn(L, 1, hkv, d, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(L, hq, d, device=dev, dtype=torch.bfloat16)
+    nf = eng.partial_floats()
+    mine = torch.empty(nf, device=dev, dtype=torch.float32)
+    gathered = torch.empty(world, nf, device=dev, dtype=torch.float32)
+    d_rows = torch.tensor([s], dtype=torch.int32, device=dev)
+    d_pos = torch.tensor([S - 1], dtype=torch.int32, device=dev)     # the token being decoded sits at S - 1
+    owner = sharding.owner_of_position(S - 1, S, page, world)
+    scale = 1.0 / float(np.sqrt(d))
+
+    def step():
+        for l in range(L):
+            if rank == owner:
+                eng.append_rope(l, 1, d_rows, d_pos, kn[l], vn[l], stream)
+            eng.attend_partial(l, s, begin, end, q[l], mine, scale, stream)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, mine)
+                eng.combine_partials(world, gathered, out[l], stream)
+            else:
+                eng.combine_partials(1, mine, out[l], stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        step()
+    barrier()
+    eng.check_kernels()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(K):
+        step()
+    e1.record(stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = float(t.item()) / K
+    eng.kernel_timing(True)
+    step()
+    kms, kn_l = eng.kernel_timing(False, read=True)
+    eng.check_kernels()
+    eng.close()
+    kv_rank = float(end - begin) * 2 * hkv * d * 2                   # this rank's K/V bytes per layer
+    peak, peak_kind = peaks()
+    res = None
+    if rank == 0:
+        achieved = kv_rank / (kms / kn_l * 1e-3) / 1e9
+        res = {"metric": "decode tokens/s/GPU + achieved HBM GB/s (% of peak) for paged attn+append",
+               "value": 1.0 / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+               "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+               "dtype": "bf16", "data": "synthetic",
+               "config": {"workload": f"c5a: {w['desc']}", "layers": L, "keys_per_gpu": end - begin,
+                          "parallelism": f"kv-range-split x{world}", "collective": "nccl all_gather of Hq*(D+2) fp32 per layer",
+                          "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer per GPU" % (kv_rank / 1e9)},
+               "hbm_gbs_step": world * kv_rank * L / (ms_step * 1e-3) / 1e9,
+               "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
+                            "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                            "bytes_per_launch": kv_rank, "us_per_launch": kms / kn_l * 1e3},
+               "gpu_launches": K * L * (3 + (1 if owner == 0 else 0)), "clocks": clocks, "e2e": None}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return res
+
+
+def run_c4(args):
+    """Chunked prefill of 4 sequences into the paged cache (one GPU)."""
+    import torch
+
+    from deusridet_b200 import PagedKVEngine, build
+    build.build()
+    world, rank, local = _dist_setup()
+    dev = torch.device(f"cuda:{local}")
+    w = dict(WORKLOADS["c4"])
+    if args.layers:
+        w["layers"] = args.layers
+    n_seq = args.seqs or w["n_seq"]
+    L, hq, hkv, d, page, S, C = w["layers"], w["hq"], w["hkv"], w["d"], w["page"], w["seq_len"], w["chunk"]
+    pages_per_seq = S // page
+    eng = PagedKVEngine(num_layers=L, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
+                        rope_theta=w["theta"], max_pages=n_seq * pages_per_seq + 16, max_seqs=n_seq,
+                        max_pages_per_seq=pages_per_seq + 1, device=local)
+    rng = np.random.default_rng(17 + rank)
+    pages = [eng.alloc_block() for _ in range(eng.max_blocks())]
+    for p in rng.permutation(eng.max_blocks()):
+        eng.free_block(int(p))
+    stream = torch.cuda.current_stream()
+    torch.manual_seed(23 + rank)
+    q = torch.randn(C, hq, d, device=dev, dtype=torch.bfloat16)
+    kn = torch.randn(C, hkv, d, device=dev, dtype=torch.bfloat16)
+    vn = torch.randn(C, hkv, d, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(C, hq, d, device=dev, dtype=torch.bfloat16)
+    scale = 1.0 / float(np.sqrt(d))
+
+    def full_prefill():
+        seqs = [eng.seq_create() for _ in range(n_seq)]
+        for pos in range(0, S, C):
+            for s in seqs:
+                assert eng.ensure_blocks_for_range(s, pos, C)       # 128 new pages per sequence and chunk
+            eng.sync_block_table(stream)
+            for s in seqs:
+                for l in range(L):
+                    eng.append_rope_chunk(l, s, pos, C, kn, vn, stream)
+                    eng.attend_prefill_chunk(l, s, pos, C, q, out, scale, stream)
+                eng.set_seq_len(s, pos + C)
+        return seqs
+
+    def release(seqs):
+        torch.cuda.synchronize()
+        for s in seqs:
+            eng.seq_release(s, discard=True)
+
+    for _ in range(max(1, min(args.warmup, 1))):
+        release(full_prefill())
+    eng.check_kernels()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    K = max(1, min(args.steps, 3))
+    e0.record(stream)
+    last = None
+    for _ in range(K):
+        if last is not None:
+            release(last)
+        last = full_prefill()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / K
+    eng.check_kernels()
+    eng.close()
+    flop = 4.0 * hq * d * (S * (S + 1) / 2.0) * L * n_seq          # QK^T and PV over the causal pairs
+    tfs = flop / (ms * 1e-3) / 1e12
+    peak = 1590.0
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak_kind = "fallback"
+    if os.path.exists(path):
+        with open(path) as f:
+            peak = float(json.load(f)["bf16_tflops_sustained"])
+        peak_kind = "measured (sustained)"
+    return {"metric": "prefill tokens/s (chunked prefill into the paged cache) + tensor TFLOP/s",
+            "value": n_seq * S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": 1,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": f"c4: {w['desc']}", "layers": L, "seqs": n_seq},
+            "roofline": {"bound": "tensor", "kernel": "attend_prefill_kernel (incl. append)", "achieved": tfs, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "TFLOP/s", "frac": tfs / peak, "traffic": None},
+            "gpu_launches": K * n_seq * (S // C) * L * 2, "clocks": clocks, "e2e": None}
 
 
 def eng_bytes(max_pages, w):
@@ -389,9 +608,19 @@ def main():
     if args.warmup < 3 and not (args.layers or args.seqs):
         args.warmup = 3
     if args.impl == "reference":
+        if args.workload not in ("c2", "c5b"):
+            args.workload = "c2"
         res = run_reference(args)
         if res is not None:
             print(json.dumps(res), flush=True)
+        return
+    if args.workload == "c5a":
+        res = run_c5a(args)
+        if res is not None:
+            print(json.dumps(res), flush=True)
+        return
+    if args.workload == "c4":
+        print(json.dumps(run_c4(args)), flush=True)
         return
     res, (w, lens) = run_ours(args)
     if res is not None:
