@@ -460,10 +460,11 @@ def run_c4(args):
             for s in seqs:
                 assert eng.ensure_blocks_for_range(s, pos, C)       # 128 new pages per sequence and chunk
             eng.sync_block_table(stream)
-            for s in seqs:
-                for l in range(L):
+            for l in range(L):
+                for s in seqs:
                     eng.append_rope_chunk(l, s, pos, C, kn, vn, stream)
-                    eng.attend_prefill_chunk(l, s, pos, C, q, out, scale, stream)
+                eng.attend_prefill_batch(l, seqs, [pos] * n_seq, [C] * n_seq, [q] * n_seq, [out] * n_seq, scale, stream)
+            for s in seqs:
                 eng.set_seq_len(s, pos + C)
         return seqs
 

@@ -86,6 +86,7 @@ SIGNATURES = {
     "drkv_append_rope_chunk": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp]),
     "drkv_attend_decode": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _vp]),
     "drkv_attend_prefill_chunk": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
+    "drkv_attend_prefill_batch": (_i, [_vp, _i, _i, _pi32, _pi32, _pi32, C.POINTER(_vp), C.POINTER(_vp), _f, _vp]),
     "drkv_attend_partial": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_combine_partials": (_i, [_vp, _i, _vp, _vp, _vp]),
     "drkv_partial_floats": (_sz, [_vp]),

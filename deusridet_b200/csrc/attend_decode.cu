@@ -452,17 +452,27 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
     const int nq = D / 4;                                // float4 per row
     float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
     float l = 0.f;
-    for (int c = warp; c < nchunks; c += kCombineWarps) {
-        const float wgt = fast_exp2((p.part_m[slot0 + c] - mmax) * kLog2e);
-        l += wgt * p.part_l[slot0 + c];
-        const float4* row = reinterpret_cast<const float4*>(p.part_o + (slot0 + c) * D);
-        if (lane < nq) {
-            const float4 v = row[lane];
-            acc0.x += wgt * v.x; acc0.y += wgt * v.y; acc0.z += wgt * v.z; acc0.w += wgt * v.w;
+    // four chunks per trip: their loads are independent, so one round trip to L2 covers all of them
+    for (int c0 = warp; c0 < nchunks; c0 += 4 * kCombineWarps) {
+        float wgt[4], lv[4];
+        float4 v0[4], v1[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int c = c0 + u * kCombineWarps;
+            const bool in = c < nchunks;
+            const int64_t sl = slot0 + (in ? c : c0);
+            wgt[u] = in ? p.part_m[sl] : -1.0e20f;
+            lv[u] = in ? p.part_l[sl] : 0.f;
+            const float4* row = reinterpret_cast<const float4*>(p.part_o + sl * D);
+            v0[u] = (in && lane < nq) ? row[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+            v1[u] = (in && lane + 32 < nq) ? row[lane + 32] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        if (lane + 32 < nq) {
-            const float4 v = row[lane + 32];
-            acc1.x += wgt * v.x; acc1.y += wgt * v.y; acc1.z += wgt * v.z; acc1.w += wgt * v.w;
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const float wg = (c0 + u * kCombineWarps < nchunks) ? fast_exp2((wgt[u] - mmax) * kLog2e) : 0.f;
+            l += wg * lv[u];
+            acc0.x += wg * v0[u].x; acc0.y += wg * v0[u].y; acc0.z += wg * v0[u].z; acc0.w += wg * v0[u].w;
+            acc1.x += wg * v1[u].x; acc1.y += wg * v1[u].y; acc1.z += wg * v1[u].z; acc1.w += wg * v1[u].w;
         }
     }
     s_acc[warp][lane] = acc0;

@@ -60,7 +60,12 @@ enum { BAR_KV_FULL = 0, BAR_KV_EMPTY = kPfStages, BAR_S_READY = 2 * kPfStages, B
 
 template <typename T>
 __global__ void __launch_bounds__(kPfThreads, 1)
-attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillParams p) {
+attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ PrefillParams p) {
+    // one sequence of the batch per grid.z; sequences with fewer tiles than grid.x leave the extra CTAs idle
+    const int p_m = p.m[blockIdx.z], p_pos_start = p.pos_start[blockIdx.z], p_row = p.row[blockIdx.z];
+    if ((int)blockIdx.x * 2 * (128 / p.group) >= p_m) return;
+    const void* const p_q = p.q[blockIdx.z];
+    void* const p_out = p.out[blockIdx.z];
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
@@ -75,9 +80,9 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPar
     const int tok_per_tile = 128 / g;
     const int rows_used = tok_per_tile * g;
     const int t0 = blockIdx.x * 2 * tok_per_tile;                       // first chunk token of tile A
-    const int t_end = min(t0 + 2 * tok_per_tile, p.m);                  // one past the last token of the CTA
-    const bool tile_b_active = t0 + tok_per_tile < p.m;
-    const int kv_hi = p.pos_start + t_end;                              // keys any row of this CTA may see
+    const int t_end = min(t0 + 2 * tok_per_tile, p_m);                  // one past the last token of the CTA
+    const bool tile_b_active = t0 + tok_per_tile < p_m;
+    const int kv_hi = p_pos_start + t_end;                              // keys any row of this CTA may see
     const int n_blocks = (kv_hi + kPfBlockN - 1) / kPfBlockN;
     const int n_groups = (kv_hi + 15) / 16;
     constexpr int fmt = Elem<T>::kUmmaFormat;
@@ -109,7 +114,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPar
     if (pages_staged) {
         for (int gi = tid; gi < n_groups; gi += kPfThreads) {
             const int logical = (gi * 16) / p.page_size;
-            int page = logical < p.table_stride ? p.tables[(int64_t)p.row * p.table_stride + logical] : -1;
+            int page = logical < p.table_stride ? p.tables[(int64_t)p_row * p.table_stride + logical] : -1;
             if (page >= p.max_pages) {
                 page = -1;
                 atomicExch(p.error_word, (int)KERR_BAD_PAGE);
@@ -122,8 +127,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPar
     if (warp < kPfSoftmaxWarps) {
         const int x = warp >> 2, r = (warp & 3) * 32 + lane;
         const int t = t0 + x * tok_per_tile + r / g;
-        const bool valid = r < rows_used && t < p.m;
-        const T* src = reinterpret_cast<const T*>(p.q) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * kPfD;
+        const bool valid = r < rows_used && t < p_m;
+        const T* src = reinterpret_cast<const T*>(p_q) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * kPfD;
         uint8_t* dst = smem + PfSmem::q + x * kPfQBytes;
 #pragma unroll
         for (int c = 0; c < kPfD / 8; c++) {
@@ -163,7 +168,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPar
                     if (pages_staged) page = s_pages[grp];
                     else {
                         const int logical = (grp * 16) / p.page_size;
-                        page = logical < p.table_stride ? __ldg(p.tables + (int64_t)p.row * p.table_stride + logical) : -1;
+                        page = logical < p.table_stride ? __ldg(p.tables + (int64_t)p_row * p.table_stride + logical) : -1;
                         if (page >= p.max_pages) page = -1;
                     }
                 }
@@ -271,9 +276,9 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPar
         const int r = (warp & 3) * 32 + lane;                           // tile row = TMEM lane
         if (x == 0 || tile_b_active) {
             const int t = t0 + x * tok_per_tile + r / g;
-            const bool valid = r < rows_used && t < p.m;
-            const int limit = valid ? p.pos_start + t + 1 : 0;          // keys [0, limit) are visible to this row
-            const int tile_min_limit = p.pos_start + t0 + x * tok_per_tile + 1;
+            const bool valid = r < rows_used && t < p_m;
+            const int limit = valid ? p_pos_start + t + 1 : 0;          // keys [0, limit) are visible to this row
+            const int tile_min_limit = p_pos_start + t0 + x * tok_per_tile + 1;
             const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
             const uint32_t t_s = tmem_base + lane_base + kPfColS + x * kPfBlockN;
             const uint32_t t_o = tmem_base + lane_base + kPfColO + x * kPfD;
@@ -291,20 +296,22 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPar
                 mbar_arrive(bars + 8 * (BAR_S_FREE + x));               // S(j+1) may overwrite the columns now
                 const int key0 = j * kPfBlockN;
                 const int holes = s_holes[j % kPfStages];
-                const bool full = (key0 + kPfBlockN <= tile_min_limit) && holes == 0;
-                float mx = -INFINITY;
+                // Blocks left of the diagonal with all pages present need no mask: that is almost all of them.
+                if (!((key0 + kPfBlockN <= tile_min_limit) && holes == 0)) {
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+#pragma unroll
+                        for (int c = 0; c < 32; c++) {
+                            const int k = h * 32 + c;
+                            if (key0 + k >= limit || ((holes >> (k >> 4)) & 1)) sv[h][c] = -INFINITY;
+                        }
+                }
+                float mx = -INFINITY;                                    // row maximum of the raw scores
 #pragma unroll
                 for (int h = 0; h < 2; h++)
 #pragma unroll
-                    for (int c = 0; c < 32; c++) {
-                        float v = sv[h][c] * p.scale_log2;
-                        if (!full) {
-                            const int k = h * 32 + c;
-                            if (key0 + k >= limit || ((holes >> (k >> 4)) & 1)) v = -INFINITY;
-                        }
-                        sv[h][c] = v;
-                        mx = fmaxf(mx, v);
-                    }
+                    for (int c = 0; c < 32; c++) mx = fmaxf(mx, sv[h][c]);
+                mx *= p.scale_log2;                                      // scale > 0: max commutes with it
                 // Keep the scale in use unless the row maximum outgrew it by more than 2^8.
                 float factor = 1.f;
                 bool need = false;
@@ -314,21 +321,34 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPar
                     m_used = mx;
                     need = j > 0;
                 }
+                // p = 2^(s * scale_log2 - m): one FMA and one EX2 per score
+                const float neg_m = -m_used;
                 float sum = 0.f;
                 uint32_t phi[32], plo[32];
+                if (!use_lo) {
 #pragma unroll
-                for (int h = 0; h < 2; h++)
+                    for (int h = 0; h < 2; h++)
 #pragma unroll
-                    for (int c = 0; c < 32; c += 2) {
-                        const float p0 = fast_exp2(sv[h][c] - m_used), p1 = fast_exp2(sv[h][c + 1] - m_used);
-                        sum += p0 + p1;
-                        const uint32_t hi = Elem<T>::pack2(p0, p1);
-                        phi[h * 16 + (c >> 1)] = hi;
-                        if (use_lo) {
+                        for (int c = 0; c < 32; c += 2) {
+                            const float p0 = fast_exp2(fmaf(sv[h][c], p.scale_log2, neg_m));
+                            const float p1 = fast_exp2(fmaf(sv[h][c + 1], p.scale_log2, neg_m));
+                            sum += p0 + p1;
+                            phi[h * 16 + (c >> 1)] = Elem<T>::pack2(p0, p1);
+                        }
+                } else {
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) {
+                            const float p0 = fast_exp2(fmaf(sv[h][c], p.scale_log2, neg_m));
+                            const float p1 = fast_exp2(fmaf(sv[h][c + 1], p.scale_log2, neg_m));
+                            sum += p0 + p1;
+                            const uint32_t hi = Elem<T>::pack2(p0, p1);
                             const float2 hf = Elem<T>::unpack2(hi);
+                            phi[h * 16 + (c >> 1)] = hi;
                             plo[h * 16 + (c >> 1)] = Elem<T>::pack2(p0 - hf.x, p1 - hf.y);
                         }
-                    }
+                }
                 l += sum;
                 if (j > 0) {
                     // PV(j-1) must have landed before O is touched or P is overwritten
@@ -361,7 +381,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPar
             } else {
                 tcgen05_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                T* orow = reinterpret_cast<T*>(p.out) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * kPfD;
+                T* orow = reinterpret_cast<T*>(p_out) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * kPfD;
 #pragma unroll 1
                 for (int c0 = 0; c0 < kPfD; c0 += 32) {
                     float ov[32];
@@ -393,11 +413,14 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const PrefillPar
 
 cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
                                   cudaStream_t stream) {
-    if (p.m <= 0) return cudaSuccess;
+    if (p.n_seq <= 0) return cudaSuccess;
     if (head_dim != kPfD || p.group < 1 || p.group > 16 || p.page_size % 16 != 0) return cudaErrorInvalidValue;
     constexpr size_t smem = 1024 + PfSmem::total;
     const int tok_per_tile = 128 / p.group;
-    dim3 grid((p.m + 2 * tok_per_tile - 1) / (2 * tok_per_tile), p.num_kv_heads);
+    int max_m = 0;
+    for (int i = 0; i < p.n_seq; i++) max_m = p.m[i] > max_m ? p.m[i] : max_m;
+    if (max_m <= 0 || p.n_seq > kMaxPrefillSeqs) return max_m <= 0 ? cudaSuccess : cudaErrorInvalidValue;
+    dim3 grid((max_m + 2 * tok_per_tile - 1) / (2 * tok_per_tile), p.num_kv_heads, p.n_seq);
     static bool configured[2][64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

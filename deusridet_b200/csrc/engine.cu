@@ -663,34 +663,47 @@ size_t drkv_partial_floats(const drkv_engine* e) {
     return e ? (size_t)e->geom.num_q_heads * (e->geom.head_dim + 2) : 0;
 }
 
-int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m, const void* q, void* out,
-                              float scale, void* stream) {
+int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_t* seqs, const int32_t* pos_start,
+                              const int32_t* m, const void* const* q, void* const* out, float scale, void* stream) {
     NEED(e);
     NEED_DEVICE(e);
     const drkv_geometry& g = e->geom;
-    if (layer < 0 || layer >= g.num_layers || seq < 0 || seq >= e->book.max_seqs() || pos_start < 0 || m < 0 || !q || !out)
-        return set_err(DRKV_ERR_INVALID, "attend_prefill_chunk: bad argument");
+    if (layer < 0 || layer >= g.num_layers || n_seq < 0 || !seqs || !pos_start || !m || !q || !out)
+        return set_err(DRKV_ERR_INVALID, "attend_prefill: bad argument");
     if (g.head_dim != 128)
-        return set_err(DRKV_ERR_INVALID, "attend_prefill_chunk: the tensor-core prefill kernel is built for head_dim 128");
-    if (m == 0) return DRKV_OK;
-    PrefillParams p{};
-    p.tables = e->d_tables;
-    p.table_stride = e->book.row_width();
-    p.row = seq;
-    p.q = q;
-    p.out = out;
-    p.layer = layer;
-    p.max_pages = e->book.max_pages();
-    p.num_q_heads = g.num_q_heads;
-    p.num_kv_heads = g.num_kv_heads;
-    p.group = g.num_q_heads / g.num_kv_heads;
-    p.page_size = g.page_size;
-    p.pos_start = pos_start;
-    p.m = m;
-    p.scale_log2 = scale * 1.4426950408889634f;
-    p.error_word = e->d_error;
-    CUDA_TRY(launch_attend_prefill(e->tmap, p, g.head_dim, g.dtype, (cudaStream_t)stream));
+        return set_err(DRKV_ERR_INVALID, "attend_prefill: the tensor-core prefill kernel is built for head_dim 128");
+    for (int i = 0; i < n_seq; i++)
+        if (seqs[i] < 0 || seqs[i] >= e->book.max_seqs() || pos_start[i] < 0 || m[i] < 0 || (m[i] > 0 && (!q[i] || !out[i])))
+            return set_err(DRKV_ERR_INVALID, "attend_prefill: bad sequence entry %d", i);
+    for (int s0 = 0; s0 < n_seq; s0 += kMaxPrefillSeqs) {
+        PrefillParams p{};
+        p.tables = e->d_tables;
+        p.table_stride = e->book.row_width();
+        p.n_seq = n_seq - s0 < kMaxPrefillSeqs ? n_seq - s0 : kMaxPrefillSeqs;
+        for (int i = 0; i < p.n_seq; i++) {
+            p.row[i] = seqs[s0 + i];
+            p.pos_start[i] = pos_start[s0 + i];
+            p.m[i] = m[s0 + i];
+            p.q[i] = q[s0 + i];
+            p.out[i] = out[s0 + i];
+        }
+        p.layer = layer;
+        p.max_pages = e->book.max_pages();
+        p.num_q_heads = g.num_q_heads;
+        p.num_kv_heads = g.num_kv_heads;
+        p.group = g.num_q_heads / g.num_kv_heads;
+        p.page_size = g.page_size;
+        p.scale_log2 = scale * 1.4426950408889634f;
+        p.error_word = e->d_error;
+        CUDA_TRY(launch_attend_prefill(e->tmap, p, g.head_dim, g.dtype, (cudaStream_t)stream));
+    }
     return DRKV_OK;
+}
+
+int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m, const void* q, void* out,
+                              float scale, void* stream) {
+    const int32_t s = seq, ps = pos_start, mm = m;
+    return drkv_attend_prefill_batch(e, layer, 1, &s, &ps, &mm, &q, &out, scale, stream);
 }
 
 }  // extern "C"

@@ -50,14 +50,16 @@ struct DecodeParams {
     int* error_word;
 };
 
-// Chunked-prefill attention of one sequence: chunk tokens [0, m) at positions pos_start + t.
+// Chunked-prefill attention: for each of n_seq sequences, chunk tokens [0, m) at positions pos_start + t.
+constexpr int kMaxPrefillSeqs = 16;   // sequences one launch can take (grid.z)
 struct PrefillParams {
     const int32_t* tables;
-    int table_stride, row;
-    const void* q;            // [m][Hq][D]
-    void* out;                // [m][Hq][D]
+    int table_stride;
+    int n_seq;
+    int row[kMaxPrefillSeqs], pos_start[kMaxPrefillSeqs], m[kMaxPrefillSeqs];
+    const void* q[kMaxPrefillSeqs];   // [m][Hq][D]
+    void* out[kMaxPrefillSeqs];       // [m][Hq][D]
     int layer, max_pages, num_q_heads, num_kv_heads, group, page_size;
-    int pos_start, m;
     float scale_log2;
     int* error_word;
 };

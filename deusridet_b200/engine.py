@@ -156,6 +156,13 @@ class PagedKVEngine:
     def attend_prefill_chunk(self, layer, seq, pos_start, m, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_prefill_chunk(self.h, layer, seq, pos_start, m, _ptr(q), _ptr(out), scale,
                                                  _stream(stream)))
+    def attend_prefill_batch(self, layer, seqs, pos_start, m, qs, outs, scale, stream=None) -> None:
+        n = len(seqs)
+        i32 = lambda v: (C.c_int32 * n)(*[int(x) for x in v])
+        ptrs = lambda v: (C.c_void_p * n)(*[_ptr(x) for x in v])
+        check(self.lib.drkv_attend_prefill_batch(self.h, layer, n, i32(seqs), i32(pos_start), i32(m), ptrs(qs),
+                                                 ptrs(outs), scale, _stream(stream)))
+
     def attend_partial(self, layer, seq, kv_begin, kv_end, q, part, scale, stream=None) -> None:
         check(self.lib.drkv_attend_partial(self.h, layer, seq, kv_begin, kv_end, _ptr(q), _ptr(part), scale,
                                            _stream(stream)))

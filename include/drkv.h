@@ -202,6 +202,12 @@ DRKV_API int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int3
  * [m][num_q_heads][head_dim]; token t attends keys 0..pos_start+t. */
 DRKV_API int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m,
                                        const void* q, void* out, float scale, void* stream);
+/* The same for several sequences in one launch (host arrays of n_seq entries; q[i] / out[i] are
+ * device pointers): independent sequences prefilling in step fill the GPU better than one chunk.
+ * No counterpart in the reference, whose prefill handles one sequence. */
+DRKV_API int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_t* seqs,
+                                       const int32_t* pos_start, const int32_t* m, const void* const* q,
+                                       void* const* out, float scale, void* stream);
 /* One sequence whose pages are split across GPUs by contiguous key range: this rank
  * attends keys [kv_begin, kv_end) of table row `seq` and returns the un-normalised partial
  * (m, l, o) per query head in fp32: part[0 .. Hq*D) = o, then Hq values m, then Hq values l.

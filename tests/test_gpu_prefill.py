@@ -92,3 +92,41 @@ def test_prefill_deep_context(drkv_lib, oracle):
 def test_prefill_with_evicted_pages(drkv_lib, oracle):
     _prefill_case(oracle, layers=1, hq=16, hkv=4, page=16, dtype=oracle.BF16, theta=1e4, chunks=[300, 90], seed=25,
                   holes=4)
+
+
+def test_prefill_batch_of_sequences(drkv_lib, oracle):
+    """Three sequences at different depths and chunk lengths in one launch."""
+    import torch
+    from deusridet_b200 import PagedKVEngine
+
+    ob = oracle
+    layers, hq, hkv, d, page, dtype = 1, 28, 4, 128, 16, ob.BF16
+    rng = np.random.default_rng(26)
+    depth, m = [0, 500, 1300], [200, 64, 37]
+    max_pages = sum((a + b + page - 1) // page for a, b in zip(depth, m)) + 6
+    eng = PagedKVEngine(num_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
+                        rope_theta=1e6, max_pages=max_pages, max_seqs=3, max_pages_per_seq=100, device=0)
+    g = ob.geom(layers, hq, hkv, d, page, dtype, d, 1e6)
+    try:
+        H.shuffled_free_stack(eng, rng)
+        seqs = [eng.seq_create() for _ in range(3)]
+        for s, a, b in zip(seqs, depth, m):
+            assert eng.ensure_blocks_for_range(s, 0, a + b)
+            eng.set_seq_len(s, a + b)
+        eng.sync_block_table()
+        pool_host = H.randn_bits(rng, ob.pool_elems(g, max_pages), dtype)
+        eng.pool_tensor().copy_(torch.from_numpy(pool_host.view(np.int16)))
+        qs = [H.randn_bits(rng, (b, hq, d), dtype) for b in m]
+        d_qs = [H.to_dev(x, dtype) for x in qs]
+        outs = [torch.zeros(b, hq, d, dtype=torch.bfloat16, device="cuda") for b in m]
+        scale = 1.0 / np.sqrt(d)
+        eng.attend_prefill_batch(0, seqs, depth, m, d_qs, outs, scale)
+        torch.cuda.synchronize()
+        eng.check_kernels()
+        for i, s in enumerate(seqs):
+            want = np.zeros((m[i], hq, d), dtype=np.uint16)
+            ob.attend_prefill(g, pool_host, max_pages, eng.table(s), 0, depth[i], m[i], qs[i], want, scale)
+            got_f, want_f = ob.to_float(H.torch_bits(outs[i]), dtype), ob.to_float(want, dtype)
+            assert (np.abs(got_f - want_f) <= np.maximum(TOL, H.ulp(want_f, dtype))).all(), f"sequence {i}"
+    finally:
+        eng.close()
