@@ -234,26 +234,41 @@ def run_ours(args):
         h_out = torch.empty(out.shape, dtype=torch.bfloat16).pin_memory()
         h_pos = torch.empty(n_seq, dtype=torch.int32).pin_memory()
         cur = lens.copy()
+        seq_arr = np.asarray(seqs, dtype=np.int32)
+
+        # Copies ride their own streams (one per direction) and are chained to the layers by events:
+        # layer l starts when its Q/K/V have landed, its output leaves as soon as it is written.
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        ev_in = [torch.cuda.Event() for _ in range(L)]
+        ev_out = [torch.cuda.Event() for _ in range(L)]
+        ev_done = torch.cuda.Event()
 
         def e2e_step():
-            for s in seqs:                              # allocate (copy-on-write aware) room for one token
-                eng.reserve(s, 1, stream)
+            eng.reserve_batch(seq_arr, 1, stream)       # allocate (copy-on-write aware) room for one token each
             eng.sync_block_table(stream)
             h_pos.copy_(torch.from_numpy(cur))
             d_pos.copy_(h_pos, non_blocking=True)
             torch.add(d_pos, 1, out=d_len)
-            q.copy_(hq_, non_blocking=True)
-            kn.copy_(hk_, non_blocking=True)
-            vn.copy_(hv_, non_blocking=True)
+            with torch.cuda.stream(s_in):
+                for l in range(L):
+                    q[l].copy_(hq_[l], non_blocking=True)
+                    kn[l].copy_(hk_[l], non_blocking=True)
+                    vn[l].copy_(hv_[l], non_blocking=True)
+                    ev_in[l].record(s_in)
             mk = int(cur.max()) + 1
             for l in range(L):
+                stream.wait_event(ev_in[l])
                 eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
                 eng.attend_decode(l, n_seq, d_rows, d_len, mk, q[l], out[l], scale, stream)
-            h_out.copy_(out, non_blocking=True)
-            stream.synchronize()                        # the caller samples from `out` before the next token
-            for i, s in enumerate(seqs):
-                cur[i] += 1
-                eng.set_seq_len(s, int(cur[i]))
+                ev_out[l].record(stream)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_out[l])
+                    h_out[l].copy_(out[l], non_blocking=True)
+            ev_done.record(s_out)
+            ev_done.synchronize()                       # the caller samples from the outputs before the next token
+            stream.synchronize()
+            cur[:] = cur + 1
+            eng.advance_batch(seq_arr, 1)
 
         for _ in range(W):
             e2e_step()

@@ -64,6 +64,8 @@ SIGNATURES = {
     "drkv_seq_ensure_pos": (_i, [_vp, _i, _i, _vp]),
     "drkv_seq_ensure_range": (_i, [_vp, _i, _i, _i, _vp]),
     "drkv_seq_reserve": (_i, [_vp, _i, _i, _vp]),
+    "drkv_seq_reserve_batch": (_i, [_vp, _i, _pi32, _i, _vp]),
+    "drkv_seq_advance_batch": (_i, [_vp, _i, _pi32, _i]),
     "drkv_seq_set_len": (_i, [_vp, _i, _i]),
     "drkv_seq_len": (_i, [_vp, _i]),
     "drkv_seq_num_pages": (_i, [_vp, _i]),
@@ -93,6 +95,10 @@ SIGNATURES = {
     "drkv_k_cache_write": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "drkv_k_cache_write_batch": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "drkv_k_decode_attention": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp, _sz, _vp]),
+    "drkv_seq_extract": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "drkv_seq_inject": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "drkv_k_extract_kv": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "drkv_k_inject_kv": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _i, _i, _i, _vp]),
     "drkv_k_decode_scratch_bytes": (_sz, [C.POINTER(Geometry), _i]),
     "drkv_k_decode_attention_noalloc": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
 }

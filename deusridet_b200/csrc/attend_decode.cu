@@ -156,8 +156,13 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     const int total_items = cum[p.n_seq];
 
     // ---- next-item prefetch state (warp-uniform except raw_next, which lane 0 owns) ----
-    int raw_next = 0;
-    bool n_valid = false, n_page_loaded = false;
+    // n_state: 0 nothing requested, 1 queue index requested (atomic in flight), 2 decoded (length and
+    // table row requested), 3 first page id requested.  The next item is requested only when the
+    // current one is within kPrefetchGroups of its end, so that a warp never sits on work that an
+    // idle warp could have taken, yet the atomic and the look-ups are off the critical path.
+    constexpr int kPrefetchGroups = 3;
+    int raw_next = 0, n_state = 0;
+    bool exhausted = false;
     int n_b = 0, n_kvh = 0, n_chunk = 0, n_trow = 0, n_kv_end = 0, n_page = -1;
     // ---- issue cursor ----
     bool c_valid = false;
@@ -169,13 +174,14 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
 
     auto fetch_raw = [&]() {
         if (lane == 0) raw_next = atomicAdd(p.work_counter, 1);
+        n_state = 1;
     };
     // queue index -> (sequence, head, chunk); requests the sequence's length and table row
     auto decode_next = [&]() {
         const int raw = __shfl_sync(0xffffffffu, raw_next, 0);
-        fetch_raw();                                   // the one after, consumed an item later
         if (raw >= total_items) {
-            n_valid = false;
+            exhausted = true;
+            n_state = 0;
             return;
         }
         int lo = 0, hi = p.n_seq;                      // largest b with cum[b] <= raw
@@ -190,16 +196,12 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         n_chunk = j - n_kvh * nch;
         n_kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + lo) : p.kv_end;
         n_trow = p.rows != nullptr ? __ldg(p.rows + lo) : p.row;
-        n_valid = true;
-        n_page_loaded = false;
+        n_state = 2;
     };
     auto load_page = [&](int trow, int tok) -> int {
         const int logical = tok / p.page_size;
         return logical < p.table_stride ? __ldg(p.tables + (int64_t)trow * p.table_stride + logical) : -1;
     };
-
-    fetch_raw();
-    decode_next();
 
     float m2[2] = {kNegBig, kNegBig};
     float lsum[2] = {0.f, 0.f};
@@ -212,14 +214,16 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         // ------------- issue: keep DEPTH groups in flight, across item boundaries -------------
         while (outstanding < DEPTH) {
             if (!c_valid) {
-                if (!n_valid) break;
+                if (n_state == 0 && !exhausted) fetch_raw();
+                if (n_state == 1) decode_next();       // waits for the atomic only if it was just issued
+                if (n_state < 2) break;                // queue drained
                 c_b = n_b; c_kvh = n_kvh; c_chunk = n_chunk; c_trow = n_trow; c_kv_end = n_kv_end;
                 c_tok_lo = base_tok + c_chunk * CT;
                 c_ngroups = (min(c_tok_lo + CT, c_kv_end) - c_tok_lo + kGroupTokens - 1) / kGroupTokens;
                 c_gi = 0;
-                c_page = n_page_loaded ? n_page : load_page(c_trow, c_tok_lo);
+                c_page = n_state == 3 ? n_page : load_page(c_trow, c_tok_lo);
                 c_valid = true;
-                decode_next();
+                n_state = 0;
             }
             const int ring = w * DEPTH + i_slot;
             const int tok0 = c_tok_lo + c_gi * kGroupTokens;
@@ -264,10 +268,16 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 // page id of the next group: same table entry while inside one page
                 if ((tok0 + kGroupTokens) % p.page_size == 0) c_page = load_page(c_trow, tok0 + kGroupTokens);
             }
-            // first page id of the prefetched item, once its table row has arrived
-            if (n_valid && !n_page_loaded) {
-                n_page = load_page(n_trow, base_tok + n_chunk * CT);
-                n_page_loaded = true;
+            // one step of the next-item pipeline per issued group, started near the end of this item
+            if (!exhausted) {
+                if (n_state == 0) {
+                    if (!c_valid || c_ngroups - c_gi <= kPrefetchGroups) fetch_raw();
+                } else if (n_state == 1) {
+                    decode_next();
+                } else if (n_state == 2) {
+                    n_page = load_page(n_trow, base_tok + n_chunk * CT);
+                    n_state = 3;
+                }
             }
         }
         if (outstanding == 0) break;                   // queue drained and every group consumed

@@ -65,6 +65,12 @@ int pick_chunk(int n_seq, int hkv, int group, int max_kv_span, int num_sms) {
     int chunk = group > 4 ? 512 : 256;
     const long warps = (long)num_sms * 8;
     auto items = [&](int c) { return (long)n_seq * hkv * ((max_kv_span + c - 1) / c); };
+    if (n_seq == 1 && items(chunk) > warps) {
+        // One long sequence: equal items, one per warp, is a perfect partition with the fewest partials.
+        const long per_head = warps / hkv > 0 ? warps / hkv : 1;
+        const long c = (max_kv_span + per_head - 1) / per_head;
+        return (int)((c + 15) / 16 * 16);
+    }
     while (chunk > 64 && items(chunk) < warps) chunk >>= 1;
     return chunk;
 }
@@ -336,6 +342,32 @@ int drkv_seq_reserve(drkv_engine* e, int seq, int n_tokens, void* stream) {
     int rc2 = run_cow(e, jobs, (cudaStream_t)stream);
     return rc < 0 ? book_err(e, rc) : rc2;
 }
+int drkv_seq_reserve_batch(drkv_engine* e, int n, const int32_t* seqs, int n_tokens, void* stream) {
+    NEED(e);
+    if (n < 0 || (n > 0 && !seqs)) return set_err(DRKV_ERR_INVALID, "reserve_batch: bad argument");
+    LOCK(e);
+    std::vector<CowJob> jobs;
+    int rc = DRKV_OK;
+    for (int i = 0; i < n && rc == DRKV_OK; i++) {
+        const int len = e->book.seq_len(seqs[i]);
+        rc = len < 0 ? DRKV_ERR_STATE : e->book.seq_ensure_range(seqs[i], len, n_tokens, &jobs);
+        if (len < 0) return set_err(DRKV_ERR_STATE, "reserve_batch: unknown sequence %d", seqs[i]);
+    }
+    int rc2 = run_cow(e, jobs, (cudaStream_t)stream);
+    return rc < 0 ? book_err(e, rc) : rc2;
+}
+int drkv_seq_advance_batch(drkv_engine* e, int n, const int32_t* seqs, int n_tokens) {
+    NEED(e);
+    if (n < 0 || (n > 0 && !seqs)) return set_err(DRKV_ERR_INVALID, "advance_batch: bad argument");
+    LOCK(e);
+    for (int i = 0; i < n; i++) {
+        const int len = e->book.seq_len(seqs[i]);
+        if (len < 0) return set_err(DRKV_ERR_STATE, "advance_batch: unknown sequence %d", seqs[i]);
+        int rc = e->book.seq_set_len(seqs[i], len + n_tokens);
+        if (rc < 0) return book_err(e, rc);
+    }
+    return DRKV_OK;
+}
 int drkv_seq_set_len(drkv_engine* e, int seq, int len) {
     NEED(e);
     LOCK(e);
@@ -550,6 +582,35 @@ int drkv_append_rope_chunk(drkv_engine* e, int layer, int seq, int pos_start, in
     p.v_src = v_src;
     CUDA_TRY(launch_append_rope(p, m, e->geom.dtype, (cudaStream_t)stream));
     return DRKV_OK;
+}
+
+static int seq_flat_copy(drkv_engine* e, int seq, int start_token, int num_tokens, void* flat, bool to_flat,
+                         void* stream) {
+    if (seq < 0 || seq >= e->book.max_seqs() || start_token < 0 || num_tokens < 0 || !flat)
+        return set_err(DRKV_ERR_INVALID, "extract/inject: bad argument");
+    FlatCopyParams p{};
+    p.layout = e->layout;
+    p.pool = e->pool;
+    p.flat = flat;
+    p.table = e->d_tables + (size_t)seq * e->book.row_width();
+    p.table_stride = e->book.row_width();
+    p.start_token = start_token;
+    p.num_tokens = num_tokens;
+    p.num_layers = e->geom.num_layers;
+    CUDA_TRY(launch_flat_paged_copy(p, to_flat, e->num_sms, (cudaStream_t)stream));
+    return DRKV_OK;
+}
+
+int drkv_seq_extract(drkv_engine* e, int seq, int start_token, int num_tokens, void* dst, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    return seq_flat_copy(e, seq, start_token, num_tokens, dst, true, stream);
+}
+
+int drkv_seq_inject(drkv_engine* e, int seq, int start_token, int num_tokens, const void* src, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    return seq_flat_copy(e, seq, start_token, num_tokens, const_cast<void*>(src), false, stream);
 }
 
 // ---- attention --------------------------------------------------------------------------

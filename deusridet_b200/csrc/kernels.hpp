@@ -30,6 +30,16 @@ struct CowParams {
     int src_page, dst_page, n_slots;
 };
 
+// Flat [layer][K|V][token][kv_head][dim] <-> paged copy of tokens [start_token, start_token + num_tokens).
+struct FlatCopyParams {
+    PoolLayout layout;
+    void* pool;
+    void* flat;
+    const int32_t* table;     // one sequence's row
+    int table_stride;
+    int start_token, num_tokens, num_layers;
+};
+
 // Split-KV decode attention.  One CTA handles (chunk of keys, KV head, sequence).
 struct DecodeParams {
     const int32_t* tables;
@@ -78,6 +88,7 @@ struct CombineParams {
 
 cudaError_t launch_append_rope(const AppendParams& p, int n_tokens, int dtype, cudaStream_t stream);
 cudaError_t launch_cow_copy(const CowParams& p, int num_layers, cudaStream_t stream);
+cudaError_t launch_flat_paged_copy(const FlatCopyParams& p, bool to_flat, int num_sms, cudaStream_t stream);
 
 // Builds the TMA descriptor of a pool: a 2-D tensor [rows][head_dim] of 2-byte elements with
 // a {64 x 16} box and 128-byte swizzle.  Returns false if the driver entry point is missing.

@@ -32,7 +32,14 @@ int stateless_pick_chunk(const drkv_geometry* g, int seq_len, int num_sms) {
     const int group = g->num_q_heads / g->num_kv_heads;
     int chunk = group > 4 ? 512 : 256;
     const long warps = (long)num_sms * 8;
-    while (chunk > 64 && (long)g->num_kv_heads * ((seq_len + chunk - 1) / chunk) < warps) chunk >>= 1;
+    const long hkv = g->num_kv_heads;
+    if (hkv * ((seq_len + chunk - 1) / chunk) > warps) {
+        // long sequence: one equal item per warp, the fewest partials
+        const long per_head = warps / hkv > 0 ? warps / hkv : 1;
+        const long c = (seq_len + per_head - 1) / per_head;
+        return (int)((c + 15) / 16 * 16);
+    }
+    while (chunk > 64 && hkv * ((seq_len + chunk - 1) / chunk) < warps) chunk >>= 1;
     return chunk;
 }
 
@@ -157,6 +164,36 @@ int drkv_k_cache_write_batch(const drkv_geometry* g, const void* src_k, const vo
     if (launch_append_rope(p, m, g->dtype, (cudaStream_t)stream) != cudaSuccess)
         return fail(DRKV_ERR_CUDA, "cache_write_batch launch failed");
     return DRKV_OK;
+}
+
+static int flat_copy(const drkv_geometry* g, void* pool, void* flat, const int32_t* table, int start_token,
+                     int num_tokens, int max_pages, bool to_flat, void* stream) {
+    if (!stateless_geometry_ok(g) || !pool || !flat || !table || start_token < 0 || num_tokens < 0 || max_pages <= 0)
+        return fail(DRKV_ERR_INVALID, "extract/inject: bad argument");
+    int dev = 0, num_sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    FlatCopyParams p{};
+    p.layout = PoolLayout::make(g->num_kv_heads, g->page_size, g->head_dim, max_pages);
+    p.pool = pool;
+    p.flat = flat;
+    p.table = table;
+    p.table_stride = INT_MAX;
+    p.start_token = start_token;
+    p.num_tokens = num_tokens;
+    p.num_layers = g->num_layers;
+    if (launch_flat_paged_copy(p, to_flat, num_sms, (cudaStream_t)stream) != cudaSuccess)
+        return fail(DRKV_ERR_CUDA, "extract/inject launch failed");
+    return DRKV_OK;
+}
+
+int drkv_k_extract_kv(const drkv_geometry* g, void* dst, const void* kv_pool, const int32_t* d_block_table,
+                      int start_token, int num_tokens, int max_pages, void* stream) {
+    return flat_copy(g, const_cast<void*>(kv_pool), dst, d_block_table, start_token, num_tokens, max_pages, true, stream);
+}
+
+int drkv_k_inject_kv(const drkv_geometry* g, void* kv_pool, const void* src, const int32_t* d_block_table,
+                     int start_token, int num_tokens, int max_pages, void* stream) {
+    return flat_copy(g, kv_pool, const_cast<void*>(src), d_block_table, start_token, num_tokens, max_pages, false, stream);
 }
 
 size_t drkv_k_decode_scratch_bytes(const drkv_geometry* g, int seq_len) {

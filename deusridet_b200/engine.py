@@ -90,6 +90,13 @@ class PagedKVEngine:
         return self.lib.drkv_seq_ensure_range(self.h, seq, pos_start, m, _stream(stream)) == 0
     def reserve(self, seq: int, n_tokens: int, stream=None) -> None:
         check(self.lib.drkv_seq_reserve(self.h, seq, n_tokens, _stream(stream)))
+    def reserve_batch(self, seqs, n_tokens: int, stream=None) -> None:
+        arr = np.ascontiguousarray(seqs, dtype=np.int32)
+        check(self.lib.drkv_seq_reserve_batch(self.h, len(arr), arr.ctypes.data_as(C.POINTER(C.c_int32)), n_tokens,
+                                              _stream(stream)))
+    def advance_batch(self, seqs, n_tokens: int) -> None:
+        arr = np.ascontiguousarray(seqs, dtype=np.int32)
+        check(self.lib.drkv_seq_advance_batch(self.h, len(arr), arr.ctypes.data_as(C.POINTER(C.c_int32)), n_tokens))
     def set_seq_len(self, seq: int, n: int) -> None: check(self.lib.drkv_seq_set_len(self.h, seq, n))
     def seq_len(self, seq: int) -> int: return check(self.lib.drkv_seq_len(self.h, seq))
     def num_logical_blocks(self, seq: int) -> int: return check(self.lib.drkv_seq_num_pages(self.h, seq))
@@ -162,6 +169,11 @@ class PagedKVEngine:
         ptrs = lambda v: (C.c_void_p * n)(*[_ptr(x) for x in v])
         check(self.lib.drkv_attend_prefill_batch(self.h, layer, n, i32(seqs), i32(pos_start), i32(m), ptrs(qs),
                                                  ptrs(outs), scale, _stream(stream)))
+
+    def extract(self, seq, start_token, num_tokens, dst, stream=None) -> None:
+        check(self.lib.drkv_seq_extract(self.h, seq, start_token, num_tokens, _ptr(dst), _stream(stream)))
+    def inject(self, seq, start_token, num_tokens, src, stream=None) -> None:
+        check(self.lib.drkv_seq_inject(self.h, seq, start_token, num_tokens, _ptr(src), _stream(stream)))
 
     def attend_partial(self, layer, seq, kv_begin, kv_end, q, part, scale, stream=None) -> None:
         check(self.lib.drkv_attend_partial(self.h, layer, seq, kv_begin, kv_end, _ptr(q), _ptr(part), scale,

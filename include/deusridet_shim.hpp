@@ -12,6 +12,8 @@
 //                  reference does in production, src/actus/awaken_consciousness.cpp:91)
 //   paged_kv_cache_write / _batch, paged_gqa_decode_attention
 //                  src/machina/paged_attention.h:27-71
+//   invoke_extract_kv_from_pages / invoke_inject_kv_to_pages
+//                  src/memoria/cache_kernels.h:44-74
 //
 // The reference reads head counts and dims from process-wide ModelConfig statics
 // (src/machina/paged_attention.cu:110-114); here the integrator fills shim_geometry() once,
@@ -206,6 +208,33 @@ inline void paged_gqa_decode_attention(const __half* Q, __half* kv_pool, const i
     if (drkv_k_decode_attention(&g, Q, kv_pool, d_block_table, out, fa_layer_idx, seq_len, max_phys_blocks, scale,
                                 scratch, scratch_bytes, stream) != DRKV_OK)
         std::fprintf(stderr, "[Machina] paged_gqa_decode_attention: %s\n", drkv_last_error());
+}
+
+// ---- src/memoria/cache_kernels.h:44-74 -----------------------------------------------------------
+inline void invoke_extract_kv_from_pages(__half* dst, const __half* kv_pool, const int* block_table, int start_token,
+                                         int num_tokens, int num_layers, int num_kv_heads, int head_dim,
+                                         int block_size, int max_phys_blocks, cudaStream_t stream) {
+    drkv_geometry g = shim_geometry();
+    g.num_layers = num_layers;
+    g.num_kv_heads = num_kv_heads;
+    g.num_q_heads = num_kv_heads * (shim_geometry().num_q_heads / shim_geometry().num_kv_heads);
+    g.head_dim = head_dim;
+    g.page_size = block_size;
+    if (drkv_k_extract_kv(&g, dst, kv_pool, block_table, start_token, num_tokens, max_phys_blocks, stream) != DRKV_OK)
+        std::fprintf(stderr, "[Memoria] invoke_extract_kv_from_pages: %s\n", drkv_last_error());
+}
+
+inline void invoke_inject_kv_to_pages(__half* kv_pool, const __half* src, const int* block_table, int start_token,
+                                      int num_tokens, int num_layers, int num_kv_heads, int head_dim, int block_size,
+                                      int max_phys_blocks, cudaStream_t stream) {
+    drkv_geometry g = shim_geometry();
+    g.num_layers = num_layers;
+    g.num_kv_heads = num_kv_heads;
+    g.num_q_heads = num_kv_heads * (shim_geometry().num_q_heads / shim_geometry().num_kv_heads);
+    g.head_dim = head_dim;
+    g.page_size = block_size;
+    if (drkv_k_inject_kv(&g, kv_pool, src, block_table, start_token, num_tokens, max_phys_blocks, stream) != DRKV_OK)
+        std::fprintf(stderr, "[Memoria] invoke_inject_kv_to_pages: %s\n", drkv_last_error());
 }
 
 }  // namespace deusridet

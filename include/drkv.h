@@ -131,6 +131,12 @@ DRKV_API int drkv_seq_ensure_pos(drkv_engine* e, int seq, int pos, void* stream)
 DRKV_API int drkv_seq_ensure_range(drkv_engine* e, int seq, int pos_start, int m, void* stream);
 /* ensure_blocks_for_range(seq_len, n): room for n more tokens after the current length. */
 DRKV_API int drkv_seq_reserve(drkv_engine* e, int seq, int n_tokens, void* stream);
+/* The per-token pair of a decode loop for a whole batch in one call each (the reference makes the
+ * two calls once per token for its single sequence, src/conscientia/stream.cpp:297, 369-370):
+ * reserve n_tokens more for every listed sequence (stops at the first failure, earlier allocations
+ * stay), and set_seq_len(seq_len + n_tokens) for every listed sequence. */
+DRKV_API int drkv_seq_reserve_batch(drkv_engine* e, int n, const int32_t* seqs, int n_tokens, void* stream);
+DRKV_API int drkv_seq_advance_batch(drkv_engine* e, int n, const int32_t* seqs, int n_tokens);
 DRKV_API int drkv_seq_set_len(drkv_engine* e, int seq, int len);   /* set_seq_len */
 DRKV_API int drkv_seq_len(const drkv_engine* e, int seq);          /* seq_len */
 DRKV_API int drkv_seq_num_pages(const drkv_engine* e, int seq);    /* num_logical_blocks = ceil(len / page) */
@@ -189,6 +195,14 @@ DRKV_API int drkv_append_rope(drkv_engine* e, int layer, int n_seq, const int32_
 DRKV_API int drkv_append_rope_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m,
                                     const void* k_src, const void* v_src, void* stream);
 
+/* ---- flat <-> paged copies ------------------------------------------------------------ */
+/* invoke_extract_kv_from_pages / invoke_inject_kv_to_pages (src/memoria/cache_kernels.h:44-74,
+ * cache_kernels.cu:30-187) for tokens [start_token, start_token + num_tokens) of one sequence, all
+ * layers.  Flat layout [layer][K|V][token][kv_head][dim].  Pages missing from the table read as
+ * zeros (extract) or are skipped (inject). */
+DRKV_API int drkv_seq_extract(drkv_engine* e, int seq, int start_token, int num_tokens, void* dst, void* stream);
+DRKV_API int drkv_seq_inject(drkv_engine* e, int seq, int start_token, int num_tokens, const void* src, void* stream);
+
 /* ---- attention ---------------------------------------------------------------------- */
 /* paged_gqa_decode_attention (paged_attention.cu:179-282), batched: q/out
  * [n_seq][num_q_heads][head_dim]; sequence i attends to keys 0..d_kv_len[i]-1 of table row
@@ -235,6 +249,14 @@ DRKV_API int drkv_k_decode_attention(const drkv_geometry* g, const void* q, cons
                                      int seq_len, int max_pages, float scale, void* scratch,
                                      size_t scratch_bytes, void* stream);
 DRKV_API size_t drkv_k_decode_scratch_bytes(const drkv_geometry* g, int seq_len);
+/* invoke_extract_kv_from_pages / invoke_inject_kv_to_pages with raw pointers
+ * (src/memoria/cache_kernels.h:44-74); num_layers, heads, dims and block size come from g. */
+DRKV_API int drkv_k_extract_kv(const drkv_geometry* g, void* dst, const void* kv_pool,
+                               const int32_t* d_block_table, int start_token, int num_tokens,
+                               int max_pages, void* stream);
+DRKV_API int drkv_k_inject_kv(const drkv_geometry* g, void* kv_pool, const void* src,
+                              const int32_t* d_block_table, int start_token, int num_tokens,
+                              int max_pages, void* stream);
 
 /* No counterpart in the reference.  drkv_k_decode_attention for callers that cannot get
  * device memory at all: hosts that own the whole GPU through their own allocator, threads that

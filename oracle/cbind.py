@@ -136,5 +136,16 @@ def cow_copy(g: Geom, pool, max_pages, src_page, dst_page, n_slots):
     lib().okv_cow_copy(C.byref(g), _p(pool), max_pages, src_page, dst_page, n_slots)
 
 
+def extract(g: Geom, pool, max_pages, table, start_token, num_tokens) -> np.ndarray:
+    dst = np.empty((g.num_layers, 2, num_tokens, g.num_kv_heads, g.head_dim), dtype=np.uint16)
+    lib().okv_extract(C.byref(g), _p(dst), _p(pool), max_pages, _p(_i32(table)), start_token, num_tokens)
+    return dst
+
+
+def inject(g: Geom, pool, src, max_pages, table, start_token, num_tokens):
+    src = np.ascontiguousarray(src, dtype=np.uint16)
+    lib().okv_inject(C.byref(g), _p(pool), _p(src), max_pages, _p(_i32(table)), start_token, num_tokens)
+
+
 def num_threads() -> int:
     return lib().okv_num_threads()

@@ -373,6 +373,37 @@ void okv_cow_copy(const okv_geom* g, uint16_t* pool, int max_pages, int src_page
                        (size_t)n_slots * g->head_dim * 2);
 }
 
+/* Flat <-> paged copies — src/memoria/cache_kernels.cu:30-87 (extract: a token whose table entry is
+ * negative reads as zeros) and :93-141 (inject: such a token is skipped).  Flat layout
+ * [layer][K|V][token][kv_head][dim], src/memoria/cache_kernels.h:29. */
+void okv_extract(const okv_geom* g, uint16_t* dst, const uint16_t* pool, int max_pages, const int32_t* table,
+                 int start_token, int num_tokens) {
+    int D = g->head_dim, H = g->num_kv_heads, P = g->page_size;
+    for (int layer = 0; layer < g->num_layers; layer++)
+        for (int kv = 0; kv < 2; kv++)
+            for (int t = 0; t < num_tokens; t++) {
+                int pos = start_token + t, page = table[pos / P];
+                for (int h = 0; h < H; h++) {
+                    uint16_t* out = dst + ((((int64_t)layer * 2 + kv) * num_tokens + t) * H + h) * D;
+                    if (page < 0) memset(out, 0, (size_t)D * 2);
+                    else memcpy(out, pool + pool_row(g, max_pages, layer, page, kv, h, pos % P), (size_t)D * 2);
+                }
+            }
+}
+void okv_inject(const okv_geom* g, uint16_t* pool, const uint16_t* src, int max_pages, const int32_t* table,
+                int start_token, int num_tokens) {
+    int D = g->head_dim, H = g->num_kv_heads, P = g->page_size;
+    for (int layer = 0; layer < g->num_layers; layer++)
+        for (int kv = 0; kv < 2; kv++)
+            for (int t = 0; t < num_tokens; t++) {
+                int pos = start_token + t, page = table[pos / P];
+                if (page < 0) continue;
+                for (int h = 0; h < H; h++)
+                    memcpy(pool + pool_row(g, max_pages, layer, page, kv, h, pos % P),
+                           src + ((((int64_t)layer * 2 + kv) * num_tokens + t) * H + h) * D, (size_t)D * 2);
+            }
+}
+
 int okv_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -227,3 +227,20 @@ def test_prefix_sharing_scenario_scaled(drkv_lib):
     assert all(k == 0 for k, _, _, _ in mod.log)
     assert eng.stats()["cow_copies"] == mod.n_cow and len(mod.cow) >= 3
     eng.close()
+
+
+def test_batch_reserve_and_advance(drkv_lib):
+    eng = _engine(40, 16, 6, 12, False)
+    mod = BookModel(40, 16, 6, 12, False)
+    seqs = [eng.seq_create() for _ in range(5)]
+    for _ in seqs:
+        mod.seq_create()
+    for step in range(40):
+        eng.reserve_batch(seqs, 3)
+        eng.advance_batch(seqs, 3)
+        for s in seqs:
+            assert mod.seq_reserve(s, 3) == 0
+            assert mod.seq_set_len(s, mod.seqs[s].len + 3) == 0
+    _same_state(eng, mod, seqs)
+    assert eng.seq_len(seqs[2]) == 120
+    eng.close()
