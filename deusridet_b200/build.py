@@ -24,6 +24,11 @@ NVCC_FLAGS = [
 ]
 
 
+def _extra_flags():
+    """Extra nvcc flags for experiments (e.g. -DDRKV_PREFETCH_GROUPS=6), from DRKV_NVCC_EXTRA."""
+    return os.environ.get("DRKV_NVCC_EXTRA", "").split()
+
+
 def _nvcc() -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
@@ -50,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     for src in CUDA_SOURCES + CXX_SOURCES:
         obj = os.path.join(objdir, os.path.splitext(src)[0] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *_extra_flags(), "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

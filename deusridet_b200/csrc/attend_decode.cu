@@ -160,7 +160,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     // table row requested), 3 first page id requested.  The next item is requested only when the
     // current one is within kPrefetchGroups of its end, so that a warp never sits on work that an
     // idle warp could have taken, yet the atomic and the look-ups are off the critical path.
-    constexpr int kPrefetchGroups = 3;
+#ifndef DRKV_PREFETCH_GROUPS
+#define DRKV_PREFETCH_GROUPS 3
+#endif
+    constexpr int kPrefetchGroups = DRKV_PREFETCH_GROUPS;
     int raw_next = 0, n_state = 0;
     bool exhausted = false;
     int n_b = 0, n_kvh = 0, n_chunk = 0, n_trow = 0, n_kv_end = 0, n_page = -1;
