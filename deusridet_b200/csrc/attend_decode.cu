@@ -175,8 +175,17 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     int slot = 0, phase = 0;
     const int64_t rows_per_plane = (int64_t)p.num_kv_heads * p.page_size;
 
+    // The first item of every warp is its own index in the grid (no atomic on the way to the first
+    // gather); later items come from the queue, which therefore starts behind those.
+    const int grid_warps = (int)gridDim.x * WARPS;
+    bool first_fetch = true;
     auto fetch_raw = [&]() {
-        if (lane == 0) raw_next = atomicAdd(p.work_counter, 1);
+        if (first_fetch) {
+            raw_next = (int)blockIdx.x * WARPS + w;
+            first_fetch = false;
+        } else if (lane == 0) {
+            raw_next = atomicAdd(p.work_counter, 1) + grid_warps;
+        }
         n_state = 1;
     };
     // queue index -> (sequence, head, chunk); requests the sequence's length and table row
@@ -428,6 +437,15 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             }
         }
     }
+    // The last warp of the grid to leave rewinds the work queue for the next launch on this stream.
+    if (lane == 0) {
+        __threadfence();
+        const int total_warps = (int)gridDim.x * WARPS;
+        if (atomicAdd(p.exit_count, 1) == total_warps - 1) {
+            *p.work_counter = 0;
+            *p.exit_count = 0;
+        }
+    }
 }
 
 // Merge of chunk partials: m = max m_c, weights exp(m_c - m); out = sum w_c o_c / sum w_c l_c.
@@ -509,9 +527,6 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
         p.out_partial[(int64_t)p.num_q_heads * D + h] = lt > 0.f ? mmax : -1.0e20f;
         p.out_partial[(int64_t)p.num_q_heads * (D + 1) + h] = lt > 0.f ? lt : 0.f;
     }
-    // The attention kernel that filled these partials is complete: rewind its work queue for
-    // the next launch on this stream.
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *p.work_counter = 0;
 }
 
 // Merge of whole-range partials in the external layout [Hq*D o | Hq m | Hq l] per part, in the

@@ -101,6 +101,7 @@ struct drkv_engine {
     int forced_chunk = 0;
     int num_sms = 148;
     int* d_work = nullptr;   // decode kernel's work-queue head
+    int* d_exit = nullptr;   // decode kernel's count of warps that have left
 
     // optional per-launch timing of the decode attention kernel (events on the launch stream)
     bool timing = false;
@@ -198,9 +199,11 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
             if ((ce = cudaEventCreateWithFlags(&e->stage_done[i], cudaEventDisableTiming)) != cudaSuccess)
                 return fail(DRKV_ERR_CUDA, "cudaEventCreate", ce);
         }
-        if ((ce = cudaMalloc(&e->d_error, 2 * sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(error)", ce);
-        if ((ce = cudaMemset(e->d_error, 0, 2 * sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMemset(error)", ce);
+        const size_t ctl_ints = 4;   // error word, queue head, exit count, padding
+        if ((ce = cudaMalloc(&e->d_error, ctl_ints * sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(error)", ce);
+        if ((ce = cudaMemset(e->d_error, 0, ctl_ints * sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMemset(error)", ce);
         e->d_work = e->d_error + 1;
+        e->d_exit = e->d_error + 2;
         if ((ce = cudaDeviceGetAttribute(&e->num_sms, cudaDevAttrMultiProcessorCount, cfg->device)) != cudaSuccess)
             return fail(DRKV_ERR_CUDA, "cudaDeviceGetAttribute", ce);
         std::vector<float> inv;
@@ -515,6 +518,7 @@ int drkv_set_chunk_tokens(drkv_engine* e, int chunk_tokens) {
     return DRKV_OK;
 }
 
+
 int drkv_kernel_timing(drkv_engine* e, int enable, double* total_ms, int* launches) {
     NEED(e);
     NEED_DEVICE(e);
@@ -652,6 +656,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     p.n_seq = n_seq;
     p.total_items = n_seq * g.num_kv_heads * max_chunks;
     p.work_counter = e->d_work;
+    p.exit_count = e->d_exit;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.error_word = e->d_error;
     const bool timed = e->timing && e->tev_used + 2 <= e->tev.size();
@@ -675,7 +680,6 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     c.max_chunks = max_chunks;
     c.out = out;
     c.out_partial = out_partial;
-    c.work_counter = e->d_work;
     CUDA_TRY(launch_combine(c, n_seq, g.dtype, stream));
     return DRKV_OK;
 }

@@ -55,7 +55,8 @@ struct DecodeParams {
     int chunk_tokens, max_chunks;
     int n_seq;
     int total_items;          // upper bound n_seq * num_kv_heads * max_chunks (sizes the grid)
-    int* work_counter;        // device int, 0 at launch; the combine kernel rewinds it
+    int* work_counter;        // device int, 0 at launch; the last warp to leave rewinds it
+    int* exit_count;          // device int, 0 at launch: warps that have left
     float scale_log2;         // scale * log2(e)
     int* error_word;
 };
@@ -83,7 +84,6 @@ struct CombineParams {
     int num_q_heads, head_dim, chunk_tokens, max_chunks;
     void* out;                // storage type [n_seq][Hq][D] (normalised) ...
     float* out_partial;       // ... or fp32 partial [Hq*D | Hq m | Hq l] when non-null
-    int* work_counter;        // the attention kernel's queue head, reset to 0 here
 };
 
 cudaError_t launch_append_rope(const AppendParams& p, int n_tokens, int dtype, cudaStream_t stream);

@@ -60,7 +60,7 @@ int stateless_decode(const drkv_geometry* g, const void* q, const void* kv_pool,
     const char* terr = nullptr;
     if (!make_pool_tensor_map(&tmap, kv_pool, g->num_layers, max_pages, g->num_kv_heads, g->page_size, g->head_dim, &terr))
         return fail(DRKV_ERR_CUDA, terr ? terr : "tensor map");
-    // header: [0] queue head, [1] error word; both start at zero for every call
+    // header: [0] queue head, [1] error word, [2] exit count; all start at zero for every call
     if (cudaMemsetAsync(scratch, 0, kStatelessHeaderBytes, stream) != cudaSuccess)
         return fail(DRKV_ERR_CUDA, "cudaMemsetAsync(scratch header) failed");
     int* header = reinterpret_cast<int*>(scratch);
@@ -91,6 +91,7 @@ int stateless_decode(const drkv_geometry* g, const void* q, const void* kv_pool,
     p.n_seq = 1;
     p.total_items = g->num_kv_heads * max_chunks;
     p.work_counter = header;
+    p.exit_count = header + 2;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.error_word = header + 1;
     if (launch_attend_decode(tmap, p, num_sms, g->head_dim, g->dtype, stream) != cudaSuccess)
@@ -109,7 +110,6 @@ int stateless_decode(const drkv_geometry* g, const void* q, const void* kv_pool,
     c.max_chunks = max_chunks;
     c.out = out;
     c.out_partial = nullptr;
-    c.work_counter = header;
     if (launch_combine(c, 1, g->dtype, stream) != cudaSuccess) return fail(DRKV_ERR_CUDA, "combine launch failed");
     return DRKV_OK;
 }

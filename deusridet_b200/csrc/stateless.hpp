@@ -9,7 +9,7 @@
 
 namespace drkv {
 
-constexpr size_t kStatelessHeaderBytes = 256;   // [0] queue head, [1] error word, rest padding
+constexpr size_t kStatelessHeaderBytes = 256;   // [0] queue head, [1] error word, [2] exit count, rest padding
 
 bool stateless_geometry_ok(const drkv_geometry* g);
 int stateless_pick_chunk(const drkv_geometry* g, int seq_len, int num_sms);

@@ -111,7 +111,7 @@ def test_batched_decode_bf16_ragged(drkv_lib, oracle):
 
 @pytest.mark.parametrize("chunk", [16, 64, 256, 2048])
 def test_decode_chunk_sizes(drkv_lib, oracle, chunk):
-    _decode_case(oracle, layers=1, hq=32, hkv=8, d=128, page=16, dtype=oracle.BF16, theta=1e6,
+    _decode_case(oracle, layers=2, hq=32, hkv=8, d=128, page=16, dtype=oracle.BF16, theta=1e6,
                  lens=[1200, 63, 64, 65, 2500], seed=3, chunk=chunk)
 
 
