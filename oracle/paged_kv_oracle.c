@@ -4,12 +4,19 @@
  * TEST INFRASTRUCTURE ONLY.  This file is the checker for the CUDA kernels and the timed
  * CPU baseline; nothing in the product links, imports or falls back to it.
  *
- * Each function follows the reference lines it cites (paths relative to the reference
- * tree).  Pinning: the pool addressing and the fp16 write + decode-attention functions are
- * checked against the reference's own compiled objects / kernels (see tests/golden/ and
- * oracle/ref_build/); the reference ships no test, golden vector or fixture for this path,
- * so bf16, batches, holes, RoPE bit patterns, prefill, split-KV partials and their merge are
- * "parity unpinned": they restate the cited kernels but nothing executable pins them.
+ * Each function follows the reference lines it cites (paths relative to the reference tree).  The
+ * reference ships no test, golden vector or fixture for this path.  Pinning, by running the reference
+ * itself:
+ *   - pool addressing, page ids, tables, eviction order: against the reference's compiled Memoria
+ *     objects (oracle/ref_build/, tests/test_bookkeeping_vs_reference.py);
+ *   - fp16 K/V write (single and batched), RoPE and decode attention: against outputs of the reference's
+ *     own CUDA kernels recorded on a B200 (tests/golden/paged_attention_reference.npz, written by
+ *     tests/golden/make_paged_attention_golden.py; tests/test_oracle_vs_reference_kernels.py) - writes
+ *     bit-exact, RoPE within the error of the reference's fast-math intrinsics, attention within 2e-3;
+ *   - bf16, batches of sequences, holes, prefill attention (its reference kernel is `static` and only
+ *     reachable through the full layer), split-KV partials and their merge, extract/inject: "parity
+ *     unpinned" - they restate the cited kernels with the same building blocks as the pinned functions,
+ *     but no reference execution pins them.
  *
  * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC (see oracle/Makefile).  Contraction
  * is off so that every rounding below is the one written.

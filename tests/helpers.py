@@ -39,3 +39,18 @@ def to_dev(bits: np.ndarray, dtype: int, device="cuda"):
     import torch
     t = torch.from_numpy(bits.view(np.int16)).to(device)
     return t.view(torch.float16 if dtype == ob.F16 else torch.bfloat16)
+
+
+def rope_fastmath_tolerance(x_bits, rot, theta, pos, dtype):
+    """Largest difference to expect, per element of rows [..., D], between an accurately evaluated RoPE and
+    the reference's device code built with --use_fast_math: __sinf/__cosf are off by about 2^-21.4 * |angle|
+    (CUDA programming guide, intrinsic error table) and __powf's relative error carries into the angle, so
+    the rotated value may move by (|x0| + |x1|) * angle * 2e-6 in addition to one rounding of the result."""
+    x = ob.to_float(x_bits, dtype).astype(np.float64)
+    half = rot // 2
+    angle = pos / theta ** (2.0 * np.arange(half) / rot)
+    mag = np.abs(x[..., :half]) + np.abs(x[..., half:rot])
+    tol = np.zeros_like(x)
+    tol[..., :half] = mag * (angle * 2e-6 + 2e-6)
+    tol[..., half:rot] = tol[..., :half]
+    return tol

@@ -1,0 +1,60 @@
+"""The CPU checker against outputs of the reference's own CUDA kernels (apply_rope,
+paged_kv_cache_write[_batch], paged_gqa_decode_attention), recorded on a B200 by
+tests/golden/make_paged_attention_golden.py into tests/golden/paged_attention_reference.npz.
+
+What is pinned, and how tightly:
+  * the K/V writes are copies: the bytes and the places must match exactly;
+  * RoPE: the reference evaluates powf/cosf/sinf as fast-math device intrinsics, whose bits no CPU
+    reproduces; the checker's rotation must agree to within the documented error of those intrinsics
+    at the angle in question plus one fp16 rounding (tests/helpers.py: rope_fastmath_tolerance);
+  * decode attention (fp32 accumulate, fast-math exp): max-abs 2e-3 on the fp16 outputs."""
+import os
+
+import numpy as np
+import pytest
+
+from tests import helpers as H
+from tests.golden import paged_cases
+
+GOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "paged_attention_reference.npz"))
+
+
+def _rope_close(got_bits, ref_bits, src_bits, c, pos, oracle):
+    a, b = oracle.to_float(got_bits, oracle.F16), oracle.to_float(ref_bits, oracle.F16)
+    tol = H.rope_fastmath_tolerance(src_bits, c["rot"], c["theta"], pos, oracle.F16)
+    tol = tol + 1.01 * H.ulp(np.maximum(np.abs(a), np.abs(b)), oracle.F16)
+    return (np.abs(a - b) <= tol).all()
+
+
+@pytest.mark.parametrize("name", sorted(paged_cases.CASES))
+def test_checker_reproduces_reference_kernels(oracle, name):
+    ob = oracle
+    c = paged_cases.build(name)
+    g, pool = c["g"], c["pool"].copy()
+    pos = c["seq_len"]
+    if c["m_batch"]:
+        ob.append(g, pool, c["max_pages"], c["table"], c["layer"], pos, c["m_batch"], c["kb"], c["vb"], rope=False)
+        pos += c["m_batch"]
+    # RoPE on Q and K at the new position (the reference rotates both, layer_attention.cu:50-68)
+    q_r, k_r = c["q"].copy(), c["k1"].copy()
+    ob.lib().okv_rope_rows(q_r.ctypes.data, c["hq"], __import__("ctypes").byref(g), pos)
+    ob.lib().okv_rope_rows(k_r.ctypes.data, c["hkv"], __import__("ctypes").byref(g), pos)
+    assert _rope_close(q_r, GOLD[name + "_q_roped"], c["q"], c, pos, ob)
+    assert _rope_close(k_r, GOLD[name + "_k_roped"], c["k1"], c, pos, ob)
+    # and it is a rotation of the right pairs, not just something small: most elements did change
+    assert (GOLD[name + "_k_roped"][:, :c["rot"]] != c["k1"][:, :c["rot"]]).mean() > 0.9
+    # dims beyond the rotary part are untouched, bit for bit
+    assert np.array_equal(q_r[:, c["rot"]:], c["q"][:, c["rot"]:])
+    assert np.array_equal(GOLD[name + "_q_roped"][:, c["rot"]:], c["q"][:, c["rot"]:])
+    # the write itself is a copy: feed it the reference's rotated K so that the bytes must be identical
+    ob.append(g, pool, c["max_pages"], c["table"], c["layer"], pos, 1, GOLD[name + "_k_roped"][None], c["v1"][None],
+              rope=False)
+    ref_pool = c["pool"].copy()
+    ref_pool[GOLD[name + "_pool_changed_idx"]] = GOLD[name + "_pool_changed_val"]
+    assert np.array_equal(pool, ref_pool), "K/V bytes or their places differ from the reference's writes"
+    # attention on the reference's own pool and rotated Q
+    out = np.zeros((1, c["hq"], c["d"]), dtype=np.uint16)
+    ob.attend_decode(g, ref_pool, c["max_pages"], c["table"][None, :], [0], [pos + 1], c["layer"],
+                     GOLD[name + "_q_roped"][None], out, 1.0 / np.sqrt(c["d"]))
+    err = np.abs(ob.to_float(out[0], ob.F16) - ob.to_float(GOLD[name + "_out"], ob.F16)).max()
+    assert err <= 2e-3, err
