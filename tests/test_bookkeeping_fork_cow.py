@@ -244,3 +244,65 @@ def test_batch_reserve_and_advance(drkv_lib):
     _same_state(eng, mod, seqs)
     assert eng.seq_len(seqs[2]) == 120
     eng.close()
+
+
+def _c3_scenario(eng, mod, seed=2026, prefix=16384, branches=8, steps=256, P=16, check_every=1):
+    """Multi-branch prefix sharing at full size: filler sequences are prefilled and released (their pages
+    become unreferenced cached pages), a 16384-token prefix is forked into 8 branches (prefix pages at
+    reference count 8), each branch appends U[0,2048] private tokens, then 256 decode steps round-robin.
+    A second family forked at 16384 + 5 exercises copy-on-write of a shared partial tail page.  The pool
+    is sized so that the active pages end at 90 % of it, which forces LRU eviction of the cached pages."""
+    rng = np.random.default_rng(seed)          # filler sizes (depend on the pool size)
+    rng_len = np.random.default_rng(seed + 1)  # private branch lengths (do not)
+
+    def both(fe, fm):
+        a, b = fe(), fm()
+        assert a == b, (a, b)
+        return a
+
+    def grow(s, n):
+        rc = both(lambda: eng.lib.drkv_seq_reserve(eng.h, s, n, None), lambda: mod.seq_reserve(s, n))
+        if rc == 0:
+            both(lambda: eng.lib.drkv_seq_advance_batch(eng.h, 1, (__import__("ctypes").c_int32 * 1)(s), n),
+                 lambda: mod.seq_set_len(s, mod.seqs[s].len + n))
+        return rc
+
+    fillers = []
+    while len(mod.free) > 64:
+        s = both(lambda: eng.lib.drkv_seq_create(eng.h), mod.seq_create)
+        assert grow(s, int(min(len(mod.free) - 32, rng.integers(40, 400))) * P) == 0
+        fillers.append(s)
+    for s in fillers:
+        both(lambda: eng.lib.drkv_seq_release(eng.h, s, 0), lambda: mod.seq_release(s, False))
+    live = []
+    for plen, nb in ((prefix, branches), (prefix // 8 + 5, 3)):
+        root = both(lambda: eng.lib.drkv_seq_create(eng.h), mod.seq_create)
+        assert grow(root, plen) == 0
+        fam = [root] + [both(lambda: eng.lib.drkv_seq_fork(eng.h, root), lambda: mod.seq_fork(root)) for _ in range(nb - 1)]
+        for b in fam:
+            assert grow(b, int(rng_len.integers(0, 2049 if plen == prefix else 200))) == 0
+        live += fam
+    _same_state(eng, mod, live)
+    for step in range(steps):
+        for b in live:
+            assert grow(b, 1) == 0
+        if step % check_every == 0 or step == steps - 1:
+            _same_state(eng, mod, live)
+            assert eng.evict_log(clear=False) == mod.log
+    return live
+
+
+def test_prefix_sharing_full_size(drkv_lib):
+    # active pages at the end: 1024 shared + 8 private tails + 256 decode tokens each + the second family,
+    # 1680 with this seed; the cap puts that at 90 % of the pool
+    pages = 1867
+    eng, mod = _engine(pages, 16, 64, 1300, False), BookModel(pages, 16, 64, 1300, False)
+    live = _c3_scenario(eng, mod, check_every=16)
+    st = eng.stats()
+    assert 0.88 <= st["pages_active"] / pages <= 0.92 and st["evictions_cached"] > 100
+    assert (eng.refcounts()[eng.table(live[0])[:1024]] == 8).all()        # the shared prefix
+    assert st["cow_copies"] == mod.n_cow and st["cow_copies"] >= 2          # the 16384/8 + 5 family split its tail page
+    assert all(k == 0 for k, _, _, _ in mod.log)                           # only unreferenced pages were victims
+    # eviction order is release order of the fillers' pages
+    assert [p for _, _, _, p in mod.log] == [p for _, _, _, p in eng.evict_log(clear=False)]
+    eng.close()
