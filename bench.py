@@ -40,6 +40,11 @@ WORKLOADS = {
     "c5a": dict(layers=8, hq=64, hkv=8, d=128, page=64, seq_len=524288, theta=1e6,
                 desc="one 524288-token sequence, 8 layers, 64/8 heads, head_dim 128, bf16, page 64, KV pages split "
                      "by contiguous range across GPUs, partial (m,l,o) all-gathered and LSE-combined"),
+    # decode branches forked from one prompt: the shared pages are read once per 16 query rows of the family
+    "c3": dict(layers=32, hq=32, hkv=8, d=128, page=16, n_seq=8, prefix=16384, lo=0, hi=2048, theta=1e6,
+               desc="multi-branch prefix sharing: 32 layers, 32/8 heads, head_dim 128, bf16, page 16; 8 decode "
+                    "branches forked from one 16384-token prefix, private tails U[0,2048], copy-on-write of the "
+                    "shared tail page, shared-prefix decode plan per step"),
     # chunked prefill into the paged cache (tensor-core bound)
     "c4": dict(layers=28, hq=28, hkv=4, d=128, page=16, n_seq=4, seq_len=32768, chunk=2048, theta=1e6,
                desc="chunked prefill: 28 layers, 28/4 heads, head_dim 128, bf16, page 16, 4 sequences x 32768 "
@@ -538,6 +543,150 @@ def run_c4(args):
             "gpu_launches": K * n_seq * (S // C) * L * 2, "clocks": clocks, "e2e": None}
 
 
+def run_c3(args):
+    """Decode steps over branches forked from one prompt (one GPU): bookkeeping (reserve with copy-on-write,
+    table sync, shared-prefix plan) + append + planned attention; the per-sequence pass is timed beside it."""
+    import torch
+
+    from deusridet_b200 import PagedKVEngine, build
+    build.build()
+    world, rank, local = _dist_setup()
+    dev = torch.device(f"cuda:{local}")
+    w = dict(WORKLOADS["c3"])
+    if args.layers:
+        w["layers"] = args.layers
+    n_seq = args.seqs or w["n_seq"]
+    L, hq, hkv, d, page, prefix = w["layers"], w["hq"], w["hkv"], w["d"], w["page"], w["prefix"]
+    K, W = args.steps, args.warmup
+    rng = np.random.default_rng(77)
+    private = rng.integers(w["lo"], w["hi"] + 1, size=n_seq).astype(np.int64)
+    room = 3 * (K + W) + 16
+    max_pages = (prefix + page - 1) // page + int(sum((int(x) + room + 2 * page - 1) // page for x in private)) + 8
+    width = (prefix + int(private.max()) + room) // page + 2
+    eng = PagedKVEngine(num_layers=L, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
+                        rope_theta=w["theta"], max_pages=max_pages, max_seqs=n_seq, max_pages_per_seq=width,
+                        device=local)
+    pages = [eng.alloc_block() for _ in range(max_pages)]
+    for p in rng.permutation(max_pages):
+        eng.free_block(int(p))
+    root = eng.seq_create()
+    eng.reserve(root, prefix - 5)                          # the shared tail page is partial: forces copy-on-write
+    eng.set_seq_len(root, prefix - 5)
+    seqs = [root] + [eng.seq_fork(root) for _ in range(n_seq - 1)]
+    stream = torch.cuda.current_stream()
+    for s_, x in zip(seqs, private):
+        eng.reserve(s_, int(x) + 5, stream)
+        eng.set_seq_len(s_, prefix + int(x))
+    cur = (prefix + private).astype(np.int32)
+    eng.sync_block_table(stream)
+    torch.manual_seed(3)
+    eng.pool_tensor().view(torch.bfloat16).normal_()
+    if args.chunk:
+        eng.set_chunk_tokens(args.chunk)
+    seq_arr = np.asarray(seqs, dtype=np.int32)
+    d_rows = torch.tensor(seqs, dtype=torch.int32, device=dev)
+    d_pos = torch.from_numpy(cur.copy()).to(dev)
+    d_len = d_pos + 1
+    q = torch.randn(L, n_seq, hq, d, device=dev, dtype=torch.bfloat16)
+    kn = torch.randn(L, n_seq, hkv, d, device=dev, dtype=torch.bfloat16)
+    vn = torch.randn(L, n_seq, hkv, d, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(L, n_seq, hq, d, device=dev, dtype=torch.bfloat16)
+    scale = 1.0 / float(np.sqrt(d))
+    eng.reserve_batch(seq_arr, 1, stream)
+    eng.sync_block_table(stream)
+    info = eng.plan_decode(seqs, (cur + 1).tolist(), stream)
+    max_kv = int(cur.max()) + 1
+
+    def planned_step():
+        for l in range(L):
+            eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
+            eng.attend_decode_planned(l, q[l], out[l], scale, stream)
+
+    def plain_step():
+        for l in range(L):
+            eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
+            eng.attend_decode(l, n_seq, d_rows, d_len, max_kv, q[l], out[l], scale, stream)
+
+    def timed(fn):
+        for _ in range(W):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(K):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        eng.kernel_timing(True)
+        fn()
+        kms, kl = eng.kernel_timing(False, read=True)
+        return e0.elapsed_time(e1) / K, kms / kl * 1e3
+
+    plain_ms, plain_us = timed(plain_step)
+    sampler = ClockSampler(local)
+    sampler.start()
+    plan_ms, plan_us = timed(planned_step)
+    clocks = sampler.stop()
+    eng.check_kernels()
+
+    # ---- end to end: host bookkeeping + plan + H2D of the step's Q/K/V + D2H of the outputs ----
+    nq, nk = n_seq * hq * d, n_seq * hkv * d
+    h_in = torch.randn(L, nq + 2 * nk, dtype=torch.bfloat16).pin_memory()
+    d_in = torch.empty(L, nq + 2 * nk, dtype=torch.bfloat16, device=dev)
+    h_out = torch.empty(out.shape, dtype=torch.bfloat16).pin_memory()
+    h_pos = torch.empty(n_seq, dtype=torch.int32).pin_memory()
+
+    def e2e_step():
+        eng.reserve_batch(seq_arr, 1, stream)
+        eng.sync_block_table(stream)
+        eng.plan_decode(seqs, (cur + 1).tolist(), stream)
+        h_pos.copy_(torch.from_numpy(cur))
+        d_pos.copy_(h_pos, non_blocking=True)
+        d_in.copy_(h_in, non_blocking=True)
+        for l in range(L):
+            eng.append_rope(l, n_seq, d_rows, d_pos, d_in[l, nq:nq + nk].view(n_seq, hkv, d),
+                            d_in[l, nq + nk:].view(n_seq, hkv, d), stream)
+            eng.attend_decode_planned(l, d_in[l, :nq].view(n_seq, hq, d), out[l], scale, stream)
+        h_out.copy_(out, non_blocking=True)
+        stream.synchronize()
+        cur[:] = cur + 1
+        eng.advance_batch(seq_arr, 1)
+
+    for _ in range(W):
+        e2e_step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / K
+    eng.check_kernels()
+    stats = eng.stats()
+    eng.close()
+    kv_tok = 2 * hkv * d * 2
+    unique = float(prefix + private.sum() + n_seq) * kv_tok      # every distinct key/value once
+    peak, peak_kind = peaks()
+    ach = unique / (plan_us * 1e-6) / 1e9
+    return {"metric": "decode tokens/s over forked branches (append + shared-prefix paged attention)",
+            "value": n_seq / (plan_ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": plan_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"c3: {w['desc']}", "layers": L, "branches": n_seq, "plan": info,
+                       "cold_cache": "the shared prefix (%.0f MB per layer) fits L2; all layers together do not"
+                                     % (prefix * kv_tok / 1e6)},
+            "per_sequence_pass": {"ms_per_step": plain_ms, "tokens_per_s": n_seq / (plain_ms * 1e-3),
+                                  "attend_us_per_launch": plain_us,
+                                  "bytes_per_launch": float(info["keys_per_sequence_pass"]) * kv_tok},
+            "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel (planned)", "achieved": ach, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "bytes_per_launch": unique, "bytes_read_per_launch": float(info["keys_planned_pass"]) * kv_tok,
+                         "us_per_launch": plan_us},
+            "gpu_launches": K * L * 3, "clocks": clocks,
+            "e2e": {"value": n_seq / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(h_in.numel() * 2 + n_seq * 4), "d2h_bytes_per_step": int(h_out.numel() * 2)},
+            "cow_copies": stats["cow_copies"]}
+
+
 def eng_bytes(max_pages, w):
     return max_pages * w["layers"] * 2 * w["hkv"] * w["page"] * w["d"] * 2
 
@@ -649,6 +798,9 @@ def main():
         return
     if args.workload == "c4":
         print(json.dumps(run_c4(args)), flush=True)
+        return
+    if args.workload == "c3":
+        print(json.dumps(run_c3(args)), flush=True)
         return
     res, (w, lens) = run_ours(args)
     if res is not None:

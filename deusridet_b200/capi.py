@@ -35,6 +35,12 @@ class Stats(C.Structure):
         "cow_copies", "cow_bytes", "table_sync_bytes", "table_syncs", "live_seqs")]
 
 
+class PlanInfo(C.Structure):
+    _fields_ = [("n_seq", C.c_int32), ("n_families", C.c_int32), ("n_blocks", C.c_int32),
+                ("chunk_tokens", C.c_int32), ("keys_per_sequence_pass", C.c_int64),
+                ("keys_planned_pass", C.c_int64)]
+
+
 class EvictRecord(C.Structure):
     _fields_ = [("kind", C.c_int32), ("seq", C.c_int32), ("logical", C.c_int32), ("page", C.c_int32)]
 
@@ -87,6 +93,10 @@ SIGNATURES = {
     "drkv_append_rope": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "drkv_append_rope_chunk": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp]),
     "drkv_attend_decode": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _vp]),
+    "drkv_plan_decode": (_i, [_vp, _i, _pi32, _pi32, _vp]),
+    "drkv_plan_get_info": (_i, [_vp, C.POINTER(PlanInfo)]),
+    "drkv_plan_dump": (_i, [_vp, _pi32, _i]),
+    "drkv_attend_decode_planned": (_i, [_vp, _i, _vp, _vp, _f, _vp]),
     "drkv_attend_prefill_chunk": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_attend_prefill_batch": (_i, [_vp, _i, _i, _pi32, _pi32, _pi32, C.POINTER(_vp), C.POINTER(_vp), _f, _vp]),
     "drkv_attend_partial": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),

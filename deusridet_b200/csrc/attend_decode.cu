@@ -42,7 +42,7 @@ enum SlotFlags : int { SLOT_FIRST = 1, SLOT_LAST = 2, SLOT_SKIP = 4, SLOT_DONE =
 // What the producer tells a consumer warp about one ring slot.
 struct alignas(16) SlotMeta {
     int b, kvh, part_slot, flags;   // part_slot: index of the partial of query row 0 of the group
-    int v_lo, v_hi, pad0, pad1;     // keys [v_lo, v_hi) of the 16 in the slot are visible
+    int v_lo, v_hi, fam, pad1;      // keys [v_lo, v_hi) of the 16 in the slot are visible; fam: family block + 1 or 0
 };
 
 template <typename T>
@@ -121,17 +121,25 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     // queue head and the scratch may all have been written by it.
     pdl_wait();
     pdl_launch_dependents();
-    // ---- items per sequence, exclusive prefix sum into cum[] ----
+    // ---- items per entry, exclusive prefix sum into cum[] ----
+    // Entries: first the family blocks of a shared-prefix plan (up to 16 query rows of several forked
+    // sequences over the chunks they have in common), then the sequences (their remaining chunks).
+    const int n_fb = p.n_fb;
+    const int n_ent = n_fb + p.n_seq;
+    auto entry_items = [&](int e) -> int {
+        if (e < n_fb) return __ldg(p.fb_chunks + e) * p.num_kv_heads;
+        const int b = e - n_fb;
+        const int kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + b) : p.kv_end;
+        int nch = kv_end > base_tok ? (kv_end - base_tok + CT - 1) / CT : 0;
+        nch = min(nch, p.max_chunks);
+        if (n_fb > 0) nch = max(nch - __ldg(p.seq_first_chunk + b), 0);
+        return nch * p.num_kv_heads;
+    };
     {
-        const int per = (p.n_seq + THREADS - 1) / THREADS;
-        const int lo = min(tid * per, p.n_seq), hi = min(lo + per, p.n_seq);
+        const int per = (n_ent + THREADS - 1) / THREADS;
+        const int lo = min(tid * per, n_ent), hi = min(lo + per, n_ent);
         int local = 0;
-        for (int b = lo; b < hi; b++) {
-            const int kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + b) : p.kv_end;
-            int nch = kv_end > base_tok ? (kv_end - base_tok + CT - 1) / CT : 0;
-            nch = min(nch, p.max_chunks);
-            local += nch * p.num_kv_heads;
-        }
+        for (int e = lo; e < hi; e++) local += entry_items(e);
         int incl = local;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -143,17 +151,14 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         int offset = 0;
         for (int i = 0; i < w; i++) offset += s_warp_tot[i];
         int run = offset + incl - local;
-        for (int b = lo; b < hi; b++) {
-            cum[b] = run;
-            const int kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + b) : p.kv_end;
-            int nch = kv_end > base_tok ? (kv_end - base_tok + CT - 1) / CT : 0;
-            nch = min(nch, p.max_chunks);
-            run += nch * p.num_kv_heads;
+        for (int e = lo; e < hi; e++) {
+            cum[e] = run;
+            run += entry_items(e);
         }
-        if (tid == THREADS - 1) cum[p.n_seq] = offset + incl;
+        if (tid == THREADS - 1) cum[n_ent] = offset + incl;
     }
     __syncthreads();
-    const int total_items = cum[p.n_seq];
+    const int total_items = cum[n_ent];
 
     // ---- next-item prefetch state (warp-uniform except raw_next, which lane 0 owns) ----
     // n_state: 0 nothing requested, 1 queue index requested (atomic in flight), 2 decoded (length and
@@ -166,10 +171,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     constexpr int kPrefetchGroups = DRKV_PREFETCH_GROUPS;
     int raw_next = 0, n_state = 0;
     bool exhausted = false;
-    int n_b = 0, n_kvh = 0, n_chunk = 0, n_trow = 0, n_kv_end = 0, n_page = -1;
+    int n_b = 0, n_kvh = 0, n_chunk = 0, n_trow = 0, n_kv_end = 0, n_page = -1, n_fam = 0;   // n_fam: family block + 1, 0 = plain
     // ---- issue cursor ----
     bool c_valid = false;
-    int c_b = 0, c_kvh = 0, c_chunk = 0, c_trow = 0, c_kv_end = 0, c_tok_lo = 0, c_ngroups = 0, c_gi = 0, c_page = -1;
+    int c_b = 0, c_kvh = 0, c_chunk = 0, c_trow = 0, c_kv_end = 0, c_tok_lo = 0, c_ngroups = 0, c_gi = 0, c_page = -1, c_fam = 0;
     int i_slot = 0, outstanding = 0;
     // ---- compute cursor ----
     int slot = 0, phase = 0;
@@ -196,18 +201,27 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             n_state = 0;
             return;
         }
-        int lo = 0, hi = p.n_seq;                      // largest b with cum[b] <= raw
+        int lo = 0, hi = n_ent;                        // largest entry with cum[e] <= raw
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
             if (cum[mid] <= raw) lo = mid; else hi = mid;
         }
-        n_b = lo;
         const int nch = (cum[lo + 1] - cum[lo]) / p.num_kv_heads;
         const int j = raw - cum[lo];
         n_kvh = j / nch;
         n_chunk = j - n_kvh * nch;
-        n_kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + lo) : p.kv_end;
-        n_trow = p.rows != nullptr ? __ldg(p.rows + lo) : p.row;
+        if (lo < n_fb) {                               // shared chunks of a family block
+            n_fam = lo + 1;
+            n_b = 0;
+            n_kv_end = base_tok + nch * CT;
+            n_trow = __ldg(p.fb_row + lo);
+        } else {
+            n_fam = 0;
+            n_b = lo - n_fb;
+            if (n_fb > 0) n_chunk += __ldg(p.seq_first_chunk + n_b);
+            n_kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + n_b) : p.kv_end;
+            n_trow = p.rows != nullptr ? __ldg(p.rows + n_b) : p.row;
+        }
         n_state = 2;
     };
     auto load_page = [&](int trow, int tok) -> int {
@@ -229,7 +243,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 if (n_state == 0 && !exhausted) fetch_raw();
                 if (n_state == 1) decode_next();       // waits for the atomic only if it was just issued
                 if (n_state < 2) break;                // queue drained
-                c_b = n_b; c_kvh = n_kvh; c_chunk = n_chunk; c_trow = n_trow; c_kv_end = n_kv_end;
+                c_b = n_b; c_kvh = n_kvh; c_chunk = n_chunk; c_trow = n_trow; c_kv_end = n_kv_end; c_fam = n_fam;
                 c_tok_lo = base_tok + c_chunk * CT;
                 c_ngroups = (min(c_tok_lo + CT, c_kv_end) - c_tok_lo + kGroupTokens - 1) / kGroupTokens;
                 c_gi = 0;
@@ -249,11 +263,12 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 SlotMeta m;
                 m.b = c_b;
                 m.kvh = c_kvh;
-                m.part_slot = (c_b * p.num_q_heads + c_kvh * p.group) * p.max_chunks + c_chunk;
+                m.part_slot = c_fam ? c_chunk : (c_b * p.num_q_heads + c_kvh * p.group) * p.max_chunks + c_chunk;
                 m.flags = (c_gi == 0 ? SLOT_FIRST : 0) | (last ? SLOT_LAST : 0) | (page < 0 ? SLOT_SKIP : 0);
                 m.v_lo = max(0, p.kv_begin - tok0);
                 m.v_hi = min(kGroupTokens, c_kv_end - tok0);
-                m.pad0 = m.pad1 = 0;
+                m.fam = c_fam;
+                m.pad1 = 0;
                 metas[ring] = m;
                 // earlier generic-proxy accesses to this slot (ldmatrix reads, zero fill) are ordered
                 // before the async-proxy writes of the new gather
@@ -303,17 +318,31 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         __syncwarp();
         const SlotMeta meta = metas[ring];
         if (meta.flags & SLOT_FIRST) {
-            // query rows of the group straight into m16k16 A fragments; rows beyond the group are zero
-            const T* qb = reinterpret_cast<const T*>(p.q) + ((int64_t)meta.b * p.num_q_heads + (int64_t)meta.kvh * p.group) * D;
-            const bool r0 = qrow < p.group, r1 = HI && (qrow + 8 < p.group);
-            const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qb + (int64_t)qrow * D + col);
-            const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qb + (int64_t)(qrow + 8) * D + col);
+            // query rows straight into m16k16 A fragments.  Plain item: row r is query head r of the group;
+            // family block: row r is head r % g of member r / g (several forked sequences share the keys).
+            // Rows beyond that are zero.
+            const T* qall = reinterpret_cast<const T*>(p.q);
+            const T* qr0 = nullptr;
+            const T* qr1 = nullptr;
+            if (meta.fam == 0) {
+                const T* qb = qall + ((int64_t)meta.b * p.num_q_heads + (int64_t)meta.kvh * p.group) * D;
+                if (qrow < p.group) qr0 = qb + (int64_t)qrow * D;
+                if (HI && qrow + 8 < p.group) qr1 = qb + (int64_t)(qrow + 8) * D;
+            } else {
+                const int32_t* mem = p.fb_members + (meta.fam - 1) * 16;
+                const int r0i = qrow / p.group, r1i = (qrow + 8) / p.group;
+                const int b0 = r0i < 16 ? __ldg(mem + r0i) : -1, b1 = (HI && r1i < 16) ? __ldg(mem + r1i) : -1;
+                if (b0 >= 0) qr0 = qall + ((int64_t)b0 * p.num_q_heads + (int64_t)meta.kvh * p.group + qrow % p.group) * D;
+                if (b1 >= 0) qr1 = qall + ((int64_t)b1 * p.num_q_heads + (int64_t)meta.kvh * p.group + (qrow + 8) % p.group) * D;
+            }
+            const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qr0 + col);
+            const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qr1 + col);
 #pragma unroll
             for (int kk = 0; kk < KSTEPS; kk++) {
-                qf[kk][0] = r0 ? __ldg(q0 + 8 * kk) : 0u;
-                qf[kk][2] = r0 ? __ldg(q0 + 8 * kk + 4) : 0u;
-                qf[kk][1] = r1 ? __ldg(q1 + 8 * kk) : 0u;
-                qf[kk][3] = r1 ? __ldg(q1 + 8 * kk + 4) : 0u;
+                qf[kk][0] = qr0 ? __ldg(q0 + 8 * kk) : 0u;
+                qf[kk][2] = qr0 ? __ldg(q0 + 8 * kk + 4) : 0u;
+                qf[kk][1] = qr1 ? __ldg(q1 + 8 * kk) : 0u;
+                qf[kk][3] = qr1 ? __ldg(q1 + 8 * kk + 4) : 0u;
             }
             m2[0] = m2[1] = kNegBig;
             lsum[0] = lsum[1] = 0.f;
@@ -421,8 +450,17 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 l += __shfl_xor_sync(0xffffffffu, l, 1);
                 l += __shfl_xor_sync(0xffffffffu, l, 2);
                 const int row = qrow + 8 * r;
-                if (row < p.group) {
-                    const int64_t ps = (int64_t)meta.part_slot + (int64_t)row * p.max_chunks;
+                int64_t ps = -1;                                   // partial slot of this row, -1: padding row
+                if (meta.fam == 0) {
+                    if (row < p.group) ps = (int64_t)meta.part_slot + (int64_t)row * p.max_chunks;
+                } else {
+                    const int mi = row / p.group;
+                    const int bm = mi < 16 ? __ldg(p.fb_members + (meta.fam - 1) * 16 + mi) : -1;
+                    if (bm >= 0)
+                        ps = ((int64_t)bm * p.num_q_heads + (int64_t)meta.kvh * p.group + row % p.group) * p.max_chunks +
+                             meta.part_slot;               // part_slot holds the chunk index for family blocks
+                }
+                if (ps >= 0) {
                     const bool empty = !(l > 0.f);
                     float* dst = p.part_o + ps * D + col;
 #pragma unroll
@@ -562,7 +600,7 @@ template <typename T, int D, bool HI>
 cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
     constexpr int WARPS = RingShape<D>::kWarps, DEPTH = RingShape<D>::kDepth, NH = D / 64;
     constexpr size_t smem = 1024 + (size_t)WARPS * DEPTH * (2 * NH * 2048 + sizeof(SlotMeta) + sizeof(uint64_t)) +
-                            (kMaxDecodeSeqs + 1) * sizeof(int);
+                            (2 * kMaxDecodeSeqs + 1) * sizeof(int);   // cum[] over family blocks + sequences
     static bool configured[64] = {};  // per instantiation and device: the attribute belongs to the context
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -579,7 +617,7 @@ cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int
 
 template <typename T, int D>
 cudaError_t launch_decode_t(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
-    return p.group > 8 ? launch_decode_hi<T, D, true>(tmap, p, num_sms, stream)
+    return (p.group > 8 || p.rows_per_item > 8) ? launch_decode_hi<T, D, true>(tmap, p, num_sms, stream)
                        : launch_decode_hi<T, D, false>(tmap, p, num_sms, stream);
 }
 
@@ -623,7 +661,7 @@ bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, in
 cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,
                                  int dtype, cudaStream_t stream) {
     if (p.total_items <= 0) return cudaSuccess;
-    if (p.n_seq > kMaxDecodeSeqs) return cudaErrorInvalidValue;
+    if (p.n_seq > kMaxDecodeSeqs || p.n_fb > kMaxDecodeSeqs) return cudaErrorInvalidValue;
     if (p.chunk_tokens % kGroupTokens != 0 || p.chunk_tokens <= 0 || p.group > 16 || p.page_size % kGroupTokens != 0)
         return cudaErrorInvalidValue;
     const bool f16 = dtype == DRKV_DTYPE_F16;

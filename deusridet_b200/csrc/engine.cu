@@ -57,22 +57,37 @@ size_t page_bytes_all_layers(const drkv_geometry& g) {
     return (size_t)g.num_layers * 2 * g.num_kv_heads * g.page_size * g.head_dim * 2;
 }
 
+// Keys per work item, given a function that counts the items a chunk size produces.  Each item writes one
+// fp32 partial per query row (rows * (D + 2) * 4 bytes against chunk * 2 * D * 2 bytes of K/V read), so
+// the chunk starts large enough to keep that a few percent.  It shrinks when that shortens the longest
+// warp's queue: warps take whole items, so the pass lasts about ceil(items / warps) items of (chunk +
+// a fixed cost per item worth ~64 keys: start-up, the partial's write and its share of the merge) each.
+template <typename ItemsFn>
+int pick_chunk_by_cost(int group, int num_sms, ItemsFn items) {
+    const long warps = (long)num_sms * 8;
+    int best = 0;
+    long best_cost = 0;
+    for (int c = group > 4 ? 512 : 256; c >= 64; c >>= 1) {
+        const long n = items(c);
+        const long cost = ((n + warps - 1) / warps) * (c + 64);
+        if (best == 0 || cost < best_cost) {
+            best = c;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
 int pick_chunk(int n_seq, int hkv, int group, int max_kv_span, int num_sms) {
-    // Keys per work item.  Each item writes one fp32 partial per query head of the group
-    // (group * (D + 2) * 4 bytes against chunk * 2 * D * 2 bytes of K/V read), so the chunk
-    // stays large enough to keep that a few percent, and shrinks only when there would be
-    // fewer items than consumer warps on the GPU.
-    int chunk = group > 4 ? 512 : 256;
     const long warps = (long)num_sms * 8;
     auto items = [&](int c) { return (long)n_seq * hkv * ((max_kv_span + c - 1) / c); };
-    if (n_seq == 1 && items(chunk) > warps) {
+    if (n_seq == 1 && items(group > 4 ? 512 : 256) > warps) {
         // One long sequence: equal items, one per warp, is a perfect partition with the fewest partials.
         const long per_head = warps / hkv > 0 ? warps / hkv : 1;
         const long c = (max_kv_span + per_head - 1) / per_head;
         return (int)((c + 15) / 16 * 16);
     }
-    while (chunk > 64 && items(chunk) < warps) chunk >>= 1;
-    return chunk;
+    return pick_chunk_by_cost(group, num_sms, items);
 }
 
 }  // namespace
@@ -115,7 +130,25 @@ struct drkv_engine {
     int stage_next = 0;
     size_t stage_ints = 0;
     int64_t sync_bytes = 0, syncs = 0, cow_bytes = 0;
+
+    // shared-prefix decode plan: device arrays in one allocation, uploaded from two pinned buffers
+    struct Plan {
+        bool valid = false;
+        int n_seq = 0, n_fb = 0, n_fam = 0, chunk = 0, max_chunks = 0, rows_per_item = 0;
+        int64_t keys_seq = 0, keys_plan = 0;
+        const int32_t *rows = nullptr, *kv_len = nullptr, *first_chunk = nullptr;
+        const int32_t *fb_row = nullptr, *fb_chunks = nullptr, *fb_members = nullptr;
+    } plan;
+    std::vector<int32_t> plan_image;   // what the device holds: rows, kv_len, first_chunk, fb_row, fb_chunks, fb_members
+    int32_t* d_plan = nullptr;
+    int32_t* h_plan[2] = {nullptr, nullptr};
+    cudaEvent_t plan_done[2] = {nullptr, nullptr};
+    bool plan_busy[2] = {false, false};
+    int plan_next = 0;
 };
+
+// ints of a plan: rows, kv_len, first_chunk per sequence; row, chunks and 16 members per family block
+static constexpr size_t kPlanInts = (size_t)kMaxDecodeSeqs * 3 + (size_t)kMaxDecodeSeqs * 18;
 
 #define LOCK(e) std::lock_guard<std::mutex> lock_((e)->mu)
 #define NEED(e)                                                        \
@@ -199,6 +232,13 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
             if ((ce = cudaEventCreateWithFlags(&e->stage_done[i], cudaEventDisableTiming)) != cudaSuccess)
                 return fail(DRKV_ERR_CUDA, "cudaEventCreate", ce);
         }
+        if ((ce = cudaMalloc(&e->d_plan, kPlanInts * 4)) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(plan)", ce);
+        for (int i = 0; i < 2; i++) {
+            if ((ce = cudaHostAlloc(&e->h_plan[i], kPlanInts * 4, cudaHostAllocDefault)) != cudaSuccess)
+                return fail(DRKV_ERR_CUDA, "cudaHostAlloc(plan)", ce);
+            if ((ce = cudaEventCreateWithFlags(&e->plan_done[i], cudaEventDisableTiming)) != cudaSuccess)
+                return fail(DRKV_ERR_CUDA, "cudaEventCreate", ce);
+        }
         const size_t ctl_ints = 4;   // error word, queue head, exit count, padding
         if ((ce = cudaMalloc(&e->d_error, ctl_ints * sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(error)", ce);
         if ((ce = cudaMemset(e->d_error, 0, ctl_ints * sizeof(int))) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMemset(error)", ce);
@@ -240,6 +280,11 @@ void drkv_destroy(drkv_engine* e) {
         cudaFree(e->d_inv_freq);
         cudaFree(e->d_error);
         cudaFree(e->d_scratch);
+        cudaFree(e->d_plan);
+        for (int i = 0; i < 2; i++) {
+            if (e->h_plan[i]) cudaFreeHost(e->h_plan[i]);
+            if (e->plan_done[i]) cudaEventDestroy(e->plan_done[i]);
+        }
         for (auto& ev : e->tev) cudaEventDestroy(ev);
         for (int i = 0; i < 2; i++) {
             if (e->h_stage[i]) cudaFreeHost(e->h_stage[i]);
@@ -620,16 +665,22 @@ int drkv_seq_inject(drkv_engine* e, int seq, int start_token, int num_tokens, co
 // ---- attention --------------------------------------------------------------------------
 static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows, const int32_t* d_kv_len,
                          int row, int kv_begin, int kv_end, int max_span, const void* q, void* out,
-                         float* out_partial, float scale, cudaStream_t stream) {
+                         float* out_partial, float scale, cudaStream_t stream,
+                         const drkv_engine::Plan* plan = nullptr) {
     const drkv_geometry& g = e->geom;
-    int chunk = e->forced_chunk ? e->forced_chunk
+    int chunk = 0;
+    if (plan) {
+        chunk = plan->chunk;   // the plan's chunk was checked against the scratch when it was made
+    } else {
+        chunk = e->forced_chunk ? e->forced_chunk
                                 : pick_chunk(n_seq, g.num_kv_heads, g.num_q_heads / g.num_kv_heads, max_span, e->num_sms);
-    auto need_bytes = [&](int c) {
-        return (size_t)n_seq * g.num_q_heads * ((max_span + c - 1) / c) * (g.head_dim + 2) * 4;
-    };
-    while (need_bytes(chunk) > e->scratch_bytes && chunk < (1 << 24)) chunk <<= 1;
-    if (need_bytes(chunk) > e->scratch_bytes)
-        return set_err(DRKV_ERR_CAPACITY, "attend: split-KV scratch too small for %d sequences x %d keys", n_seq, max_span);
+        auto need_bytes = [&](int c) {
+            return (size_t)n_seq * g.num_q_heads * ((max_span + c - 1) / c) * (g.head_dim + 2) * 4;
+        };
+        while (need_bytes(chunk) > e->scratch_bytes && chunk < (1 << 24)) chunk <<= 1;
+        if (need_bytes(chunk) > e->scratch_bytes)
+            return set_err(DRKV_ERR_CAPACITY, "attend: split-KV scratch too small for %d sequences x %d keys", n_seq, max_span);
+    }
     const int max_chunks = (max_span + chunk - 1) / chunk;
     const size_t n_slots = (size_t)n_seq * g.num_q_heads * max_chunks;
 
@@ -655,6 +706,14 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     p.max_chunks = max_chunks;
     p.n_seq = n_seq;
     p.total_items = n_seq * g.num_kv_heads * max_chunks;
+    if (plan && plan->n_fb > 0) {
+        p.n_fb = plan->n_fb;
+        p.rows_per_item = plan->rows_per_item;
+        p.fb_row = plan->fb_row;
+        p.fb_chunks = plan->fb_chunks;
+        p.fb_members = plan->fb_members;
+        p.seq_first_chunk = plan->first_chunk;
+    }
     p.work_counter = e->d_work;
     p.exit_count = e->d_exit;
     p.scale_log2 = scale * 1.4426950408889634f;
@@ -701,6 +760,177 @@ int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_ro
         if (rc != DRKV_OK) return rc;
     }
     return DRKV_OK;
+}
+
+int drkv_plan_decode(drkv_engine* e, int n_seq, const int32_t* seqs, const int32_t* kv_len, void* stream_) {
+    NEED(e);
+    if (n_seq < 0 || n_seq > kMaxDecodeSeqs || (n_seq > 0 && (!seqs || !kv_len)))
+        return set_err(DRKV_ERR_INVALID, "plan_decode: bad argument (at most %d sequences)", kMaxDecodeSeqs);
+    LOCK(e);
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const drkv_geometry& g = e->geom;
+    const int P = g.page_size, group = g.num_q_heads / g.num_kv_heads;
+    const int per_block = 16 / group;   // sequences whose query rows fill one 16-row tile
+    drkv_engine::Plan& pl = e->plan;
+    pl.valid = false;
+
+    // families: runs of consecutive entries whose tables start with the same pages as the run's first
+    struct Fam { int first, count, shared_tokens; };
+    std::vector<Fam> fams;
+    std::vector<int> fam_of(n_seq, -1);
+    int max_kv = 0;
+    int64_t keys_seq = 0;
+    for (int i = 0; i < n_seq; i++) {
+        if (seqs[i] < 0 || seqs[i] >= e->book.max_seqs() || e->book.seq(seqs[i]) == nullptr || kv_len[i] < 0)
+            return set_err(DRKV_ERR_INVALID, "plan_decode: entry %d is not a live sequence", i);
+        if (kv_len[i] > e->book.row_width() * P)
+            return set_err(DRKV_ERR_INVALID, "plan_decode: entry %d is longer than a block table", i);
+        max_kv = kv_len[i] > max_kv ? kv_len[i] : max_kv;
+        keys_seq += kv_len[i];
+    }
+    for (int i = 0; i < n_seq && per_block >= 2;) {
+        const std::vector<int32_t>& lead = e->book.seq(seqs[i])->table;
+        int shared = kv_len[i], j = i + 1;
+        for (; j < n_seq; j++) {
+            const std::vector<int32_t>& t = e->book.seq(seqs[j])->table;
+            const size_t lim = lead.size() < t.size() ? lead.size() : t.size();
+            size_t c = 0;
+            while (c < lim && lead[c] >= 0 && lead[c] == t[c]) c++;
+            int common = (int)c * P;
+            if (kv_len[j] < common) common = kv_len[j];
+            if (common < 64 || common * 2 < shared) break;   // too little in common with the run so far
+            if (common < shared) shared = common;
+        }
+        if (j - i >= 2) {
+            for (int k = i; k < j; k++) fam_of[k] = (int)fams.size();
+            fams.push_back(Fam{i, j - i, shared});
+        }
+        i = j;
+    }
+
+    // chunk: as for an unplanned pass, but counted over the planned items
+    auto planned_items = [&](int c, int64_t* keys) {
+        int64_t items = 0, k = 0;
+        for (const Fam& f : fams) {
+            const int sc = f.shared_tokens / c;
+            items += (int64_t)((f.count + per_block - 1) / per_block) * sc;
+            k += (int64_t)((f.count + per_block - 1) / per_block) * sc * c;
+        }
+        for (int i = 0; i < n_seq; i++) {
+            const int first = fam_of[i] >= 0 ? fams[fam_of[i]].shared_tokens / c : 0;
+            const int nch = (kv_len[i] + c - 1) / c;
+            items += nch > first ? nch - first : 0;
+            k += kv_len[i] > first * c ? kv_len[i] - first * c : 0;
+        }
+        if (keys) *keys = k;
+        return items * g.num_kv_heads;
+    };
+    int chunk = e->forced_chunk;
+    if (!chunk) {
+        chunk = pick_chunk_by_cost(group, e->num_sms, [&](int c) { return (long)planned_items(c, nullptr); });
+    }
+    if (e->has_device) {
+        auto need_bytes = [&](int c) {
+            return (size_t)n_seq * g.num_q_heads * ((max_kv + c - 1) / c) * (g.head_dim + 2) * 4;
+        };
+        while (need_bytes(chunk) > e->scratch_bytes && chunk < (1 << 24)) chunk <<= 1;
+        if (need_bytes(chunk) > e->scratch_bytes)
+            return set_err(DRKV_ERR_CAPACITY, "plan_decode: split-KV scratch too small for %d sequences x %d keys", n_seq, max_kv);
+    }
+
+    // the plan's image (an engine without a device keeps it for inspection only)
+    e->plan_image.assign(3 * (size_t)n_seq + 18 * (size_t)(n_seq / 2 + 1), 0);
+    int32_t* h = e->plan_image.data();
+    int32_t* h_rows = h;
+    int32_t* h_len = h + n_seq;
+    int32_t* h_first = h + 2 * (size_t)n_seq;
+    int n_fb = 0, n_fam = 0, max_members = 0;
+    for (const Fam& f : fams)
+        if (f.shared_tokens / chunk > 0) n_fb += (f.count + per_block - 1) / per_block;
+    int32_t* h_fb_row = h + 3 * (size_t)n_seq;
+    int32_t* h_fb_chunks = h_fb_row + n_fb;
+    int32_t* h_fb_members = h_fb_chunks + n_fb;
+    for (int i = 0; i < n_seq; i++) {
+        h_rows[i] = seqs[i];
+        h_len[i] = kv_len[i];
+        h_first[i] = fam_of[i] >= 0 ? fams[fam_of[i]].shared_tokens / chunk : 0;
+    }
+    int k = 0;
+    for (const Fam& f : fams) {
+        const int sc = f.shared_tokens / chunk;
+        if (sc == 0) continue;
+        n_fam++;
+        for (int m0 = 0; m0 < f.count; m0 += per_block, k++) {
+            h_fb_row[k] = seqs[f.first];
+            h_fb_chunks[k] = sc;
+            const int nm = f.count - m0 < per_block ? f.count - m0 : per_block;
+            max_members = nm > max_members ? nm : max_members;
+            for (int i = 0; i < 16; i++) h_fb_members[16 * k + i] = i < nm ? f.first + m0 + i : -1;
+        }
+    }
+    const size_t ints = 3 * (size_t)n_seq + 18 * (size_t)n_fb;
+    e->plan_image.resize(ints);
+    if (e->has_device) {
+        const int b = e->plan_next;
+        if (e->plan_busy[b]) CUDA_TRY(cudaEventSynchronize(e->plan_done[b]));
+        if (ints > 0) {
+            memcpy(e->h_plan[b], e->plan_image.data(), ints * 4);
+            CUDA_TRY(cudaMemcpyAsync(e->d_plan, e->h_plan[b], ints * 4, cudaMemcpyHostToDevice, stream));
+        }
+        CUDA_TRY(cudaEventRecord(e->plan_done[b], stream));
+        e->plan_busy[b] = true;
+        e->plan_next ^= 1;
+    }
+
+    pl.n_seq = n_seq;
+    pl.n_fb = n_fb;
+    pl.n_fam = n_fam;
+    pl.chunk = chunk;
+    pl.max_chunks = (max_kv + chunk - 1) / chunk;
+    pl.rows_per_item = max_members * group;
+    pl.keys_seq = keys_seq;
+    planned_items(chunk, &pl.keys_plan);
+    pl.rows = e->d_plan;
+    pl.kv_len = e->d_plan + n_seq;
+    pl.first_chunk = e->d_plan + 2 * (size_t)n_seq;
+    pl.fb_row = e->d_plan + 3 * (size_t)n_seq;
+    pl.fb_chunks = pl.fb_row + n_fb;
+    pl.fb_members = pl.fb_chunks + n_fb;
+    pl.valid = true;
+    return DRKV_OK;
+}
+
+int drkv_plan_get_info(const drkv_engine* e, drkv_plan_info* out) {
+    NEED(e);
+    if (!out) return set_err(DRKV_ERR_INVALID, "null argument");
+    if (!e->plan.valid) return set_err(DRKV_ERR_INVALID, "no decode plan");
+    out->n_seq = e->plan.n_seq;
+    out->n_families = e->plan.n_fam;
+    out->n_blocks = e->plan.n_fb;
+    out->chunk_tokens = e->plan.chunk;
+    out->keys_per_sequence_pass = e->plan.keys_seq;
+    out->keys_planned_pass = e->plan.keys_plan;
+    return DRKV_OK;
+}
+
+int drkv_plan_dump(const drkv_engine* e, int32_t* out, int cap) {
+    NEED(e);
+    if (!e->plan.valid) return set_err(DRKV_ERR_INVALID, "no decode plan");
+    const int n = (int)e->plan_image.size();
+    if (out) memcpy(out, e->plan_image.data(), (size_t)(n < cap ? n : cap) * 4);
+    return n;
+}
+
+int drkv_attend_decode_planned(drkv_engine* e, int layer, const void* q, void* out, float scale, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (layer < 0 || layer >= e->geom.num_layers || !q || !out)
+        return set_err(DRKV_ERR_INVALID, "attend_decode_planned: bad argument");
+    const drkv_engine::Plan& pl = e->plan;
+    if (!pl.valid) return set_err(DRKV_ERR_INVALID, "attend_decode_planned: no decode plan");
+    if (pl.n_seq == 0 || pl.max_chunks == 0) return DRKV_OK;
+    return decode_common(e, layer, pl.n_seq, pl.rows, pl.kv_len, 0, 0, 0, pl.max_chunks * pl.chunk, q, out, nullptr,
+                         scale, (cudaStream_t)stream, &pl);
 }
 
 int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end, const void* q, float* part,

@@ -54,6 +54,14 @@ struct DecodeParams {
     int layer, max_pages, num_q_heads, num_kv_heads, group, page_size;
     int chunk_tokens, max_chunks;
     int n_seq;
+    // shared-prefix plan (all null / 0 without one): family block k covers chunks [0, fb_chunks[k]) of table
+    // row fb_row[k] for the batch entries fb_members[16 k + i] (-1 = none); sequence b starts at chunk
+    // seq_first_chunk[b].  rows_per_item: query rows a family block fills (members * group), else 0.
+    int n_fb, rows_per_item;
+    const int32_t* fb_row;
+    const int32_t* fb_chunks;
+    const int32_t* fb_members;
+    const int32_t* seq_first_chunk;
     int total_items;          // upper bound n_seq * num_kv_heads * max_chunks (sizes the grid)
     int* work_counter;        // device int, 0 at launch; the last warp to leave rewinds it
     int* exit_count;          // device int, 0 at launch: warps that have left

@@ -160,6 +160,27 @@ class PagedKVEngine:
     def attend_decode(self, layer, n_seq, d_rows, d_kv_len, max_kv_len, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_decode(self.h, layer, n_seq, _ptr(d_rows), _ptr(d_kv_len), max_kv_len, _ptr(q),
                                           _ptr(out), scale, _stream(stream)))
+    def plan_decode(self, seqs, kv_len, stream=None) -> dict:
+        """Shared-prefix plan for a decode batch (host lists); returns the plan's summary."""
+        n = len(seqs)
+        i32 = lambda v: (C.c_int32 * n)(*[int(x) for x in v])
+        check(self.lib.drkv_plan_decode(self.h, n, i32(seqs), i32(kv_len), _stream(stream)))
+        info = capi.PlanInfo()
+        check(self.lib.drkv_plan_get_info(self.h, C.byref(info)))
+        return {f: getattr(info, f) for f, _ in capi.PlanInfo._fields_}
+    def plan_dump(self) -> dict:
+        """The current plan's arrays (see drkv_plan_dump)."""
+        n = check(self.lib.drkv_plan_dump(self.h, None, 0))
+        buf = np.empty(n, dtype=np.int32)
+        check(self.lib.drkv_plan_dump(self.h, buf.ctypes.data_as(C.POINTER(C.c_int32)), n))
+        info = capi.PlanInfo()
+        check(self.lib.drkv_plan_get_info(self.h, C.byref(info)))
+        ns, nb = info.n_seq, info.n_blocks
+        return {"rows": buf[:ns], "kv_len": buf[ns:2 * ns], "first_chunk": buf[2 * ns:3 * ns],
+                "fb_row": buf[3 * ns:3 * ns + nb], "fb_chunks": buf[3 * ns + nb:3 * ns + 2 * nb],
+                "fb_members": buf[3 * ns + 2 * nb:].reshape(nb, 16)}
+    def attend_decode_planned(self, layer, q, out, scale, stream=None) -> None:
+        check(self.lib.drkv_attend_decode_planned(self.h, layer, _ptr(q), _ptr(out), scale, _stream(stream)))
     def attend_prefill_chunk(self, layer, seq, pos_start, m, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_prefill_chunk(self.h, layer, seq, pos_start, m, _ptr(q), _ptr(out), scale,
                                                  _stream(stream)))

@@ -212,6 +212,30 @@ DRKV_API int drkv_seq_inject(drkv_engine* e, int seq, int start_token, int num_t
 DRKV_API int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows,
                                 const int32_t* d_kv_len, int max_kv_len, const void* q, void* out,
                                 float scale, void* stream);
+/* Shared-prefix decode.  The reference's decode kernel (paged_attention.cu:179-282) walks every
+ * sequence's whole block table, so branches forked from one prompt (CacheManager block tables that
+ * start with the same page ids) each read the shared pages again.  A plan finds, among CONSECUTIVE
+ * batch entries, families whose host tables start with the same pages; the planned pass reads those
+ * pages once per 16 query rows of the family, and every sequence's remaining keys as before.  The
+ * result is the same attention (same partial/merge arithmetic, different grouping of rows).
+ * seqs / kv_len are HOST arrays of n_seq (<= 2048) entries; the plan is uploaded on `stream` and
+ * holds until the next call that changes a block table.  No counterpart in the reference. */
+typedef struct drkv_plan_info {
+    int32_t n_seq, n_families, n_blocks, chunk_tokens;
+    int64_t keys_per_sequence_pass; /* sum of kv_len: key positions an unplanned pass reads per kv head */
+    int64_t keys_planned_pass;      /* key positions the planned pass reads per kv head */
+} drkv_plan_info;
+DRKV_API int drkv_plan_decode(drkv_engine* e, int n_seq, const int32_t* seqs, const int32_t* kv_len,
+                              void* stream);
+DRKV_API int drkv_plan_get_info(const drkv_engine* e, drkv_plan_info* out);
+/* The plan as the kernel reads it, for inspection (works on an engine without a device; returns the
+ * number of ints): rows[n_seq], kv_len[n_seq], first_chunk[n_seq] (chunks of each sequence that its
+ * family's blocks cover), then per block: table row of the family's first member [n_blocks], shared
+ * chunks [n_blocks], batch indices of up to 16 members, -1 padded [n_blocks][16]. */
+DRKV_API int drkv_plan_dump(const drkv_engine* e, int32_t* out, int cap);
+/* q/out [n_seq][num_q_heads][head_dim] in the plan's batch order. */
+DRKV_API int drkv_attend_decode_planned(drkv_engine* e, int layer, const void* q, void* out,
+                                        float scale, void* stream);
 /* paged_prefill_attention_kernel (paged_attention.cu:465-554): q/out
  * [m][num_q_heads][head_dim]; token t attends keys 0..pos_start+t. */
 DRKV_API int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m,
