@@ -45,6 +45,14 @@ struct alignas(16) SlotMeta {
     int v_lo, v_hi, fam, pad1;      // keys [v_lo, v_hi) of the 16 in the slot are visible; fam: family block + 1 or 0
 };
 
+#ifdef DRKV_WARP_TRACE
+// Debug build only: per-warp timestamps (ns) of the last launch: start, first data, last item start, end, items.
+__device__ unsigned long long g_warp_trace[148 * 8][5];
+#define TRACE(i, v) do { if (lane == 0) g_warp_trace[blockIdx.x * WARPS + w][i] = (v); } while (0)
+#else
+#define TRACE(i, v) do { } while (0)
+#endif
+
 template <typename T>
 struct Mma;
 template <>
@@ -159,6 +167,11 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     }
     __syncthreads();
     const int total_items = cum[n_ent];
+    TRACE(0, global_timer());
+#ifdef DRKV_WARP_TRACE
+    unsigned long long trace_items = 0;
+    bool trace_first = true;
+#endif
 
     // ---- next-item prefetch state (warp-uniform except raw_next, which lane 0 owns) ----
     // n_state: 0 nothing requested, 1 queue index requested (atomic in flight), 2 decoded (length and
@@ -317,6 +330,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         }
         __syncwarp();
         const SlotMeta meta = metas[ring];
+#ifdef DRKV_WARP_TRACE
+        if (trace_first) { TRACE(1, global_timer()); trace_first = false; }
+        if (meta.flags & SLOT_FIRST) { TRACE(2, global_timer()); trace_items++; }
+#endif
         if (meta.flags & SLOT_FIRST) {
             // query rows straight into m16k16 A fragments.  Plain item: row r is query head r of the group;
             // family block: row r is head r % g of member r / g (several forked sequences share the keys).
@@ -475,6 +492,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             }
         }
     }
+#ifdef DRKV_WARP_TRACE
+    TRACE(3, global_timer());
+    TRACE(4, trace_items);
+#endif
     // The last warp of the grid to leave rewinds the work queue for the next launch on this stream.
     if (lane == 0) {
         __threadfence();
@@ -622,6 +643,12 @@ cudaError_t launch_decode_t(const CUtensorMap& tmap, const DecodeParams& p, int 
 }
 
 }  // namespace
+
+#ifdef DRKV_WARP_TRACE
+extern "C" __attribute__((visibility("default"))) int drkv_debug_warp_trace(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_warp_trace, sizeof(g_warp_trace));
+}
+#endif
 
 bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages, int num_kv_heads,
                           int page_size, int head_dim, const char** err) {
