@@ -176,6 +176,8 @@ def run_ours(args):
         pool[off:off + step_elems].normal_()
     if args.chunk:
         eng.set_chunk_tokens(args.chunk)
+    if args.scorer:
+        eng.scorer_enable(0.95)                         # per-page attention mass + score update ride along
 
     d_rows = torch.tensor(seqs, dtype=torch.int32, device=dev)
     d_pos = torch.from_numpy(lens).to(dev)
@@ -191,6 +193,8 @@ def run_ours(args):
         for l in range(L):
             eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
             eng.attend_decode(l, n_seq, d_rows, d_len, max_kv, q[l], out[l], scale, stream)
+        if args.scorer:
+            eng.scorer_step(stream)
 
     def barrier():
         if world > 1:
@@ -219,6 +223,8 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t.item()) / K
     launches = K * L * 3                               # append, attention, combine per layer
+    if args.scorer:
+        launches += K * (L + 1)                        # + page mass per layer, score update per step
 
     # ---- dominant kernel: per-launch duration from events around each launch ----
     eng.kernel_timing(True)
@@ -318,6 +324,7 @@ def run_ours(args):
             "config": {"workload": f"{args.workload}: {w['desc']}", "layers": L, "seqs_per_gpu": n_seq,
                        "sum_ctx": int(lens.sum()), "page": page, "pool_pages": max_pages,
                        "pool_gb": round(eng_bytes(max_pages, w) / 1e9, 2), "parallelism": f"dp{world}",
+                       "importance_scorer": bool(args.scorer),
                        "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer" % (kv_bytes / 1e9)},
             "tokens_per_s_per_gpu": n_seq / (ms_step * 1e-3),
             "hbm_gbs_step": all_bytes * L / (ms_step * 1e-3) / 1e9,
@@ -779,6 +786,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling a small case)")
     ap.add_argument("--seqs", type=int, default=0, help="override sequences per GPU (profiling a small case)")
     ap.add_argument("--chunk", type=int, default=0, help="keys per split-KV chunk (0 = automatic)")
+    ap.add_argument("--scorer", action="store_true", help="c2/c5b: also produce per-page attention mass and scores")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

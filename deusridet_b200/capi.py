@@ -97,6 +97,11 @@ SIGNATURES = {
     "drkv_plan_get_info": (_i, [_vp, C.POINTER(PlanInfo)]),
     "drkv_plan_dump": (_i, [_vp, _pi32, _i]),
     "drkv_attend_decode_planned": (_i, [_vp, _i, _vp, _vp, _f, _vp]),
+    "drkv_scorer_enable": (_i, [_vp, _f]),
+    "drkv_scorer_update": (_i, [_vp, _i, _vp, _i, _vp]),
+    "drkv_scorer_step": (_i, [_vp, _vp]),
+    "drkv_scorer_sync": (_i, [_vp, _vp]),
+    "drkv_scorer_scores": (_i, [_vp, _i, C.POINTER(C.c_float), _i]),
     "drkv_attend_prefill_chunk": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_attend_prefill_batch": (_i, [_vp, _i, _i, _pi32, _pi32, _pi32, C.POINTER(_vp), C.POINTER(_vp), _f, _vp]),
     "drkv_attend_partial": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),

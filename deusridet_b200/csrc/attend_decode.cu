@@ -42,7 +42,8 @@ enum SlotFlags : int { SLOT_FIRST = 1, SLOT_LAST = 2, SLOT_SKIP = 4, SLOT_DONE =
 // What the producer tells a consumer warp about one ring slot.
 struct alignas(16) SlotMeta {
     int b, kvh, part_slot, flags;   // part_slot: index of the partial of query row 0 of the group
-    int v_lo, v_hi, fam, pad1;      // keys [v_lo, v_hi) of the 16 in the slot are visible; fam: family block + 1 or 0
+    int v_lo, v_hi, fam, tile;      // keys [v_lo, v_hi) of the 16 in the slot are visible; fam: family block + 1 or 0;
+                                    // tile: index of the 16-key group within the sequence
 };
 
 #ifdef DRKV_WARP_TRACE
@@ -191,6 +192,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     int i_slot = 0, outstanding = 0;
     // ---- compute cursor ----
     int slot = 0, phase = 0;
+    int mass_row[2] = {-1, -1};     // with tile masses on: this lane's query rows as (sequence, head) indices, -1 = padding
     const int64_t rows_per_plane = (int64_t)p.num_kv_heads * p.page_size;
 
     // The first item of every warp is its own index in the grid (no atomic on the way to the first
@@ -281,7 +283,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 m.v_lo = max(0, p.kv_begin - tok0);
                 m.v_hi = min(kGroupTokens, c_kv_end - tok0);
                 m.fam = c_fam;
-                m.pad1 = 0;
+                m.tile = tok0 / kGroupTokens;
                 metas[ring] = m;
                 // earlier generic-proxy accesses to this slot (ldmatrix reads, zero fill) are ordered
                 // before the async-proxy writes of the new gather
@@ -352,6 +354,11 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 if (b0 >= 0) qr0 = qall + ((int64_t)b0 * p.num_q_heads + (int64_t)meta.kvh * p.group + qrow % p.group) * D;
                 if (b1 >= 0) qr1 = qall + ((int64_t)b1 * p.num_q_heads + (int64_t)meta.kvh * p.group + (qrow + 8) % p.group) * D;
             }
+            if (p.tile_lse != nullptr) {
+                const int64_t per_row = (int64_t)D;
+                mass_row[0] = qr0 ? (int)((qr0 - qall) / per_row) : -1;
+                mass_row[1] = qr1 ? (int)((qr1 - qall) / per_row) : -1;
+            }
             const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qr0 + col);
             const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qr1 + col);
 #pragma unroll
@@ -417,6 +424,15 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 const float p0 = fast_exp2(x0 - mnew), p1 = fast_exp2(x1 - mnew);
                 const float p8 = fast_exp2(x8 - mnew), p9 = fast_exp2(x9 - mnew);
                 lsum[r] = lsum[r] * alpha[r] + ((p0 + p1) + (p8 + p9));
+                if (p.tile_lse != nullptr) {
+                    // log2 of this tile's un-normalised probability mass for the row, on the scale of the
+                    // final log-sum-exp: mass share = 2^(tile_lse - lse2) once the merge knows lse2
+                    float ts = (p0 + p1) + (p8 + p9);
+                    ts += __shfl_xor_sync(0xffffffffu, ts, 1);
+                    ts += __shfl_xor_sync(0xffffffffu, ts, 2);
+                    if ((lane & 3) == 0 && mass_row[r] >= 0)
+                        p.tile_lse[(int64_t)mass_row[r] * p.max_tiles + meta.tile] = ts > 0.f ? mnew + __log2f(ts) : -INFINITY;
+                }
                 split_pack<T>(p0, p1, phi[r], plo[r]);          // a0 (r=0) / a1 (r=1)
                 split_pack<T>(p8, p9, phi[2 + r], plo[2 + r]);  // a2 / a3
             }
@@ -453,6 +469,11 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     }
                 }
             }
+        }
+        else if (p.tile_lse != nullptr && (lane & 3) == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; r++)
+                if (mass_row[r] >= 0) p.tile_lse[(int64_t)mass_row[r] * p.max_tiles + meta.tile] = -INFINITY;
         }
         __syncwarp();                                  // every lane is done with the slot's shared memory
         outstanding--;
@@ -582,10 +603,54 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
             reinterpret_cast<T*>(p.out)[((int64_t)b * p.num_q_heads + h) * D + d] = Elem<T>::from_f(acc / lt);
         }
     }
+    if (p.lse2_out != nullptr && threadIdx.x == 0)
+        p.lse2_out[(int64_t)b * p.num_q_heads + h] = lt > 0.f ? mmax * kLog2e + __log2f(lt) : INFINITY;
     if (p.out_partial != nullptr && threadIdx.x == 0) {
         p.out_partial[(int64_t)p.num_q_heads * D + h] = lt > 0.f ? mmax : -1.0e20f;
         p.out_partial[(int64_t)p.num_q_heads * (D + 1) + h] = lt > 0.f ? lt : 0.f;
     }
+}
+
+// Attention mass per page, the importance scorer's input (importance_scorer.h:8-15: "accumulates
+// per-block attention weights across all Full Attention layers"): new[row][page] += sum over query
+// heads and the page's keys of the softmax probability.  One thread per (sequence, page); a warp's
+// lanes take consecutive pages, so the tile values of one head are read contiguously.
+__global__ void __launch_bounds__(128) page_mass_kernel(const PageMassParams p) {
+    pdl_wait();                                          // tile values and lse2 come from the two preceding kernels
+    pdl_launch_dependents();
+    const int b = blockIdx.y;
+    const int page = blockIdx.x * blockDim.x + threadIdx.x;
+    const int kv_end = p.kv_len[b];
+    const int tiles_per_page = p.page_size / kGroupTokens;
+    const int n_tiles = (kv_end + kGroupTokens - 1) / kGroupTokens;
+    if (page * tiles_per_page >= n_tiles) return;
+    const int t1 = min((page + 1) * tiles_per_page, n_tiles);
+    float mass = 0.f;
+    for (int h = 0; h < p.num_q_heads; h++) {
+        const float lse2 = p.lse2[(int64_t)b * p.num_q_heads + h];
+        const float* row = p.tile_lse + ((int64_t)b * p.num_q_heads + h) * p.max_tiles;
+        for (int t = page * tiles_per_page; t < t1; t++) mass += fast_exp2(row[t] - lse2);
+    }
+    float* dst = p.fresh + (int64_t)p.rows[b] * p.table_stride + page;
+    *dst += mass;
+}
+
+// score = score * decay + new, then new = 0 (importance_scorer.cu:27-37, one fused multiply-add).
+__global__ void importance_update_kernel(float* scores, float* fresh, int64_t n, float decay) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    scores[i] = __fmaf_rn(scores[i], decay, fresh[i]);
+    fresh[i] = 0.f;
+}
+
+// ImportanceScorer::update with caller-provided values (importance_scorer.cu:27-37,68-73).
+__global__ void importance_add_kernel(float* scores, const float* new_scores, int n, float decay) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) scores[i] = __fmaf_rn(scores[i], decay, new_scores[i]);
 }
 
 // Merge of whole-range partials in the external layout [Hq*D o | Hq m | Hq l] per part, in the
@@ -705,6 +770,23 @@ cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p,
         default:
             return cudaErrorInvalidValue;
     }
+}
+
+cudaError_t launch_page_mass(const PageMassParams& p, int n_seq, int max_kv_len, cudaStream_t stream) {
+    const int pages = (max_kv_len + p.page_size - 1) / p.page_size;
+    if (pages <= 0 || n_seq <= 0) return cudaSuccess;
+    return launch_pdl(page_mass_kernel, dim3((pages + 127) / 128, n_seq), dim3(128), 0, stream, p);
+}
+
+cudaError_t launch_importance_update(float* scores, float* fresh, int64_t n, float decay, cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    return launch_pdl(importance_update_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, scores, fresh,
+                      n, decay);
+}
+
+cudaError_t launch_importance_add(float* scores, const float* new_scores, int n, float decay, cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    return launch_pdl(importance_add_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, scores, new_scores, n, decay);
 }
 
 cudaError_t launch_combine(const CombineParams& p, int n_seq, int dtype, cudaStream_t stream) {

@@ -145,6 +145,19 @@ struct drkv_engine {
     cudaEvent_t plan_done[2] = {nullptr, nullptr};
     bool plan_busy[2] = {false, false};
     int plan_next = 0;
+
+    // importance scorer (off until drkv_scorer_enable): scores per (sequence row, logical page)
+    struct Scorer {
+        bool on = false;
+        float decay = 0.95f;
+        std::vector<float> h_scores;                 // host mirror [max_seqs][row_width], what eviction reads
+        float* d_scores = nullptr;                   // running scores
+        float* d_fresh = nullptr;                    // attention mass accumulated since the last step
+        float* d_tile_lse = nullptr;                 // decode kernel's per-tile values of one launch
+        float* d_lse2 = nullptr;                     // merge kernel's log-sum-exp per (sequence, head)
+        int max_tiles = 0;
+        std::vector<std::pair<int, int>> pending;    // rows to reset (src = -1) or copy from src, at the next stream call
+    } scorer;
 };
 
 // ints of a plan: rows, kv_len, first_chunk per sequence; row, chunks and 16 members per family block
@@ -281,6 +294,10 @@ void drkv_destroy(drkv_engine* e) {
         cudaFree(e->d_error);
         cudaFree(e->d_scratch);
         cudaFree(e->d_plan);
+        cudaFree(e->scorer.d_scores);
+        cudaFree(e->scorer.d_fresh);
+        cudaFree(e->scorer.d_tile_lse);
+        cudaFree(e->scorer.d_lse2);
         for (int i = 0; i < 2; i++) {
             if (e->h_plan[i]) cudaFreeHost(e->h_plan[i]);
             if (e->plan_done[i]) cudaEventDestroy(e->plan_done[i]);
@@ -349,10 +366,43 @@ size_t drkv_pool_v_offset(const drkv_engine* e, int layer, int page) {
 }
 
 // ---- sequences --------------------------------------------------------------------------
+// A new row starts with zero scores, a fork with its parent's: the host mirror now, the device at
+// the next scorer call that carries a stream.
+static void scorer_new_row(drkv_engine* e, int row, int src) {
+    if (!e->scorer.on || row < 0) return;
+    const size_t w = (size_t)e->book.row_width();
+    float* dst = e->scorer.h_scores.data() + (size_t)row * w;
+    if (src >= 0)
+        memcpy(dst, e->scorer.h_scores.data() + (size_t)src * w, w * sizeof(float));
+    else
+        memset(dst, 0, w * sizeof(float));
+    e->scorer.pending.push_back({row, src});
+}
+
+static int scorer_flush_pending(drkv_engine* e, cudaStream_t stream) {
+    if (!e->has_device) {
+        e->scorer.pending.clear();
+        return DRKV_OK;
+    }
+    const size_t w = (size_t)e->book.row_width();
+    for (const auto& pr : e->scorer.pending) {
+        float* dst = e->scorer.d_scores + (size_t)pr.first * w;
+        if (pr.second >= 0)
+            CUDA_TRY(cudaMemcpyAsync(dst, e->scorer.d_scores + (size_t)pr.second * w, w * 4, cudaMemcpyDeviceToDevice, stream));
+        else
+            CUDA_TRY(cudaMemsetAsync(dst, 0, w * 4, stream));
+        CUDA_TRY(cudaMemsetAsync(e->scorer.d_fresh + (size_t)pr.first * w, 0, w * 4, stream));
+    }
+    e->scorer.pending.clear();
+    return DRKV_OK;
+}
+
 int drkv_seq_create(drkv_engine* e) {
     NEED(e);
     LOCK(e);
-    return book_err(e, e->book.seq_create());
+    const int row = book_err(e, e->book.seq_create());
+    scorer_new_row(e, row, -1);
+    return row;
 }
 int drkv_seq_release(drkv_engine* e, int seq, int discard) {
     NEED(e);
@@ -362,7 +412,9 @@ int drkv_seq_release(drkv_engine* e, int seq, int discard) {
 int drkv_seq_fork(drkv_engine* e, int parent) {
     NEED(e);
     LOCK(e);
-    return book_err(e, e->book.seq_fork(parent));
+    const int row = book_err(e, e->book.seq_fork(parent));
+    scorer_new_row(e, row, parent);
+    return row;
 }
 int drkv_seq_ensure_pos(drkv_engine* e, int seq, int pos, void* stream) {
     NEED(e);
@@ -714,6 +766,13 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
         p.fb_members = plan->fb_members;
         p.seq_first_chunk = plan->first_chunk;
     }
+    const bool scored = e->scorer.on && d_rows != nullptr && out_partial == nullptr;
+    if (scored) {
+        int rc = scorer_flush_pending(e, stream);
+        if (rc != DRKV_OK) return rc;
+        p.tile_lse = e->scorer.d_tile_lse;
+        p.max_tiles = e->scorer.max_tiles;
+    }
     p.work_counter = e->d_work;
     p.exit_count = e->d_exit;
     p.scale_log2 = scale * 1.4426950408889634f;
@@ -739,7 +798,21 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     c.max_chunks = max_chunks;
     c.out = out;
     c.out_partial = out_partial;
+    c.lse2_out = scored ? e->scorer.d_lse2 : nullptr;
     CUDA_TRY(launch_combine(c, n_seq, g.dtype, stream));
+    if (scored) {
+        PageMassParams pm{};
+        pm.tile_lse = e->scorer.d_tile_lse;
+        pm.lse2 = e->scorer.d_lse2;
+        pm.rows = d_rows;
+        pm.kv_len = d_kv_len;
+        pm.fresh = e->scorer.d_fresh;
+        pm.num_q_heads = g.num_q_heads;
+        pm.max_tiles = e->scorer.max_tiles;
+        pm.page_size = g.page_size;
+        pm.table_stride = e->book.row_width();
+        CUDA_TRY(launch_page_mass(pm, n_seq, max_span, stream));
+    }
     return DRKV_OK;
 }
 
@@ -931,6 +1004,89 @@ int drkv_attend_decode_planned(drkv_engine* e, int layer, const void* q, void* o
     if (pl.n_seq == 0 || pl.max_chunks == 0) return DRKV_OK;
     return decode_common(e, layer, pl.n_seq, pl.rows, pl.kv_len, 0, 0, 0, pl.max_chunks * pl.chunk, q, out, nullptr,
                          scale, (cudaStream_t)stream, &pl);
+}
+
+// ---- importance scorer ---------------------------------------------------------------------
+int drkv_scorer_enable(drkv_engine* e, float decay) {
+    NEED(e);
+    LOCK(e);
+    drkv_engine::Scorer& sc = e->scorer;
+    if (!(decay >= 0.f)) {                               // negative: detach; eviction is oldest-first again
+        sc.on = false;
+        e->book.attach_scores(nullptr);
+        return DRKV_OK;
+    }
+    const size_t n = (size_t)e->book.max_seqs() * e->book.row_width();
+    sc.decay = decay;
+    if (sc.h_scores.size() != n) sc.h_scores.assign(n, 0.f);
+    if (e->has_device && sc.d_scores == nullptr) {
+        const drkv_geometry& g = e->geom;
+        sc.max_tiles = e->book.row_width() * (g.page_size / 16);
+        const size_t launch_seqs = e->book.max_seqs() < kMaxDecodeSeqs ? e->book.max_seqs() : kMaxDecodeSeqs;
+        CUDA_TRY(cudaMalloc(&sc.d_scores, n * 4));
+        CUDA_TRY(cudaMalloc(&sc.d_fresh, n * 4));
+        CUDA_TRY(cudaMalloc(&sc.d_tile_lse, launch_seqs * g.num_q_heads * sc.max_tiles * 4));
+        CUDA_TRY(cudaMalloc(&sc.d_lse2, launch_seqs * g.num_q_heads * 4));
+        CUDA_TRY(cudaMemset(sc.d_scores, 0, n * 4));     // importance_scorer.cu:57
+        CUDA_TRY(cudaMemset(sc.d_fresh, 0, n * 4));
+    }
+    sc.on = true;
+    e->book.attach_scores(sc.h_scores.data());
+    return DRKV_OK;
+}
+
+int drkv_scorer_update(drkv_engine* e, int seq, const float* new_scores, int num_blocks, void* stream) {
+    NEED(e);
+    LOCK(e);
+    if (!e->scorer.on) return set_err(DRKV_ERR_STATE, "scorer_update: the scorer is not enabled");
+    if (seq < 0 || seq >= e->book.max_seqs() || num_blocks < 0 || num_blocks > e->book.row_width() ||
+        (num_blocks > 0 && !new_scores))
+        return set_err(DRKV_ERR_INVALID, "scorer_update: bad argument");
+    const size_t off = (size_t)seq * e->book.row_width();
+    if (!e->has_device) {
+        float* row = e->scorer.h_scores.data() + off;
+        for (int i = 0; i < num_blocks; i++) row[i] = fmaf(row[i], e->scorer.decay, new_scores[i]);
+        return DRKV_OK;
+    }
+    int rc = scorer_flush_pending(e, (cudaStream_t)stream);
+    if (rc != DRKV_OK) return rc;
+    CUDA_TRY(launch_importance_add(e->scorer.d_scores + off, new_scores, num_blocks, e->scorer.decay, (cudaStream_t)stream));
+    return DRKV_OK;
+}
+
+int drkv_scorer_step(drkv_engine* e, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    LOCK(e);
+    if (!e->scorer.on) return set_err(DRKV_ERR_STATE, "scorer_step: the scorer is not enabled");
+    int rc = scorer_flush_pending(e, (cudaStream_t)stream);
+    if (rc != DRKV_OK) return rc;
+    const int64_t n = (int64_t)e->book.max_seqs() * e->book.row_width();
+    CUDA_TRY(launch_importance_update(e->scorer.d_scores, e->scorer.d_fresh, n, e->scorer.decay, (cudaStream_t)stream));
+    return DRKV_OK;
+}
+
+int drkv_scorer_sync(drkv_engine* e, void* stream) {
+    NEED(e);
+    LOCK(e);
+    if (!e->scorer.on) return set_err(DRKV_ERR_STATE, "scorer_sync: the scorer is not enabled");
+    if (!e->has_device) return DRKV_OK;
+    int rc = scorer_flush_pending(e, (cudaStream_t)stream);
+    if (rc != DRKV_OK) return rc;
+    CUDA_TRY(cudaMemcpyAsync(e->scorer.h_scores.data(), e->scorer.d_scores, e->scorer.h_scores.size() * 4,
+                             cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));   // importance_scorer.cu:91-96 is synchronous too
+    return DRKV_OK;
+}
+
+int drkv_scorer_scores(const drkv_engine* e, int seq, float* out, int cap) {
+    NEED(e);
+    if (!e->scorer.on) return set_err(DRKV_ERR_STATE, "scorer_scores: the scorer is not enabled");
+    if (seq < 0 || seq >= e->book.max_seqs() || !out || cap < 0) return set_err(DRKV_ERR_INVALID, "scorer_scores: bad argument");
+    const int w = e->book.row_width();
+    const int n = cap < w ? cap : w;
+    memcpy(out, e->scorer.h_scores.data() + (size_t)seq * w, (size_t)n * 4);
+    return n;
 }
 
 int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end, const void* q, float* part,

@@ -62,6 +62,9 @@ struct DecodeParams {
     const int32_t* fb_chunks;
     const int32_t* fb_members;
     const int32_t* seq_first_chunk;
+    // tile masses for the importance scorer (null = off): tile_lse[(seq * Hq + head) * max_tiles + tile]
+    float* tile_lse;
+    int max_tiles;
     int total_items;          // upper bound n_seq * num_kv_heads * max_chunks (sizes the grid)
     int* work_counter;        // device int, 0 at launch; the last warp to leave rewinds it
     int* exit_count;          // device int, 0 at launch: warps that have left
@@ -92,7 +95,21 @@ struct CombineParams {
     int num_q_heads, head_dim, chunk_tokens, max_chunks;
     void* out;                // storage type [n_seq][Hq][D] (normalised) ...
     float* out_partial;       // ... or fp32 partial [Hq*D | Hq m | Hq l] when non-null
+    float* lse2_out;          // optional [n_seq][Hq]: log2 of the softmax denominator on the kernel's score scale
 };
+
+// Importance scorer: per-page attention mass from the decode kernel's tile values.
+struct PageMassParams {
+    const float* tile_lse;    // [(seq * Hq + head) * max_tiles + tile]
+    const float* lse2;        // [n_seq][Hq]
+    const int32_t* rows;      // [n_seq] table rows
+    const int32_t* kv_len;    // [n_seq]
+    float* fresh;             // [max_seqs][table_stride] accumulator of new scores
+    int num_q_heads, max_tiles, page_size, table_stride;
+};
+cudaError_t launch_page_mass(const PageMassParams& p, int n_seq, int max_kv_len, cudaStream_t stream);
+cudaError_t launch_importance_update(float* scores, float* fresh, int64_t n, float decay, cudaStream_t stream);
+cudaError_t launch_importance_add(float* scores, const float* new_scores, int n, float decay, cudaStream_t stream);
 
 cudaError_t launch_append_rope(const AppendParams& p, int n_tokens, int dtype, cudaStream_t stream);
 cudaError_t launch_cow_copy(const CowParams& p, int num_layers, cudaStream_t stream);

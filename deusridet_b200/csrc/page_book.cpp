@@ -88,6 +88,27 @@ int PageBook::evict_cached(int n) {
 
 bool PageBook::evict_one_of(int seq) {
     Seq& s = seqs_[seq];
+    if (scores_ != nullptr) {
+        const float* sc = scores_ + (size_t)seq * row_width_;
+        auto best = s.alloc_order.end();
+        for (auto it = s.alloc_order.begin(); it != s.alloc_order.end(); ++it) {
+            const int page = s.table[*it];
+            if (page < 0 || refcount_[page] > 1) continue;   // not resident / shared: not a candidate
+            if (best == s.alloc_order.end() || sc[*it] < sc[*best]) best = it;   // strict <: first minimum
+        }
+        if (best != s.alloc_order.end()) {
+            const int idx = *best, page = s.table[idx];
+            s.alloc_order.erase(best);
+            refcount_[page] = 0;
+            state_[page] = PageState::FREE;
+            free_stack_.push_back(page);
+            s.table[idx] = -1;
+            mark_dirty(s, idx);
+            evict_log_.push_back({1, seq, idx, page});
+            n_evict_stream++;
+            return true;
+        }
+    }
     for (auto it = s.alloc_order.begin(); it != s.alloc_order.end();) {
         int idx = *it;
         int page = s.table[idx];

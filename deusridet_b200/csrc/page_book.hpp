@@ -78,6 +78,12 @@ public:
     int seq_evict(int seq, int n);
     int evict_cached(int n);
     int ensure_free(int seq, int n_free);
+    // Importance-guided victims (cache_manager.cpp:185-205 with importance_scorer.cu:75-87): with
+    // scores attached, a sequence's victim is the resident, unshared entry of its allocation order
+    // with the lowest score, the first one on ties; without candidates the oldest-first walk applies.
+    // `scores` is a [max_seqs][row_width] host array the caller keeps alive; nullptr detaches.
+    void attach_scores(const float* scores) { scores_ = scores; }
+    bool scores_attached() const { return scores_ != nullptr; }
 
     // ---- inspection ----
     const std::vector<int32_t>& refcounts() const { return refcount_; }
@@ -106,6 +112,7 @@ private:
     std::vector<Seq> seqs_;
     std::vector<EvictRecord> evict_log_;
     std::string err_;
+    const float* scores_ = nullptr;
 
     int fail(int code, const std::string& msg) {
         err_ = msg;

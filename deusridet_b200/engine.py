@@ -181,6 +181,22 @@ class PagedKVEngine:
                 "fb_members": buf[3 * ns + 2 * nb:].reshape(nb, 16)}
     def attend_decode_planned(self, layer, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_decode_planned(self.h, layer, _ptr(q), _ptr(out), scale, _stream(stream)))
+    # ---- importance scorer (ImportanceScorer + CacheManager::pick_eviction_candidate) ----------
+    def scorer_enable(self, decay: float = 0.95) -> None: check(self.lib.drkv_scorer_enable(self.h, decay))
+    def scorer_disable(self) -> None: check(self.lib.drkv_scorer_enable(self.h, -1.0))
+    def scorer_update(self, seq: int, new_scores, stream=None) -> None:
+        """ImportanceScorer::update: a device tensor on a device engine, a float32 array on one without."""
+        if isinstance(new_scores, np.ndarray):
+            arr = np.ascontiguousarray(new_scores, dtype=np.float32)
+            check(self.lib.drkv_scorer_update(self.h, seq, arr.ctypes.data, len(arr), _stream(stream)))
+        else:
+            check(self.lib.drkv_scorer_update(self.h, seq, _ptr(new_scores), new_scores.numel(), _stream(stream)))
+    def scorer_step(self, stream=None) -> None: check(self.lib.drkv_scorer_step(self.h, _stream(stream)))
+    def scorer_sync(self, stream=None) -> None: check(self.lib.drkv_scorer_sync(self.h, _stream(stream)))
+    def scorer_scores(self, seq: int) -> np.ndarray:
+        out = np.empty(self.table_stride(), dtype=np.float32)
+        n = check(self.lib.drkv_scorer_scores(self.h, seq, out.ctypes.data_as(C.POINTER(C.c_float)), len(out)))
+        return out[:n]
     def attend_prefill_chunk(self, layer, seq, pos_start, m, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_prefill_chunk(self.h, layer, seq, pos_start, m, _ptr(q), _ptr(out), scale,
                                                  _stream(stream)))

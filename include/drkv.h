@@ -236,6 +236,28 @@ DRKV_API int drkv_plan_dump(const drkv_engine* e, int32_t* out, int cap);
 /* q/out [n_seq][num_q_heads][head_dim] in the plan's batch order. */
 DRKV_API int drkv_attend_decode_planned(drkv_engine* e, int layer, const void* q, void* out,
                                         float scale, void* stream);
+/* ---- importance-guided eviction ------------------------------------------------------------
+ * ImportanceScorer (importance_scorer.h:25-67, importance_scorer.cu:27-99) attached to the eviction
+ * policy (cache_manager.cpp:185-205): one fp32 score per (sequence, logical page), updated as
+ * score = score * decay + new, copied to a host mirror on request; a sequence's victim becomes the
+ * resident, unshared page with the lowest mirrored score (the first such in allocation order)
+ * instead of its oldest.  The reference never produces `new` (no caller of update()); here
+ * drkv_attend_decode and drkv_attend_decode_planned accumulate, while the scorer is enabled, the
+ * softmax probability mass each page received, summed over query heads and layers ("per-block
+ * attention weights across all Full Attention layers", importance_scorer.h:8-10), and
+ * drkv_scorer_step folds that into the scores once per token. */
+/* ImportanceScorer::init: decay >= 0 enables (scores start at 0), decay < 0 detaches. */
+DRKV_API int drkv_scorer_enable(drkv_engine* e, float decay);
+/* ImportanceScorer::update for the first num_blocks logical pages of one sequence with values the
+ * caller provides: a device pointer on an engine with a device, a host pointer on one without. */
+DRKV_API int drkv_scorer_update(drkv_engine* e, int seq, const float* new_scores, int num_blocks, void* stream);
+/* score = score * decay + accumulated attention mass, for every sequence; the accumulator restarts. */
+DRKV_API int drkv_scorer_step(drkv_engine* e, void* stream);
+/* ImportanceScorer::sync_to_host: device scores to the host mirror eviction reads; synchronises the stream. */
+DRKV_API int drkv_scorer_sync(drkv_engine* e, void* stream);
+/* ImportanceScorer::score for a whole sequence: the mirrored scores of its logical pages; returns the count. */
+DRKV_API int drkv_scorer_scores(const drkv_engine* e, int seq, float* out, int cap);
+
 /* paged_prefill_attention_kernel (paged_attention.cu:465-554): q/out
  * [m][num_q_heads][head_dim]; token t attends keys 0..pos_start+t. */
 DRKV_API int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m,

@@ -45,6 +45,7 @@ class BookModel:
         self.log: List[Tuple[int, int, int, int]] = []          # (kind, seq, logical, page)
         self.cow: List[Tuple[int, int, int]] = []               # (src, dst, valid slots) device copies
         self.n_cow = 0                                          # pages replaced, with or without a copy
+        self.scores = None                                      # {seq: [float per logical page]} once a scorer is attached
 
     # ---- pool ---------------------------------------------------------------------------
     def pool_alloc(self) -> int:
@@ -87,6 +88,25 @@ class BookModel:
 
     def _evict_one_of(self, s: int) -> bool:
         seq = self.seqs[s]
+        if self.scores is not None:
+            # cache_manager.cpp:185-205 + importance_scorer.cu:75-87: lowest score among the resident
+            # (and here: unshared) entries, first minimum in allocation order
+            best = -1
+            for i, idx in enumerate(seq.order):
+                p = seq.table[idx]
+                if p < 0 or self.ref[p] > 1:
+                    continue
+                if best < 0 or self.scores[s][idx] < self.scores[s][seq.order[best]]:
+                    best = i
+            if best >= 0:
+                idx = seq.order[best]
+                p = seq.table[idx]
+                del seq.order[best]
+                self.ref[p], self.state[p] = 0, FREE
+                self.free.append(p)
+                seq.table[idx] = -1
+                self.log.append((1, s, idx, p))
+                return True
         i = 0
         while i < len(seq.order):
             idx = seq.order[i]

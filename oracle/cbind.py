@@ -115,6 +115,21 @@ def attend_decode_f64(g: Geom, pool, max_pages, tables, rows, kv_len, layer, q, 
     return out
 
 
+def page_mass(g: Geom, pool, max_pages, tables, rows, kv_len, layer, q, mass, scale):
+    """Adds the layer's attention mass per (batch entry, logical page) to `mass` (float64 [n_seq][stride])."""
+    tables = _i32(tables)
+    rows, kv_len = _i32(rows), _i32(kv_len)
+    assert mass.dtype == np.float64 and mass.flags.c_contiguous
+    lib().okv_page_mass(C.byref(g), _p(pool), max_pages, _p(tables), tables.shape[-1], _p(rows), _p(kv_len), len(rows),
+                        layer, _p(q), _p(mass), mass.shape[-1], C.c_float(scale))
+
+
+def importance_update(scores: np.ndarray, fresh: np.ndarray, decay: float) -> None:
+    assert scores.dtype == np.float32 and fresh.dtype == np.float32 and scores.flags.c_contiguous
+    fresh = np.ascontiguousarray(fresh)
+    lib().okv_importance_update(_p(scores), _p(fresh), scores.size, C.c_float(decay))
+
+
 def attend_prefill(g: Geom, pool, max_pages, table, layer, pos_start, m, q, out, scale):
     lib().okv_attend_prefill(C.byref(g), _p(pool), max_pages, _p(_i32(table)), layer, pos_start, m, _p(q), _p(out),
                              C.c_float(scale))

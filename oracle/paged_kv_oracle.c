@@ -303,6 +303,48 @@ void okv_attend_decode_f64(const okv_geom* g, const uint16_t* pool, int max_page
     }
 }
 
+/* Attention mass per logical page, the input the importance scorer is declared for
+ * (src/memoria/importance_scorer.h:8-15: per-block attention weights accumulated across layers; the
+ * reference has no producer, so the definition is this build's): mass[b][j] += sum over query heads h
+ * and keys t of page j of softmax_t(scale * q_h . k_t), in fp64.  mass [n_seq][mass_stride], added to. */
+void okv_page_mass(const okv_geom* g, const uint16_t* pool, int max_pages, const int32_t* tables, int table_stride,
+                   const int32_t* rows, const int32_t* kv_len, int n_seq, int layer, const uint16_t* q,
+                   double* mass, int mass_stride, float scale) {
+    int Hq = g->num_q_heads, D = g->head_dim, group = g->num_q_heads / g->num_kv_heads, P = g->page_size;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int b = 0; b < n_seq; b++) {
+        const int32_t* table = tables + (int64_t)rows[b] * table_stride;
+        int n = kv_len[b];
+        double* s = (double*)malloc(sizeof(double) * (size_t)(n > 0 ? n : 1));
+        for (int h = 0; h < Hq; h++) {
+            const uint16_t* qr = q + ((int64_t)b * Hq + h) * D;
+            int kvh = h / group;
+            double mx = -1e300, l = 0;
+            for (int t = 0; t < n; t++) {
+                int page = table[t / P];
+                if (page < 0) { s[t] = -1e300; continue; }
+                const uint16_t* k = pool + pool_row(g, max_pages, layer, page, 0, kvh, t % P);
+                double dot = 0;
+                for (int d = 0; d < D; d++) dot += (double)st_to_f(qr[d], g->dtype) * (double)st_to_f(k[d], g->dtype);
+                s[t] = dot * (double)scale;
+                if (s[t] > mx) mx = s[t];
+            }
+            for (int t = 0; t < n; t++)
+                if (table[t / P] >= 0) l += exp(s[t] - mx);
+            if (!(l > 0)) continue;
+            for (int t = 0; t < n; t++)
+                if (table[t / P] >= 0) mass[(int64_t)b * mass_stride + t / P] += exp(s[t] - mx) / l;
+        }
+        free(s);
+    }
+}
+
+/* ImportanceScorer::update's arithmetic (src/memoria/importance_scorer.cu:27-37): the device compiler
+ * contracts scores[b] * decay + new_scores[b] into one fused multiply-add. */
+void okv_importance_update(float* scores, const float* fresh, int n, float decay) {
+    for (int i = 0; i < n; i++) scores[i] = fmaf(scores[i], decay, fresh[i]);
+}
+
 /* Chunked-prefill attention — src/machina/paged_attention.cu:465-554: q/out [m][Hq][D]; token t
  * of the chunk sees causal_len = pos_start + t + 1 keys; same recurrence. */
 void okv_attend_prefill(const okv_geom* g, const uint16_t* pool, int max_pages, const int32_t* table, int layer,

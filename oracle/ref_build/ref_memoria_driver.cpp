@@ -64,6 +64,32 @@ void* ref_cm_create(int num_fa_layers, int n_pages, int block_size) {
     return c;
 }
 void ref_cm_destroy(void* h) { delete (CacheManager*)h; }
+
+// CacheManager with the reference's ImportanceScorer attached (cache_manager.h:67-71; the manager
+// borrows the scorer).  One handle owns both.
+struct ScoredManager {
+    ImportanceScorer scorer;
+    CacheManager cm;
+};
+void* ref_scored_create(int num_fa_layers, int n_pages, int block_size, float decay, void** cm_out) {
+    ScoredManager* s = new ScoredManager();
+    if (!s->scorer.init(2 * n_pages, decay) ||
+        !s->cm.init(budget_for(num_fa_layers, n_pages, block_size), "", block_size, nullptr, &s->scorer)) {
+        delete s;
+        return nullptr;
+    }
+    *cm_out = &s->cm;
+    return s;
+}
+void ref_scored_destroy(void* h) { delete (ScoredManager*)h; }
+// ImportanceScorer::update followed by sync_to_host, the sequence a caller needs before the policy
+// sees new values.  new_scores is "device" memory of the stub runtime, i.e. host memory.
+void ref_scored_update(void* h, const float* new_scores, int n) {
+    ScoredManager* s = (ScoredManager*)h;
+    s->scorer.update(new_scores, n);
+    s->scorer.sync_to_host();
+}
+float ref_scored_score(void* h, int idx) { return ((ScoredManager*)h)->scorer.score(idx); }
 int ref_cm_ensure(void* h, int pos) { return ((CacheManager*)h)->ensure_blocks_for(pos) ? 1 : 0; }
 int ref_cm_ensure_range(void* h, int pos, int m) {
     return ((CacheManager*)h)->ensure_blocks_for_range(pos, m) ? 1 : 0;

@@ -4,6 +4,7 @@
 #include "machina/layer.h"
 #include "machina/model.h"
 #include "machina/paged_attention.h"
+#include "memoria/importance_scorer.h"
 #include <cstdio>
 #include <cstdlib>
 
@@ -68,5 +69,24 @@ void refp_decode_attention(const void* q, void* pool, const int* table, void* ou
 }
 
 int refp_sync(void) { return (int)cudaDeviceSynchronize(); }
+
+// ImportanceScorer (src/memoria/importance_scorer.h:25-67): `steps` updates of n scores with the host
+// arrays new_scores[step][n]; out[step][n] = the mirrored scores after each update.
+int refp_importance_run(const float* new_scores, int steps, int n, float decay, float* out) {
+    ImportanceScorer scorer;
+    if (!scorer.init(n, decay)) return -1;
+    float* d_new = nullptr;
+    if (cudaMalloc(&d_new, sizeof(float) * n) != cudaSuccess) return -2;
+    for (int s = 0; s < steps; s++) {
+        cudaMemcpy(d_new, new_scores + (size_t)s * n, sizeof(float) * n, cudaMemcpyHostToDevice);
+        cudaDeviceSynchronize();             // the scorer runs on its own stream
+        scorer.update(d_new, n);
+        scorer.sync_to_host();
+        for (int i = 0; i < n; i++) out[(size_t)s * n + i] = scorer.score(i);
+    }
+    cudaFree(d_new);
+    scorer.destroy();
+    return (int)cudaGetLastError();
+}
 
 }  // extern "C"

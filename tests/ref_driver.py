@@ -21,6 +21,11 @@ def ref_lib():
         L.ref_cm_create.restype = C.c_void_p
         L.ref_bp_create.restype = C.c_void_p
         L.ref_bp_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_size_t]
+        L.ref_scored_create.restype = C.c_void_p
+        L.ref_scored_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_float, C.POINTER(C.c_void_p)]
+        L.ref_scored_update.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.ref_scored_score.restype = C.c_float
+        L.ref_scored_score.argtypes = [C.c_void_p, C.c_int]
         for n in ("ref_bp_total_bytes", "ref_bp_k_offset", "ref_bp_v_offset"):
             getattr(L, n).restype = C.c_size_t
         for n in dir(L):
@@ -56,6 +61,23 @@ class RefCacheManager:
         return list(buf)[:got]
 
 
+class RefScoredCacheManager(RefCacheManager):
+    """The reference's CacheManager with its own ImportanceScorer attached."""
+    def __init__(self, layers, pages, page_size, decay):
+        self.L = ref_lib()
+        cm = C.c_void_p()
+        self.owner = C.c_void_p(self.L.ref_scored_create(layers, pages, page_size, decay, C.byref(cm)))
+        assert self.owner.value
+        self.h = cm
+        self.width = 2 * pages
+    def close(self): self.L.ref_scored_destroy(self.owner)
+    def score_update(self, values):
+        arr = np.ascontiguousarray(values, dtype=np.float32)
+        self.L.ref_scored_update(self.owner, arr.ctypes.data, len(arr))
+    def scores(self):
+        return np.array([self.L.ref_scored_score(self.owner, i) for i in range(self.width)], dtype=np.float32)
+
+
 class RefBlockPool:
     def __init__(self, layers, pages, page_size, extra=0):
         self.L = ref_lib()
@@ -70,12 +92,16 @@ class RefBlockPool:
 
 class EngineAsCacheManager:
     """The same calls on libdrkv.so (bookkeeping-only engine, one sequence, stream_evict on)."""
-    def __init__(self, layers, pages, page_size):
+    def __init__(self, layers, pages, page_size, decay=None):
         from deusridet_b200 import PagedKVEngine
         self.e = PagedKVEngine(num_layers=layers, num_q_heads=24, num_kv_heads=4, head_dim=256, page_size=page_size,
                                dtype="f16", rotary_dim=64, max_pages=pages, max_seqs=1, device=-1, stream_evict=True)
+        if decay is not None:
+            self.e.scorer_enable(decay)
         self.s = self.e.seq_create()
         self.held = []
+    def score_update(self, values): self.e.scorer_update(self.s, np.asarray(values, dtype=np.float32))
+    def scores(self): return self.e.scorer_scores(self.s)
     def close(self): self.e.close()
     def ensure(self, pos): return 1 if self.e.ensure_blocks_for(self.s, pos) else 0
     def ensure_range(self, pos, m): return 1 if self.e.ensure_blocks_for_range(self.s, pos, m) else 0
@@ -92,10 +118,21 @@ class EngineAsCacheManager:
 
 class ModelAsCacheManager:
     """The same calls on the Python model (oracle/bookkeeping.py)."""
-    def __init__(self, layers, pages, page_size):
+    def __init__(self, layers, pages, page_size, decay=None):
         from oracle.bookkeeping import BookModel
         self.m = BookModel(pages, page_size, 1, 0, True)
         self.s = self.m.seq_create()
+        self.decay = decay
+        if decay is not None:
+            self.m.scores = {self.s: np.zeros(2 * pages, dtype=np.float32)}
+    def score_update(self, values):
+        from oracle import cbind
+        v = np.asarray(values, dtype=np.float32)
+        row = self.m.scores[self.s]
+        head = np.ascontiguousarray(row[:len(v)])
+        cbind.importance_update(head, v, self.decay)
+        row[:len(v)] = head
+    def scores(self): return self.m.scores[self.s]
     def close(self): pass
     def ensure(self, pos): return 1 if self.m.seq_ensure_pos(self.s, pos) == 0 else 0
     def ensure_range(self, pos, m): return 1 if self.m.seq_ensure_range(self.s, pos, m) == 0 else 0
@@ -110,7 +147,7 @@ class ModelAsCacheManager:
     def table(self, n): return self.m.table(self.s)[:n]
 
 
-def random_ops(seed, pages, page_size, n_ops):
+def random_ops(seed, pages, page_size, n_ops, scored=False):
     """Seeded mix of the calls Conscientia makes (ensure / ensure_range / set_seq_len) plus
     evictions, ensure_free and direct pool traffic.  Only valid pool frees are generated: the
     reference's free_block has no double-free check (block_pool.cpp:71-74)."""
@@ -119,6 +156,10 @@ def random_ops(seed, pages, page_size, n_ops):
     limit = 2 * pages * page_size
     for _ in range(n_ops):
         r = rng.random()
+        if scored and rng.random() < 0.2:
+            # new importance values for the first n logical blocks: coarse values make ties, which the
+            # policy breaks by allocation order
+            ops.append(["score", int(rng.integers(1, 2 * pages + 1)), int(rng.random() < 0.5), int(rng.integers(1 << 30))])
         if r < 0.35:
             ops.append(["ensure", int(pos)])
             pos = min(pos + int(rng.integers(1, 2 * page_size)), limit + page_size)
@@ -139,6 +180,13 @@ def random_ops(seed, pages, page_size, n_ops):
         else:
             ops.append(["pool_free_last"])
     return ops
+
+
+def score_values(op):
+    """The values of a ["score", n, coarse, seed] operation."""
+    rng = np.random.default_rng(op[3])
+    vals = rng.integers(0, 4, size=op[1]) * 0.25 if op[2] else rng.random(op[1])
+    return vals.astype(np.float32)
 
 
 def run_ops(cm, ops, pages):
@@ -163,12 +211,17 @@ def run_ops(cm, ops, pages):
             r = cm.pool_alloc()
             if r >= 0:
                 held.append(r)
+        elif k == "score":
+            cm.score_update(score_values(op)); r = op[1]
         elif k == "pool_free_last":
             r = -9
             if held:
                 r = held.pop()
                 cm.pool_free(r)
         tab = np.asarray(cm.table(width), dtype=np.int32)
-        out.append([int(r), cm.free_blocks(), cm.used(), cm.num_logical(), zlib.crc32(tab.tobytes())])
+        rec = [int(r), cm.free_blocks(), cm.used(), cm.num_logical(), zlib.crc32(tab.tobytes())]
+        if k == "score":
+            rec.append(zlib.crc32(np.asarray(cm.scores(), dtype=np.float32).tobytes()))
+        out.append(rec)
     out.append([int(x) for x in cm.table(width)])
     return out

@@ -47,6 +47,52 @@ def test_engine_matches_live_reference_objects(drkv_lib, seed):
     assert got == want
 
 
+# ---- CacheManager with an ImportanceScorer attached (cache_manager.cpp:185-205, importance_scorer.cu:75-87) ----
+@pytest.mark.parametrize("case", GOLDEN["scored"], ids=lambda c: f"seed{c['seed']}-{c['pages']}pages-decay{c['decay']}")
+def test_scored_engine_matches_recorded_reference_trace(drkv_lib, case):
+    eng = R.EngineAsCacheManager(2, case["pages"], case["page_size"], decay=case["decay"])
+    got = R.run_ops(eng, case["ops"], case["pages"])
+    eng.close()
+    for i, (g, w) in enumerate(zip(got, case["trace"])):
+        assert g == w, f"op {i} {case['ops'][i] if i < len(case['ops']) else 'final table'}: {g} != {w}"
+    assert len(got) == len(case["trace"])
+    assert any(op[0] == "evict" and rec[0] > 0 for op, rec in zip(case["ops"], case["trace"]))
+
+
+@pytest.mark.parametrize("case", GOLDEN["scored"], ids=lambda c: f"seed{c['seed']}-{c['pages']}pages-decay{c['decay']}")
+def test_scored_python_model_matches_recorded_reference_trace(oracle, case):
+    m = R.ModelAsCacheManager(2, case["pages"], case["page_size"], decay=case["decay"])
+    assert R.run_ops(m, case["ops"], case["pages"]) == case["trace"]
+
+
+@pytest.mark.skipif(not R.ref_available(), reason="oracle/_ref not built (reference tree not mounted)")
+@pytest.mark.parametrize("seed", range(200, 210))
+def test_scored_engine_matches_live_reference_objects(drkv_lib, seed):
+    pages = [4, 7, 16, 40][seed % 4]
+    psize = [16, 64, 256][seed % 3]
+    decay = [0.95, 0.5, 1.0][seed % 3]
+    ops = R.random_ops(seed, pages, psize, 400, scored=True)
+    ref = R.RefScoredCacheManager(3, pages, psize, decay)
+    eng = R.EngineAsCacheManager(3, pages, psize, decay=decay)
+    want, got = R.run_ops(ref, ops, pages), R.run_ops(eng, ops, pages)
+    ref.close()
+    eng.close()
+    assert got == want
+
+
+def test_scored_eviction_differs_from_oldest_first(drkv_lib):
+    """The policy matters: with scores attached the victim is the lowest-scored page, not the oldest."""
+    import numpy as np
+    eng = R.EngineAsCacheManager(1, 8, 16, decay=0.5)
+    for pos in range(0, 6 * 16, 16):
+        assert eng.ensure(pos)
+    eng.score_update(np.array([5, 4, 0.5, 3, 0.5, 9], dtype=np.float32))
+    assert eng.evict(2) == 2
+    t = eng.table(8)
+    assert t[2] == -1 and t[4] == -1 and all(t[i] >= 0 for i in (0, 1, 3, 5))   # ties: allocation order
+    eng.close()
+
+
 @pytest.mark.parametrize("case", GOLDEN["pool"], ids=lambda c: f"{c['layers']}L-{c['pages']}p")
 def test_pool_sizing_and_offsets(drkv_lib, oracle, case):
     """max_blocks from the budget by integer division, total_bytes, k/v byte offsets

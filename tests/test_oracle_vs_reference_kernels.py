@@ -58,3 +58,15 @@ def test_checker_reproduces_reference_kernels(oracle, name):
                      GOLD[name + "_q_roped"][None], out, 1.0 / np.sqrt(c["d"]))
     err = np.abs(ob.to_float(out[0], ob.F16) - ob.to_float(GOLD[name + "_out"], ob.F16)).max()
     assert err <= 2e-3, err
+
+
+def test_importance_update_matches_reference_kernel_record(oracle):
+    """score = fma(score, decay, new) against the scores the reference's own ImportanceScorer held after
+    each update on a B200 (src/memoria/importance_scorer.cu:27-37, 68-96)."""
+    from tests.golden.make_importance_golden import importance_cases
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "importance_reference.npz"))
+    for name, (decay, new) in importance_cases().items():
+        scores = np.zeros(new.shape[1], dtype=np.float32)
+        for k in range(new.shape[0]):
+            oracle.importance_update(scores, new[k], decay)
+            assert np.array_equal(scores, gold[name][k]), f"{name} step {k}"
