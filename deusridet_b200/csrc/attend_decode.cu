@@ -97,7 +97,9 @@ __device__ __forceinline__ void split_pack(float p0, float p1, uint32_t& hi, uin
 // table look-ups sit on the critical path.  An item's partial goes straight from the
 // accumulators to global memory; there is no block-level barrier after start-up.
 // HI: the GQA group has more than 8 query heads, so rows 8..15 of the 16-row tile are live.
-template <typename T, int D, bool HI>
+// EXT compiles in the two extensions that cost the plain pass time when merely present: shared-prefix
+// family blocks and the per-tile masses of the importance scorer.
+template <typename T, int D, bool HI, bool EXT>
 __global__ void __launch_bounds__(RingShape<D>::kWarps * 32, 1)
 attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams p) {
     constexpr int WARPS = RingShape<D>::kWarps, DEPTH = RingShape<D>::kDepth;
@@ -133,7 +135,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     // ---- items per entry, exclusive prefix sum into cum[] ----
     // Entries: first the family blocks of a shared-prefix plan (up to 16 query rows of several forked
     // sequences over the chunks they have in common), then the sequences (their remaining chunks).
-    const int n_fb = p.n_fb;
+    const int n_fb = EXT ? p.n_fb : 0;
     const int n_ent = n_fb + p.n_seq;
     auto entry_items = [&](int e) -> int {
         if (e < n_fb) return __ldg(p.fb_chunks + e) * p.num_kv_heads;
@@ -278,7 +280,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 SlotMeta m;
                 m.b = c_b;
                 m.kvh = c_kvh;
-                m.part_slot = c_fam ? c_chunk : (c_b * p.num_q_heads + c_kvh * p.group) * p.max_chunks + c_chunk;
+                m.part_slot = (EXT && c_fam) ? c_chunk : (c_b * p.num_q_heads + c_kvh * p.group) * p.max_chunks + c_chunk;
                 m.flags = (c_gi == 0 ? SLOT_FIRST : 0) | (last ? SLOT_LAST : 0) | (page < 0 ? SLOT_SKIP : 0);
                 m.v_lo = max(0, p.kv_begin - tok0);
                 m.v_hi = min(kGroupTokens, c_kv_end - tok0);
@@ -343,7 +345,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             const T* qall = reinterpret_cast<const T*>(p.q);
             const T* qr0 = nullptr;
             const T* qr1 = nullptr;
-            if (meta.fam == 0) {
+            if (!EXT || meta.fam == 0) {
                 const T* qb = qall + ((int64_t)meta.b * p.num_q_heads + (int64_t)meta.kvh * p.group) * D;
                 if (qrow < p.group) qr0 = qb + (int64_t)qrow * D;
                 if (HI && qrow + 8 < p.group) qr1 = qb + (int64_t)(qrow + 8) * D;
@@ -354,10 +356,17 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 if (b0 >= 0) qr0 = qall + ((int64_t)b0 * p.num_q_heads + (int64_t)meta.kvh * p.group + qrow % p.group) * D;
                 if (b1 >= 0) qr1 = qall + ((int64_t)b1 * p.num_q_heads + (int64_t)meta.kvh * p.group + (qrow + 8) % p.group) * D;
             }
-            if (p.tile_lse != nullptr) {
-                const int64_t per_row = (int64_t)D;
-                mass_row[0] = qr0 ? (int)((qr0 - qall) / per_row) : -1;
-                mass_row[1] = qr1 ? (int)((qr1 - qall) / per_row) : -1;
+            if (EXT && p.tile_lse != nullptr) {
+                // value of (sequence b, kv head, tile, head-in-group j) at ((b * Hkv + kvh) * max_tiles + tile) * g + j:
+                // the rows of one group land in one 32-byte sector per tile
+                auto base_of = [&](const T* qr) -> int {
+                    if (qr == nullptr) return -1;
+                    const int rowi = (int)((qr - qall) / (int64_t)D);          // b * Hq + kvh * g + j
+                    const int bq = rowi / p.num_q_heads, j = rowi % p.group;
+                    return (bq * p.num_kv_heads + meta.kvh) * p.max_tiles * p.group + j;
+                };
+                mass_row[0] = base_of(qr0);
+                mass_row[1] = base_of(qr1);
             }
             const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qr0 + col);
             const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qr1 + col);
@@ -424,14 +433,14 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 const float p0 = fast_exp2(x0 - mnew), p1 = fast_exp2(x1 - mnew);
                 const float p8 = fast_exp2(x8 - mnew), p9 = fast_exp2(x9 - mnew);
                 lsum[r] = lsum[r] * alpha[r] + ((p0 + p1) + (p8 + p9));
-                if (p.tile_lse != nullptr) {
+                if (EXT && p.tile_lse != nullptr) {
                     // log2 of this tile's un-normalised probability mass for the row, on the scale of the
                     // final log-sum-exp: mass share = 2^(tile_lse - lse2) once the merge knows lse2
                     float ts = (p0 + p1) + (p8 + p9);
                     ts += __shfl_xor_sync(0xffffffffu, ts, 1);
                     ts += __shfl_xor_sync(0xffffffffu, ts, 2);
                     if ((lane & 3) == 0 && mass_row[r] >= 0)
-                        p.tile_lse[(int64_t)mass_row[r] * p.max_tiles + meta.tile] = ts > 0.f ? mnew + __log2f(ts) : -INFINITY;
+                        p.tile_lse[mass_row[r] + meta.tile * p.group] = ts > 0.f ? mnew + __log2f(ts) : -INFINITY;
                 }
                 split_pack<T>(p0, p1, phi[r], plo[r]);          // a0 (r=0) / a1 (r=1)
                 split_pack<T>(p8, p9, phi[2 + r], plo[2 + r]);  // a2 / a3
@@ -470,10 +479,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 }
             }
         }
-        else if (p.tile_lse != nullptr && (lane & 3) == 0) {
+        else if (EXT && p.tile_lse != nullptr && (lane & 3) == 0) {
 #pragma unroll
             for (int r = 0; r < NR; r++)
-                if (mass_row[r] >= 0) p.tile_lse[(int64_t)mass_row[r] * p.max_tiles + meta.tile] = -INFINITY;
+                if (mass_row[r] >= 0) p.tile_lse[mass_row[r] + meta.tile * p.group] = -INFINITY;
         }
         __syncwarp();                                  // every lane is done with the slot's shared memory
         outstanding--;
@@ -489,7 +498,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 l += __shfl_xor_sync(0xffffffffu, l, 2);
                 const int row = qrow + 8 * r;
                 int64_t ps = -1;                                   // partial slot of this row, -1: padding row
-                if (meta.fam == 0) {
+                if (!EXT || meta.fam == 0) {
                     if (row < p.group) ps = (int64_t)meta.part_slot + (int64_t)row * p.max_chunks;
                 } else {
                     const int mi = row / p.group;
@@ -626,10 +635,12 @@ __global__ void __launch_bounds__(128) page_mass_kernel(const PageMassParams p) 
     if (page * tiles_per_page >= n_tiles) return;
     const int t1 = min((page + 1) * tiles_per_page, n_tiles);
     float mass = 0.f;
-    for (int h = 0; h < p.num_q_heads; h++) {
-        const float lse2 = p.lse2[(int64_t)b * p.num_q_heads + h];
-        const float* row = p.tile_lse + ((int64_t)b * p.num_q_heads + h) * p.max_tiles;
-        for (int t = page * tiles_per_page; t < t1; t++) mass += fast_exp2(row[t] - lse2);
+    const int g = p.num_q_heads / p.num_kv_heads;
+    for (int kvh = 0; kvh < p.num_kv_heads; kvh++) {
+        const float* lse2 = p.lse2 + (int64_t)b * p.num_q_heads + kvh * g;
+        const float* tl = p.tile_lse + ((int64_t)b * p.num_kv_heads + kvh) * p.max_tiles * g;
+        for (int t = page * tiles_per_page; t < t1; t++)
+            for (int j = 0; j < g; j++) mass += fast_exp2(tl[t * g + j] - lse2[j]);
     }
     float* dst = p.fresh + (int64_t)p.rows[b] * p.table_stride + page;
     *dst += mass;
@@ -682,7 +693,7 @@ combine_external_kernel(int n_parts, const float* parts, int hq, int D, void* ou
     }
 }
 
-template <typename T, int D, bool HI>
+template <typename T, int D, bool HI, bool EXT>
 cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
     constexpr int WARPS = RingShape<D>::kWarps, DEPTH = RingShape<D>::kDepth, NH = D / 64;
     constexpr size_t smem = 1024 + (size_t)WARPS * DEPTH * (2 * NH * 2048 + sizeof(SlotMeta) + sizeof(uint64_t)) +
@@ -692,19 +703,23 @@ cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        e = cudaFuncSetAttribute(attend_decode_kernel<T, D, HI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(attend_decode_kernel<T, D, HI, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     int grid = (p.total_items + WARPS - 1) / WARPS;
     if (grid > num_sms) grid = num_sms;
-    return launch_pdl(attend_decode_kernel<T, D, HI>, dim3(grid), dim3(WARPS * 32), smem, stream, tmap, p);
+    return launch_pdl(attend_decode_kernel<T, D, HI, EXT>, dim3(grid), dim3(WARPS * 32), smem, stream, tmap, p);
 }
 
 template <typename T, int D>
 cudaError_t launch_decode_t(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
-    return (p.group > 8 || p.rows_per_item > 8) ? launch_decode_hi<T, D, true>(tmap, p, num_sms, stream)
-                       : launch_decode_hi<T, D, false>(tmap, p, num_sms, stream);
+    const bool ext = p.n_fb > 0 || p.tile_lse != nullptr;
+    if (p.group > 8 || p.rows_per_item > 8)
+        return ext ? launch_decode_hi<T, D, true, true>(tmap, p, num_sms, stream)
+                   : launch_decode_hi<T, D, true, false>(tmap, p, num_sms, stream);
+    return ext ? launch_decode_hi<T, D, false, true>(tmap, p, num_sms, stream)
+               : launch_decode_hi<T, D, false, false>(tmap, p, num_sms, stream);
 }
 
 }  // namespace

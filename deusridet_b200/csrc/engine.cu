@@ -808,6 +808,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
         pm.kv_len = d_kv_len;
         pm.fresh = e->scorer.d_fresh;
         pm.num_q_heads = g.num_q_heads;
+        pm.num_kv_heads = g.num_kv_heads;
         pm.max_tiles = e->scorer.max_tiles;
         pm.page_size = g.page_size;
         pm.table_stride = e->book.row_width();

@@ -62,7 +62,7 @@ struct DecodeParams {
     const int32_t* fb_chunks;
     const int32_t* fb_members;
     const int32_t* seq_first_chunk;
-    // tile masses for the importance scorer (null = off): tile_lse[(seq * Hq + head) * max_tiles + tile]
+    // tile masses for the importance scorer (null = off): tile_lse[((seq * Hkv + kv_head) * max_tiles + tile) * group + head_in_group]
     float* tile_lse;
     int max_tiles;
     int total_items;          // upper bound n_seq * num_kv_heads * max_chunks (sizes the grid)
@@ -100,12 +100,12 @@ struct CombineParams {
 
 // Importance scorer: per-page attention mass from the decode kernel's tile values.
 struct PageMassParams {
-    const float* tile_lse;    // [(seq * Hq + head) * max_tiles + tile]
+    const float* tile_lse;    // [((seq * Hkv + kv_head) * max_tiles + tile) * group + head_in_group]
     const float* lse2;        // [n_seq][Hq]
     const int32_t* rows;      // [n_seq] table rows
     const int32_t* kv_len;    // [n_seq]
     float* fresh;             // [max_seqs][table_stride] accumulator of new scores
-    int num_q_heads, max_tiles, page_size, table_stride;
+    int num_q_heads, num_kv_heads, max_tiles, page_size, table_stride;
 };
 cudaError_t launch_page_mass(const PageMassParams& p, int n_seq, int max_kv_len, cudaStream_t stream);
 cudaError_t launch_importance_update(float* scores, float* fresh, int64_t n, float decay, cudaStream_t stream);
