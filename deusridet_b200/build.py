@@ -15,8 +15,8 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdrkv.so")
 
 CUDA_SOURCES = ["engine.cu", "append.cu", "attend_decode.cu", "stateless.cu", "decode_noalloc.cu", "attend_prefill.cu", "gather_scatter.cu"]
-CXX_SOURCES = ["page_book.cpp"]
-HEADERS = ["kernels.hpp", "kv_common.cuh", "page_book.hpp", "stateless.hpp", "sm100_primitives.cuh", os.path.join("..", "..", "include", "drkv.h")]
+CXX_SOURCES = ["page_book.cpp", "page_store.cpp"]
+HEADERS = ["kernels.hpp", "kv_common.cuh", "page_book.hpp", "page_store.hpp", "stateless.hpp", "sm100_primitives.cuh", os.path.join("..", "..", "include", "drkv.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -41,6 +41,11 @@ class PlanInfo(C.Structure):
                 ("keys_planned_pass", C.c_int64)]
 
 
+class TierStats(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in (
+        "pages_stored", "swap_outs", "swap_ins", "bytes_out", "bytes_in", "prefetch_hits", "page_file_bytes")]
+
+
 class EvictRecord(C.Structure):
     _fields_ = [("kind", C.c_int32), ("seq", C.c_int32), ("logical", C.c_int32), ("page", C.c_int32)]
 
@@ -97,6 +102,12 @@ SIGNATURES = {
     "drkv_plan_get_info": (_i, [_vp, C.POINTER(PlanInfo)]),
     "drkv_plan_dump": (_i, [_vp, _pi32, _i]),
     "drkv_attend_decode_planned": (_i, [_vp, _i, _vp, _vp, _f, _vp]),
+    "drkv_tier_enable": (_i, [_vp, C.c_char_p]),
+    "drkv_tier_disable": (_i, [_vp]),
+    "drkv_tier_prefetch": (_i, [_vp, _i, _i]),
+    "drkv_tier_drain": (_i, [_vp]),
+    "drkv_tier_get_stats": (_i, [_vp, C.POINTER(TierStats)]),
+    "drkv_seq_locations": (_i, [_vp, _i, C.POINTER(C.c_int8), _i]),
     "drkv_scorer_enable": (_i, [_vp, _f]),
     "drkv_scorer_update": (_i, [_vp, _i, _vp, _i, _vp]),
     "drkv_scorer_step": (_i, [_vp, _vp]),

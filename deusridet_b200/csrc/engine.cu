@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -11,6 +12,7 @@
 #include "../../include/drkv.h"
 #include "kernels.hpp"
 #include "page_book.hpp"
+#include "page_store.hpp"
 #include "stateless.hpp"
 
 using namespace drkv;
@@ -158,7 +160,17 @@ struct drkv_engine {
         int max_tiles = 0;
         std::vector<std::pair<int, int>> pending;    // rows to reset (src = -1) or copy from src, at the next stream call
     } scorer;
+
+    // storage tier behind the pool (off until drkv_tier_enable)
+    std::unique_ptr<PageStore> store;
+    cudaStream_t last_stream = nullptr;              // stream of the most recent kernel launches
 };
+
+// Remembers the stream kernels were last launched on: page copies to the storage tier wait for it.
+static inline void note_stream(drkv_engine* e, cudaStream_t s) {
+    e->last_stream = s;
+    if (e->store) e->store->set_order_stream(s);
+}
 
 // ints of a plan: rows, kv_len, first_chunk per sequence; row, chunks and 16 members per family block
 static constexpr size_t kPlanInts = (size_t)kMaxDecodeSeqs * 3 + (size_t)kMaxDecodeSeqs * 18;
@@ -285,6 +297,8 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
 
 void drkv_destroy(drkv_engine* e) {
     if (!e) return;
+    e->book.attach_tier(nullptr);
+    e->store.reset();                                // joins the prefetch thread; stored files stay on disk
     if (e->has_device) {
         cudaSetDevice(e->device);
         cudaDeviceSynchronize();
@@ -658,6 +672,7 @@ int drkv_append_rope(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows
     NEED_DEVICE(e);
     if (layer < 0 || layer >= e->geom.num_layers || n_seq < 0 || !d_rows || !d_pos || !k_src || !v_src)
         return set_err(DRKV_ERR_INVALID, "append_rope: bad argument");
+    note_stream(e, (cudaStream_t)stream);
     AppendParams p = append_params(e, layer);
     p.rows = d_rows;
     p.pos = d_pos;
@@ -674,6 +689,7 @@ int drkv_append_rope_chunk(drkv_engine* e, int layer, int seq, int pos_start, in
     if (layer < 0 || layer >= e->geom.num_layers || m < 0 || pos_start < 0 || !k_src || !v_src || seq < 0 ||
         seq >= e->book.max_seqs())
         return set_err(DRKV_ERR_INVALID, "append_rope_chunk: bad argument");
+    note_stream(e, (cudaStream_t)stream);
     AppendParams p = append_params(e, layer);
     p.rows = nullptr;
     p.pos = nullptr;
@@ -720,6 +736,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
                          float* out_partial, float scale, cudaStream_t stream,
                          const drkv_engine::Plan* plan = nullptr) {
     const drkv_geometry& g = e->geom;
+    note_stream(e, stream);
     int chunk = 0;
     if (plan) {
         chunk = plan->chunk;   // the plan's chunk was checked against the scratch when it was made
@@ -1005,6 +1022,75 @@ int drkv_attend_decode_planned(drkv_engine* e, int layer, const void* q, void* o
     if (pl.n_seq == 0 || pl.max_chunks == 0) return DRKV_OK;
     return decode_common(e, layer, pl.n_seq, pl.rows, pl.kv_len, 0, 0, 0, pl.max_chunks * pl.chunk, q, out, nullptr,
                          scale, (cudaStream_t)stream, &pl);
+}
+
+// ---- storage tier --------------------------------------------------------------------------
+int drkv_tier_enable(drkv_engine* e, const char* dir) {
+    NEED(e);
+    if (!dir || !*dir) return set_err(DRKV_ERR_INVALID, "tier_enable: empty directory");
+    LOCK(e);
+    std::unique_ptr<PageStore> st(new PageStore());
+    std::string err;
+    const size_t page_bytes = (size_t)2 * e->geom.num_kv_heads * e->geom.page_size * e->geom.head_dim * 2;
+    if (!st->init(dir, e->pool, e->geom.num_layers, page_bytes * (size_t)e->book.max_pages(), page_bytes, &err))
+        return set_err(DRKV_ERR_STATE, "%s", err.c_str());
+    st->set_order_stream(e->last_stream);
+    e->store = std::move(st);
+    e->book.attach_tier(e->store.get());
+    return DRKV_OK;
+}
+
+int drkv_tier_disable(drkv_engine* e) {
+    NEED(e);
+    LOCK(e);
+    if (e->book.stored_pages() > 0)
+        return set_err(DRKV_ERR_STATE, "tier_disable: %d pages are still stored", e->book.stored_pages());
+    e->book.attach_tier(nullptr);
+    e->store.reset();
+    return DRKV_OK;
+}
+
+int drkv_tier_prefetch(drkv_engine* e, int seq, int logical) {
+    NEED(e);
+    LOCK(e);
+    if (!e->store) return set_err(DRKV_ERR_STATE, "tier_prefetch: no storage tier");
+    if (e->book.seq_location(seq, logical) != LOC_SSD) return 0;    // cache_manager.cpp:168-169: nothing to do
+    return e->store->prefetch(seq, logical) ? 1 : 0;
+}
+
+int drkv_tier_drain(drkv_engine* e) {
+    NEED(e);
+    if (!e->store) return set_err(DRKV_ERR_STATE, "tier_drain: no storage tier");
+    e->store->drain();
+    return DRKV_OK;
+}
+
+int drkv_tier_get_stats(const drkv_engine* ce, drkv_tier_stats* out) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    NEED(e);
+    if (!out) return set_err(DRKV_ERR_INVALID, "null argument");
+    LOCK(e);
+    memset(out, 0, sizeof(*out));
+    out->pages_stored = e->book.stored_pages();
+    out->swap_outs = e->book.n_swap_out;
+    out->swap_ins = e->book.n_swap_in;
+    if (e->store) {
+        out->bytes_out = e->store->bytes_out;
+        out->bytes_in = e->store->bytes_in;
+        out->prefetch_hits = e->store->prefetch_hits;
+        out->page_file_bytes = (int64_t)e->store->file_bytes();
+    }
+    return DRKV_OK;
+}
+
+int drkv_seq_locations(const drkv_engine* ce, int seq, int8_t* out, int cap) {
+    drkv_engine* e = const_cast<drkv_engine*>(ce);
+    NEED(e);
+    LOCK(e);
+    if (!e->book.seq_live(seq) || !out || cap < 0) return set_err(DRKV_ERR_INVALID, "seq_locations: bad argument");
+    const int n = cap < e->book.row_width() ? cap : e->book.row_width();
+    for (int i = 0; i < n; i++) out[i] = (int8_t)e->book.seq_location(seq, i);
+    return n;
 }
 
 // ---- importance scorer ---------------------------------------------------------------------

@@ -86,7 +86,35 @@ int PageBook::evict_cached(int n) {
     return done;
 }
 
-bool PageBook::evict_one_of(int seq) {
+// The victim leaves the allocation order first (cache_manager.cpp:124-127); then its page is written to
+// the tier (kind 2) when one is attached and the write succeeds, else discarded (kind 1).
+void PageBook::retire(int seq, std::deque<int>::iterator it, bool may_store) {
+    Seq& s = seqs_[seq];
+    const int idx = *it, page = s.table[idx];
+    s.alloc_order.erase(it);
+    bool stored = false;
+    if (tier_ != nullptr && may_store) stored = tier_->swap_out(seq, idx, page);   // cache_manager.cpp:132-141
+    refcount_[page] = 0;
+    state_[page] = PageState::FREE;
+    free_stack_.push_back(page);  // cache_manager.cpp:144-147, 232-236
+    s.table[idx] = -1;
+    mark_dirty(s, idx);
+    if (stored) {
+        if (s.loc[idx] != LOC_SSD) n_stored_++;
+        s.loc[idx] = LOC_SSD;
+        n_swap_out++;
+    } else {
+        if (s.loc[idx] == LOC_SSD) {
+            n_stored_--;
+            if (tier_) tier_->drop(seq, idx);
+        }
+        s.loc[idx] = LOC_INVALID;
+    }
+    evict_log_.push_back({stored ? 2 : 1, seq, idx, page});
+    n_evict_stream++;
+}
+
+bool PageBook::evict_one_of(int seq, bool may_store) {
     Seq& s = seqs_[seq];
     if (scores_ != nullptr) {
         const float* sc = scores_ + (size_t)seq * row_width_;
@@ -97,15 +125,7 @@ bool PageBook::evict_one_of(int seq) {
             if (best == s.alloc_order.end() || sc[*it] < sc[*best]) best = it;   // strict <: first minimum
         }
         if (best != s.alloc_order.end()) {
-            const int idx = *best, page = s.table[idx];
-            s.alloc_order.erase(best);
-            refcount_[page] = 0;
-            state_[page] = PageState::FREE;
-            free_stack_.push_back(page);
-            s.table[idx] = -1;
-            mark_dirty(s, idx);
-            evict_log_.push_back({1, seq, idx, page});
-            n_evict_stream++;
+            retire(seq, best, may_store);
             return true;
         }
     }
@@ -120,28 +140,28 @@ bool PageBook::evict_one_of(int seq) {
             ++it;
             continue;
         }
-        s.alloc_order.erase(it);
-        refcount_[page] = 0;
-        state_[page] = PageState::FREE;
-        free_stack_.push_back(page);  // discard path, cache_manager.cpp:144-147
-        s.table[idx] = -1;
-        mark_dirty(s, idx);
-        evict_log_.push_back({1, seq, idx, page});
-        n_evict_stream++;
+        retire(seq, it, may_store);
         return true;
     }
     return false;
 }
 
-int PageBook::take_page(int seq) {
+int PageBook::take_page(int seq, bool may_store) {
     int id = pool_alloc();
     if (id >= 0) return id;
     if (!lru_.empty()) {
         evict_cached(1);
         return pool_alloc();
     }
-    if (stream_evict_ && seq_live(seq) && evict_one_of(seq)) return pool_alloc();  // cache_manager.cpp:310-319
+    if (stream_evict_ && seq_live(seq) && evict_one_of(seq, may_store)) return pool_alloc();  // cache_manager.cpp:310-319
     return -1;
+}
+
+int PageBook::seq_location(int seq, int logical) const {
+    if (!seq_live(seq) || logical < 0 || logical >= row_width_) return DRKV_ERR_INVALID;
+    const Seq& s = seqs_[seq];
+    if (s.table[logical] >= 0) return LOC_GPU;
+    return s.loc[logical] == LOC_SSD ? LOC_SSD : LOC_INVALID;
 }
 
 int PageBook::seq_evict(int seq, int n) {
@@ -171,6 +191,7 @@ int PageBook::seq_create() {
         s.live = true;
         s.len = 0;
         if ((int)s.table.size() != row_width_) s.table.assign(row_width_, -1);
+        s.loc.assign(row_width_, LOC_INVALID);
         s.alloc_order.clear();
         live_++;
         return i;
@@ -183,7 +204,14 @@ int PageBook::seq_release(int seq, bool discard) {
     Seq& s = seqs_[seq];
     for (int idx = 0; idx < row_width_; idx++) {
         int page = s.table[idx];
-        if (page < 0) continue;
+        if (page < 0) {
+            if (s.loc[idx] == LOC_SSD) {                   // its stored copy goes with the sequence
+                if (tier_) tier_->drop(seq, idx);
+                s.loc[idx] = LOC_INVALID;
+                n_stored_--;
+            }
+            continue;
+        }
         unref(page, discard);
         s.table[idx] = -1;
         mark_dirty(s, idx);
@@ -233,6 +261,23 @@ int PageBook::seq_ensure_pos(int seq, int pos, std::vector<CowJob>* jobs) {
         s.table[idx] = fresh;
         mark_dirty(s, idx);
         n_cow++;
+        return DRKV_OK;
+    }
+    if (s.loc[idx] == LOC_SSD && tier_ != nullptr) {
+        // swap_block_from_ssd (cache_manager.cpp:243-292): a page for it, discarding (never storing) a
+        // victim when the pool is empty; then the stored bytes; on failure the page goes back.
+        int back = take_page(seq, /*may_store=*/false);
+        if (back < 0) return fail(DRKV_ERR_EXHAUSTED, "swap-in: pool exhausted, nothing evictable");
+        if (!tier_->swap_in(seq, idx, back)) {
+            pool_free(back);
+            return fail(DRKV_ERR_STATE, "swap-in: the stored page could not be read");
+        }
+        s.table[idx] = back;
+        s.loc[idx] = LOC_INVALID;
+        n_stored_--;
+        n_swap_in++;
+        s.alloc_order.push_back(idx);
+        mark_dirty(s, idx);
         return DRKV_OK;
     }
     int fresh = take_page(seq);  // alloc_logical_block, cache_manager.cpp:306-326

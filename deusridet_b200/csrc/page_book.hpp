@@ -40,6 +40,19 @@ struct DirtyRange {
 
 enum class PageState : int8_t { FREE = 0, ACTIVE = 1, CACHED = 2 };
 
+// Where a logical page of a sequence lives (BlockLocation, cache_manager.h:42-46).
+enum PageLocation : int8_t { LOC_INVALID = 0, LOC_GPU = 1, LOC_SSD = 2 };
+
+// Storage behind the pool (KVSwapper's role, kv_swapper.h:52-120).  The book decides what moves, the
+// engine implements the moves; both calls are synchronous, as CacheManager's are
+// (cache_manager.cpp:215-241, 243-292).
+struct TierIO {
+    virtual ~TierIO() = default;
+    virtual bool swap_out(int seq, int logical, int page) = 0;   // page contents -> storage
+    virtual bool swap_in(int seq, int logical, int page) = 0;    // storage -> page
+    virtual void drop(int seq, int logical) = 0;                 // the stored copy is no longer needed
+};
+
 class PageBook {
 public:
     struct Seq {
@@ -47,6 +60,7 @@ public:
         int len = 0;
         std::vector<int32_t> table;    // logical -> page, -1 = hole / not allocated
         std::deque<int> alloc_order;   // logical indices, oldest allocation first (lru_order_)
+        std::vector<int8_t> loc;       // PageLocation per logical page; only LOC_SSD is authoritative
         int dirty_lo = 0, dirty_hi = 0;
     };
 
@@ -83,6 +97,12 @@ public:
     // with the lowest score, the first one on ties; without candidates the oldest-first walk applies.
     // `scores` is a [max_seqs][row_width] host array the caller keeps alive; nullptr detaches.
     void attach_scores(const float* scores) { scores_ = scores; }
+    // With a tier attached a sequence's own victims are written out instead of discarded, and ensure
+    // on a stored page brings it back (cache_manager.cpp:84-93, 132-141).
+    void attach_tier(TierIO* io) { tier_ = io; }
+    int seq_location(int seq, int logical) const;
+    int stored_pages() const { return n_stored_; }
+    int64_t n_swap_out = 0, n_swap_in = 0;
     bool scores_attached() const { return scores_ != nullptr; }
 
     // ---- inspection ----
@@ -113,6 +133,8 @@ private:
     std::vector<EvictRecord> evict_log_;
     std::string err_;
     const float* scores_ = nullptr;
+    TierIO* tier_ = nullptr;
+    int n_stored_ = 0;
 
     int fail(int code, const std::string& msg) {
         err_ = msg;
@@ -129,8 +151,9 @@ private:
     }
     // A page for `seq`: free stack, else the LRU head of the cached pages, else (stream
     // mode) after the sequence has discarded one of its own pages.  -1 when none.
-    int take_page(int seq);
-    bool evict_one_of(int seq);
+    int take_page(int seq, bool may_store = true);
+    bool evict_one_of(int seq, bool may_store = true);
+    void retire(int seq, std::deque<int>::iterator it, bool may_store);
     void unref(int page, bool discard);
 };
 

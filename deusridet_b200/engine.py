@@ -181,6 +181,20 @@ class PagedKVEngine:
                 "fb_members": buf[3 * ns + 2 * nb:].reshape(nb, 16)}
     def attend_decode_planned(self, layer, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_decode_planned(self.h, layer, _ptr(q), _ptr(out), scale, _stream(stream)))
+    # ---- storage tier (KVSwapper + CacheManager swap paths) -----------------------------------
+    def tier_enable(self, directory: str) -> None: check(self.lib.drkv_tier_enable(self.h, directory.encode()))
+    def tier_disable(self) -> None: check(self.lib.drkv_tier_disable(self.h))
+    def prefetch_block(self, seq: int, logical: int) -> int: return check(self.lib.drkv_tier_prefetch(self.h, seq, logical))
+    def tier_drain(self) -> None: check(self.lib.drkv_tier_drain(self.h))
+    def tier_stats(self) -> dict:
+        st = capi.TierStats()
+        check(self.lib.drkv_tier_get_stats(self.h, C.byref(st)))
+        return {f: getattr(st, f) for f, _ in capi.TierStats._fields_}
+    def locations(self, seq: int) -> np.ndarray:
+        out = np.empty(self.table_stride(), dtype=np.int8)
+        n = check(self.lib.drkv_seq_locations(self.h, seq, out.ctypes.data_as(C.POINTER(C.c_int8)), len(out)))
+        return out[:n]
+
     # ---- importance scorer (ImportanceScorer + CacheManager::pick_eviction_candidate) ----------
     def scorer_enable(self, decay: float = 0.95) -> None: check(self.lib.drkv_scorer_enable(self.h, decay))
     def scorer_disable(self) -> None: check(self.lib.drkv_scorer_enable(self.h, -1.0))

@@ -7,9 +7,11 @@
 // unchanged: same class names, method names, argument meaning, bool / -1 failure convention.
 //
 //   BlockPool      src/memoria/block_pool.h:58-123
-//   CacheManager   src/memoria/cache_manager.h:52-169 (SSD tier and importance scorer: not
-//                  carried over; the pointers are accepted and ignored, which is also what the
-//                  reference does in production, src/actus/awaken_consciousness.cpp:91)
+//   CacheManager   src/memoria/cache_manager.h:52-169
+//   KVSwapper      src/memoria/kv_swapper.h:52-120: a token here; a non-null swapper together with a
+//                  cache_dir switches the engine's storage tier on (cache_manager.cpp:132, 56-66)
+//   ImportanceScorer src/memoria/importance_scorer.h:25-67: init / update / sync_to_host / score /
+//                  least_important forward to the engine's scorer once a CacheManager has adopted it
 //   paged_kv_cache_write / _batch, paged_gqa_decode_attention
 //                  src/machina/paged_attention.h:27-71
 //   invoke_extract_kv_from_pages / invoke_inject_kv_to_pages
@@ -50,8 +52,68 @@ struct PagedKVConfig {
     static constexpr int BLOCK_SIZE = 256;
 };
 
-class KVSwapper;         // accepted and ignored, see the header comment
-class ImportanceScorer;
+class BlockPool;
+
+// The engine moves pages itself; what remains of the swapper is the fact that one was configured.
+class KVSwapper {
+public:
+    bool init(BlockPool&, const std::string& ssd_dir, int /*staging_blocks*/ = 2) {
+        dir_ = ssd_dir;
+        return true;
+    }
+    void drain() {}
+    void shutdown() {}
+    int pending() const { return 0; }
+    const std::string& dir() const { return dir_; }
+
+private:
+    std::string dir_;
+};
+
+class ImportanceScorer {
+public:
+    bool init(int max_blocks, float decay = 0.95f) {
+        max_blocks_ = max_blocks;
+        decay_ = decay;
+        return max_blocks > 0;
+    }
+    // d_block_scores: device memory (host memory when the engine has no device), as in the reference.
+    void update(const float* d_block_scores, int num_blocks) {
+        if (e_ && drkv_scorer_update(e_, seq_, d_block_scores, num_blocks, nullptr) != DRKV_OK)
+            std::fprintf(stderr, "[Memoria] ImportanceScorer: %s\n", drkv_last_error());
+    }
+    void sync_to_host() {
+        if (e_) drkv_scorer_sync(e_, nullptr);
+    }
+    float score(int logical_block) const {
+        if (!e_ || logical_block < 0 || logical_block >= max_blocks_) return 0.0f;   // importance_scorer.cu:86-89
+        std::string buf((size_t)max_blocks_ * sizeof(float), '\0');
+        float* f = reinterpret_cast<float*>(&buf[0]);
+        const int n = drkv_scorer_scores(e_, seq_, f, max_blocks_);
+        return logical_block < n ? f[logical_block] : 0.0f;
+    }
+    int least_important(const int* gpu_resident, int n) const {                   // importance_scorer.cu:75-87
+        if (n <= 0) return -1;
+        int min_idx = gpu_resident[0];
+        float min_score = score(min_idx);
+        for (int i = 1; i < n; i++) {
+            const float sc = score(gpu_resident[i]);
+            if (sc < min_score) {
+                min_score = sc;
+                min_idx = gpu_resident[i];
+            }
+        }
+        return min_idx;
+    }
+    void destroy() { e_ = nullptr; }
+    float decay() const { return decay_; }
+
+private:
+    friend class CacheManager;
+    drkv_engine* e_ = nullptr;
+    int seq_ = 0, max_blocks_ = 0;
+    float decay_ = 0.95f;
+};
 
 class BlockPool {
 public:
@@ -120,10 +182,19 @@ public:
     CacheManager& operator=(const CacheManager&) = delete;
 
     bool init(size_t kv_budget_bytes, const std::string& cache_dir = "",
-              int block_size = PagedKVConfig::BLOCK_SIZE, KVSwapper* = nullptr, ImportanceScorer* = nullptr) {
-        (void)cache_dir;
+              int block_size = PagedKVConfig::BLOCK_SIZE, KVSwapper* swapper = nullptr,
+              ImportanceScorer* scorer = nullptr) {
         if (!pool_.init_rows(kv_budget_bytes, block_size, 1, 0, 1)) return false;
+        if (scorer != nullptr) {                       // before the row exists, so that it starts scored
+            if (!ok(drkv_scorer_enable(pool_.e_, scorer->decay()))) return false;
+            scorer->e_ = pool_.e_;
+        }
         seq_ = drkv_seq_create(pool_.e_);
+        if (scorer != nullptr) scorer->seq_ = seq_;
+        // cache_manager.cpp:56-66, 132: stored only with a directory AND a swapper; a directory that
+        // cannot be created switches the tier off with a warning
+        if (seq_ >= 0 && swapper != nullptr && !cache_dir.empty() && drkv_tier_enable(pool_.e_, cache_dir.c_str()) != DRKV_OK)
+            std::fprintf(stderr, "[Memoria] Cannot create SSD cache dir: %s\n", cache_dir.c_str());
         return seq_ >= 0;
     }
     bool ensure_blocks_for(int pos) { return ok(drkv_seq_ensure_pos(pool_.e_, seq_, pos, nullptr)); }
@@ -141,11 +212,16 @@ public:
     int num_logical_blocks() const { return pool_.e_ ? drkv_seq_num_pages(pool_.e_, seq_) : 0; }
     int evict_blocks(int n) { return pool_.e_ ? drkv_seq_evict(pool_.e_, seq_, n) : 0; }
     bool ensure_free_blocks(int n_free) { return pool_.e_ && drkv_ensure_free(pool_.e_, seq_, n_free) == 1; }
-    void prefetch_block(int) {}
+    void prefetch_block(int logical_idx) {
+        if (pool_.e_) drkv_tier_prefetch(pool_.e_, seq_, logical_idx);
+    }
     BlockPool& block_pool() { return pool_; }
     const BlockPool& block_pool() const { return pool_; }
     int gpu_blocks_used() const { return pool_.max_blocks() - pool_.free_count(); }
-    int ssd_blocks_used() const { return 0; }
+    int ssd_blocks_used() const {
+        drkv_tier_stats st = {};
+        return (pool_.e_ && drkv_tier_get_stats(pool_.e_, &st) == DRKV_OK) ? (int)st.pages_stored : 0;
+    }
     int free_blocks() const { return pool_.free_count(); }
     void destroy() {
         pool_.destroy();

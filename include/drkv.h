@@ -83,7 +83,8 @@ typedef struct drkv_stats {
 } drkv_stats;
 
 /* One eviction, in the order it happened.  kind 0: an unreferenced cached page was
- * reclaimed (seq = logical = -1).  kind 1: a sequence discarded one of its own pages. */
+ * reclaimed (seq = logical = -1).  kind 1: a sequence discarded one of its own pages.
+ * kind 2: a sequence's page was written to the storage tier and its pool page freed. */
 typedef struct drkv_evict_record {
     int32_t kind, seq, logical, page;
 } drkv_evict_record;
@@ -236,6 +237,28 @@ DRKV_API int drkv_plan_dump(const drkv_engine* e, int32_t* out, int cap);
 /* q/out [n_seq][num_q_heads][head_dim] in the plan's batch order. */
 DRKV_API int drkv_attend_decode_planned(drkv_engine* e, int layer, const void* q, void* out,
                                         float scale, void* stream);
+/* ---- storage tier behind the pool --------------------------------------------------------------
+ * KVSwapper (kv_swapper.h:52-120, kv_swapper.cpp:179-300) and CacheManager's swap paths
+ * (cache_manager.cpp:132-141, 215-292): with a tier enabled, a page that a sequence evicts from
+ * itself is written to `dir` (row 0: block_<logical>.kv as cache_manager.cpp:211-213, other rows
+ * seq<row>_block_<logical>.kv) instead of discarded, and drkv_seq_ensure_pos / _range / _reserve on a
+ * stored page allocates a pool page (discarding, never storing, a victim if the pool is empty) and
+ * reads it back.  File = for every layer the K plane then the V plane of the page, sized from the
+ * engine's geometry (the reference sizes it from compile-time constants).  Both moves are synchronous,
+ * as in the reference.  On an engine without a device the files are empty markers. */
+typedef struct drkv_tier_stats {
+    int64_t pages_stored, swap_outs, swap_ins, bytes_out, bytes_in, prefetch_hits, page_file_bytes;
+} drkv_tier_stats;
+DRKV_API int drkv_tier_enable(drkv_engine* e, const char* dir);
+DRKV_API int drkv_tier_disable(drkv_engine* e);       /* refused while pages are stored */
+/* CacheManager::prefetch_block (cache_manager.cpp:166-180): background read of a stored page into host
+ * memory, so that the swap-in skips the file.  Returns 1 if queued, 0 if the page is not stored. */
+DRKV_API int drkv_tier_prefetch(drkv_engine* e, int seq, int logical);
+DRKV_API int drkv_tier_drain(drkv_engine* e);          /* waits for queued prefetches */
+DRKV_API int drkv_tier_get_stats(const drkv_engine* e, drkv_tier_stats* out);
+/* BlockLocation per logical page of a sequence (cache_manager.h:42-46): 0 invalid, 1 in the pool, 2 stored. */
+DRKV_API int drkv_seq_locations(const drkv_engine* e, int seq, int8_t* out, int cap);
+
 /* ---- importance-guided eviction ------------------------------------------------------------
  * ImportanceScorer (importance_scorer.h:25-67, importance_scorer.cu:27-99) attached to the eviction
  * policy (cache_manager.cpp:185-205): one fp32 score per (sequence, logical page), updated as

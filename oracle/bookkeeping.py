@@ -28,6 +28,7 @@ class Seq:
         self.len = 0
         self.table = [-1] * width
         self.order = deque()  # logical indices, oldest allocation first (lru_order_)
+        self.stored = set()   # logical pages held by the storage tier (BlockLocation::SSD)
 
 
 class BookModel:
@@ -46,6 +47,9 @@ class BookModel:
         self.cow: List[Tuple[int, int, int]] = []               # (src, dst, valid slots) device copies
         self.n_cow = 0                                          # pages replaced, with or without a copy
         self.scores = None                                      # {seq: [float per logical page]} once a scorer is attached
+        self.tier = False                                       # storage tier attached: own victims are stored, not discarded
+        self.swap_ins = []                                      # (seq, logical, page) in order
+        self.files = set()                                      # (seq, logical) files the tier holds
 
     # ---- pool ---------------------------------------------------------------------------
     def pool_alloc(self) -> int:
@@ -86,7 +90,27 @@ class BookModel:
             done += 1
         return done
 
-    def _evict_one_of(self, s: int) -> bool:
+    def _retire(self, s: int, pos_in_order: int, may_store: bool) -> None:
+        """The victim leaves the allocation order, then is stored (kind 2, cache_manager.cpp:132-141,
+        215-241) or discarded (kind 1, cache_manager.cpp:144-147)."""
+        seq = self.seqs[s]
+        idx = seq.order[pos_in_order]
+        p = seq.table[idx]
+        del seq.order[pos_in_order]
+        stored = self.tier and may_store
+        self.ref[p], self.state[p] = 0, FREE
+        self.free.append(p)
+        seq.table[idx] = -1
+        if stored:
+            seq.stored.add(idx)
+            self.files.add((s, idx))
+        else:
+            if idx in seq.stored:
+                seq.stored.discard(idx)
+                self.files.discard((s, idx))
+        self.log.append((2 if stored else 1, s, idx, p))
+
+    def _evict_one_of(self, s: int, may_store: bool = True) -> bool:
         seq = self.seqs[s]
         if self.scores is not None:
             # cache_manager.cpp:185-205 + importance_scorer.cu:75-87: lowest score among the resident
@@ -99,13 +123,7 @@ class BookModel:
                 if best < 0 or self.scores[s][idx] < self.scores[s][seq.order[best]]:
                     best = i
             if best >= 0:
-                idx = seq.order[best]
-                p = seq.table[idx]
-                del seq.order[best]
-                self.ref[p], self.state[p] = 0, FREE
-                self.free.append(p)
-                seq.table[idx] = -1
-                self.log.append((1, s, idx, p))
+                self._retire(s, best, may_store)
                 return True
         i = 0
         while i < len(seq.order):
@@ -117,25 +135,21 @@ class BookModel:
             if self.ref[p] > 1:                                 # shared with a fork: never a victim
                 i += 1
                 continue
-            del seq.order[i]
-            self.ref[p], self.state[p] = 0, FREE
-            self.free.append(p)                                 # discard path, cache_manager.cpp:144-147
-            seq.table[idx] = -1
-            self.log.append((1, s, idx, p))
+            self._retire(s, i, may_store)
             return True
         return False
 
     def _live(self, s: int) -> bool:
         return 0 <= s < len(self.seqs) and self.seqs[s] is not None
 
-    def _take(self, s: int) -> int:
+    def _take(self, s: int, may_store: bool = True) -> int:
         p = self.pool_alloc()
         if p >= 0:
             return p
         if self.lru:
             self.evict_cached(1)
             return self.pool_alloc()
-        if self.stream_evict and self._live(s) and self._evict_one_of(s):   # cache_manager.cpp:310-319
+        if self.stream_evict and self._live(s) and self._evict_one_of(s, may_store):   # cache_manager.cpp:310-319
             return self.pool_alloc()
         return -1
 
@@ -170,6 +184,8 @@ class BookModel:
         for p in self.seqs[s].table:
             if p >= 0:
                 self._unref(p, discard)
+        for idx in self.seqs[s].stored:                         # stored copies go with the sequence
+            self.files.discard((s, idx))
         self.seqs[s] = None
         return OK
 
@@ -210,6 +226,18 @@ class BookModel:
             self.ref[p] -= 1
             seq.table[idx] = fresh
             self.n_cow += 1
+            return OK
+        if self.tier and idx in seq.stored:
+            # swap_block_from_ssd (cache_manager.cpp:243-292): the page for it may cost a victim, which is
+            # discarded, never stored
+            back = self._take(s, may_store=False)
+            if back < 0:
+                return ERR_EXHAUSTED
+            seq.table[idx] = back
+            seq.stored.discard(idx)
+            self.files.discard((s, idx))                        # the pool holds the only copy again
+            seq.order.append(idx)
+            self.swap_ins.append((s, idx, back))
             return OK
         fresh = self._take(s)                                   # cache_manager.cpp:306-326
         if fresh < 0:

@@ -5,6 +5,7 @@
 #ifdef SCENARIO_USE_REFERENCE
 #include "memoria/block_pool.h"
 #include "memoria/cache_manager.h"
+#include "memoria/importance_scorer.h"
 #include "communis/log.h"
 #define PER_PAGE_BYTES ((size_t)2 * 2 * 4 * 16 * 256 * 2)   // layers * K,V * 4 heads * 16 slots * 256 dims * 2 B
 #else
@@ -81,5 +82,38 @@ int main() {
     const int eva = cm.evict_blocks(100);
     std::printf("evict_all=%d\n", eva);
     dump("end", cm, NL);
+
+    // The same manager with an importance scorer attached: victims follow the scores, ties the
+    // allocation order.  The values live in host memory, which is what "device" memory is in both
+    // builds of this scenario (CUDA stub / engine without a device).
+    ImportanceScorer scorer;
+    const bool sc_ok = scorer.init(NL, 0.5f);
+    CacheManager scored;
+    const bool scm_ok = scored.init(8 * PER_PAGE_BYTES, "", 16, nullptr, &scorer);
+    std::printf("scored init=%d %d\n", (int)sc_ok, (int)scm_ok);
+    for (int pos = 0; pos < 7 * 16; pos += 16) scored.ensure_blocks_for(pos);
+    scored.set_seq_len(7 * 16);
+    const float first[7] = {4.f, 1.f, 3.f, 1.f, 0.5f, 2.f, 0.5f};
+    scorer.update(first, 7);
+    scorer.sync_to_host();
+    std::printf("scores");
+    for (int i = 0; i < 8; i++) std::printf(" %.4f", scorer.score(i));
+    std::printf("\n");
+    std::printf("scored evict2=%d\n", scored.evict_blocks(2));
+    dump("scored after evict", scored, NL);
+    const float second[7] = {0.f, 0.f, 0.f, 8.f, 0.f, 0.f, 0.f};
+    scorer.update(second, 7);
+    scorer.sync_to_host();
+    std::printf("scores");
+    for (int i = 0; i < 8; i++) std::printf(" %.4f", scorer.score(i));
+    std::printf("\n");
+    for (int pos = 7 * 16; pos < 12 * 16; pos += 16) {      // the pool runs dry: allocation evicts by score
+        const bool more = scored.ensure_blocks_for(pos);
+        char tag[32];
+        std::snprintf(tag, sizeof tag, "scored ensure(%d)=%d", pos, (int)more);
+        dump(tag, scored, NL);
+    }
+    scored.destroy();
+    scorer.destroy();
     return 0;
 }
