@@ -58,6 +58,38 @@ struct PfSmem {
 enum { BAR_KV_FULL = 0, BAR_KV_EMPTY = kPfStages, BAR_S_READY = 2 * kPfStages, BAR_S_FREE = BAR_S_READY + 2,
        BAR_P_READY = BAR_S_FREE + 2, BAR_O_READY = BAR_P_READY + 2 };
 
+#ifdef DRKV_PF_TRACE
+// Debug build only: clock cycles the first softmax warp of each tile of CTA 0 spent per phase, summed over
+// the key blocks of the last launch: wait S, load S, math, wait O, store P; then the block count.
+__device__ long long g_pf_trace[2][6];
+__device__ long long g_pf_trace_prod[4];  // producer lane 0: wait empty, set-up, issue, blocks
+__device__ long long g_pf_trace_mma[8];
+__device__ long long g_pf_trace_fine[4];
+__device__ long long g_pf_trace_each[16];   // cycles per instruction of one QK group (8) and one PV group (4+)   // MMA thread: wait KV, wait S free 0/1, wait P 0/1, issue, blocks
+#define PF_CLK() clock64()
+#else
+#define PF_CLK() 0ll
+#endif
+
+// 2^x on the FMA pipe for x in [-126, ~9]: nearest integer by the magic-number add, degree-3 minimax of
+// 2^f on [-0.5, 0.5] (relative error 7.6e-5, below half an ulp of a bf16 or fp16 probability), exponent
+// added as an integer.  The exponential unit (16 results per clock per SM) is as loaded as the tensor
+// pipe on paper; DRKV_PF_POLY of every four pairs take this route instead.  Measured on c4: 0 -> 514,
+// 1 -> 495, 2 -> 469, 3 -> 448 TFLOP/s, i.e. the exponential unit is not what the softmax warps wait
+// for, so the default is 0.
+#ifndef DRKV_PF_POLY
+#define DRKV_PF_POLY 0
+#endif
+__device__ __forceinline__ float poly_exp2(float x) {
+    x = fmaxf(x, -126.f);
+    const float t = x + 12582912.f;                       // 1.5 * 2^23: the low mantissa bits hold round(x)
+    const float f = x - (t - 12582912.f);
+    float r = fmaf(f, 0.055205513f, 0.24261390f);
+    r = fmaf(r, f, 0.69325477f);
+    r = fmaf(r, f, 0.99992770f);
+    return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kPfThreads, 1)
 attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ PrefillParams p) {
@@ -143,70 +175,87 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem;
 
+#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT >= 7
+    const int kPfLoopBlocks = 0;                     // timing experiment: only the MMA thread runs its loop
+#else
+    const int kPfLoopBlocks = n_blocks;
+#endif
     if (warp == kPfProducerWarp) {
         // ------------------------------- TMA producer -------------------------------
         const int64_t rows_per_plane = (int64_t)p.num_kv_heads * p.page_size;
-        for (int j = 0; j < n_blocks; j++) {
+        long long pt[3] = {0, 0, 0};
+        for (int j = 0; j < kPfLoopBlocks; j++) {
             const int s = j % kPfStages, u = j / kPfStages;
             bool ok = true;
+            const long long b0 = PF_CLK();
             if (lane == 0) ok = mbar_wait(bars + 8 * (BAR_KV_EMPTY + s), (u & 1) ^ 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) {
                 if (lane == 0) { atomicExch(p.error_word, (int)KERR_WAIT_EMPTY); s_dead = 1; }
                 break;
             }
+            const long long b1 = PF_CLK();
             uint8_t* kdst = smem + PfSmem::kv + s * 2 * kPfKBytes;
             uint8_t* vdst = kdst + kPfKBytes;
-            int holes = 0;
-            uint32_t bytes = 0;
-            int pg[4];
-#pragma unroll
-            for (int gi = 0; gi < 4; gi++) {
-                const int grp = j * 4 + gi;
-                int page = -1;
-                if (grp < n_groups) {
-                    if (pages_staged) page = s_pages[grp];
-                    else {
-                        const int logical = (grp * 16) / p.page_size;
-                        page = logical < p.table_stride ? __ldg(p.tables + (int64_t)p_row * p.table_stride + logical) : -1;
-                        if (page >= p.max_pages) page = -1;
-                    }
-                }
-                pg[gi] = page;
-                if (page < 0) {
-                    holes |= 1 << gi;
-                    // nothing will be loaded: give the MMAs zeros instead of stale shared memory
-                    for (int i = lane; i < 2 * 2 * 16 * 8; i += 32) {       // K and V, 2 halves, 16 rows, 8 chunks
-                        const int kvsel = i >> 8, h = (i >> 7) & 1, r = (i >> 3) & 15, c = i & 7;
-                        uint8_t* base = (kvsel ? vdst : kdst) + h * (kPfBlockN * 128) + (gi * 16 + r) * 128 + c * 16;
-                        *reinterpret_cast<Vec16*>(base) = Vec16{{0u, 0u, 0u, 0u}};
-                    }
-                } else {
-                    bytes += 2 * 2 * 2048;
+            // Sixteen box loads per block (4 groups of 16 keys x K|V x two 64-dim halves): lane l < 16 looks
+            // up its group's page and issues its own load, so the warp pays one issue latency per block
+            // instead of sixteen (a single thread needed ~135 cycles per load).
+            const int gi = (lane >> 2) & 3, kvsel = (lane >> 1) & 1, h = lane & 1;
+            const int grp = j * 4 + gi;
+            int page = -1;
+            if (grp < n_groups) {
+                if (pages_staged) page = s_pages[grp];
+                else {
+                    const int logical = (grp * 16) / p.page_size;
+                    page = logical < p.table_stride ? __ldg(p.tables + (int64_t)p_row * p.table_stride + logical) : -1;
+                    if (page >= p.max_pages) page = -1;
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 5
+            page = -1;                                                    // timing experiment: no loads at all
+#endif
+            const unsigned missing = __ballot_sync(0xffffffffu, page < 0) & 0xffffu;   // 4 lanes per group agree
+            const int holes = ((missing >> 0) & 1) | (((missing >> 4) & 1) << 1) | (((missing >> 8) & 1) << 2) |
+                              (((missing >> 12) & 1) << 3);
+            const uint32_t bytes = (uint32_t)(16 - __popc(missing)) * 2048u;
+#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 5
+            if (false) {
+#else
+            if (holes) {
+#endif
+                // nothing will be loaded there: give the MMAs zeros instead of stale shared memory
+                for (int g4 = 0; g4 < 4; g4++) {
+                    if (!((holes >> g4) & 1)) continue;
+                    for (int i = lane; i < 2 * 2 * 16 * 8; i += 32) {       // K and V, 2 halves, 16 rows, 8 chunks
+                        const int ks = i >> 8, hh = (i >> 7) & 1, r = (i >> 3) & 15, c = i & 7;
+                        uint8_t* base = (ks ? vdst : kdst) + hh * (kPfBlockN * 128) + (g4 * 16 + r) * 128 + c * 16;
+                        *reinterpret_cast<Vec16*>(base) = Vec16{{0u, 0u, 0u, 0u}};
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
             __syncwarp();
+            const long long b2 = PF_CLK();
             if (lane == 0) {
                 s_holes[s] = holes;
                 mbar_arrive_expect_tx(bars + 8 * (BAR_KV_FULL + s), bytes);
-#pragma unroll
-                for (int gi = 0; gi < 4; gi++) {
-                    if (pg[gi] < 0) continue;
-                    const int tok = (j * 4 + gi) * 16;
-                    const int64_t rk = (((int64_t)p.layer * p.max_pages + pg[gi]) * 2) * rows_per_plane +
-                                       (int64_t)kvh * p.page_size + (tok % p.page_size);
-                    const int64_t rv = rk + rows_per_plane;
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        tma_load_2d(smem_u32(kdst) + h * (kPfBlockN * 128) + gi * 2048, &tmap, h * 64, (int)rk,
-                                    bars + 8 * (BAR_KV_FULL + s));
-                        tma_load_2d(smem_u32(vdst) + h * (kPfBlockN * 128) + gi * 2048, &tmap, h * 64, (int)rv,
-                                    bars + 8 * (BAR_KV_FULL + s));
-                    }
-                }
             }
+            __syncwarp();
+            if (lane < 16 && page >= 0) {
+                const int tok = grp * 16;
+                const int64_t row = (((int64_t)p.layer * p.max_pages + page) * 2 + kvsel) * rows_per_plane +
+                                    (int64_t)kvh * p.page_size + (tok % p.page_size);
+                tma_load_2d(smem_u32(kvsel ? vdst : kdst) + h * (kPfBlockN * 128) + gi * 2048, &tmap, h * 64, (int)row,
+                            bars + 8 * (BAR_KV_FULL + s));
+            }
+            pt[0] += b1 - b0; pt[1] += b2 - b1; pt[2] += PF_CLK() - b2;
         }
+#ifdef DRKV_PF_TRACE
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) {
+            for (int i = 0; i < 3; i++) g_pf_trace_prod[i] = pt[i];
+            g_pf_trace_prod[3] = n_blocks;
+        }
+#endif
     } else if (warp == kPfMmaWarp) {
         // ------------------------------- MMA issuer -------------------------------
         if (lane == 0) {
@@ -214,28 +263,57 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 128, kPfD, 0, 1);
             const int n_tiles = tile_b_active ? 2 : 1;
             bool dead = false;
+            long long fine[4] = {0, 0, 0, 0};   // debug builds: cycles in QK MMAs, QK commit, PV MMAs, PV commit
+            // Descriptors differ only in the start-address field of their low word (address >> 4 in bits
+            // [0,14)), so every MMA costs one add on top of the instruction itself: built once, the single
+            // issuing thread is not what the tensor pipe waits for (descriptor arithmetic per MMA cost
+            // 70-150 cycles against 32-64 of work).
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);     // SBO 1024, version 1, 128-byte swizzle
+            constexpr uint32_t kLboK = (16u >> 4) << 16;                            // K-major operands
+            constexpr uint32_t kLboV = ((uint32_t)(kPfBlockN * 128) >> 4) << 16;    // V, MN-major: next 64-dim run
+            auto mk = [](uint32_t lo, uint32_t hi) -> uint64_t { return ((uint64_t)hi << 32) | lo; };
+            const uint32_t q_lo0 = (((sbase + PfSmem::q) & 0x3FFFFu) >> 4) | kLboK;
+            const uint32_t kv_lo0 = ((sbase + PfSmem::kv) & 0x3FFFFu) >> 4;
             auto issue_qk = [&](int x, int s) {
-                const uint32_t qa = sbase + PfSmem::q + x * kPfQBytes;
-                const uint32_t kb = sbase + PfSmem::kv + s * 2 * kPfKBytes;
+                const long long f0 = PF_CLK();
+                const uint32_t qa = q_lo0 + x * (kPfQBytes >> 4);
+                const uint32_t kb = (kv_lo0 + s * (2 * kPfKBytes >> 4)) | kLboK;
+                const uint32_t d = tmem_base + kPfColS + x * kPfBlockN;
 #pragma unroll
                 for (int kk = 0; kk < kPfD / 16; kk++) {
-                    const uint32_t off_q = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-                    const uint32_t off_k = (kk >> 2) * (kPfBlockN * 128) + (kk & 3) * 32;
-                    umma_f16(tmem_base + kPfColS + x * kPfBlockN, umma_desc_sw128(qa + off_q, 16, 1024),
-                             umma_desc_sw128(kb + off_k, 16, 1024), idesc_qk, kk > 0);
+                    const uint32_t off_q = ((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4;
+                    const uint32_t off_k = ((kk >> 2) * (kPfBlockN * 128) + (kk & 3) * 32) >> 4;
+                    umma_f16(d, mk(qa + off_q, kDescHi), mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
                 }
+                const long long f1 = PF_CLK();
                 umma_commit(bars + 8 * (BAR_S_READY + x));
+                fine[0] += f1 - f0; fine[1] += PF_CLK() - f1;
             };
             auto issue_pv = [&](int x, int s, bool first_block) {
+                const long long f0 = PF_CLK();
                 const uint32_t pa = tmem_base + kPfColP + x * 64;       // hi at +0, lo at +32; 8 columns per 16 keys
-                const uint32_t vb = sbase + PfSmem::kv + s * 2 * kPfKBytes + kPfKBytes;
+                const uint32_t vb = (kv_lo0 + s * (2 * kPfKBytes >> 4) + (kPfKBytes >> 4)) | kLboV;
+                const uint32_t d = tmem_base + kPfColO + x * kPfD;
+                // Straight-line variants: between two MMAs the issuing thread executes nothing but the next
+                // descriptor add.  A run-time predicate or branch per MMA costs this lone thread 20-80 cycles
+                // each, more than the 32-64 cycles of tensor work an instruction carries.
+                const uint32_t acc0 = first_block ? 0u : 1u;
+                if (!use_lo) {
+                    umma_f16_ts(d, pa, mk(vb, kDescHi), idesc_pv, acc0);
+                    umma_f16_ts(d, pa + 8, mk(vb + 1 * (2048 >> 4), kDescHi), idesc_pv, 1u);
+                    umma_f16_ts(d, pa + 16, mk(vb + 2 * (2048 >> 4), kDescHi), idesc_pv, 1u);
+                    umma_f16_ts(d, pa + 24, mk(vb + 3 * (2048 >> 4), kDescHi), idesc_pv, 1u);
+                } else {
 #pragma unroll
-                for (int kk = 0; kk < kPfBlockN / 16; kk++) {
-                    const uint64_t vdesc = umma_desc_sw128(vb + kk * 2048, kPfBlockN * 128, 1024);
-                    umma_f16_ts(tmem_base + kPfColO + x * kPfD, pa + kk * 8, vdesc, idesc_pv, !(first_block && kk == 0));
-                    if (use_lo) umma_f16_ts(tmem_base + kPfColO + x * kPfD, pa + 32 + kk * 8, vdesc, idesc_pv, true);
+                    for (int kk = 0; kk < kPfBlockN / 16; kk++) {
+                        const uint64_t vdesc = mk(vb + kk * (2048 >> 4), kDescHi);
+                        umma_f16_ts(d, pa + kk * 8, vdesc, idesc_pv, kk == 0 ? acc0 : 1u);
+                        umma_f16_ts(d, pa + 32 + kk * 8, vdesc, idesc_pv, 1u);
+                    }
                 }
+                const long long f1 = PF_CLK();
                 umma_commit(bars + 8 * (BAR_O_READY + x));
+                fine[2] += f1 - f0; fine[3] += PF_CLK() - f1;
             };
             // S(0) for both tiles
             if (!mbar_wait(bars + 8 * (BAR_KV_FULL + 0), 0)) dead = true;
@@ -243,28 +321,91 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 tcgen05_fence_after();
                 for (int x = 0; x < n_tiles; x++) issue_qk(x, 0);
             }
+            long long mt[6] = {0, 0, 0, 0, 0, 0};
+#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 8
+            {   // timing experiment: the stand-alone probe's loop, verbatim, inside this kernel
+                constexpr uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+                const uint32_t sa = sbase;
+                const uint32_t q_lo = ((sa & 0x3FFFFu) >> 4) | (1u << 16);
+                const uint32_t kv_lo = (((sa + 64 * 1024) & 0x3FFFFu) >> 4);
+                const uint32_t iq = umma_idesc_f16(1, 128, 64, 0, 0), ip = umma_idesc_f16(1, 128, 128, 0, 1);
+                const uint32_t tmem = tmem_base;
+                const long long a2 = PF_CLK();
+                for (int j = 0; j < n_blocks; j++) {
+                    const int s = j & 3;
+                    for (int x = 0; x < 2; x++) {
+                        const uint32_t qa = q_lo + x * (32768 >> 4), kb = (kv_lo + s * (32768 >> 4)) | (1u << 16);
+#pragma unroll
+                        for (int kk = 0; kk < 8; kk++)
+                            umma_f16(tmem + 0 + x * 64, mk(qa + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), hi),
+                                     mk(kb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), hi), iq, kk > 0);
+                        umma_commit(bars + 8 * (BAR_S_READY + x));
+                    }
+                    for (int x = 0; x < 2; x++) {
+                        const uint32_t vb = (kv_lo + s * (32768 >> 4) + (16384 >> 4)) | ((8192u >> 4) << 16);
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++)
+                            umma_f16_ts(tmem + 128 + x * 128, tmem + 384 + x * 64 + kk * 8, mk(vb + kk * (2048 >> 4), hi), ip, true);
+                        umma_commit(bars + 8 * (BAR_O_READY + x));
+                    }
+                }
+                mt[5] = PF_CLK() - a2;
+                dead = true;
+            }
+#endif
+#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 7
+            {   // timing experiment: the whole MMA sequence back to back, nobody else working
+                const long long a2 = PF_CLK();
+                for (int j = 0; j < n_blocks; j++) {
+                    for (int x = 0; x < n_tiles; x++) issue_qk(x, (j + 1) % kPfStages);
+                    for (int x = 0; x < n_tiles; x++) issue_pv(x, j % kPfStages, j == 0);
+                }
+                mt[5] = PF_CLK() - a2;
+                dead = true;
+            }
+#endif
             for (int j = 0; j < n_blocks && !dead; j++) {
                 const int s = j % kPfStages;
                 // S(j+1): as soon as the softmax warps have pulled S(j) out of tensor memory
                 if (j + 1 < n_blocks) {
                     const int s1 = (j + 1) % kPfStages;
+                    const long long a0 = PF_CLK();
                     if (!mbar_wait(bars + 8 * (BAR_KV_FULL + s1), ((j + 1) / kPfStages) & 1)) { dead = true; break; }
+                    mt[0] += PF_CLK() - a0;
                     for (int x = 0; x < n_tiles && !dead; x++) {
+                        const long long a1 = PF_CLK();
                         if (!mbar_wait(bars + 8 * (BAR_S_FREE + x), j & 1)) { dead = true; break; }
+                        const long long a2 = PF_CLK();
                         tcgen05_fence_after();
                         issue_qk(x, s1);
+                        mt[1 + x] += a2 - a1;
+                        mt[5] += PF_CLK() - a2;
                     }
                     if (dead) break;
                 }
                 // O += P(j) V(j)
                 for (int x = 0; x < n_tiles && !dead; x++) {
+                    const long long a1 = PF_CLK();
                     if (!mbar_wait(bars + 8 * (BAR_P_READY + x), j & 1)) { dead = true; break; }
+                    const long long a2 = PF_CLK();
                     tcgen05_fence_after();
                     issue_pv(x, s, j == 0);
+                    mt[3 + x] += a2 - a1;
+                    mt[5] += PF_CLK() - a2;
                 }
                 if (dead) break;
                 umma_commit(bars + 8 * (BAR_KV_EMPTY + s));        // both MMAs that read this stage are done
             }
+#ifdef DRKV_PF_TRACE
+            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+                for (int i = 0; i < 6; i++) g_pf_trace_mma[i] = mt[i];
+                g_pf_trace_mma[6] = n_blocks;
+                for (int i = 0; i < 4; i++) g_pf_trace_fine[i] = fine[i];
+            }
+#endif
+#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT >= 7
+            dead = false;
+#endif
             if (dead) {
                 atomicExch(p.error_word, (int)KERR_WAIT_FULL);
                 s_dead = 1;
@@ -285,19 +426,36 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             const uint32_t t_p = tmem_base + lane_base + kPfColP + x * 64;
             float m_used = kNegBigPf, l = 0.f;
             bool dead = false;
-            for (int j = 0; j < n_blocks; j++) {
+            long long ph[5] = {0, 0, 0, 0, 0};
+            for (int j = 0; j < kPfLoopBlocks; j++) {
+                const long long c0 = PF_CLK();
                 if (!mbar_wait(bars + 8 * (BAR_S_READY + x), j & 1)) { dead = true; break; }
+                const long long c1 = PF_CLK();
                 tcgen05_fence_after();
+#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 4
+                {                                                         // timing experiment: handshakes only
+                    tcgen05_fence_before();
+                    mbar_arrive(bars + 8 * (BAR_S_FREE + x));
+                    if (j > 0 && !mbar_wait(bars + 8 * (BAR_O_READY + x), (j - 1) & 1)) { dead = true; break; }
+                    tcgen05_fence_after();
+                    tcgen05_fence_before();
+                    mbar_arrive(bars + 8 * (BAR_P_READY + x));
+                    l = 1.f;
+                    continue;
+                }
+#endif
                 float sv[2][32];
                 tmem_ld32(t_s, sv[0]);
                 tmem_ld32(t_s + 32, sv[1]);
                 tmem_wait_ld();
+                const long long c2 = PF_CLK();
                 tcgen05_fence_before();
                 mbar_arrive(bars + 8 * (BAR_S_FREE + x));               // S(j+1) may overwrite the columns now
                 const int key0 = j * kPfBlockN;
                 const int holes = s_holes[j % kPfStages];
                 // Blocks left of the diagonal with all pages present need no mask: that is almost all of them.
-                if (!((key0 + kPfBlockN <= tile_min_limit) && holes == 0)) {
+                const bool unmasked = (key0 + kPfBlockN <= tile_min_limit) && holes == 0;
+                if (!unmasked) {
 #pragma unroll
                     for (int h = 0; h < 2; h++)
 #pragma unroll
@@ -306,11 +464,16 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                             if (key0 + k >= limit || ((holes >> (k >> 4)) & 1)) sv[h][c] = -INFINITY;
                         }
                 }
-                float mx = -INFINITY;                                    // row maximum of the raw scores
+                // row maximum of the raw scores: eight independent chains instead of one 64 deep
+                float mx8[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) mx8[i] = fmaxf(sv[0][i], sv[1][i]);
 #pragma unroll
                 for (int h = 0; h < 2; h++)
 #pragma unroll
-                    for (int c = 0; c < 32; c++) mx = fmaxf(mx, sv[h][c]);
+                    for (int c = 8; c < 32; c++) mx8[c & 7] = fmaxf(mx8[c & 7], sv[h][c]);
+                float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                 fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
                 mx *= p.scale_log2;                                      // scale > 0: max commutes with it
                 // Keep the scale in use unless the row maximum outgrew it by more than 2^8.
                 float factor = 1.f;
@@ -323,16 +486,40 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 }
                 // p = 2^(s * scale_log2 - m): one FMA and one EX2 per score
                 const float neg_m = -m_used;
-                float sum = 0.f;
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};                    // independent partial sums
                 uint32_t phi[32], plo[32];
-                if (!use_lo) {
+#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 1
+                if (true) {                                               // timing experiment: no max, no exponentials
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) phi[h * 16 + (c >> 1)] = Elem<T>::pack2(sv[h][c], sv[h][c + 1]);
+                    sum4[0] = 1.f;
+                } else
+#endif
+                if (!use_lo && unmasked) {
+                    // the common block: no -inf among the scores, single-term P; part of the exponentials
+                    // are evaluated on the FMA pipe
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) {
+                            const float a0 = fmaf(sv[h][c], p.scale_log2, neg_m);
+                            const float a1 = fmaf(sv[h][c + 1], p.scale_log2, neg_m);
+                            const bool poly = ((c >> 1) & 3) < DRKV_PF_POLY;
+                            const float p0 = poly ? poly_exp2(a0) : fast_exp2(a0);
+                            const float p1 = poly ? poly_exp2(a1) : fast_exp2(a1);
+                            sum4[(c >> 1) & 3] += p0 + p1;
+                            phi[h * 16 + (c >> 1)] = Elem<T>::pack2(p0, p1);
+                        }
+                } else if (!use_lo) {
 #pragma unroll
                     for (int h = 0; h < 2; h++)
 #pragma unroll
                         for (int c = 0; c < 32; c += 2) {
                             const float p0 = fast_exp2(fmaf(sv[h][c], p.scale_log2, neg_m));
                             const float p1 = fast_exp2(fmaf(sv[h][c + 1], p.scale_log2, neg_m));
-                            sum += p0 + p1;
+                            sum4[(c >> 1) & 3] += p0 + p1;
                             phi[h * 16 + (c >> 1)] = Elem<T>::pack2(p0, p1);
                         }
                 } else {
@@ -342,14 +529,15 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                         for (int c = 0; c < 32; c += 2) {
                             const float p0 = fast_exp2(fmaf(sv[h][c], p.scale_log2, neg_m));
                             const float p1 = fast_exp2(fmaf(sv[h][c + 1], p.scale_log2, neg_m));
-                            sum += p0 + p1;
+                            sum4[(c >> 1) & 3] += p0 + p1;
                             const uint32_t hi = Elem<T>::pack2(p0, p1);
                             const float2 hf = Elem<T>::unpack2(hi);
                             phi[h * 16 + (c >> 1)] = hi;
                             plo[h * 16 + (c >> 1)] = Elem<T>::pack2(p0 - hf.x, p1 - hf.y);
                         }
                 }
-                l += sum;
+                l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                const long long c3 = PF_CLK();
                 if (j > 0) {
                     // PV(j-1) must have landed before O is touched or P is overwritten
                     if (!mbar_wait(bars + 8 * (BAR_O_READY + x), (j - 1) & 1)) { dead = true; break; }
@@ -367,13 +555,22 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                         tmem_wait_st();
                     }
                 }
+                const long long c4 = PF_CLK();
                 // P(j) into tensor memory: 64 keys = 32 packed columns (hi), then the lo term
                 tmem_st32(t_p, phi);
                 if (use_lo) tmem_st32(t_p + 32, plo);
                 tmem_wait_st();
                 tcgen05_fence_before();
                 mbar_arrive(bars + 8 * (BAR_P_READY + x));
+                const long long c5 = PF_CLK();
+                ph[0] += c1 - c0; ph[1] += c2 - c1; ph[2] += c3 - c2; ph[3] += c4 - c3; ph[4] += c5 - c4;
             }
+#ifdef DRKV_PF_TRACE
+            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp & 3) == 0 && lane == 0) {
+                for (int i = 0; i < 5; i++) g_pf_trace[x][i] = ph[i];
+                g_pf_trace[x][5] = n_blocks;
+            }
+#endif
             if (!dead && !mbar_wait(bars + 8 * (BAR_O_READY + x), (n_blocks - 1) & 1)) dead = true;
             if (dead) {
                 atomicExch(p.error_word, (int)KERR_WAIT_FULL);
@@ -410,6 +607,17 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
 }
 
 }  // namespace
+
+#ifdef DRKV_PF_TRACE
+extern "C" __attribute__((visibility("default"))) int drkv_debug_prefill_trace(long long* out) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_pf_trace, sizeof(g_pf_trace));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 12, g_pf_trace_mma, sizeof(g_pf_trace_mma));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 20, g_pf_trace_prod, sizeof(g_pf_trace_prod));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 24, g_pf_trace_fine, sizeof(g_pf_trace_fine));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 28, g_pf_trace_each, sizeof(g_pf_trace_each));
+    return (int)e;
+}
+#endif
 
 cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
                                   cudaStream_t stream) {
