@@ -33,7 +33,7 @@ constexpr int kPfStages = 4;                   // K/V blocks in flight
 constexpr int kPfSoftmaxWarps = 8;             // 4 per tile
 constexpr int kPfProducerWarp = 8;
 constexpr int kPfMmaWarp = 9;
-constexpr int kPfThreads = 10 * 32;
+constexpr int kPfThreads = 11 * 32;           // 8 softmax warps, TMA producer, one MMA issuer per tile
 constexpr int kPfTmemCols = 512;
 constexpr int kPfQBytes = 128 * kPfD * 2;      // one Q tile: [2 halves][128 rows][128 B]
 constexpr int kPfKBytes = kPfBlockN * kPfD * 2;   // K (or V) of one block: [2 halves][64 keys][128 B]
@@ -126,7 +126,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         s_dead = 0;
         for (int s = 0; s < kPfStages; s++) {
             mbar_init(bars + 8 * (BAR_KV_FULL + s), 1);
-            mbar_init(bars + 8 * (BAR_KV_EMPTY + s), 1);
+            mbar_init(bars + 8 * (BAR_KV_EMPTY + s), tile_b_active ? 2 : 1);   // one commit per issuing thread
         }
         for (int x = 0; x < 2; x++) {
             mbar_init(bars + 8 * (BAR_S_READY + x), 1);
@@ -175,16 +175,11 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem;
 
-#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT >= 7
-    const int kPfLoopBlocks = 0;                     // timing experiment: only the MMA thread runs its loop
-#else
-    const int kPfLoopBlocks = n_blocks;
-#endif
     if (warp == kPfProducerWarp) {
         // ------------------------------- TMA producer -------------------------------
         const int64_t rows_per_plane = (int64_t)p.num_kv_heads * p.page_size;
         long long pt[3] = {0, 0, 0};
-        for (int j = 0; j < kPfLoopBlocks; j++) {
+        for (int j = 0; j < n_blocks; j++) {
             const int s = j % kPfStages, u = j / kPfStages;
             bool ok = true;
             const long long b0 = PF_CLK();
@@ -211,18 +206,11 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                     if (page >= p.max_pages) page = -1;
                 }
             }
-#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 5
-            page = -1;                                                    // timing experiment: no loads at all
-#endif
             const unsigned missing = __ballot_sync(0xffffffffu, page < 0) & 0xffffu;   // 4 lanes per group agree
             const int holes = ((missing >> 0) & 1) | (((missing >> 4) & 1) << 1) | (((missing >> 8) & 1) << 2) |
                               (((missing >> 12) & 1) << 3);
             const uint32_t bytes = (uint32_t)(16 - __popc(missing)) * 2048u;
-#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 5
-            if (false) {
-#else
             if (holes) {
-#endif
                 // nothing will be loaded there: give the MMAs zeros instead of stale shared memory
                 for (int g4 = 0; g4 < 4; g4++) {
                     if (!((holes >> g4) & 1)) continue;
@@ -256,114 +244,71 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             g_pf_trace_prod[3] = n_blocks;
         }
 #endif
-    } else if (warp == kPfMmaWarp) {
-        // ------------------------------- MMA issuer -------------------------------
-        if (lane == 0) {
+    } else if (warp >= kPfMmaWarp) {
+        // ------------------------------- MMA issuers -------------------------------
+        // One thread per tile: warp kPfMmaWarp + x issues S = Q K^T and O += P V of tile x.  Each thread is
+        // a serial stream of waits, a handful of instructions and commits; two of them keep the tensor pipe
+        // fed while one waits for its softmax warps.
+        const int x = warp - kPfMmaWarp;
+        if (lane == 0 && (x == 0 || tile_b_active)) {
             constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, 128, kPfBlockN, 0, 0);
             constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 128, kPfD, 0, 1);
-            const int n_tiles = tile_b_active ? 2 : 1;
             bool dead = false;
             long long fine[4] = {0, 0, 0, 0};   // debug builds: cycles in QK MMAs, QK commit, PV MMAs, PV commit
             // Descriptors differ only in the start-address field of their low word (address >> 4 in bits
-            // [0,14)), so every MMA costs one add on top of the instruction itself: built once, the single
-            // issuing thread is not what the tensor pipe waits for (descriptor arithmetic per MMA cost
-            // 70-150 cycles against 32-64 of work).
+            // [0,14)): one add per MMA.  Between two MMAs the issuing thread executes nothing else: a run-time
+            // predicate or branch per instruction costs this lone thread 20-80 cycles, more than the 32-64
+            // cycles of tensor work an instruction carries.
             constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);     // SBO 1024, version 1, 128-byte swizzle
             constexpr uint32_t kLboK = (16u >> 4) << 16;                            // K-major operands
             constexpr uint32_t kLboV = ((uint32_t)(kPfBlockN * 128) >> 4) << 16;    // V, MN-major: next 64-dim run
             auto mk = [](uint32_t lo, uint32_t hi) -> uint64_t { return ((uint64_t)hi << 32) | lo; };
-            const uint32_t q_lo0 = (((sbase + PfSmem::q) & 0x3FFFFu) >> 4) | kLboK;
+            const uint32_t qa = ((((sbase + PfSmem::q) & 0x3FFFFu) >> 4) | kLboK) + x * (kPfQBytes >> 4);
             const uint32_t kv_lo0 = ((sbase + PfSmem::kv) & 0x3FFFFu) >> 4;
-            auto issue_qk = [&](int x, int s) {
+            const uint32_t d_s = tmem_base + kPfColS + x * kPfBlockN;
+            const uint32_t d_o = tmem_base + kPfColO + x * kPfD;
+            const uint32_t pa = tmem_base + kPfColP + x * 64;           // hi at +0, lo at +32; 8 columns per 16 keys
+            auto issue_qk = [&](int s) {
                 const long long f0 = PF_CLK();
-                const uint32_t qa = q_lo0 + x * (kPfQBytes >> 4);
                 const uint32_t kb = (kv_lo0 + s * (2 * kPfKBytes >> 4)) | kLboK;
-                const uint32_t d = tmem_base + kPfColS + x * kPfBlockN;
 #pragma unroll
                 for (int kk = 0; kk < kPfD / 16; kk++) {
                     const uint32_t off_q = ((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4;
                     const uint32_t off_k = ((kk >> 2) * (kPfBlockN * 128) + (kk & 3) * 32) >> 4;
-                    umma_f16(d, mk(qa + off_q, kDescHi), mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
+                    umma_f16(d_s, mk(qa + off_q, kDescHi), mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
                 }
                 const long long f1 = PF_CLK();
                 umma_commit(bars + 8 * (BAR_S_READY + x));
                 fine[0] += f1 - f0; fine[1] += PF_CLK() - f1;
             };
-            auto issue_pv = [&](int x, int s, bool first_block) {
+            auto issue_pv = [&](int s, bool first_block) {
                 const long long f0 = PF_CLK();
-                const uint32_t pa = tmem_base + kPfColP + x * 64;       // hi at +0, lo at +32; 8 columns per 16 keys
                 const uint32_t vb = (kv_lo0 + s * (2 * kPfKBytes >> 4) + (kPfKBytes >> 4)) | kLboV;
-                const uint32_t d = tmem_base + kPfColO + x * kPfD;
-                // Straight-line variants: between two MMAs the issuing thread executes nothing but the next
-                // descriptor add.  A run-time predicate or branch per MMA costs this lone thread 20-80 cycles
-                // each, more than the 32-64 cycles of tensor work an instruction carries.
                 const uint32_t acc0 = first_block ? 0u : 1u;
                 if (!use_lo) {
-                    umma_f16_ts(d, pa, mk(vb, kDescHi), idesc_pv, acc0);
-                    umma_f16_ts(d, pa + 8, mk(vb + 1 * (2048 >> 4), kDescHi), idesc_pv, 1u);
-                    umma_f16_ts(d, pa + 16, mk(vb + 2 * (2048 >> 4), kDescHi), idesc_pv, 1u);
-                    umma_f16_ts(d, pa + 24, mk(vb + 3 * (2048 >> 4), kDescHi), idesc_pv, 1u);
+                    umma_f16_ts(d_o, pa, mk(vb, kDescHi), idesc_pv, acc0);
+                    umma_f16_ts(d_o, pa + 8, mk(vb + 1 * (2048 >> 4), kDescHi), idesc_pv, 1u);
+                    umma_f16_ts(d_o, pa + 16, mk(vb + 2 * (2048 >> 4), kDescHi), idesc_pv, 1u);
+                    umma_f16_ts(d_o, pa + 24, mk(vb + 3 * (2048 >> 4), kDescHi), idesc_pv, 1u);
                 } else {
 #pragma unroll
                     for (int kk = 0; kk < kPfBlockN / 16; kk++) {
                         const uint64_t vdesc = mk(vb + kk * (2048 >> 4), kDescHi);
-                        umma_f16_ts(d, pa + kk * 8, vdesc, idesc_pv, kk == 0 ? acc0 : 1u);
-                        umma_f16_ts(d, pa + 32 + kk * 8, vdesc, idesc_pv, 1u);
+                        umma_f16_ts(d_o, pa + kk * 8, vdesc, idesc_pv, kk == 0 ? acc0 : 1u);
+                        umma_f16_ts(d_o, pa + 32 + kk * 8, vdesc, idesc_pv, 1u);
                     }
                 }
                 const long long f1 = PF_CLK();
                 umma_commit(bars + 8 * (BAR_O_READY + x));
                 fine[2] += f1 - f0; fine[3] += PF_CLK() - f1;
             };
-            // S(0) for both tiles
+            // S(0)
             if (!mbar_wait(bars + 8 * (BAR_KV_FULL + 0), 0)) dead = true;
             if (!dead) {
                 tcgen05_fence_after();
-                for (int x = 0; x < n_tiles; x++) issue_qk(x, 0);
+                issue_qk(0);
             }
             long long mt[6] = {0, 0, 0, 0, 0, 0};
-#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 8
-            {   // timing experiment: the stand-alone probe's loop, verbatim, inside this kernel
-                constexpr uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-                const uint32_t sa = sbase;
-                const uint32_t q_lo = ((sa & 0x3FFFFu) >> 4) | (1u << 16);
-                const uint32_t kv_lo = (((sa + 64 * 1024) & 0x3FFFFu) >> 4);
-                const uint32_t iq = umma_idesc_f16(1, 128, 64, 0, 0), ip = umma_idesc_f16(1, 128, 128, 0, 1);
-                const uint32_t tmem = tmem_base;
-                const long long a2 = PF_CLK();
-                for (int j = 0; j < n_blocks; j++) {
-                    const int s = j & 3;
-                    for (int x = 0; x < 2; x++) {
-                        const uint32_t qa = q_lo + x * (32768 >> 4), kb = (kv_lo + s * (32768 >> 4)) | (1u << 16);
-#pragma unroll
-                        for (int kk = 0; kk < 8; kk++)
-                            umma_f16(tmem + 0 + x * 64, mk(qa + (((kk >> 2) * 16384 + (kk & 3) * 32) >> 4), hi),
-                                     mk(kb + (((kk >> 2) * 8192 + (kk & 3) * 32) >> 4), hi), iq, kk > 0);
-                        umma_commit(bars + 8 * (BAR_S_READY + x));
-                    }
-                    for (int x = 0; x < 2; x++) {
-                        const uint32_t vb = (kv_lo + s * (32768 >> 4) + (16384 >> 4)) | ((8192u >> 4) << 16);
-#pragma unroll
-                        for (int kk = 0; kk < 4; kk++)
-                            umma_f16_ts(tmem + 128 + x * 128, tmem + 384 + x * 64 + kk * 8, mk(vb + kk * (2048 >> 4), hi), ip, true);
-                        umma_commit(bars + 8 * (BAR_O_READY + x));
-                    }
-                }
-                mt[5] = PF_CLK() - a2;
-                dead = true;
-            }
-#endif
-#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 7
-            {   // timing experiment: the whole MMA sequence back to back, nobody else working
-                const long long a2 = PF_CLK();
-                for (int j = 0; j < n_blocks; j++) {
-                    for (int x = 0; x < n_tiles; x++) issue_qk(x, (j + 1) % kPfStages);
-                    for (int x = 0; x < n_tiles; x++) issue_pv(x, j % kPfStages, j == 0);
-                }
-                mt[5] = PF_CLK() - a2;
-                dead = true;
-            }
-#endif
             for (int j = 0; j < n_blocks && !dead; j++) {
                 const int s = j % kPfStages;
                 // S(j+1): as soon as the softmax warps have pulled S(j) out of tensor memory
@@ -371,40 +316,28 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                     const int s1 = (j + 1) % kPfStages;
                     const long long a0 = PF_CLK();
                     if (!mbar_wait(bars + 8 * (BAR_KV_FULL + s1), ((j + 1) / kPfStages) & 1)) { dead = true; break; }
-                    mt[0] += PF_CLK() - a0;
-                    for (int x = 0; x < n_tiles && !dead; x++) {
-                        const long long a1 = PF_CLK();
-                        if (!mbar_wait(bars + 8 * (BAR_S_FREE + x), j & 1)) { dead = true; break; }
-                        const long long a2 = PF_CLK();
-                        tcgen05_fence_after();
-                        issue_qk(x, s1);
-                        mt[1 + x] += a2 - a1;
-                        mt[5] += PF_CLK() - a2;
-                    }
-                    if (dead) break;
-                }
-                // O += P(j) V(j)
-                for (int x = 0; x < n_tiles && !dead; x++) {
                     const long long a1 = PF_CLK();
-                    if (!mbar_wait(bars + 8 * (BAR_P_READY + x), j & 1)) { dead = true; break; }
+                    if (!mbar_wait(bars + 8 * (BAR_S_FREE + x), j & 1)) { dead = true; break; }
                     const long long a2 = PF_CLK();
                     tcgen05_fence_after();
-                    issue_pv(x, s, j == 0);
-                    mt[3 + x] += a2 - a1;
-                    mt[5] += PF_CLK() - a2;
+                    issue_qk(s1);
+                    mt[0] += a1 - a0; mt[1] += a2 - a1; mt[5] += PF_CLK() - a2;
                 }
-                if (dead) break;
-                umma_commit(bars + 8 * (BAR_KV_EMPTY + s));        // both MMAs that read this stage are done
+                // O += P(j) V(j)
+                const long long a1 = PF_CLK();
+                if (!mbar_wait(bars + 8 * (BAR_P_READY + x), j & 1)) { dead = true; break; }
+                const long long a2 = PF_CLK();
+                tcgen05_fence_after();
+                issue_pv(s, j == 0);
+                mt[3] += a2 - a1; mt[5] += PF_CLK() - a2;
+                umma_commit(bars + 8 * (BAR_KV_EMPTY + s));        // this tile's MMAs that read the stage are done
             }
 #ifdef DRKV_PF_TRACE
-            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && x == 0) {
                 for (int i = 0; i < 6; i++) g_pf_trace_mma[i] = mt[i];
                 g_pf_trace_mma[6] = n_blocks;
                 for (int i = 0; i < 4; i++) g_pf_trace_fine[i] = fine[i];
             }
-#endif
-#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT >= 7
-            dead = false;
 #endif
             if (dead) {
                 atomicExch(p.error_word, (int)KERR_WAIT_FULL);
@@ -427,23 +360,11 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             float m_used = kNegBigPf, l = 0.f;
             bool dead = false;
             long long ph[5] = {0, 0, 0, 0, 0};
-            for (int j = 0; j < kPfLoopBlocks; j++) {
+            for (int j = 0; j < n_blocks; j++) {
                 const long long c0 = PF_CLK();
                 if (!mbar_wait(bars + 8 * (BAR_S_READY + x), j & 1)) { dead = true; break; }
                 const long long c1 = PF_CLK();
                 tcgen05_fence_after();
-#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 4
-                {                                                         // timing experiment: handshakes only
-                    tcgen05_fence_before();
-                    mbar_arrive(bars + 8 * (BAR_S_FREE + x));
-                    if (j > 0 && !mbar_wait(bars + 8 * (BAR_O_READY + x), (j - 1) & 1)) { dead = true; break; }
-                    tcgen05_fence_after();
-                    tcgen05_fence_before();
-                    mbar_arrive(bars + 8 * (BAR_P_READY + x));
-                    l = 1.f;
-                    continue;
-                }
-#endif
                 float sv[2][32];
                 tmem_ld32(t_s, sv[0]);
                 tmem_ld32(t_s + 32, sv[1]);
@@ -488,15 +409,6 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 const float neg_m = -m_used;
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};                    // independent partial sums
                 uint32_t phi[32], plo[32];
-#if defined(DRKV_PF_EXPERIMENT) && DRKV_PF_EXPERIMENT == 1
-                if (true) {                                               // timing experiment: no max, no exponentials
-#pragma unroll
-                    for (int h = 0; h < 2; h++)
-#pragma unroll
-                        for (int c = 0; c < 32; c += 2) phi[h * 16 + (c >> 1)] = Elem<T>::pack2(sv[h][c], sv[h][c + 1]);
-                    sum4[0] = 1.f;
-                } else
-#endif
                 if (!use_lo && unmasked) {
                     // the common block: no -inf among the scores, single-term P; part of the exponentials
                     // are evaluated on the FMA pipe
