@@ -295,12 +295,8 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     const uint32_t dst = smem_u32(smem + ring * SLOT_BYTES);
                     const int64_t rk = (((int64_t)p.layer * p.max_pages + page) * 2) * rows_per_plane +
                                        (int64_t)c_kvh * p.page_size + (tok0 % p.page_size);
-                    const int64_t rv = rk + rows_per_plane;
-#pragma unroll
-                    for (int h = 0; h < NH; h++) {
-                        tma_load_2d(dst + h * 2048, &tmap, h * 64, (int)rk, bar_full + 8 * ring);
-                        tma_load_2d(dst + TILE_BYTES + h * 2048, &tmap, h * 64, (int)rv, bar_full + 8 * ring);
-                    }
+                    // one box: 16 key rows x the whole head dim x the K and the V plane (8 KB at D = 128)
+                    tma_load_4d(dst, &tmap, 0, 0, (int)rk, 0, bar_full + 8 * ring);
                 }
             }
             if (++i_slot == DEPTH) i_slot = 0;
@@ -394,7 +390,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 for (int i = lane; i < kGroupTokens * NH * 8; i += 32) {
                     const int r = i / (NH * 8), c = i - r * (NH * 8);
                     if (r >= v_hi || r < v_lo)
-                        *reinterpret_cast<Vec16*>(vt + (c >> 3) * 2048 + swz(r, c & 7)) = Vec16{{0u, 0u, 0u, 0u}};
+                        *reinterpret_cast<Vec16*>(vt + swz_rows(r, c, NH * 128)) = Vec16{{0u, 0u, 0u, 0u}};
                 }
                 __syncwarp();
             }
@@ -408,7 +404,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 for (int kk = 0; kk < KSTEPS; kk++) {
                     const int c = 2 * kk + (mi & 1);
                     uint32_t kb[4];
-                    ldmatrix_x4(kb, kbase + (c >> 3) * 2048 + swz(key, c & 7));
+                    ldmatrix_x4(kb, kbase + swz_rows(key, c, NH * 128));
                     Mma<T>::run(s0[0], s0[1], s0[2], s0[3], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], kb[0], kb[1]);
                     Mma<T>::run(s1[0], s1[1], s1[2], s1[3], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], kb[2], kb[3]);
                 }
@@ -463,7 +459,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 for (int j = 0; j < NT; j += 2) {
                     const int c = j + (mi >> 1);
                     uint32_t vb[4];
-                    ldmatrix_x4_trans(vb, vbase + (c >> 3) * 2048 + swz(key, c & 7));
+                    ldmatrix_x4_trans(vb, vbase + swz_rows(key, c, NH * 128));
                     if (HI) {
                         Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], phi[0], phi[1], phi[2], phi[3], vb[0], vb[1]);
                         Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[0], vb[1]);
@@ -760,6 +756,44 @@ bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, in
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         if (err) *err = "cuTensorMapEncodeTiled failed";
+        return false;
+    }
+    return true;
+}
+
+// Decode's descriptor: the pool as [plane offset 0/1][head row][64-dim half][64 elements], so that one box
+// of {64, D/64, 16, 2} brings 16 key rows of one head, all dims, K and V (the V plane of a page starts
+// num_kv_heads * page_size rows after its K plane).  The row dimension stops one plane short of the end so
+// that plane offset 1 stays inside the pool.  Shared-memory image: K rows then V rows, full rows of D * 2
+// bytes, 128-byte swizzle.
+bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages, int num_kv_heads,
+                               int page_size, int head_dim, const char** err) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) {
+        if (err) *err = "cuTensorMapEncodeTiled is not available from this driver";
+        return false;
+    }
+    EncodeFn encode = reinterpret_cast<EncodeFn>(fn);
+    const uint64_t plane_rows = (uint64_t)num_kv_heads * page_size;
+    const uint64_t rows = (uint64_t)num_layers * max_pages * 2 * plane_rows;
+    if (rows >= (1ull << 31)) {
+        if (err) *err = "pool has more than 2^31 head rows: not addressable by one TMA descriptor";
+        return false;
+    }
+    const int nh = head_dim / 64;
+    cuuint64_t gdim[4] = {64, (cuuint64_t)nh, (cuuint64_t)(rows - plane_rows), 2};
+    cuuint64_t gstride[3] = {128, (cuuint64_t)head_dim * 2, (cuuint64_t)plane_rows * head_dim * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)nh, 16, 2};
+    cuuint32_t estride[4] = {1, 1, 1, 1};
+    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(pool), gdim, gstride, box, estride,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        if (err) *err = "cuTensorMapEncodeTiled (decode slot descriptor) failed";
         return false;
     }
     return true;

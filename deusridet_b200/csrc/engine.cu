@@ -113,7 +113,8 @@ struct drkv_engine {
     int* d_error = nullptr;
     float* d_scratch = nullptr;
     size_t scratch_bytes = 0;
-    CUtensorMap tmap{};
+    CUtensorMap tmap{};        // 2-D view, 16-row x 64-element boxes: the prefill kernel's
+    CUtensorMap tmap_slot{};   // 4-D view, one box per 16 keys x head_dim x (K, V): the decode kernel's
     PoolLayout layout{};
     int forced_chunk = 0;
     int num_sms = 148;
@@ -286,6 +287,12 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
         const char* terr = nullptr;
         if (!make_pool_tensor_map(&e->tmap, e->pool, geom->num_layers, (int)max_pages, geom->num_kv_heads,
                                   geom->page_size, geom->head_dim, &terr)) {
+            set_err(DRKV_ERR_CUDA, "%s", terr ? terr : "tensor map");
+            drkv_destroy(e);
+            return DRKV_ERR_CUDA;
+        }
+        if (!make_pool_slot_tensor_map(&e->tmap_slot, e->pool, geom->num_layers, (int)max_pages, geom->num_kv_heads,
+                                       geom->page_size, geom->head_dim, &terr)) {
             set_err(DRKV_ERR_CUDA, "%s", terr ? terr : "tensor map");
             drkv_destroy(e);
             return DRKV_ERR_CUDA;
@@ -796,7 +803,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     p.error_word = e->d_error;
     const bool timed = e->timing && e->tev_used + 2 <= e->tev.size();
     if (timed) CUDA_TRY(cudaEventRecord(e->tev[e->tev_used], stream));
-    CUDA_TRY(launch_attend_decode(e->tmap, p, e->num_sms, g.head_dim, g.dtype, stream));
+    CUDA_TRY(launch_attend_decode(e->tmap_slot, p, e->num_sms, g.head_dim, g.dtype, stream));
     if (timed) {
         CUDA_TRY(cudaEventRecord(e->tev[e->tev_used + 1], stream));
         e->tev_used += 2;

@@ -120,6 +120,10 @@ cudaError_t launch_flat_paged_copy(const FlatCopyParams& p, bool to_flat, int nu
 bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
                           int num_kv_heads, int page_size, int head_dim, const char** err);
 
+// The decode kernel's descriptor: 4-D view whose one box is 16 key rows x head_dim x (K, V).
+bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
+                               int num_kv_heads, int page_size, int head_dim, const char** err);
+
 cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,
                                  int dtype, cudaStream_t stream);
 constexpr int kMaxDecodeSeqs = 2048;   // sequences one decode-attention launch can take

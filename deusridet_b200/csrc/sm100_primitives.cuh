@@ -55,6 +55,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -76,6 +82,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // the 16-byte chunk index is XORed with the row index modulo 8 (tile base 1024-aligned).
 __device__ __forceinline__ uint32_t swz(int row, int chunk16) {
     return (uint32_t)(row * 128 + ((chunk16 ^ (row & 7)) << 4));
+}
+
+// Byte offset of 16-byte chunk `chunk16` (0 .. row_bytes/16) of row `row` in a tile of full rows
+// ([row][row_bytes], row_bytes a multiple of 128) written by TMA with 128-byte swizzle: within every
+// 128-byte segment the chunk index is XORed with bits 7-9 of the offset (tile base 1024-aligned).
+__device__ __forceinline__ uint32_t swz_rows(int row, int chunk16, int row_bytes) {
+    const uint32_t seg = (uint32_t)(row * row_bytes) + (uint32_t)(chunk16 >> 3) * 128u;
+    return seg + ((((uint32_t)chunk16 & 7u) ^ ((seg >> 7) & 7u)) << 4);
 }
 
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {

@@ -58,7 +58,7 @@ int stateless_decode(const drkv_geometry* g, const void* q, const void* kv_pool,
         return fail(DRKV_ERR_NO_DEVICE, "no CUDA device is current");
     CUtensorMap tmap;
     const char* terr = nullptr;
-    if (!make_pool_tensor_map(&tmap, kv_pool, g->num_layers, max_pages, g->num_kv_heads, g->page_size, g->head_dim, &terr))
+    if (!make_pool_slot_tensor_map(&tmap, kv_pool, g->num_layers, max_pages, g->num_kv_heads, g->page_size, g->head_dim, &terr))
         return fail(DRKV_ERR_CUDA, terr ? terr : "tensor map");
     // header: [0] queue head, [1] error word, [2] exit count; all start at zero for every call
     if (cudaMemsetAsync(scratch, 0, kStatelessHeaderBytes, stream) != cudaSuccess)
