@@ -706,6 +706,7 @@ def cpu_pass(w, lens, repeats, seed=5):
     returns seconds per layer-pass and the thread count."""
     from oracle import cbind as ob
     ob.lib()
+    ob.use_all_cores()                                   # torchrun exports OMP_NUM_THREADS=1
     hq, hkv, d, page = w["hq"], w["hkv"], w["d"], w["page"]
     n_seq = len(lens)
     g = ob.geom(1, hq, hkv, d, page, ob.BF16, d, w["theta"])

@@ -164,3 +164,11 @@ def inject(g: Geom, pool, src, max_pages, table, start_token, num_tokens):
 
 def num_threads() -> int:
     return lib().okv_num_threads()
+
+
+def use_all_cores() -> int:
+    """Sets the OpenMP team to the cores this process may run on (whatever OMP_NUM_THREADS said); returns it."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().okv_set_num_threads(n)
+    return num_threads()

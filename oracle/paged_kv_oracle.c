@@ -453,6 +453,15 @@ void okv_inject(const okv_geom* g, uint16_t* pool, const uint16_t* src, int max_
             }
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; a timed baseline asks for the host's cores itself. */
+void okv_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int okv_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
