@@ -400,11 +400,24 @@ def run_c5a(args):
     d_pos = torch.tensor([S - 1], dtype=torch.int32, device=dev)     # the token being decoded sits at S - 1
     owner = sharding.owner_of_position(S - 1, S, page, world)
     scale = 1.0 / float(np.sqrt(d))
+    use_peer = args.collective == "peer"
+    if use_peer:
+        # exchange areas: one CUDA IPC handle per rank, passed around once through the process group
+        handle = torch.frombuffer(bytearray(eng.exchange_create(world, rank)), dtype=torch.uint8).to(dev)
+        handles = torch.empty(world, 64, dtype=torch.uint8, device=dev)
+        if world > 1:
+            dist.all_gather_into_tensor(handles, handle)
+        else:
+            handles[0] = handle
+        eng.exchange_connect([bytes(h.cpu().numpy().tobytes()) for h in handles])
 
     def step():
         for l in range(L):
             if rank == owner:
                 eng.append_rope(l, 1, d_rows, d_pos, kn[l], vn[l], stream)
+            if use_peer:
+                eng.attend_exchange(l, s, begin, end, q[l], out[l], scale, stream)   # partial, peer stores, merge
+                continue
             eng.attend_partial(l, s, begin, end, q[l], mine, scale, stream)
             if world > 1:
                 dist.all_gather_into_tensor(gathered, mine)
@@ -440,6 +453,9 @@ def run_c5a(args):
     step()
     kms, kn_l = eng.kernel_timing(False, read=True)
     eng.check_kernels()
+    if use_peer:
+        barrier()                                                    # nobody tears down while a peer may still push
+        eng.exchange_destroy()
     eng.close()
     kv_rank = float(end - begin) * 2 * hkv * d * 2                   # this rank's K/V bytes per layer
     peak, peak_kind = peaks()
@@ -451,7 +467,10 @@ def run_c5a(args):
                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                "dtype": "bf16", "data": "synthetic",
                "config": {"workload": f"c5a: {w['desc']}", "layers": L, "keys_per_gpu": end - begin,
-                          "parallelism": f"kv-range-split x{world}", "collective": "nccl all_gather of Hq*(D+2) fp32 per layer",
+                          "parallelism": f"kv-range-split x{world}",
+                          "collective": ("partials pushed to every rank by peer stores + per-head flags, merged in the same "
+                                         "kernel (no library collective)") if use_peer
+                          else "nccl all_gather of Hq*(D+2) fp32 per layer",
                           "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer per GPU" % (kv_rank / 1e9)},
                "hbm_gbs_step": world * kv_rank * L / (ms_step * 1e-3) / 1e9,
                "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
@@ -787,6 +806,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling a small case)")
     ap.add_argument("--seqs", type=int, default=0, help="override sequences per GPU (profiling a small case)")
     ap.add_argument("--chunk", type=int, default=0, help="keys per split-KV chunk (0 = automatic)")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="c5a: fused peer-store exchange + merge kernel, or NCCL all-gather + merge")
     ap.add_argument("--scorer", action="store_true", help="c2/c5b: also produce per-page attention mass and scores")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -115,6 +115,10 @@ SIGNATURES = {
     "drkv_scorer_scores": (_i, [_vp, _i, C.POINTER(C.c_float), _i]),
     "drkv_attend_prefill_chunk": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_attend_prefill_batch": (_i, [_vp, _i, _i, _pi32, _pi32, _pi32, C.POINTER(_vp), C.POINTER(_vp), _f, _vp]),
+    "drkv_exchange_create": (_i, [_vp, _i, _i, C.POINTER(C.c_uint8)]),
+    "drkv_exchange_connect": (_i, [_vp, C.POINTER(C.c_uint8)]),
+    "drkv_exchange_destroy": (_i, [_vp]),
+    "drkv_attend_exchange": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_attend_partial": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_combine_partials": (_i, [_vp, _i, _vp, _vp, _vp]),
     "drkv_partial_floats": (_sz, [_vp]),

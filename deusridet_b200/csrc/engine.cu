@@ -162,6 +162,17 @@ struct drkv_engine {
         std::vector<std::pair<int, int>> pending;    // rows to reset (src = -1) or copy from src, at the next stream call
     } scorer;
 
+    // cross-GPU exchange of one sequence's split-KV partials (off until drkv_exchange_create)
+    struct Exchange {
+        int world = 0, rank = 0;
+        uint32_t seq_no = 0;
+        void* area = nullptr;                        // this rank's slots + flags, one allocation
+        size_t flags_offset = 0;
+        void* peer_area[kMaxExchangeRanks] = {};     // every rank's area as mapped here (own = area)
+        bool connected = false;
+        float* d_partial = nullptr;                  // this rank's partial of the current call
+    } xchg;
+
     // storage tier behind the pool (off until drkv_tier_enable)
     std::unique_ptr<PageStore> store;
     cudaStream_t last_stream = nullptr;              // stream of the most recent kernel launches
@@ -208,6 +219,8 @@ static int run_cow(drkv_engine* e, const std::vector<CowJob>& jobs, cudaStream_t
 }
 
 extern "C" {
+
+static void exchange_release(drkv_engine* e);
 
 const char* drkv_last_error(void) { return g_err.c_str(); }
 
@@ -306,6 +319,11 @@ void drkv_destroy(drkv_engine* e) {
     if (!e) return;
     e->book.attach_tier(nullptr);
     e->store.reset();                                // joins the prefetch thread; stored files stay on disk
+    if (e->has_device) {
+        cudaSetDevice(e->device);
+        cudaDeviceSynchronize();
+        exchange_release(e);
+    }
     if (e->has_device) {
         cudaSetDevice(e->device);
         cudaDeviceSynchronize();
@@ -623,7 +641,7 @@ int drkv_kernel_error(drkv_engine* e) {
     CUDA_TRY(cudaMemcpy(&code, e->d_error, sizeof(int), cudaMemcpyDeviceToHost));
     if (code != 0) {
         cudaMemset(e->d_error, 0, sizeof(int));
-        return set_err(DRKV_ERR_CUDA, "a kernel reported error code %d (1 = load wait, 2 = ring wait, 3 = page id)", code);
+        return set_err(DRKV_ERR_CUDA, "a kernel reported error code %d (1 = load wait, 2 = ring wait, 3 = page id, 4 = peer wait)", code);
     }
     return DRKV_OK;
 }
@@ -1193,6 +1211,101 @@ int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begin, int kv
     if (span < 1) span = 1;   // an empty range still has to produce the (-1e20, 0, 0) partial
     return decode_common(e, layer, 1, nullptr, nullptr, seq, kv_begin, kv_end, span, q, nullptr, part, scale,
                          (cudaStream_t)stream);
+}
+
+// ---- cross-GPU exchange ---------------------------------------------------------------------
+static void exchange_release(drkv_engine* e) {
+    drkv_engine::Exchange& x = e->xchg;
+    for (int r = 0; r < x.world; r++)
+        if (x.connected && r != x.rank && x.peer_area[r]) cudaIpcCloseMemHandle(x.peer_area[r]);
+    if (x.area) cudaFree(x.area);
+    if (x.d_partial) cudaFree(x.d_partial);
+    x = drkv_engine::Exchange();
+}
+
+int drkv_exchange_create(drkv_engine* e, int world, int rank, uint8_t* handle_out) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (world < 1 || world > kMaxExchangeRanks || rank < 0 || rank >= world || !handle_out)
+        return set_err(DRKV_ERR_INVALID, "exchange_create: bad argument (at most %d ranks)", kMaxExchangeRanks);
+    static_assert(sizeof(cudaIpcMemHandle_t) == DRKV_IPC_HANDLE_BYTES, "IPC handle size");
+    LOCK(e);
+    CUDA_TRY(cudaSetDevice(e->device));
+    exchange_release(e);
+    drkv_engine::Exchange& x = e->xchg;
+    const size_t per_rank = (size_t)e->geom.num_q_heads * (e->geom.head_dim + 2) * sizeof(float);
+    x.flags_offset = (2 * (size_t)world * per_rank + 255) / 256 * 256;
+    const size_t bytes = x.flags_offset + (size_t)world * e->geom.num_q_heads * sizeof(uint32_t);
+    CUDA_TRY(cudaMalloc(&x.area, bytes));
+    CUDA_TRY(cudaMemset(x.area, 0, bytes));
+    CUDA_TRY(cudaMalloc(&x.d_partial, per_rank));
+    CUDA_TRY(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t h;
+    CUDA_TRY(cudaIpcGetMemHandle(&h, x.area));
+    memcpy(handle_out, &h, sizeof(h));
+    x.world = world;
+    x.rank = rank;
+    x.peer_area[rank] = x.area;
+    return DRKV_OK;
+}
+
+int drkv_exchange_connect(drkv_engine* e, const uint8_t* handles) {
+    NEED(e);
+    NEED_DEVICE(e);
+    LOCK(e);
+    drkv_engine::Exchange& x = e->xchg;
+    if (x.world == 0 || !handles) return set_err(DRKV_ERR_STATE, "exchange_connect: no exchange area / null handles");
+    CUDA_TRY(cudaSetDevice(e->device));
+    for (int r = 0; r < x.world; r++) {
+        if (r == x.rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * DRKV_IPC_HANDLE_BYTES, sizeof(h));
+        CUDA_TRY(cudaIpcOpenMemHandle(&x.peer_area[r], h, cudaIpcMemLazyEnablePeerAccess));
+    }
+    x.connected = true;
+    return DRKV_OK;
+}
+
+int drkv_exchange_destroy(drkv_engine* e) {
+    NEED(e);
+    NEED_DEVICE(e);
+    LOCK(e);
+    CUDA_TRY(cudaSetDevice(e->device));
+    CUDA_TRY(cudaDeviceSynchronize());
+    exchange_release(e);
+    return DRKV_OK;
+}
+
+int drkv_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end, const void* q, void* out,
+                         float scale, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    drkv_engine::Exchange& x = e->xchg;
+    if (x.world == 0 || (x.world > 1 && !x.connected))
+        return set_err(DRKV_ERR_STATE, "attend_exchange: create and connect the exchange first");
+    if (layer < 0 || layer >= e->geom.num_layers || seq < 0 || seq >= e->book.max_seqs() || kv_begin < 0 || !q || !out)
+        return set_err(DRKV_ERR_INVALID, "attend_exchange: bad argument");
+    int span = kv_end - (kv_begin / 16) * 16;
+    if (span < 1) span = 1;
+    int rc = decode_common(e, layer, 1, nullptr, nullptr, seq, kv_begin, kv_end, span, q, nullptr, x.d_partial, scale,
+                           (cudaStream_t)stream);
+    if (rc != DRKV_OK) return rc;
+    ExchangeParams p{};
+    for (int r = 0; r < x.world; r++) {
+        p.peer_slots[r] = static_cast<float*>(x.peer_area[r]);
+        p.peer_flags[r] = reinterpret_cast<uint32_t*>(static_cast<char*>(x.peer_area[r]) + x.flags_offset);
+    }
+    p.local_partial = x.d_partial;
+    p.out = out;
+    p.world = x.world;
+    p.rank = x.rank;
+    p.seq_no = ++x.seq_no;
+    p.parity = (int)(p.seq_no & 1u);
+    p.num_q_heads = e->geom.num_q_heads;
+    p.head_dim = e->geom.head_dim;
+    p.error_word = e->d_error;
+    CUDA_TRY(launch_exchange_merge(p, e->geom.dtype, (cudaStream_t)stream));
+    return DRKV_OK;
 }
 
 int drkv_combine_partials(drkv_engine* e, int n_parts, const float* parts, void* out, void* stream) {

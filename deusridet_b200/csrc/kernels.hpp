@@ -111,6 +111,19 @@ cudaError_t launch_page_mass(const PageMassParams& p, int n_seq, int max_kv_len,
 cudaError_t launch_importance_update(float* scores, float* fresh, int64_t n, float decay, cudaStream_t stream);
 cudaError_t launch_importance_add(float* scores, const float* new_scores, int n, float decay, cudaStream_t stream);
 
+// Cross-GPU merge of one sequence's split-KV partials by peer stores (exchange.cu).
+constexpr int kMaxExchangeRanks = 16;
+struct ExchangeParams {
+    float* peer_slots[kMaxExchangeRanks];       // every rank's slot area, as mapped into this process
+    uint32_t* peer_flags[kMaxExchangeRanks];    // every rank's flag array
+    const float* local_partial;                 // [Hq*D o | Hq m | Hq l] of this rank
+    void* out;                                  // [Hq][D], storage type
+    int world, rank, parity, num_q_heads, head_dim;
+    uint32_t seq_no;
+    int* error_word;
+};
+cudaError_t launch_exchange_merge(const ExchangeParams& p, int dtype, cudaStream_t stream);
+
 cudaError_t launch_append_rope(const AppendParams& p, int n_tokens, int dtype, cudaStream_t stream);
 cudaError_t launch_cow_copy(const CowParams& p, int num_layers, cudaStream_t stream);
 cudaError_t launch_flat_paged_copy(const FlatCopyParams& p, bool to_flat, int num_sms, cudaStream_t stream);

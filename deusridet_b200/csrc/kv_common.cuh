@@ -162,6 +162,6 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 
 // Error word shared by all kernels of one engine: 0 = fine.  A kernel that gives up on a
 // bounded wait stores a code here instead of trapping, so the context stays usable.
-enum KernelError : int { KERR_NONE = 0, KERR_WAIT_FULL = 1, KERR_WAIT_EMPTY = 2, KERR_BAD_PAGE = 3 };
+enum KernelError : int { KERR_NONE = 0, KERR_WAIT_FULL = 1, KERR_WAIT_EMPTY = 2, KERR_BAD_PAGE = 3, KERR_WAIT_PEER = 4 };
 
 }  // namespace drkv

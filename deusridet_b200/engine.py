@@ -226,6 +226,21 @@ class PagedKVEngine:
     def inject(self, seq, start_token, num_tokens, src, stream=None) -> None:
         check(self.lib.drkv_seq_inject(self.h, seq, start_token, num_tokens, _ptr(src), _stream(stream)))
 
+    # ---- cross-GPU exchange of split-KV partials by peer stores --------------------------------
+    def exchange_create(self, world: int, rank: int) -> bytes:
+        """Allocates this rank's exchange area; returns its 64-byte CUDA IPC handle."""
+        buf = (C.c_uint8 * 64)()
+        check(self.lib.drkv_exchange_create(self.h, world, rank, buf))
+        return bytes(buf)
+    def exchange_connect(self, handles: Sequence[bytes]) -> None:
+        blob = b"".join(handles)
+        arr = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        check(self.lib.drkv_exchange_connect(self.h, arr))
+    def exchange_destroy(self) -> None: check(self.lib.drkv_exchange_destroy(self.h))
+    def attend_exchange(self, layer, seq, kv_begin, kv_end, q, out, scale, stream=None) -> None:
+        check(self.lib.drkv_attend_exchange(self.h, layer, seq, kv_begin, kv_end, _ptr(q), _ptr(out), scale,
+                                            _stream(stream)))
+
     def attend_partial(self, layer, seq, kv_begin, kv_end, q, part, scale, stream=None) -> None:
         check(self.lib.drkv_attend_partial(self.h, layer, seq, kv_begin, kv_end, _ptr(q), _ptr(part), scale,
                                            _stream(stream)))

@@ -297,6 +297,20 @@ DRKV_API int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, con
  * Empty range: m = -1e20, l = 0, o = 0 (asr_ops_attn.cu:38-42). */
 DRKV_API int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end,
                                  const void* q, float* part, float scale, void* stream);
+/* The same split across GPUs with the merge fused with the exchange: drkv_attend_exchange computes this
+ * rank's partial over [kv_begin, kv_end) and then ONE kernel pushes it into every rank's exchange area
+ * with peer stores over NVLink, raises a per-(rank, head) flag, waits (bounded: a rank that never arrives
+ * ends the wait after 2 s with kernel error 4, nothing traps) for the peers' flags and writes the merged
+ * output; no library collective is called.  Every rank makes the same sequence of drkv_attend_exchange
+ * calls.  Set-up: each rank (one process per GPU, same node) creates its area and gets a 64-byte CUDA IPC
+ * handle, the ranks exchange handles by any host-side means, each connects to all.  No counterpart in the
+ * reference, which is single-GPU. */
+#define DRKV_IPC_HANDLE_BYTES 64
+DRKV_API int drkv_exchange_create(drkv_engine* e, int world, int rank, uint8_t* handle_out /* [64] */);
+DRKV_API int drkv_exchange_connect(drkv_engine* e, const uint8_t* handles /* [world][64] */);
+DRKV_API int drkv_exchange_destroy(drkv_engine* e);   /* after a host-side barrier: peers must be done */
+DRKV_API int drkv_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end,
+                                  const void* q, void* out, float scale, void* stream);
 /* contiguous_split_k_merge_kernel (asr_ops_attn.cu:88-108): merges n_parts partials laid
  * out as drkv_attend_partial writes them (parts[p] at p * (Hq*(D+2)) floats). */
 DRKV_API int drkv_combine_partials(drkv_engine* e, int n_parts, const float* parts, void* out,
