@@ -22,6 +22,7 @@
 #include "kernels.hpp"
 #include "kv_common.cuh"
 #include "sm100_primitives.cuh"
+#include "exchange.cuh"
 
 namespace drkv {
 
@@ -598,6 +599,18 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
     float lt = 0.f;
 #pragma unroll
     for (int i = 0; i < kCombineWarps; i++) lt += s_l[i];
+    if (p.xchg.world > 0) {
+        // one sequence split over several GPUs: this head's partial goes to every rank, theirs come here
+        __shared__ int s_ok;
+        float acc = 0.f;
+        if ((int)threadIdx.x < D) {
+#pragma unroll
+            for (int i = 0; i < kCombineWarps; i++) acc += reinterpret_cast<const float*>(&s_acc[i][0])[threadIdx.x];
+        }
+        const bool any = lt > 0.f;
+        exchange_and_merge<T>(p.xchg, h, p.num_q_heads, D, any ? acc : 0.f, any ? mmax : -1.0e20f, any ? lt : 0.f, p.out, &s_ok);
+        return;
+    }
     for (int d = threadIdx.x; d < D; d += kCombineWarps * 32) {
         float acc = 0.f;
 #pragma unroll

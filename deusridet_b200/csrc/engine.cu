@@ -170,7 +170,6 @@ struct drkv_engine {
         size_t flags_offset = 0;
         void* peer_area[kMaxExchangeRanks] = {};     // every rank's area as mapped here (own = area)
         bool connected = false;
-        float* d_partial = nullptr;                  // this rank's partial of the current call
     } xchg;
 
     // storage tier behind the pool (off until drkv_tier_enable)
@@ -759,7 +758,7 @@ int drkv_seq_inject(drkv_engine* e, int seq, int start_token, int num_tokens, co
 static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows, const int32_t* d_kv_len,
                          int row, int kv_begin, int kv_end, int max_span, const void* q, void* out,
                          float* out_partial, float scale, cudaStream_t stream,
-                         const drkv_engine::Plan* plan = nullptr) {
+                         const drkv_engine::Plan* plan = nullptr, const ExchangeParams* xchg = nullptr) {
     const drkv_geometry& g = e->geom;
     note_stream(e, stream);
     int chunk = 0;
@@ -841,6 +840,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     c.out = out;
     c.out_partial = out_partial;
     c.lse2_out = scored ? e->scorer.d_lse2 : nullptr;
+    if (xchg) c.xchg = *xchg;
     CUDA_TRY(launch_combine(c, n_seq, g.dtype, stream));
     if (scored) {
         PageMassParams pm{};
@@ -1219,7 +1219,6 @@ static void exchange_release(drkv_engine* e) {
     for (int r = 0; r < x.world; r++)
         if (x.connected && r != x.rank && x.peer_area[r]) cudaIpcCloseMemHandle(x.peer_area[r]);
     if (x.area) cudaFree(x.area);
-    if (x.d_partial) cudaFree(x.d_partial);
     x = drkv_engine::Exchange();
 }
 
@@ -1238,7 +1237,6 @@ int drkv_exchange_create(drkv_engine* e, int world, int rank, uint8_t* handle_ou
     const size_t bytes = x.flags_offset + (size_t)world * e->geom.num_q_heads * sizeof(uint32_t);
     CUDA_TRY(cudaMalloc(&x.area, bytes));
     CUDA_TRY(cudaMemset(x.area, 0, bytes));
-    CUDA_TRY(cudaMalloc(&x.d_partial, per_rank));
     CUDA_TRY(cudaDeviceSynchronize());
     cudaIpcMemHandle_t h;
     CUDA_TRY(cudaIpcGetMemHandle(&h, x.area));
@@ -1287,25 +1285,19 @@ int drkv_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int k
         return set_err(DRKV_ERR_INVALID, "attend_exchange: bad argument");
     int span = kv_end - (kv_begin / 16) * 16;
     if (span < 1) span = 1;
-    int rc = decode_common(e, layer, 1, nullptr, nullptr, seq, kv_begin, kv_end, span, q, nullptr, x.d_partial, scale,
-                           (cudaStream_t)stream);
-    if (rc != DRKV_OK) return rc;
     ExchangeParams p{};
     for (int r = 0; r < x.world; r++) {
         p.peer_slots[r] = static_cast<float*>(x.peer_area[r]);
         p.peer_flags[r] = reinterpret_cast<uint32_t*>(static_cast<char*>(x.peer_area[r]) + x.flags_offset);
     }
-    p.local_partial = x.d_partial;
-    p.out = out;
     p.world = x.world;
     p.rank = x.rank;
     p.seq_no = ++x.seq_no;
     p.parity = (int)(p.seq_no & 1u);
-    p.num_q_heads = e->geom.num_q_heads;
-    p.head_dim = e->geom.head_dim;
     p.error_word = e->d_error;
-    CUDA_TRY(launch_exchange_merge(p, e->geom.dtype, (cudaStream_t)stream));
-    return DRKV_OK;
+    // the merge kernel's CTA of head h exchanges that head with the peers and writes the final output
+    return decode_common(e, layer, 1, nullptr, nullptr, seq, kv_begin, kv_end, span, q, out, nullptr, scale,
+                         (cudaStream_t)stream, nullptr, &p);
 }
 
 int drkv_combine_partials(drkv_engine* e, int n_parts, const float* parts, void* out, void* stream) {

@@ -86,6 +86,17 @@ struct PrefillParams {
     int* error_word;
 };
 
+// Cross-GPU merge of one sequence's split-KV partials by peer stores, the tail of the merge kernel
+// (exchange.cuh); world == 0: off.
+constexpr int kMaxExchangeRanks = 16;
+struct ExchangeParams {
+    float* peer_slots[kMaxExchangeRanks];       // every rank's slot area, as mapped into this process
+    uint32_t* peer_flags[kMaxExchangeRanks];    // every rank's flag array
+    int world, rank, parity;
+    uint32_t seq_no;
+    int* error_word;
+};
+
 struct CombineParams {
     const float* part_o;
     const float* part_m;
@@ -96,6 +107,7 @@ struct CombineParams {
     void* out;                // storage type [n_seq][Hq][D] (normalised) ...
     float* out_partial;       // ... or fp32 partial [Hq*D | Hq m | Hq l] when non-null
     float* lse2_out;          // optional [n_seq][Hq]: log2 of the softmax denominator on the kernel's score scale
+    ExchangeParams xchg;      // with xchg.world > 0 (one sequence): exchange with the peers, then write `out`
 };
 
 // Importance scorer: per-page attention mass from the decode kernel's tile values.
@@ -111,18 +123,6 @@ cudaError_t launch_page_mass(const PageMassParams& p, int n_seq, int max_kv_len,
 cudaError_t launch_importance_update(float* scores, float* fresh, int64_t n, float decay, cudaStream_t stream);
 cudaError_t launch_importance_add(float* scores, const float* new_scores, int n, float decay, cudaStream_t stream);
 
-// Cross-GPU merge of one sequence's split-KV partials by peer stores (exchange.cu).
-constexpr int kMaxExchangeRanks = 16;
-struct ExchangeParams {
-    float* peer_slots[kMaxExchangeRanks];       // every rank's slot area, as mapped into this process
-    uint32_t* peer_flags[kMaxExchangeRanks];    // every rank's flag array
-    const float* local_partial;                 // [Hq*D o | Hq m | Hq l] of this rank
-    void* out;                                  // [Hq][D], storage type
-    int world, rank, parity, num_q_heads, head_dim;
-    uint32_t seq_no;
-    int* error_word;
-};
-cudaError_t launch_exchange_merge(const ExchangeParams& p, int dtype, cudaStream_t stream);
 
 cudaError_t launch_append_rope(const AppendParams& p, int n_tokens, int dtype, cudaStream_t stream);
 cudaError_t launch_cow_copy(const CowParams& p, int num_layers, cudaStream_t stream);
