@@ -386,15 +386,15 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                         }
                 }
                 // row maximum of the raw scores: eight independent chains instead of one 64 deep
-                float mx8[8];
+                // four independent chains of three-input maxima: 32 instructions for 64 scores
+                float mx4[4];
 #pragma unroll
-                for (int i = 0; i < 8; i++) mx8[i] = fmaxf(sv[0][i], sv[1][i]);
+                for (int i = 0; i < 4; i++) mx4[i] = fmaxf(sv[0][2 * i], sv[0][2 * i + 1]);
 #pragma unroll
-                for (int h = 0; h < 2; h++)
+                for (int c = 8; c < 32; c += 2) mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], sv[0][c], sv[0][c + 1]);
 #pragma unroll
-                    for (int c = 8; c < 32; c++) mx8[c & 7] = fmaxf(mx8[c & 7], sv[h][c]);
-                float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                                 fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+                for (int c = 0; c < 32; c += 2) mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], sv[1][c], sv[1][c + 1]);
+                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                 mx *= p.scale_log2;                                      // scale > 0: max commutes with it
                 // Keep the scale in use unless the row maximum outgrew it by more than 2^8.
                 float factor = 1.f;
@@ -408,8 +408,11 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 // p = 2^(s * scale_log2 - m): one FMA and one EX2 per score
                 const float neg_m = -m_used;
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};                    // independent partial sums
+                const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+                const unsigned long long negm2 = pack_f32x2(neg_m, neg_m);
+                unsigned long long sum2[4] = {0ull, 0ull, 0ull, 0ull};    // packed pairs of partial sums (+0.f, +0.f)
                 uint32_t phi[32], plo[32];
-                if (!use_lo && unmasked) {
+                if (DRKV_PF_POLY > 0 && !use_lo && unmasked) {
                     // the common block: no -inf among the scores, single-term P; part of the exponentials
                     // are evaluated on the FMA pipe
 #pragma unroll
@@ -425,15 +428,24 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                             phi[h * 16 + (c >> 1)] = Elem<T>::pack2(p0, p1);
                         }
                 } else if (!use_lo) {
+                    // two scores per multiply-add and per add (packed fp32 pairs), one exponential each, one
+                    // conversion per pair
 #pragma unroll
                     for (int h = 0; h < 2; h++)
 #pragma unroll
                         for (int c = 0; c < 32; c += 2) {
-                            const float p0 = fast_exp2(fmaf(sv[h][c], p.scale_log2, neg_m));
-                            const float p1 = fast_exp2(fmaf(sv[h][c + 1], p.scale_log2, neg_m));
-                            sum4[(c >> 1) & 3] += p0 + p1;
+                            float a0, a1;
+                            unpack_f32x2(fma_f32x2(pack_f32x2(sv[h][c], sv[h][c + 1]), scale2, negm2), a0, a1);
+                            const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+                            sum2[(c >> 1) & 3] = add_f32x2(sum2[(c >> 1) & 3], pack_f32x2(p0, p1));
                             phi[h * 16 + (c >> 1)] = Elem<T>::pack2(p0, p1);
                         }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        float s0, s1;
+                        unpack_f32x2(sum2[i], s0, s1);
+                        sum4[i] = s0 + s1;
+                    }
                 } else {
 #pragma unroll
                     for (int h = 0; h < 2; h++)
