@@ -413,20 +413,26 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 unsigned long long sum2[4] = {0ull, 0ull, 0ull, 0ull};    // packed pairs of partial sums (+0.f, +0.f)
                 uint32_t phi[32], plo[32];
                 if (DRKV_PF_POLY > 0 && !use_lo && unmasked) {
-                    // the common block: no -inf among the scores, single-term P; part of the exponentials
-                    // are evaluated on the FMA pipe
+                    // the common block (no -inf among the scores), with DRKV_PF_POLY of every four pairs taking
+                    // their exponentials from the FMA-pipe polynomial instead of the exponential unit
 #pragma unroll
                     for (int h = 0; h < 2; h++)
 #pragma unroll
                         for (int c = 0; c < 32; c += 2) {
-                            const float a0 = fmaf(sv[h][c], p.scale_log2, neg_m);
-                            const float a1 = fmaf(sv[h][c + 1], p.scale_log2, neg_m);
+                            float a0, a1;
+                            unpack_f32x2(fma_f32x2(pack_f32x2(sv[h][c], sv[h][c + 1]), scale2, negm2), a0, a1);
                             const bool poly = ((c >> 1) & 3) < DRKV_PF_POLY;
                             const float p0 = poly ? poly_exp2(a0) : fast_exp2(a0);
                             const float p1 = poly ? poly_exp2(a1) : fast_exp2(a1);
-                            sum4[(c >> 1) & 3] += p0 + p1;
+                            sum2[(c >> 1) & 3] = add_f32x2(sum2[(c >> 1) & 3], pack_f32x2(p0, p1));
                             phi[h * 16 + (c >> 1)] = Elem<T>::pack2(p0, p1);
                         }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        float s0, s1;
+                        unpack_f32x2(sum2[i], s0, s1);
+                        sum4[i] = s0 + s1;
+                    }
                 } else if (!use_lo) {
                     // two scores per multiply-add and per add (packed fp32 pairs), one exponential each, one
                     // conversion per pair
