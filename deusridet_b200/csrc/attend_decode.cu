@@ -136,16 +136,37 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     // ---- items per entry, exclusive prefix sum into cum[] ----
     // Entries: first the family blocks of a shared-prefix plan (up to 16 query rows of several forked
     // sequences over the chunks they have in common), then the sequences (their remaining chunks).
+    // With a tail split (p.tail_chunks > 0) the last tail_chunks chunks of every sequence are cut into
+    // p.tail_split pieces that form a third group of entries at the END of the queue: the warps run out
+    // of work within a quarter-chunk of one another instead of a whole chunk.
     const int n_fb = EXT ? p.n_fb : 0;
-    const int n_ent = n_fb + p.n_seq;
+    const int TAILC = p.tail_chunks, TAILS = p.tail_split;
+    const int SUBK = TAILC > 0 ? CT / TAILS : CT;     // keys per tail piece
+    const int slot_stride = p.max_chunks + TAILC * TAILS;   // partial slots per query row: chunks, then tail pieces
+    const int n_ent = n_fb + p.n_seq + (TAILC > 0 ? p.n_seq : 0);
+    struct SeqShape { int kv_end, first, nbig, nsmall; };
+    auto seq_shape = [&](int b) -> SeqShape {
+        SeqShape q;
+        q.kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + b) : p.kv_end;
+        int nch = q.kv_end > base_tok ? (q.kv_end - base_tok + CT - 1) / CT : 0;
+        nch = min(nch, p.max_chunks);
+        q.first = n_fb > 0 ? min(__ldg(p.seq_first_chunk + b), nch) : 0;
+        q.nbig = max(q.first, nch - TAILC);           // chunks [first, nbig) whole, [nbig, nch) in pieces
+        const int ntail = nch - q.nbig;
+        q.nsmall = 0;
+        if (ntail > 0) {
+            const int rem_last = min(q.kv_end - base_tok, nch * CT) - (nch - 1) * CT;
+            q.nsmall = (ntail - 1) * TAILS + (rem_last + SUBK - 1) / SUBK;
+        }
+        return q;
+    };
     auto entry_items = [&](int e) -> int {
         if (e < n_fb) return __ldg(p.fb_chunks + e) * p.num_kv_heads;
-        const int b = e - n_fb;
-        const int kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + b) : p.kv_end;
-        int nch = kv_end > base_tok ? (kv_end - base_tok + CT - 1) / CT : 0;
-        nch = min(nch, p.max_chunks);
-        if (n_fb > 0) nch = max(nch - __ldg(p.seq_first_chunk + b), 0);
-        return nch * p.num_kv_heads;
+        if (e < n_fb + p.n_seq) {
+            const SeqShape q = seq_shape(e - n_fb);
+            return (q.nbig - q.first) * p.num_kv_heads;
+        }
+        return seq_shape(e - n_fb - p.n_seq).nsmall * p.num_kv_heads;
     };
     {
         const int per = (n_ent + THREADS - 1) / THREADS;
@@ -188,10 +209,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     constexpr int kPrefetchGroups = DRKV_PREFETCH_GROUPS;
     int raw_next = 0, n_state = 0;
     bool exhausted = false;
-    int n_b = 0, n_kvh = 0, n_chunk = 0, n_trow = 0, n_kv_end = 0, n_page = -1, n_fam = 0;   // n_fam: family block + 1, 0 = plain
+    int n_b = 0, n_kvh = 0, n_slot = 0, n_tok_lo = 0, n_tok_hi = 0, n_trow = 0, n_page = -1, n_fam = 0;   // n_fam: family block + 1, 0 = plain
     // ---- issue cursor ----
     bool c_valid = false;
-    int c_b = 0, c_kvh = 0, c_chunk = 0, c_trow = 0, c_kv_end = 0, c_tok_lo = 0, c_ngroups = 0, c_gi = 0, c_page = -1, c_fam = 0;
+    int c_b = 0, c_kvh = 0, c_slot = 0, c_trow = 0, c_tok_hi = 0, c_tok_lo = 0, c_ngroups = 0, c_gi = 0, c_page = -1, c_fam = 0;
     int i_slot = 0, outstanding = 0;
     // ---- compute cursor ----
     int slot = 0, phase = 0;
@@ -224,20 +245,31 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             const int mid = (lo + hi) >> 1;
             if (cum[mid] <= raw) lo = mid; else hi = mid;
         }
-        const int nch = (cum[lo + 1] - cum[lo]) / p.num_kv_heads;
+        const int per_head = (cum[lo + 1] - cum[lo]) / p.num_kv_heads;
         const int j = raw - cum[lo];
-        n_kvh = j / nch;
-        n_chunk = j - n_kvh * nch;
+        n_kvh = j / per_head;
+        const int i = j - n_kvh * per_head;
         if (lo < n_fb) {                               // shared chunks of a family block
             n_fam = lo + 1;
             n_b = 0;
-            n_kv_end = base_tok + nch * CT;
+            n_slot = i;
+            n_tok_lo = base_tok + i * CT;
+            n_tok_hi = n_tok_lo + CT;
             n_trow = __ldg(p.fb_row + lo);
         } else {
             n_fam = 0;
-            n_b = lo - n_fb;
-            if (n_fb > 0) n_chunk += __ldg(p.seq_first_chunk + n_b);
-            n_kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + n_b) : p.kv_end;
+            const bool piece = lo >= n_fb + p.n_seq;
+            n_b = lo - n_fb - (piece ? p.n_seq : 0);
+            const SeqShape q = seq_shape(n_b);
+            if (!piece) {                              // a whole chunk
+                n_slot = q.first + i;
+                n_tok_lo = base_tok + n_slot * CT;
+                n_tok_hi = min(n_tok_lo + CT, q.kv_end);
+            } else {                                   // a piece of one of the last chunks
+                n_slot = p.max_chunks + i;
+                n_tok_lo = base_tok + (q.nbig + i / TAILS) * CT + (i % TAILS) * SUBK;
+                n_tok_hi = min(n_tok_lo + SUBK, q.kv_end);
+            }
             n_trow = p.rows != nullptr ? __ldg(p.rows + n_b) : p.row;
         }
         n_state = 2;
@@ -261,9 +293,8 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 if (n_state == 0 && !exhausted) fetch_raw();
                 if (n_state == 1) decode_next();       // waits for the atomic only if it was just issued
                 if (n_state < 2) break;                // queue drained
-                c_b = n_b; c_kvh = n_kvh; c_chunk = n_chunk; c_trow = n_trow; c_kv_end = n_kv_end; c_fam = n_fam;
-                c_tok_lo = base_tok + c_chunk * CT;
-                c_ngroups = (min(c_tok_lo + CT, c_kv_end) - c_tok_lo + kGroupTokens - 1) / kGroupTokens;
+                c_b = n_b; c_kvh = n_kvh; c_slot = n_slot; c_trow = n_trow; c_tok_lo = n_tok_lo; c_tok_hi = n_tok_hi; c_fam = n_fam;
+                c_ngroups = (c_tok_hi - c_tok_lo + kGroupTokens - 1) / kGroupTokens;
                 c_gi = 0;
                 c_page = n_state == 3 ? n_page : load_page(c_trow, c_tok_lo);
                 c_valid = true;
@@ -281,10 +312,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 SlotMeta m;
                 m.b = c_b;
                 m.kvh = c_kvh;
-                m.part_slot = (EXT && c_fam) ? c_chunk : (c_b * p.num_q_heads + c_kvh * p.group) * p.max_chunks + c_chunk;
+                m.part_slot = (EXT && c_fam) ? c_slot : (c_b * p.num_q_heads + c_kvh * p.group) * slot_stride + c_slot;
                 m.flags = (c_gi == 0 ? SLOT_FIRST : 0) | (last ? SLOT_LAST : 0) | (page < 0 ? SLOT_SKIP : 0);
                 m.v_lo = max(0, p.kv_begin - tok0);
-                m.v_hi = min(kGroupTokens, c_kv_end - tok0);
+                m.v_hi = min(kGroupTokens, c_tok_hi - tok0);
                 m.fam = c_fam;
                 m.tile = tok0 / kGroupTokens;
                 metas[ring] = m;
@@ -316,7 +347,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 } else if (n_state == 1) {
                     decode_next();
                 } else if (n_state == 2) {
-                    n_page = load_page(n_trow, base_tok + n_chunk * CT);
+                    n_page = load_page(n_trow, n_tok_lo);
                     n_state = 3;
                 }
             }
@@ -496,12 +527,12 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 const int row = qrow + 8 * r;
                 int64_t ps = -1;                                   // partial slot of this row, -1: padding row
                 if (!EXT || meta.fam == 0) {
-                    if (row < p.group) ps = (int64_t)meta.part_slot + (int64_t)row * p.max_chunks;
+                    if (row < p.group) ps = (int64_t)meta.part_slot + (int64_t)row * slot_stride;
                 } else {
                     const int mi = row / p.group;
                     const int bm = mi < 16 ? __ldg(p.fb_members + (meta.fam - 1) * 16 + mi) : -1;
                     if (bm >= 0)
-                        ps = ((int64_t)bm * p.num_q_heads + (int64_t)meta.kvh * p.group + row % p.group) * p.max_chunks +
+                        ps = ((int64_t)bm * p.num_q_heads + (int64_t)meta.kvh * p.group + row % p.group) * slot_stride +
                              meta.part_slot;               // part_slot holds the chunk index for family blocks
                 }
                 if (ps >= 0) {
@@ -552,12 +583,26 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
     pdl_launch_dependents();
     const int kv_end = p.kv_len != nullptr ? p.kv_len[b] : p.kv_end;
     const int base = (p.kv_begin / kGroupTokens) * kGroupTokens;
-    int nchunks = kv_end > base ? (kv_end - base + p.chunk_tokens - 1) / p.chunk_tokens : 0;
-    nchunks = min(nchunks, p.max_chunks);
-    const int64_t slot0 = ((int64_t)b * p.num_q_heads + h) * p.max_chunks;
+    int nch = kv_end > base ? (kv_end - base + p.chunk_tokens - 1) / p.chunk_tokens : 0;
+    nch = min(nch, p.max_chunks);
+    // partial slots of this row: whole chunks [0, nbig) at their index, then the pieces of the last chunks
+    // (see the tail split in attend_decode_kernel) from index max_chunks on
+    const int tailc = p.tail_chunks, tails = p.tail_split;
+    const int first = (tailc > 0 && p.seq_first_chunk != nullptr) ? min(p.seq_first_chunk[b], nch) : 0;
+    const int nbig = tailc > 0 ? max(first, nch - tailc) : nch;
+    int nsmall = 0;
+    if (nch > nbig) {
+        const int subk = p.chunk_tokens / tails;
+        const int rem_last = min(kv_end - base, nch * p.chunk_tokens) - (nch - 1) * p.chunk_tokens;
+        nsmall = (nch - nbig - 1) * tails + (rem_last + subk - 1) / subk;
+    }
+    const int nchunks = nbig + nsmall;
+    const int skip = p.max_chunks - nbig;                // list index i >= nbig lives at slot i + skip
+    const int64_t slot0 = ((int64_t)b * p.num_q_heads + h) * (p.max_chunks + tailc * tails);
 
     float mloc = -1.0e20f;
-    for (int c = threadIdx.x; c < nchunks; c += kCombineWarps * 32) mloc = fmaxf(mloc, p.part_m[slot0 + c]);
+    for (int c = threadIdx.x; c < nchunks; c += kCombineWarps * 32)
+        mloc = fmaxf(mloc, p.part_m[slot0 + c + (c >= nbig ? skip : 0)]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
     if (lane == 0) s_m[warp] = mloc;
@@ -577,7 +622,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
         for (int u = 0; u < 4; u++) {
             const int c = c0 + u * kCombineWarps;
             const bool in = c < nchunks;
-            const int64_t sl = slot0 + (in ? c : c0);
+            const int cc = in ? c : c0;
+            const int64_t sl = slot0 + cc + (cc >= nbig ? skip : 0);
             wgt[u] = in ? p.part_m[sl] : -1.0e20f;
             lv[u] = in ? p.part_l[sl] : 0.f;
             const float4* row = reinterpret_cast<const float4*>(p.part_o + sl * D);
@@ -706,7 +752,7 @@ template <typename T, int D, bool HI, bool EXT>
 cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
     constexpr int WARPS = RingShape<D>::kWarps, DEPTH = RingShape<D>::kDepth, NH = D / 64;
     constexpr size_t smem = 1024 + (size_t)WARPS * DEPTH * (2 * NH * 2048 + sizeof(SlotMeta) + sizeof(uint64_t)) +
-                            (2 * kMaxDecodeSeqs + 1) * sizeof(int);   // cum[] over family blocks + sequences
+                            (3 * kMaxDecodeSeqs + 1) * sizeof(int);   // cum[]: family blocks, sequences, their tail pieces
     static bool configured[64] = {};  // per instantiation and device: the attribute belongs to the context
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -817,6 +863,9 @@ cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p,
     if (p.total_items <= 0) return cudaSuccess;
     if (p.n_seq > kMaxDecodeSeqs || p.n_fb > kMaxDecodeSeqs) return cudaErrorInvalidValue;
     if (p.chunk_tokens % kGroupTokens != 0 || p.chunk_tokens <= 0 || p.group > 16 || p.page_size % kGroupTokens != 0)
+        return cudaErrorInvalidValue;
+    if (p.tail_chunks < 0 || (p.tail_chunks > 0 && (p.tail_split < 1 || p.chunk_tokens % p.tail_split != 0 ||
+                                                    (p.chunk_tokens / p.tail_split) % kGroupTokens != 0)))
         return cudaErrorInvalidValue;
     const bool f16 = dtype == DRKV_DTYPE_F16;
     switch (head_dim) {

@@ -117,6 +117,7 @@ struct drkv_engine {
     CUtensorMap tmap_slot{};   // 4-D view, one box per 16 keys x head_dim x (K, V): the decode kernel's
     PoolLayout layout{};
     int forced_chunk = 0;
+    int tail_mode = 0;         // tail split of the decode pass: 0 off (default: it measured slower), -1 automatic, n > 0: the last n chunks
     int num_sms = 148;
     int* d_work = nullptr;   // decode kernel's work-queue head
     int* d_exit = nullptr;   // decode kernel's count of warps that have left
@@ -645,6 +646,13 @@ int drkv_kernel_error(drkv_engine* e) {
     return DRKV_OK;
 }
 
+int drkv_set_tail_split(drkv_engine* e, int mode) {
+    NEED(e);
+    if (mode < -1 || mode > 4) return set_err(DRKV_ERR_INVALID, "tail split: -1 (automatic), 0 (off) or 1..4 chunks");
+    e->tail_mode = mode;
+    return DRKV_OK;
+}
+
 int drkv_set_chunk_tokens(drkv_engine* e, int chunk_tokens) {
     NEED(e);
     if (chunk_tokens != 0 && (chunk_tokens % 16 != 0 || chunk_tokens < 16))
@@ -775,7 +783,26 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
             return set_err(DRKV_ERR_CAPACITY, "attend: split-KV scratch too small for %d sequences x %d keys", n_seq, max_span);
     }
     const int max_chunks = (max_span + chunk - 1) / chunk;
-    const size_t n_slots = (size_t)n_seq * g.num_q_heads * max_chunks;
+    // Tail split: when the pass is several chunks deep per warp, the last chunks of every sequence are
+    // queued last and in 64-key pieces, about one chunk's worth of work per warp in total, so that the
+    // warps finish within a piece of one another.
+    int tail_chunks = 0, tail_split = 1;
+    {
+        const long warps = (long)e->num_sms * 8, streams = (long)n_seq * g.num_kv_heads;
+        const long items = streams * max_chunks;
+        const bool forced = e->tail_mode > 0 && chunk >= 32 && chunk % 32 == 0;
+        const bool automatic = e->tail_mode < 0 && chunk >= 128 && chunk % 64 == 0 && items >= 3 * warps;
+        if (d_rows != nullptr && (forced || automatic)) {
+            tail_split = chunk >= 128 && chunk % 64 == 0 ? chunk / 64 : 2;
+            tail_chunks = forced ? e->tail_mode : (int)((warps + streams / 2) / streams);
+            if (tail_chunks < 1) tail_chunks = 1;
+            if (tail_chunks > 4) tail_chunks = 4;
+            const size_t need = (size_t)n_seq * g.num_q_heads * (max_chunks + tail_chunks * tail_split) * (g.head_dim + 2) * 4;
+            if (need > e->scratch_bytes) tail_chunks = 0;
+        }
+    }
+    const int slot_stride = max_chunks + tail_chunks * tail_split;
+    const size_t n_slots = (size_t)n_seq * g.num_q_heads * slot_stride;
 
     DecodeParams p{};
     p.tables = e->d_tables;
@@ -797,6 +824,8 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     p.page_size = g.page_size;
     p.chunk_tokens = chunk;
     p.max_chunks = max_chunks;
+    p.tail_chunks = tail_chunks;
+    p.tail_split = tail_split;
     p.n_seq = n_seq;
     p.total_items = n_seq * g.num_kv_heads * max_chunks;
     if (plan && plan->n_fb > 0) {
@@ -837,6 +866,9 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     c.head_dim = g.head_dim;
     c.chunk_tokens = chunk;
     c.max_chunks = max_chunks;
+    c.tail_chunks = tail_chunks;
+    c.tail_split = tail_split;
+    c.seq_first_chunk = (plan && plan->n_fb > 0) ? plan->first_chunk : nullptr;
     c.out = out;
     c.out_partial = out_partial;
     c.lse2_out = scored ? e->scorer.d_lse2 : nullptr;

@@ -53,6 +53,7 @@ struct DecodeParams {
     float* part_l;            // [n_seq][Hq][max_chunks]
     int layer, max_pages, num_q_heads, num_kv_heads, group, page_size;
     int chunk_tokens, max_chunks;
+    int tail_chunks, tail_split;   // last tail_chunks chunks of a sequence go as tail_split pieces each (0: off)
     int n_seq;
     // shared-prefix plan (all null / 0 without one): family block k covers chunks [0, fb_chunks[k]) of table
     // row fb_row[k] for the batch entries fb_members[16 k + i] (-1 = none); sequence b starts at chunk
@@ -104,6 +105,8 @@ struct CombineParams {
     const int32_t* kv_len;    // [n_seq] or nullptr
     int kv_begin, kv_end;
     int num_q_heads, head_dim, chunk_tokens, max_chunks;
+    int tail_chunks, tail_split;          // as in DecodeParams
+    const int32_t* seq_first_chunk;       // shared-prefix plan's first own chunk per sequence, or nullptr
     void* out;                // storage type [n_seq][Hq][D] (normalised) ...
     float* out_partial;       // ... or fp32 partial [Hq*D | Hq m | Hq l] when non-null
     float* lse2_out;          // optional [n_seq][Hq]: log2 of the softmax denominator on the kernel's score scale

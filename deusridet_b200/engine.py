@@ -138,6 +138,7 @@ class PagedKVEngine:
     def d_block_table(self) -> int: return self.lib.drkv_device_tables(self.h) or 0
     def table_stride(self) -> int: return self.lib.drkv_table_stride(self.h)
     def check_kernels(self) -> None: check(self.lib.drkv_kernel_error(self.h))
+    def set_tail_split(self, mode: int) -> None: check(self.lib.drkv_set_tail_split(self.h, mode))
     def set_chunk_tokens(self, n: int) -> None: check(self.lib.drkv_set_chunk_tokens(self.h, n))
 
     def kernel_timing(self, enable: bool, read: bool = False):
