@@ -68,12 +68,18 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []
+        self.t_begin = None
+
+    def mark_begin(self):
+        """Only samples that arrive from now on count: call right before the timed region.  (nvidia-smi takes
+        longer to start than a short timed region lasts, so it is started well before.)"""
+        self.t_begin = time.perf_counter()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -81,7 +87,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -93,7 +99,10 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        t_end = time.perf_counter()
+        for t, ln in self.lines:
+            if self.t_begin is not None and not (self.t_begin <= t <= t_end):
+                continue
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 7:
                 continue
@@ -202,22 +211,23 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-resident timing: `value` ----
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(W):
         device_step()
     barrier()
     eng.check_kernels()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark_begin()
     e0.record(stream)
     for _ in range(K):
         device_step()
     e1.record(stream)
     barrier()
-    ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
+    ms = e0.elapsed_time(e1)
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -430,15 +440,16 @@ def run_c5a(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(W):
         step()
     barrier()
     eng.check_kernels()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark_begin()
     e0.record(stream)
     for _ in range(K):
         step()
