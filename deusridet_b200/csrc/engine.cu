@@ -65,11 +65,14 @@ size_t page_bytes_all_layers(const drkv_geometry& g) {
 // warp's queue: warps take whole items, so the pass lasts about ceil(items / warps) items of (chunk +
 // a fixed cost per item worth ~64 keys: start-up, the partial's write and its share of the merge) each.
 template <typename ItemsFn>
-int pick_chunk_by_cost(int group, int num_sms, ItemsFn items) {
+int pick_chunk_by_cost(int group, int num_sms, bool exact, ItemsFn items) {
     const long warps = (long)num_sms * 8;
     int best = 0;
     long best_cost = 0;
-    for (int c = group > 4 ? 512 : 256; c >= 64; c >>= 1) {
+    // Every multiple of 16 is a legal chunk.  With exact item counts (a decode plan knows every length) the
+    // search goes down in steps of 16 and can land on a size whose items just fit a whole number of rounds;
+    // with only an upper bound of the lengths it stays on powers of two.  Ties go to the larger chunk.
+    for (int c = group > 4 ? 512 : 256; c >= 64; c = exact ? c - 16 : c >> 1) {
         const long n = items(c);
         const long cost = ((n + warps - 1) / warps) * (c + 64);
         if (best == 0 || cost < best_cost) {
@@ -89,7 +92,7 @@ int pick_chunk(int n_seq, int hkv, int group, int max_kv_span, int num_sms) {
         const long c = (max_kv_span + per_head - 1) / per_head;
         return (int)((c + 15) / 16 * 16);
     }
-    return pick_chunk_by_cost(group, num_sms, items);
+    return pick_chunk_by_cost(group, num_sms, false, items);
 }
 
 }  // namespace
@@ -975,7 +978,7 @@ int drkv_plan_decode(drkv_engine* e, int n_seq, const int32_t* seqs, const int32
     };
     int chunk = e->forced_chunk;
     if (!chunk) {
-        chunk = pick_chunk_by_cost(group, e->num_sms, [&](int c) { return (long)planned_items(c, nullptr); });
+        chunk = pick_chunk_by_cost(group, e->num_sms, true, [&](int c) { return (long)planned_items(c, nullptr); });
     }
     if (e->has_device) {
         auto need_bytes = [&](int c) {
