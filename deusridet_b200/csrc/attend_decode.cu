@@ -858,6 +858,39 @@ bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layer
     return true;
 }
 
+// The prefill kernel's V descriptor for head_dim 128: [64-dim half (stride 128 B)][head row (stride 256 B)][64],
+// box {64, 16, 2}: one copy brings both halves of 16 value rows as [half][row][128 B], the MN-major layout
+// the PV MMA reads.  The half dimension has the smaller stride; a driver that refuses such a view makes the
+// caller keep two boxes per group.
+bool make_pool_vhalves_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages, int num_kv_heads,
+                                  int page_size, int head_dim, const char** err) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (head_dim != 128 || cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        fn == nullptr) {
+        if (err) *err = "no V-halves descriptor";
+        return false;
+    }
+    EncodeFn encode = reinterpret_cast<EncodeFn>(fn);
+    const uint64_t rows = (uint64_t)num_layers * max_pages * 2 * num_kv_heads * page_size;
+    if (rows >= (1ull << 31)) return false;
+    cuuint64_t gdim[3] = {64, (cuuint64_t)rows, 2};
+    cuuint64_t gstride[2] = {(cuuint64_t)head_dim * 2, 128};
+    cuuint32_t box[3] = {64, 16, 2};
+    cuuint32_t estride[3] = {1, 1, 1};
+    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(pool), gdim, gstride, box, estride,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        if (err) *err = "cuTensorMapEncodeTiled refused the V-halves view";
+        return false;
+    }
+    return true;
+}
+
 cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,
                                  int dtype, cudaStream_t stream) {
     if (p.total_items <= 0) return cudaSuccess;

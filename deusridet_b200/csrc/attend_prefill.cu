@@ -92,7 +92,8 @@ __device__ __forceinline__ float poly_exp2(float x) {
 
 template <typename T>
 __global__ void __launch_bounds__(kPfThreads, 1)
-attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ PrefillParams p) {
+attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_v,
+                      const __grid_constant__ PrefillParams p) {
     // one sequence of the batch per grid.z; sequences with fewer tiles than grid.x leave the extra CTAs idle
     const int p_m = p.m[blockIdx.z], p_pos_start = p.pos_start[blockIdx.z], p_row = p.row[blockIdx.z];
     if ((int)blockIdx.x * 2 * (128 / p.group) >= p_m) return;
@@ -136,6 +137,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_v) : "memory");
     }
     if (warp == kPfMmaWarp) tmem_alloc(sbase + PfSmem::tmem, kPfTmemCols);
     pdl_wait();                                  // Q, the pool and the table may come from the preceding kernel
@@ -192,31 +194,34 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             const long long b1 = PF_CLK();
             uint8_t* kdst = smem + PfSmem::kv + s * 2 * kPfKBytes;
             uint8_t* vdst = kdst + kPfKBytes;
-            // Sixteen box loads per block (4 groups of 16 keys x K|V x two 64-dim halves): lane l < 16 looks
-            // up its group's page and issues its own load, so the warp pays one issue latency per block
-            // instead of sixteen (a single thread needed ~135 cycles per load).
-            const int gi = (lane >> 2) & 3, kvsel = (lane >> 1) & 1, h = lane & 1;
-            const int grp = j * 4 + gi;
+            // Box loads of a block of 4 groups of 16 keys.  K: one box per group and 64-dim half (the K-major
+            // operand layout keeps the halves 8 KB apart).  V: one box per group with the V-halves view
+            // ([half][16 rows][128 B] is exactly what the PV MMA of that group reads), else two like K.  Every
+            // box is issued by its own lane: a single thread needs ~135 cycles per load.
+            const bool vh = p.v_halves != 0;
+            const int my_gi = lane & 3;
             int page = -1;
-            if (grp < n_groups) {
-                if (pages_staged) page = s_pages[grp];
-                else {
-                    const int logical = (grp * 16) / p.page_size;
-                    page = logical < p.table_stride ? __ldg(p.tables + (int64_t)p_row * p.table_stride + logical) : -1;
-                    if (page >= p.max_pages) page = -1;
+            {
+                const int grp = j * 4 + my_gi;
+                if (grp < n_groups) {
+                    if (pages_staged) page = s_pages[grp];
+                    else {
+                        const int logical = (grp * 16) / p.page_size;
+                        page = logical < p.table_stride ? __ldg(p.tables + (int64_t)p_row * p.table_stride + logical) : -1;
+                        if (page >= p.max_pages) page = -1;
+                    }
                 }
             }
-            const unsigned missing = __ballot_sync(0xffffffffu, page < 0) & 0xffffu;   // 4 lanes per group agree
-            const int holes = ((missing >> 0) & 1) | (((missing >> 4) & 1) << 1) | (((missing >> 8) & 1) << 2) |
-                              (((missing >> 12) & 1) << 3);
-            const uint32_t bytes = (uint32_t)(16 - __popc(missing)) * 2048u;
+            const int holes = (int)(__ballot_sync(0xffffffffu, page < 0) & 0xfu);      // lanes 0..3 hold groups 0..3
+            const uint32_t bytes = (uint32_t)(4 - __popc(holes)) * (2u * kPfKBytes / 4u);
             if (holes) {
                 // nothing will be loaded there: give the MMAs zeros instead of stale shared memory
                 for (int g4 = 0; g4 < 4; g4++) {
                     if (!((holes >> g4) & 1)) continue;
                     for (int i = lane; i < 2 * 2 * 16 * 8; i += 32) {       // K and V, 2 halves, 16 rows, 8 chunks
                         const int ks = i >> 8, hh = (i >> 7) & 1, r = (i >> 3) & 15, c = i & 7;
-                        uint8_t* base = (ks ? vdst : kdst) + hh * (kPfBlockN * 128) + (g4 * 16 + r) * 128 + c * 16;
+                        uint8_t* base = (ks && vh) ? vdst + g4 * 4096 + hh * 2048 + r * 128 + c * 16
+                                                   : (ks ? vdst : kdst) + hh * (kPfBlockN * 128) + (g4 * 16 + r) * 128 + c * 16;
                         *reinterpret_cast<Vec16*>(base) = Vec16{{0u, 0u, 0u, 0u}};
                     }
                 }
@@ -229,12 +234,21 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 mbar_arrive_expect_tx(bars + 8 * (BAR_KV_FULL + s), bytes);
             }
             __syncwarp();
-            if (lane < 16 && page >= 0) {
-                const int tok = grp * 16;
-                const int64_t row = (((int64_t)p.layer * p.max_pages + page) * 2 + kvsel) * rows_per_plane +
+            // box of this lane: 0..7 K (group, half); then V: 8..11 (group) with the halves view, else 8..15 (group, half)
+            const bool is_k = lane < 8;
+            const int gi = is_k ? (lane >> 1) : (vh ? lane - 8 : (lane - 8) >> 1);
+            const int h = lane & 1;
+            const bool active = lane < (vh ? 12 : 16);
+            const int bpage = __shfl_sync(0xffffffffu, page, gi & 3);
+            if (active && bpage >= 0) {
+                const int tok = (j * 4 + gi) * 16;
+                const int64_t row = (((int64_t)p.layer * p.max_pages + bpage) * 2 + (is_k ? 0 : 1)) * rows_per_plane +
                                     (int64_t)kvh * p.page_size + (tok % p.page_size);
-                tma_load_2d(smem_u32(kvsel ? vdst : kdst) + h * (kPfBlockN * 128) + gi * 2048, &tmap, h * 64, (int)row,
-                            bars + 8 * (BAR_KV_FULL + s));
+                if (is_k || !vh)
+                    tma_load_2d(smem_u32(is_k ? kdst : vdst) + h * (kPfBlockN * 128) + gi * 2048, &tmap, h * 64, (int)row,
+                                bars + 8 * (BAR_KV_FULL + s));
+                else
+                    tma_load_3d(smem_u32(vdst) + gi * 4096, &tmap_v, 0, (int)row, 0, bars + 8 * (BAR_KV_FULL + s));
             }
             pt[0] += b1 - b0; pt[1] += b2 - b1; pt[2] += PF_CLK() - b2;
         }
@@ -261,7 +275,9 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             // cycles of tensor work an instruction carries.
             constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);     // SBO 1024, version 1, 128-byte swizzle
             constexpr uint32_t kLboK = (16u >> 4) << 16;                            // K-major operands
-            constexpr uint32_t kLboV = ((uint32_t)(kPfBlockN * 128) >> 4) << 16;    // V, MN-major: next 64-dim run
+            // V, MN-major: the next 64-dim run is 8 KB on with two boxes per group, 2 KB with the halves view
+            const uint32_t kLboV = (p.v_halves ? (2048u >> 4) : ((uint32_t)(kPfBlockN * 128) >> 4)) << 16;
+            const uint32_t v_step = p.v_halves ? (4096u >> 4) : (2048u >> 4);        // from one group of 16 keys to the next
             auto mk = [](uint32_t lo, uint32_t hi) -> uint64_t { return ((uint64_t)hi << 32) | lo; };
             const uint32_t qa = ((((sbase + PfSmem::q) & 0x3FFFFu) >> 4) | kLboK) + x * (kPfQBytes >> 4);
             const uint32_t kv_lo0 = ((sbase + PfSmem::kv) & 0x3FFFFu) >> 4;
@@ -287,13 +303,13 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 const uint32_t acc0 = first_block ? 0u : 1u;
                 if (!use_lo) {
                     umma_f16_ts(d_o, pa, mk(vb, kDescHi), idesc_pv, acc0);
-                    umma_f16_ts(d_o, pa + 8, mk(vb + 1 * (2048 >> 4), kDescHi), idesc_pv, 1u);
-                    umma_f16_ts(d_o, pa + 16, mk(vb + 2 * (2048 >> 4), kDescHi), idesc_pv, 1u);
-                    umma_f16_ts(d_o, pa + 24, mk(vb + 3 * (2048 >> 4), kDescHi), idesc_pv, 1u);
+                    umma_f16_ts(d_o, pa + 8, mk(vb + 1 * v_step, kDescHi), idesc_pv, 1u);
+                    umma_f16_ts(d_o, pa + 16, mk(vb + 2 * v_step, kDescHi), idesc_pv, 1u);
+                    umma_f16_ts(d_o, pa + 24, mk(vb + 3 * v_step, kDescHi), idesc_pv, 1u);
                 } else {
 #pragma unroll
                     for (int kk = 0; kk < kPfBlockN / 16; kk++) {
-                        const uint64_t vdesc = mk(vb + kk * (2048 >> 4), kDescHi);
+                        const uint64_t vdesc = mk(vb + kk * v_step, kDescHi);
                         umma_f16_ts(d_o, pa + kk * 8, vdesc, idesc_pv, kk == 0 ? acc0 : 1u);
                         umma_f16_ts(d_o, pa + 32 + kk * 8, vdesc, idesc_pv, 1u);
                     }
@@ -549,8 +565,11 @@ extern "C" __attribute__((visibility("default"))) int drkv_debug_prefill_trace(l
 }
 #endif
 
-cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
-                                  cudaStream_t stream) {
+cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const CUtensorMap* tmap_v, const PrefillParams& p_in,
+                                  int head_dim, int dtype, cudaStream_t stream) {
+    PrefillParams p = p_in;
+    p.v_halves = tmap_v != nullptr ? 1 : 0;
+    const CUtensorMap& tv = tmap_v != nullptr ? *tmap_v : tmap;
     if (p.n_seq <= 0) return cudaSuccess;
     if (head_dim != kPfD || p.group < 1 || p.group > 16 || p.page_size % 16 != 0) return cudaErrorInvalidValue;
     constexpr size_t smem = 1024 + PfSmem::total;
@@ -570,8 +589,8 @@ cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& 
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[ti][dev] = true;
     }
-    if (ti == 0) return launch_pdl(attend_prefill_kernel<__half>, grid, dim3(kPfThreads), smem, stream, tmap, p);
-    return launch_pdl(attend_prefill_kernel<__nv_bfloat16>, grid, dim3(kPfThreads), smem, stream, tmap, p);
+    if (ti == 0) return launch_pdl(attend_prefill_kernel<__half>, grid, dim3(kPfThreads), smem, stream, tmap, tv, p);
+    return launch_pdl(attend_prefill_kernel<__nv_bfloat16>, grid, dim3(kPfThreads), smem, stream, tmap, tv, p);
 }
 
 }  // namespace drkv

@@ -3,6 +3,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -117,6 +118,8 @@ struct drkv_engine {
     float* d_scratch = nullptr;
     size_t scratch_bytes = 0;
     CUtensorMap tmap{};        // 2-D view, 16-row x 64-element boxes: the prefill kernel's
+    CUtensorMap tmap_v{};      // 3-D view of both 64-dim halves of 16 rows: the prefill kernel's V loads (optional)
+    bool has_tmap_v = false;
     CUtensorMap tmap_slot{};   // 4-D view, one box per 16 keys x head_dim x (K, V): the decode kernel's
     PoolLayout layout{};
     int forced_chunk = 0;
@@ -307,6 +310,9 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
             drkv_destroy(e);
             return DRKV_ERR_CUDA;
         }
+        e->has_tmap_v = make_pool_vhalves_tensor_map(&e->tmap_v, e->pool, geom->num_layers, (int)max_pages, geom->num_kv_heads,
+                                                     geom->page_size, geom->head_dim, nullptr) &&
+                        getenv("DRKV_NO_VHALVES") == nullptr;
         if (!make_pool_slot_tensor_map(&e->tmap_slot, e->pool, geom->num_layers, (int)max_pages, geom->num_kv_heads,
                                        geom->page_size, geom->head_dim, &terr)) {
             set_err(DRKV_ERR_CUDA, "%s", terr ? terr : "tensor map");
@@ -1380,7 +1386,8 @@ int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_
         p.page_size = g.page_size;
         p.scale_log2 = scale * 1.4426950408889634f;
         p.error_word = e->d_error;
-        CUDA_TRY(launch_attend_prefill(e->tmap, p, g.head_dim, g.dtype, (cudaStream_t)stream));
+        CUDA_TRY(launch_attend_prefill(e->tmap, e->has_tmap_v ? &e->tmap_v : nullptr, p, g.head_dim, g.dtype,
+                                       (cudaStream_t)stream));
     }
     return DRKV_OK;
 }

@@ -85,6 +85,7 @@ struct PrefillParams {
     int layer, max_pages, num_q_heads, num_kv_heads, group, page_size;
     float scale_log2;
     int* error_word;
+    int v_halves;             // set by the launcher: V comes through the V-halves view, one box per 16 keys
 };
 
 // Cross-GPU merge of one sequence's split-KV partials by peer stores, the tail of the merge kernel
@@ -143,7 +144,11 @@ bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layer
 cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,
                                  int dtype, cudaStream_t stream);
 constexpr int kMaxDecodeSeqs = 2048;   // sequences one decode-attention launch can take
-cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
+bool make_pool_vhalves_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
+                                  int num_kv_heads, int page_size, int head_dim, const char** err);
+// tmap_v: the V-halves view, or nullptr (then V is loaded with the 2-D boxes of tmap as K is).
+cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const CUtensorMap* tmap_v, const PrefillParams& p, int head_dim,
+                                  int dtype,
                                   cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, int n_seq, int dtype, cudaStream_t stream);
 
