@@ -391,7 +391,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     if (qr == nullptr) return -1;
                     const int rowi = (int)((qr - qall) / (int64_t)D);          // b * Hq + kvh * g + j
                     const int bq = rowi / p.num_q_heads, j = rowi % p.group;
-                    return (bq * p.num_kv_heads + meta.kvh) * p.max_tiles * p.group + j;
+                    return ((bq * p.num_kv_heads + meta.kvh) * p.max_tiles * p.group + j) * 4 + (lane & 3);
                 };
                 mass_row[0] = base_of(qr0);
                 mass_row[1] = base_of(qr1);
@@ -462,13 +462,12 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 const float p8 = fast_exp2(x8 - mnew), p9 = fast_exp2(x9 - mnew);
                 lsum[r] = lsum[r] * alpha[r] + ((p0 + p1) + (p8 + p9));
                 if (EXT && p.tile_lse != nullptr) {
-                    // log2 of this tile's un-normalised probability mass for the row, on the scale of the
-                    // final log-sum-exp: mass share = 2^(tile_lse - lse2) once the merge knows lse2
-                    float ts = (p0 + p1) + (p8 + p9);
-                    ts += __shfl_xor_sync(0xffffffffu, ts, 1);
-                    ts += __shfl_xor_sync(0xffffffffu, ts, 2);
-                    if ((lane & 3) == 0 && mass_row[r] >= 0)
-                        p.tile_lse[mass_row[r] + meta.tile * p.group] = ts > 0.f ? mnew + __log2f(ts) : -INFINITY;
+                    // log2 of the un-normalised probability mass of this lane's four keys of the tile, on the
+                    // scale of the final log-sum-exp: mass share = 2^(tile_lse - lse2) once the merge knows lse2.
+                    // The four lanes of a row store their own value: no shuffle on the softmax's critical path.
+                    const float ts = (p0 + p1) + (p8 + p9);
+                    if (mass_row[r] >= 0)
+                        p.tile_lse[mass_row[r] + meta.tile * p.group * 4] = ts > 0.f ? mnew + __log2f(ts) : -INFINITY;
                 }
                 split_pack<T>(p0, p1, phi[r], plo[r]);          // a0 (r=0) / a1 (r=1)
                 split_pack<T>(p8, p9, phi[2 + r], plo[2 + r]);  // a2 / a3
@@ -507,10 +506,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 }
             }
         }
-        else if (EXT && p.tile_lse != nullptr && (lane & 3) == 0) {
+        else if (EXT && p.tile_lse != nullptr) {
 #pragma unroll
             for (int r = 0; r < NR; r++)
-                if (mass_row[r] >= 0) p.tile_lse[mass_row[r] + meta.tile * p.group] = -INFINITY;
+                if (mass_row[r] >= 0) p.tile_lse[mass_row[r] + meta.tile * p.group * 4] = -INFINITY;
         }
         __syncwarp();                                  // every lane is done with the slot's shared memory
         outstanding--;
@@ -682,23 +681,36 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
 __global__ void __launch_bounds__(128) page_mass_kernel(const PageMassParams p) {
     pdl_wait();                                          // tile values and lse2 come from the two preceding kernels
     pdl_launch_dependents();
-    const int b = blockIdx.y;
-    const int page = blockIdx.x * blockDim.x + threadIdx.x;
+    // 32 pages x 4 slices of the kv heads per CTA; the slices are added in a fixed order (no atomics: the sums
+    // are reproducible)
+    __shared__ float s_part[4][32];
+    const int b = blockIdx.y, lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int page = blockIdx.x * 32 + lane;
     const int kv_end = p.kv_len[b];
     const int tiles_per_page = p.page_size / kGroupTokens;
     const int n_tiles = (kv_end + kGroupTokens - 1) / kGroupTokens;
-    if (page * tiles_per_page >= n_tiles) return;
+    const bool live = page * tiles_per_page < n_tiles;
     const int t1 = min((page + 1) * tiles_per_page, n_tiles);
-    float mass = 0.f;
     const int g = p.num_q_heads / p.num_kv_heads;
-    for (int kvh = 0; kvh < p.num_kv_heads; kvh++) {
-        const float* lse2 = p.lse2 + (int64_t)b * p.num_q_heads + kvh * g;
-        const float* tl = p.tile_lse + ((int64_t)b * p.num_kv_heads + kvh) * p.max_tiles * g;
-        for (int t = page * tiles_per_page; t < t1; t++)
-            for (int j = 0; j < g; j++) mass += fast_exp2(tl[t * g + j] - lse2[j]);
+    float mass = 0.f;
+    if (live) {
+        for (int kvh = slice; kvh < p.num_kv_heads; kvh += 4) {
+            const float* lse2 = p.lse2 + (int64_t)b * p.num_q_heads + kvh * g;
+            const float4* tl = reinterpret_cast<const float4*>(p.tile_lse) + ((int64_t)b * p.num_kv_heads + kvh) * p.max_tiles * g;
+            for (int t = page * tiles_per_page; t < t1; t++)
+                for (int j = 0; j < g; j++) {
+                    const float4 v = tl[t * g + j];      // the four lanes' shares of row j of this tile
+                    const float l2 = lse2[j];
+                    mass += (fast_exp2(v.x - l2) + fast_exp2(v.y - l2)) + (fast_exp2(v.z - l2) + fast_exp2(v.w - l2));
+                }
+        }
     }
-    float* dst = p.fresh + (int64_t)p.rows[b] * p.table_stride + page;
-    *dst += mass;
+    s_part[slice][lane] = mass;
+    __syncthreads();
+    if (slice == 0 && live) {
+        float* dst = p.fresh + (int64_t)p.rows[b] * p.table_stride + page;
+        *dst += (s_part[0][lane] + s_part[1][lane]) + (s_part[2][lane] + s_part[3][lane]);
+    }
 }
 
 // score = score * decay + new, then new = 0 (importance_scorer.cu:27-37, one fused multiply-add).
@@ -919,7 +931,7 @@ cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p,
 cudaError_t launch_page_mass(const PageMassParams& p, int n_seq, int max_kv_len, cudaStream_t stream) {
     const int pages = (max_kv_len + p.page_size - 1) / p.page_size;
     if (pages <= 0 || n_seq <= 0) return cudaSuccess;
-    return launch_pdl(page_mass_kernel, dim3((pages + 127) / 128, n_seq), dim3(128), 0, stream, p);
+    return launch_pdl(page_mass_kernel, dim3((pages + 31) / 32, n_seq), dim3(128), 0, stream, p);
 }
 
 cudaError_t launch_importance_update(float* scores, float* fresh, int64_t n, float decay, cudaStream_t stream) {

@@ -1178,7 +1178,7 @@ int drkv_scorer_enable(drkv_engine* e, float decay) {
         const size_t launch_seqs = e->book.max_seqs() < kMaxDecodeSeqs ? e->book.max_seqs() : kMaxDecodeSeqs;
         CUDA_TRY(cudaMalloc(&sc.d_scores, n * 4));
         CUDA_TRY(cudaMalloc(&sc.d_fresh, n * 4));
-        CUDA_TRY(cudaMalloc(&sc.d_tile_lse, launch_seqs * g.num_q_heads * sc.max_tiles * 4));
+        CUDA_TRY(cudaMalloc(&sc.d_tile_lse, launch_seqs * g.num_q_heads * sc.max_tiles * 4 * sizeof(float)));   // 4 values per row-tile
         CUDA_TRY(cudaMalloc(&sc.d_lse2, launch_seqs * g.num_q_heads * 4));
         CUDA_TRY(cudaMemset(sc.d_scores, 0, n * 4));     // importance_scorer.cu:57
         CUDA_TRY(cudaMemset(sc.d_fresh, 0, n * 4));

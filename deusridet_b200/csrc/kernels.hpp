@@ -63,7 +63,7 @@ struct DecodeParams {
     const int32_t* fb_chunks;
     const int32_t* fb_members;
     const int32_t* seq_first_chunk;
-    // tile masses for the importance scorer (null = off): tile_lse[((seq * Hkv + kv_head) * max_tiles + tile) * group + head_in_group]
+    // tile masses for the importance scorer (null = off): tile_lse[(((seq * Hkv + kv_head) * max_tiles + tile) * group + head_in_group) * 4 + quarter]
     float* tile_lse;
     int max_tiles;
     int total_items;          // upper bound n_seq * num_kv_heads * max_chunks (sizes the grid)
@@ -116,7 +116,7 @@ struct CombineParams {
 
 // Importance scorer: per-page attention mass from the decode kernel's tile values.
 struct PageMassParams {
-    const float* tile_lse;    // [((seq * Hkv + kv_head) * max_tiles + tile) * group + head_in_group]
+    const float* tile_lse;    // [(((seq * Hkv + kv_head) * max_tiles + tile) * group + head_in_group) * 4 + quarter]
     const float* lse2;        // [n_seq][Hq]
     const int32_t* rows;      // [n_seq] table rows
     const int32_t* kv_len;    // [n_seq]
