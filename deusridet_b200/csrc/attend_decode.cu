@@ -9,14 +9,18 @@
 //     src/sensus/auditus/asr/asr_ops_attn.cu:88-108);
 //   * every K/V byte is read from HBM once per KV head: the query heads of a group share
 //     the tile (the reference re-reads it once per query head);
-//   * pages are gathered by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
-//     into per-warp shared-memory rings guarded by mbarriers (192 KB in flight per SM),
-//     issued by a producer warp that walks the block table;
-//   * QK^T and PV run as m16n8k16 tensor-core tiles with fp32 accumulation: the 4..16
-//     query rows of a GQA group are far from a dense contraction (the tensor pipe stays
-//     under 10 % busy), they only keep the SM's issue slots free so that the kernel stays
-//     HBM-bound; softmax statistics are reduced with warp shuffles in fp32.  P is fed to
-//     the PV product as a two-term (hi + lo) split so that it carries ~16 significant bits.
+//   * pages are gathered by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast): ONE 4-D box per
+//     ring slot brings the K and V rows of 16 keys of one head (8 KB at head_dim 128) into the shared-memory
+//     ring that every warp owns (3 slots, 192 KB in flight per SM, mbarrier-guarded); lane 0 of the warp
+//     walks the block table and issues the copies ahead of the tile being computed, across item boundaries;
+//   * QK^T and PV run as m16n8k16 tensor-core tiles with fp32 accumulation: the 4..16 query rows of a GQA
+//     group are far from a dense contraction (the tensor pipe is about a quarter busy), they only keep the
+//     SM's issue slots free so that the kernel stays HBM-bound; softmax statistics are reduced with warp
+//     shuffles in fp32.  P is fed to the PV product as a two-term (hi + lo) split so that it carries ~16
+//     significant bits;
+//   * a shared-prefix plan adds work items whose 16 query rows come from several forked sequences over the
+//     chunks their block tables have in common, and the importance scorer's per-tile probability masses
+//     are a by-product (both compiled only into the EXT instantiation).
 // Holes (table entry < 0) contribute nothing.  All waits are bounded; a wait that gives
 // up records a code in the engine's error word and the CTA retires without trapping.
 #include "kernels.hpp"

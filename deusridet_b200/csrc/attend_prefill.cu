@@ -10,9 +10,11 @@
 // with the S and O accumulators and P in tensor memory (2 x (64 + 128 + 64) = all 512 columns).
 // P is stored as a two-term split (hi + lo, 32 packed columns each); the lo term is multiplied in
 // only by CTAs whose rows see at most 1024 keys, where single-term 16-bit weights would cost more
-// than the 2e-3 bound on rows dominated by a handful of keys.  One thread
-// issues all MMAs; while the tensor pipe works on one tile, the four softmax warps of the other
-// tile run (ping-pong), so the K/V block fetched by TMA is used by 256 query rows.  O stays in
+// than the 2e-3 bound on rows dominated by a handful of keys.  One thread per tile
+// issues that tile's MMAs (a lone issuing thread is a serial stream of waits, instructions and
+// commits: two of them overlap), one warp issues the box loads of a key block from as many lanes as
+// there are boxes, eight softmax warps (four per tile, one row per thread) do the arithmetic; the
+// K/V block fetched by TMA is used by 256 query rows.  O stays in
 // TMEM across key blocks and is rescaled there only when a row's running maximum has grown by
 // more than 2^8 since the scale in use was chosen; the final division by l undoes the stale
 // scale.  Same recurrence and mask as the reference: token t sees keys [0, pos_start + t],
