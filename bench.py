@@ -60,6 +60,19 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def read_stream_gbs(eng, stream):
+    """Read-only streaming bandwidth of this GPU over the first 8 GiB of the engine's pool (the reference's own
+    ceiling method, tools/probe_bw.cu): the second denominator beside the measured copy peak."""
+    import ctypes as C
+    pool = eng.pool_tensor()
+    nbytes = min(pool.numel() * pool.element_size(), 8 << 30)
+    if nbytes < (256 << 20):
+        return None
+    out = C.c_double()
+    rc = eng.lib.drkv_probe_read_bandwidth(pool.data_ptr(), nbytes, 10, stream.cuda_stream, C.byref(out))
+    return float(out.value) if rc == 0 else None
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -243,6 +256,7 @@ def run_ours(args):
     kms, kn_launch = eng.kernel_timing(False, read=True)
     kv_bytes, all_bytes = algorithmic_bytes_per_layer(w, lens)
     peak, peak_kind = peaks()
+    read_peak = read_stream_gbs(eng, stream)
     achieved = kv_bytes / (kms / kn_launch * 1e-3) / 1e9 if kn_launch else None
     # DRAM bytes per algorithmic K/V byte of attend_decode_kernel, from the ncu capture summarised in
     # profiles/attend_decode_kernel_c2.md (small case; traffic grows in proportion to the keys processed)
@@ -341,6 +355,8 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
                          "traffic": kv_bytes * traffic_ratio, "bytes_per_launch": kv_bytes,
+                         "read_stream_gbs": read_peak,
+                         "frac_of_read_stream": achieved / read_peak if (achieved and read_peak) else None,
                          "us_per_launch": kms / kn_launch * 1e3 if kn_launch else None},
             "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
             "cow_copies": stats["cow_copies"],

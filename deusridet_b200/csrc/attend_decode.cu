@@ -35,12 +35,16 @@ namespace {
 constexpr int kGroupTokens = 16;                               // keys per ring slot
 constexpr float kNegBig = -1.0e30f;                            // "no key seen yet" in the log2 domain
 
-// Ring geometry per head_dim: consumer warps per CTA and slots per warp ring, sized so that
-// warps * depth * (K tile + V tile) = 192 KB of loads can be in flight per SM.
+// Ring geometry per head_dim: consumer warps per CTA and slots per warp ring.  At head_dim 128 a warp
+// has one 8 KB gather landing while it computes the previous one: 148 SMs x 8 warps x 8 KB = 9.7 MB in
+// flight, about bandwidth x loaded latency.  A third slot per warp (19 MB in flight) made the pass over
+// long items 8 % slower: the memory system serves fewer, not more, concurrent streams better.  At 64 and
+// 256 the pass is bound by the instruction stream of the warps, not by the loads in flight (measured:
+// 2 to 6 slots within 1 %), and 256 uses the room of the shallower ring for more warps.
 template <int D> struct RingShape;
 template <> struct RingShape<64>  { static constexpr int kWarps = 8, kDepth = 6; };
-template <> struct RingShape<128> { static constexpr int kWarps = 8, kDepth = 3; };
-template <> struct RingShape<256> { static constexpr int kWarps = 4, kDepth = 3; };
+template <> struct RingShape<128> { static constexpr int kWarps = 8, kDepth = 2; };
+template <> struct RingShape<256> { static constexpr int kWarps = 6, kDepth = 2; };
 
 enum SlotFlags : int { SLOT_FIRST = 1, SLOT_LAST = 2, SLOT_SKIP = 4, SLOT_DONE = 8 };
 
@@ -53,7 +57,7 @@ struct alignas(16) SlotMeta {
 
 #ifdef DRKV_WARP_TRACE
 // Debug build only: per-warp timestamps (ns) of the last launch: start, first data, last item start, end, items.
-__device__ unsigned long long g_warp_trace[148 * 8][5];
+__device__ unsigned long long g_warp_trace[148 * 8][8];   // start, first data, last item start, end, items, cycles waiting for data, cycles in item start, cycles in the issue path
 #define TRACE(i, v) do { if (lane == 0) g_warp_trace[blockIdx.x * WARPS + w][i] = (v); } while (0)
 #else
 #define TRACE(i, v) do { } while (0)
@@ -98,7 +102,7 @@ __device__ __forceinline__ void split_pack(float p0, float p1, uint32_t& hi, uin
 // of DEPTH slots (16 keys of K and V each), its 16-row query fragments and its (m, l, o)
 // state.  Its lane 0 issues the TMA gathers DEPTH - 1 groups ahead of the group being
 // computed, across item boundaries, and the next item (queue index, length, table row, first
-// page id) is fetched while the current one is processed, so that neither the atomic nor the
+// 32 page ids) is fetched while the current one is processed, so that neither the atomic nor the
 // table look-ups sit on the critical path.  An item's partial goes straight from the
 // accumulators to global memory; there is no block-level barrier after start-up.
 // HI: the GQA group has more than 8 query heads, so rows 8..15 of the 16-row tile are live.
@@ -200,6 +204,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
 #ifdef DRKV_WARP_TRACE
     unsigned long long trace_items = 0;
     bool trace_first = true;
+    long long tr_wait = 0, tr_first = 0, tr_issue = 0;
+#define TCLK() clock64()
+#else
+#define TCLK() 0ll
 #endif
 
     // ---- next-item prefetch state (warp-uniform except raw_next, which lane 0 owns) ----
@@ -213,10 +221,15 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     constexpr int kPrefetchGroups = DRKV_PREFETCH_GROUPS;
     int raw_next = 0, n_state = 0;
     bool exhausted = false;
-    int n_b = 0, n_kvh = 0, n_slot = 0, n_tok_lo = 0, n_tok_hi = 0, n_trow = 0, n_page = -1, n_fam = 0;   // n_fam: family block + 1, 0 = plain
+    int n_b = 0, n_kvh = 0, n_slot = 0, n_tok_lo = 0, n_tok_hi = 0, n_trow = 0, n_fam = 0;   // n_fam: family block + 1, 0 = plain
+    int n_pv = -1;              // per lane: page id of logical page (n_tok_lo / page_size) + lane of the next item
     // ---- issue cursor ----
     bool c_valid = false;
-    int c_b = 0, c_kvh = 0, c_slot = 0, c_trow = 0, c_tok_hi = 0, c_tok_lo = 0, c_ngroups = 0, c_gi = 0, c_page = -1, c_fam = 0;
+    int c_b = 0, c_kvh = 0, c_slot = 0, c_trow = 0, c_tok_hi = 0, c_tok_lo = 0, c_ngroups = 0, c_gi = 0, c_fam = 0;
+    // Page ids come 32 at a time: lane i holds the id of logical page c_pv_base + i (c_pv) and of the 32 after
+    // those (c_pvn), loaded a window ahead; a group's id is a shuffle away.  A table load per group would sit
+    // on the issue path with the latency of a saturated memory system.
+    int c_pv = -1, c_pvn = -1, c_pv_base = 0, c_logical = 0, c_off = 0;
     int i_slot = 0, outstanding = 0;
     // ---- compute cursor ----
     int slot = 0, phase = 0;
@@ -278,10 +291,12 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         }
         n_state = 2;
     };
-    auto load_page = [&](int trow, int tok) -> int {
-        const int logical = tok / p.page_size;
+    auto load_window = [&](int trow, int first_logical) -> int {
+        const int logical = first_logical + lane;
         return logical < p.table_stride ? __ldg(p.tables + (int64_t)trow * p.table_stride + logical) : -1;
     };
+    const int plane2 = 2 * (int)rows_per_plane;                  // head rows of one (layer, page): K plane + V plane
+    const int layer_page0 = p.layer * p.max_pages;
 
     float m2[2] = {kNegBig, kNegBig};
     float lsum[2] = {0.f, 0.f};
@@ -292,6 +307,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
 
     while (true) {
         // ------------- issue: keep DEPTH groups in flight, across item boundaries -------------
+        const long long tc0 = TCLK();
         while (outstanding < DEPTH) {
             if (!c_valid) {
                 if (n_state == 0 && !exhausted) fetch_raw();
@@ -300,13 +316,22 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 c_b = n_b; c_kvh = n_kvh; c_slot = n_slot; c_trow = n_trow; c_tok_lo = n_tok_lo; c_tok_hi = n_tok_hi; c_fam = n_fam;
                 c_ngroups = (c_tok_hi - c_tok_lo + kGroupTokens - 1) / kGroupTokens;
                 c_gi = 0;
-                c_page = n_state == 3 ? n_page : load_page(c_trow, c_tok_lo);
+                c_logical = c_tok_lo / p.page_size;
+                c_off = c_tok_lo - c_logical * p.page_size;
+                c_pv_base = c_logical;
+                c_pv = n_state == 3 ? n_pv : load_window(c_trow, c_logical);
+                c_pvn = load_window(c_trow, c_logical + 32);
                 c_valid = true;
                 n_state = 0;
             }
             const int ring = w * DEPTH + i_slot;
             const int tok0 = c_tok_lo + c_gi * kGroupTokens;
-            int page = c_page;
+            if (c_logical - c_pv_base >= 32) {             // next window of page ids (requested 32 pages ago)
+                c_pv = c_pvn;
+                c_pv_base += 32;
+                c_pvn = load_window(c_trow, c_pv_base + 32);
+            }
+            int page = __shfl_sync(0xffffffffu, c_pv, c_logical - c_pv_base);
             if (page >= p.max_pages) {
                 page = -1;
                 if (lane == 0) atomicExch(p.error_word, (int)KERR_BAD_PAGE);
@@ -329,10 +354,10 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 mbar_arrive_expect_tx(bar_full + 8 * ring, page >= 0 ? SLOT_BYTES : 0);
                 if (page >= 0) {
                     const uint32_t dst = smem_u32(smem + ring * SLOT_BYTES);
-                    const int64_t rk = (((int64_t)p.layer * p.max_pages + page) * 2) * rows_per_plane +
-                                       (int64_t)c_kvh * p.page_size + (tok0 % p.page_size);
+                    // head row of the group's first key in the K plane (the descriptor has fewer than 2^31 rows)
+                    const int rk = (layer_page0 + page) * plane2 + c_kvh * p.page_size + c_off;
                     // one box: 16 key rows x the whole head dim x the K and the V plane (8 KB at D = 128)
-                    tma_load_4d(dst, &tmap, 0, 0, (int)rk, 0, bar_full + 8 * ring);
+                    tma_load_4d(dst, &tmap, 0, 0, rk, 0, bar_full + 8 * ring);
                 }
             }
             if (++i_slot == DEPTH) i_slot = 0;
@@ -341,8 +366,11 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 c_valid = false;
             } else {
                 c_gi++;
-                // page id of the next group: same table entry while inside one page
-                if ((tok0 + kGroupTokens) % p.page_size == 0) c_page = load_page(c_trow, tok0 + kGroupTokens);
+                c_off += kGroupTokens;
+                if (c_off == p.page_size) {
+                    c_off = 0;
+                    c_logical++;
+                }
             }
             // one step of the next-item pipeline per issued group, started near the end of this item
             if (!exhausted) {
@@ -351,12 +379,13 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 } else if (n_state == 1) {
                     decode_next();
                 } else if (n_state == 2) {
-                    n_page = load_page(n_trow, n_tok_lo);
+                    n_pv = load_window(n_trow, n_tok_lo / p.page_size);
                     n_state = 3;
                 }
             }
         }
         if (outstanding == 0) break;                   // queue drained and every group consumed
+        const long long tc1 = TCLK();
 
         // ------------- compute the oldest group in flight -------------
         const int ring = w * DEPTH + slot;
@@ -365,8 +394,11 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             break;
         }
         __syncwarp();
+        const long long tc2 = TCLK();
         const SlotMeta meta = metas[ring];
 #ifdef DRKV_WARP_TRACE
+        tr_issue += tc1 - tc0;
+        tr_wait += tc2 - tc1;
         if (trace_first) { TRACE(1, global_timer()); trace_first = false; }
         if (meta.flags & SLOT_FIRST) { TRACE(2, global_timer()); trace_items++; }
 #endif
@@ -409,6 +441,15 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 qf[kk][1] = qr1 ? __ldg(q1 + 8 * kk) : 0u;
                 qf[kk][3] = qr1 ? __ldg(q1 + 8 * kk + 4) : 0u;
             }
+#ifdef DRKV_WARP_TRACE
+            {   // force the query loads to land here so that their latency is attributed to the item start
+                uint32_t x = 0;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; kk++) x ^= qf[kk][0] ^ qf[kk][1] ^ qf[kk][2] ^ qf[kk][3];
+                if (x == 0x12345678u) tr_first += 1;
+                tr_first += TCLK() - tc2;
+            }
+#endif
             m2[0] = m2[1] = kNegBig;
             lsum[0] = lsum[1] = 0.f;
 #pragma unroll
@@ -556,6 +597,9 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
 #ifdef DRKV_WARP_TRACE
     TRACE(3, global_timer());
     TRACE(4, trace_items);
+    TRACE(5, tr_wait);
+    TRACE(6, tr_first);
+    TRACE(7, tr_issue);
 #endif
     // The last warp of the grid to leave rewinds the work queue for the next launch on this stream.
     if (lane == 0) {
@@ -905,6 +949,10 @@ bool make_pool_vhalves_tensor_map(CUtensorMap* out, const void* pool, int num_la
         return false;
     }
     return true;
+}
+
+int decode_warps_per_cta(int head_dim) {
+    return head_dim == 64 ? RingShape<64>::kWarps : head_dim == 128 ? RingShape<128>::kWarps : RingShape<256>::kWarps;
 }
 
 cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,

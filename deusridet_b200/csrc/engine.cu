@@ -66,8 +66,7 @@ size_t page_bytes_all_layers(const drkv_geometry& g) {
 // warp's queue: warps take whole items, so the pass lasts about ceil(items / warps) items of (chunk +
 // a fixed cost per item worth ~64 keys: start-up, the partial's write and its share of the merge) each.
 template <typename ItemsFn>
-int pick_chunk_by_cost(int group, int num_sms, bool exact, ItemsFn items) {
-    const long warps = (long)num_sms * 8;
+int pick_chunk_by_cost(int group, long warps, bool exact, ItemsFn items) {
     int best = 0;
     long best_cost = 0;
     // Every multiple of 16 is a legal chunk.  With exact item counts (a decode plan knows every length) the
@@ -84,8 +83,7 @@ int pick_chunk_by_cost(int group, int num_sms, bool exact, ItemsFn items) {
     return best;
 }
 
-int pick_chunk(int n_seq, int hkv, int group, int max_kv_span, int num_sms) {
-    const long warps = (long)num_sms * 8;
+int pick_chunk(int n_seq, int hkv, int group, int max_kv_span, long warps) {
     auto items = [&](int c) { return (long)n_seq * hkv * ((max_kv_span + c - 1) / c); };
     if (n_seq == 1 && items(group > 4 ? 512 : 256) > warps) {
         // One long sequence: equal items, one per warp, is a perfect partition with the fewest partials.
@@ -93,7 +91,7 @@ int pick_chunk(int n_seq, int hkv, int group, int max_kv_span, int num_sms) {
         const long c = (max_kv_span + per_head - 1) / per_head;
         return (int)((c + 15) / 16 * 16);
     }
-    return pick_chunk_by_cost(group, num_sms, false, items);
+    return pick_chunk_by_cost(group, warps, false, items);
 }
 
 }  // namespace
@@ -783,7 +781,8 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
         chunk = plan->chunk;   // the plan's chunk was checked against the scratch when it was made
     } else {
         chunk = e->forced_chunk ? e->forced_chunk
-                                : pick_chunk(n_seq, g.num_kv_heads, g.num_q_heads / g.num_kv_heads, max_span, e->num_sms);
+                                : pick_chunk(n_seq, g.num_kv_heads, g.num_q_heads / g.num_kv_heads, max_span,
+                                             (long)e->num_sms * decode_warps_per_cta(g.head_dim));
         auto need_bytes = [&](int c) {
             return (size_t)n_seq * g.num_q_heads * ((max_span + c - 1) / c) * (g.head_dim + 2) * 4;
         };
@@ -797,7 +796,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     // warps finish within a piece of one another.
     int tail_chunks = 0, tail_split = 1;
     {
-        const long warps = (long)e->num_sms * 8, streams = (long)n_seq * g.num_kv_heads;
+        const long warps = (long)e->num_sms * decode_warps_per_cta(g.head_dim), streams = (long)n_seq * g.num_kv_heads;
         const long items = streams * max_chunks;
         const bool forced = e->tail_mode > 0 && chunk >= 32 && chunk % 32 == 0;
         const bool automatic = e->tail_mode < 0 && chunk >= 128 && chunk % 64 == 0 && items >= 3 * warps;
@@ -984,7 +983,7 @@ int drkv_plan_decode(drkv_engine* e, int n_seq, const int32_t* seqs, const int32
     };
     int chunk = e->forced_chunk;
     if (!chunk) {
-        chunk = pick_chunk_by_cost(group, e->num_sms, true, [&](int c) { return (long)planned_items(c, nullptr); });
+        chunk = pick_chunk_by_cost(group, (long)e->num_sms * decode_warps_per_cta(e->geom.head_dim), true, [&](int c) { return (long)planned_items(c, nullptr); });
     }
     if (e->has_device) {
         auto need_bytes = [&](int c) {

@@ -144,6 +144,7 @@ bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layer
 cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,
                                  int dtype, cudaStream_t stream);
 constexpr int kMaxDecodeSeqs = 2048;   // sequences one decode-attention launch can take
+int decode_warps_per_cta(int head_dim);  // warps of one decode CTA, each with its own queue of items
 bool make_pool_vhalves_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
                                   int num_kv_heads, int page_size, int head_dim, const char** err);
 // tmap_v: the V-halves view, or nullptr (then V is loaded with the 2-D boxes of tmap as K is).
