@@ -48,12 +48,17 @@ template <> struct RingShape<256> { static constexpr int kWarps = 6, kDepth = 2;
 
 enum SlotFlags : int { SLOT_FIRST = 1, SLOT_LAST = 2, SLOT_SKIP = 4, SLOT_DONE = 8 };
 
-// What the producer tells a consumer warp about one ring slot.
-struct alignas(16) SlotMeta {
-    int b, kvh, part_slot, flags;   // part_slot: index of the partial of query row 0 of the group
-    int v_lo, v_hi, fam, tile;      // keys [v_lo, v_hi) of the 16 in the slot are visible; fam: family block + 1 or 0;
-                                    // tile: index of the 16-key group within the sequence
+// What lane 0 leaves for its warp about one ring slot: one 8-byte store per group; everything that is the
+// same for all groups of an item is written once per item.
+struct alignas(8) SlotMeta {
+    int flags;                      // SlotFlags | (item entry << kItemShift)
+    int tok0;                       // first key of the group (a multiple of 16)
 };
+struct alignas(16) ItemMeta {
+    int b, kvh, part_slot, fam;     // part_slot: index of the partial of query row 0; fam: family block + 1 or 0
+    int tok_hi, pad0, pad1, pad2;   // keys of the item end here
+};
+constexpr int kItemShift = 4, kItemEntries = 8;   // a ring holds at most 6 groups, so at most 7 items are live
 
 #ifdef DRKV_WARP_TRACE
 // Debug build only: per-warp timestamps (ns) of the last launch: start, first data, last item start, end, items.
@@ -126,6 +131,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     uint64_t* bars = reinterpret_cast<uint64_t*>(metas + WARPS * DEPTH);               // full[WARPS][DEPTH]
     int* cum = reinterpret_cast<int*>(bars + WARPS * DEPTH);                           // [n_seq + 1]
     __shared__ int s_warp_tot[WARPS];
+    __shared__ ItemMeta s_items[WARPS][kItemEntries];
 
     const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
     const uint32_t bar_full = smem_u32(bars);
@@ -230,6 +236,8 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     // those (c_pvn), loaded a window ahead; a group's id is a shuffle away.  A table load per group would sit
     // on the issue path with the latency of a saturated memory system.
     int c_pv = -1, c_pvn = -1, c_pv_base = 0, c_logical = 0, c_off = 0;
+    int c_item = 0;             // entry of s_items[w] that describes the item being issued
+    bool zero_filled = false;   // some lane has written zeros into a ring slot since the last proxy fence
     int i_slot = 0, outstanding = 0;
     // ---- compute cursor ----
     int slot = 0, phase = 0;
@@ -323,6 +331,17 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 c_pvn = load_window(c_trow, c_logical + 32);
                 c_valid = true;
                 n_state = 0;
+                c_item = (c_item + 1) & (kItemEntries - 1);
+                if (lane == 0) {
+                    ItemMeta im;
+                    im.b = c_b;
+                    im.kvh = c_kvh;
+                    im.part_slot = (EXT && c_fam) ? c_slot : (c_b * p.num_q_heads + c_kvh * p.group) * slot_stride + c_slot;
+                    im.fam = c_fam;
+                    im.tok_hi = c_tok_hi;
+                    im.pad0 = im.pad1 = im.pad2 = 0;
+                    s_items[w][c_item] = im;
+                }
             }
             const int ring = w * DEPTH + i_slot;
             const int tok0 = c_tok_lo + c_gi * kGroupTokens;
@@ -339,18 +358,13 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             const bool last = (c_gi == c_ngroups - 1);
             if (lane == 0) {
                 SlotMeta m;
-                m.b = c_b;
-                m.kvh = c_kvh;
-                m.part_slot = (EXT && c_fam) ? c_slot : (c_b * p.num_q_heads + c_kvh * p.group) * slot_stride + c_slot;
-                m.flags = (c_gi == 0 ? SLOT_FIRST : 0) | (last ? SLOT_LAST : 0) | (page < 0 ? SLOT_SKIP : 0);
-                m.v_lo = max(0, p.kv_begin - tok0);
-                m.v_hi = min(kGroupTokens, c_tok_hi - tok0);
-                m.fam = c_fam;
-                m.tile = tok0 / kGroupTokens;
+                m.flags = (c_gi == 0 ? SLOT_FIRST : 0) | (last ? SLOT_LAST : 0) | (page < 0 ? SLOT_SKIP : 0) | (c_item << kItemShift);
+                m.tok0 = tok0;
                 metas[ring] = m;
-                // earlier generic-proxy accesses to this slot (ldmatrix reads, zero fill) are ordered
-                // before the async-proxy writes of the new gather
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                // Generic-proxy WRITES to the ring (the zero fill of an end group's hidden V rows, made visible
+                // to this lane by the __syncwarp that closed that group) are ordered before the async-proxy
+                // writes of the new gather.  Reads need no fence: the ldmatrix results have been consumed.
+                if (zero_filled) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive_expect_tx(bar_full + 8 * ring, page >= 0 ? SLOT_BYTES : 0);
                 if (page >= 0) {
                     const uint32_t dst = smem_u32(smem + ring * SLOT_BYTES);
@@ -360,6 +374,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     tma_load_4d(dst, &tmap, 0, 0, rk, 0, bar_full + 8 * ring);
                 }
             }
+            zero_filled = false;
             if (++i_slot == DEPTH) i_slot = 0;
             outstanding++;
             if (last) {
@@ -396,6 +411,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         __syncwarp();
         const long long tc2 = TCLK();
         const SlotMeta meta = metas[ring];
+        const ItemMeta* item = &s_items[w][(meta.flags >> kItemShift) & (kItemEntries - 1)];
 #ifdef DRKV_WARP_TRACE
         tr_issue += tc1 - tc0;
         tr_wait += tc2 - tc1;
@@ -409,16 +425,16 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             const T* qall = reinterpret_cast<const T*>(p.q);
             const T* qr0 = nullptr;
             const T* qr1 = nullptr;
-            if (!EXT || meta.fam == 0) {
-                const T* qb = qall + ((int64_t)meta.b * p.num_q_heads + (int64_t)meta.kvh * p.group) * D;
+            if (!EXT || item->fam == 0) {
+                const T* qb = qall + ((int64_t)item->b * p.num_q_heads + (int64_t)item->kvh * p.group) * D;
                 if (qrow < p.group) qr0 = qb + (int64_t)qrow * D;
                 if (HI && qrow + 8 < p.group) qr1 = qb + (int64_t)(qrow + 8) * D;
             } else {
-                const int32_t* mem = p.fb_members + (meta.fam - 1) * 16;
+                const int32_t* mem = p.fb_members + (item->fam - 1) * 16;
                 const int r0i = qrow / p.group, r1i = (qrow + 8) / p.group;
                 const int b0 = r0i < 16 ? __ldg(mem + r0i) : -1, b1 = (HI && r1i < 16) ? __ldg(mem + r1i) : -1;
-                if (b0 >= 0) qr0 = qall + ((int64_t)b0 * p.num_q_heads + (int64_t)meta.kvh * p.group + qrow % p.group) * D;
-                if (b1 >= 0) qr1 = qall + ((int64_t)b1 * p.num_q_heads + (int64_t)meta.kvh * p.group + (qrow + 8) % p.group) * D;
+                if (b0 >= 0) qr0 = qall + ((int64_t)b0 * p.num_q_heads + (int64_t)item->kvh * p.group + qrow % p.group) * D;
+                if (b1 >= 0) qr1 = qall + ((int64_t)b1 * p.num_q_heads + (int64_t)item->kvh * p.group + (qrow + 8) % p.group) * D;
             }
             if (EXT && p.tile_lse != nullptr) {
                 // value of (sequence b, kv head, tile, head-in-group j) at ((b * Hkv + kvh) * max_tiles + tile) * g + j:
@@ -427,7 +443,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     if (qr == nullptr) return -1;
                     const int rowi = (int)((qr - qall) / (int64_t)D);          // b * Hq + kvh * g + j
                     const int bq = rowi / p.num_q_heads, j = rowi % p.group;
-                    return ((bq * p.num_kv_heads + meta.kvh) * p.max_tiles * p.group + j) * 4 + (lane & 3);
+                    return ((bq * p.num_kv_heads + item->kvh) * p.max_tiles * p.group + j) * 4 + (lane & 3);
                 };
                 mass_row[0] = base_of(qr0);
                 mass_row[1] = base_of(qr1);
@@ -458,7 +474,12 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 for (int j = 0; j < 2 * NR; j++) o[i][j] = 0.f;
         }
         if (!(meta.flags & SLOT_SKIP)) {
-            const int v_lo = meta.v_lo, v_hi = meta.v_hi;
+            // keys [v_lo, v_hi) of the 16 in the slot are visible: all of them except in an item's end groups
+            int v_lo = 0, v_hi = kGroupTokens;
+            if (meta.flags & (SLOT_FIRST | SLOT_LAST)) {
+                v_lo = max(0, p.kv_begin - meta.tok0);
+                v_hi = min(kGroupTokens, item->tok_hi - meta.tok0);
+            }
             uint8_t* kt = smem + ring * SLOT_BYTES;
             uint8_t* vt = kt + TILE_BYTES;
             if (v_hi < kGroupTokens || v_lo > 0) {
@@ -470,6 +491,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                         *reinterpret_cast<Vec16*>(vt + swz_rows(r, c, NH * 128)) = Vec16{{0u, 0u, 0u, 0u}};
                 }
                 __syncwarp();
+                zero_filled = true;
             }
             // ---- S = Q K^T : 16 rows x 16 keys ----
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -512,7 +534,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     // The four lanes of a row store their own value: no shuffle on the softmax's critical path.
                     const float ts = (p0 + p1) + (p8 + p9);
                     if (mass_row[r] >= 0)
-                        p.tile_lse[mass_row[r] + meta.tile * p.group * 4] = ts > 0.f ? mnew + __log2f(ts) : -INFINITY;
+                        p.tile_lse[mass_row[r] + (meta.tok0 / kGroupTokens) * p.group * 4] = ts > 0.f ? mnew + __log2f(ts) : -INFINITY;
                 }
                 split_pack<T>(p0, p1, phi[r], plo[r]);          // a0 (r=0) / a1 (r=1)
                 split_pack<T>(p8, p9, phi[2 + r], plo[2 + r]);  // a2 / a3
@@ -554,7 +576,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         else if (EXT && p.tile_lse != nullptr) {
 #pragma unroll
             for (int r = 0; r < NR; r++)
-                if (mass_row[r] >= 0) p.tile_lse[mass_row[r] + meta.tile * p.group * 4] = -INFINITY;
+                if (mass_row[r] >= 0) p.tile_lse[mass_row[r] + (meta.tok0 / kGroupTokens) * p.group * 4] = -INFINITY;
         }
         __syncwarp();                                  // every lane is done with the slot's shared memory
         outstanding--;
@@ -570,14 +592,14 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 l += __shfl_xor_sync(0xffffffffu, l, 2);
                 const int row = qrow + 8 * r;
                 int64_t ps = -1;                                   // partial slot of this row, -1: padding row
-                if (!EXT || meta.fam == 0) {
-                    if (row < p.group) ps = (int64_t)meta.part_slot + (int64_t)row * slot_stride;
+                if (!EXT || item->fam == 0) {
+                    if (row < p.group) ps = (int64_t)item->part_slot + (int64_t)row * slot_stride;
                 } else {
                     const int mi = row / p.group;
-                    const int bm = mi < 16 ? __ldg(p.fb_members + (meta.fam - 1) * 16 + mi) : -1;
+                    const int bm = mi < 16 ? __ldg(p.fb_members + (item->fam - 1) * 16 + mi) : -1;
                     if (bm >= 0)
-                        ps = ((int64_t)bm * p.num_q_heads + (int64_t)meta.kvh * p.group + row % p.group) * slot_stride +
-                             meta.part_slot;               // part_slot holds the chunk index for family blocks
+                        ps = ((int64_t)bm * p.num_q_heads + (int64_t)item->kvh * p.group + row % p.group) * slot_stride +
+                             item->part_slot;               // part_slot holds the chunk index for family blocks
                 }
                 if (ps >= 0) {
                     const bool empty = !(l > 0.f);

@@ -121,7 +121,7 @@ struct drkv_engine {
     CUtensorMap tmap_slot{};   // 4-D view, one box per 16 keys x head_dim x (K, V): the decode kernel's
     PoolLayout layout{};
     int forced_chunk = 0;
-    int tail_mode = 0;         // tail split of the decode pass: 0 off (default: it measured slower), -1 automatic, n > 0: the last n chunks
+    int tail_mode = -1;        // tail split of the decode pass: -1 automatic (default), 0 off, n > 0: the last n chunks
     int num_sms = 148;
     int* d_work = nullptr;   // decode kernel's work-queue head
     int* d_exit = nullptr;   // decode kernel's count of warps that have left
@@ -780,9 +780,15 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     if (plan) {
         chunk = plan->chunk;   // the plan's chunk was checked against the scratch when it was made
     } else {
+        const long warps = (long)e->num_sms * decode_warps_per_cta(g.head_dim);
         chunk = e->forced_chunk ? e->forced_chunk
-                                : pick_chunk(n_seq, g.num_kv_heads, g.num_q_heads / g.num_kv_heads, max_span,
-                                             (long)e->num_sms * decode_warps_per_cta(g.head_dim));
+                                : pick_chunk(n_seq, g.num_kv_heads, g.num_q_heads / g.num_kv_heads, max_span, warps);
+        // A batch several 512-key items deep per warp: long items (fewer starts, fewer partials), and the last
+        // chunk of every sequence in 64-key pieces at the end of the queue, which evens out the finish
+        // (measured on 64 sequences of 1-8 k keys: 2.5-4 % off the launch against 256-key items).
+        if (!e->forced_chunk && e->tail_mode < 0 && d_rows != nullptr &&
+            (long)n_seq * g.num_kv_heads * ((max_span + 511) / 512) >= 3 * warps)
+            chunk = 512;
         auto need_bytes = [&](int c) {
             return (size_t)n_seq * g.num_q_heads * ((max_span + c - 1) / c) * (g.head_dim + 2) * 4;
         };
@@ -791,9 +797,8 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
             return set_err(DRKV_ERR_CAPACITY, "attend: split-KV scratch too small for %d sequences x %d keys", n_seq, max_span);
     }
     const int max_chunks = (max_span + chunk - 1) / chunk;
-    // Tail split: when the pass is several chunks deep per warp, the last chunks of every sequence are
-    // queued last and in 64-key pieces, about one chunk's worth of work per warp in total, so that the
-    // warps finish within a piece of one another.
+    // Tail split: when the pass is several chunks deep per warp, the last chunk of every sequence is
+    // queued last and in 64-key pieces, so that the warps finish within a piece of one another.
     int tail_chunks = 0, tail_split = 1;
     {
         const long warps = (long)e->num_sms * decode_warps_per_cta(g.head_dim), streams = (long)n_seq * g.num_kv_heads;
@@ -802,7 +807,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
         const bool automatic = e->tail_mode < 0 && chunk >= 128 && chunk % 64 == 0 && items >= 3 * warps;
         if (d_rows != nullptr && (forced || automatic)) {
             tail_split = chunk >= 128 && chunk % 64 == 0 ? chunk / 64 : 2;
-            tail_chunks = forced ? e->tail_mode : (int)((warps + streams / 2) / streams);
+            tail_chunks = forced ? e->tail_mode : 1;      // two chunks in pieces measured slower than one
             if (tail_chunks < 1) tail_chunks = 1;
             if (tail_chunks > 4) tail_chunks = 4;
             const size_t need = (size_t)n_seq * g.num_q_heads * (max_chunks + tail_chunks * tail_split) * (g.head_dim + 2) * 4;

@@ -176,9 +176,9 @@ DRKV_API int drkv_kernel_error(drkv_engine* e);
  * else a positive multiple of 16.  Tuning knob, no counterpart in the reference. */
 DRKV_API int drkv_set_chunk_tokens(drkv_engine* e, int chunk_tokens);
 /* Tail split of the batched decode pass: the last `mode` chunks of every sequence are queued last and in
- * 64-key pieces so that the persistent warps finish close together.  0: off (the default: on the measured
- * workloads the extra work items cost more than the even finish gains), -1: automatic (on when the pass is at
- * least three chunks deep per warp), 1..4: forced. */
+ * 64-key pieces so that the persistent warps finish close together.  -1: automatic (the default: on, with
+ * 512-key chunks and one tail chunk, when the pass is at least three chunks deep per warp), 0: off,
+ * 1..4: forced. */
 DRKV_API int drkv_set_tail_split(drkv_engine* e, int mode);
 /* Measurement aid (the reference brackets its kernels with cudaEvents the same way,
  * src/machina/forward.cu:265-275): while enabled, every launch of the decode attention kernel
