@@ -143,10 +143,12 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
     }
-    // Only the barrier set-up overlaps the preceding kernel: lengths, tables, the pool, the
-    // queue head and the scratch may all have been written by it.
-    pdl_wait();
-    pdl_launch_dependents();
+    // What runs before pdl_wait() overlaps the tail of the preceding kernel.  That kernel may still be writing
+    // the pool (an append), the query or the scratch; everything launched before it has completed, because a
+    // kernel of this library releases its dependents only after its own wait, and any other kernel releases
+    // them by completing.  Lengths, rows, block tables and plan arrays are written by copies or by kernels
+    // further back, never by the kernel directly in front of an attention launch, so the prefix sum, the
+    // warp's first item and its page ids are worked out up here; the first gather comes after the wait.
     // ---- items per entry, exclusive prefix sum into cum[] ----
     // Entries: first the family blocks of a shared-prefix plan (up to 16 query rows of several forked
     // sequences over the chunks they have in common), then the sequences (their remaining chunks).
@@ -312,6 +314,16 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     uint32_t qf[KSTEPS][4];
     const int col = (lane & 3) * 2;
     const int qrow = lane >> 2;
+
+    // the warp's first item (its own index in the grid: no queue access) and the first window of its page ids
+    fetch_raw();
+    decode_next();
+    if (n_state == 2) {
+        n_pv = load_window(n_trow, n_tok_lo / p.page_size);
+        n_state = 3;
+    }
+    pdl_wait();
+    pdl_launch_dependents();
 
     while (true) {
         // ------------- issue: keep DEPTH groups in flight, across item boundaries -------------
