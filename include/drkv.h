@@ -214,7 +214,12 @@ DRKV_API int drkv_seq_inject(drkv_engine* e, int seq, int start_token, int num_t
  * [n_seq][num_q_heads][head_dim]; sequence i attends to keys 0..d_kv_len[i]-1 of table row
  * d_rows[i].  max_kv_len is a host-side upper bound of the d_kv_len values (it sizes the
  * grid).  Table entries < 0 are skipped.  A sequence with no visible key leaves its output
- * rows untouched (paged_attention.cu:266-268). */
+ * rows untouched (paged_attention.cu:266-268).
+ * The kernels are launched with programmatic dependent launch, and the attention kernel reads
+ * d_rows, d_kv_len and the block table while the kernel in front of it may still be running
+ * (everything before THAT kernel has completed).  Arrays written by copies, by ordinary kernels
+ * or by this library's kernels are therefore safe; a caller's own kernel that writes them AND
+ * signals programmatic completion early must not be the launch directly in front. */
 DRKV_API int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows,
                                 const int32_t* d_kv_len, int max_kv_len, const void* q, void* out,
                                 float scale, void* stream);
