@@ -649,9 +649,11 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
 // Merge of chunk partials: m = max m_c, weights exp(m_c - m); out = sum w_c o_c / sum w_c l_c.
 // Left unwritten when no key was visible (paged_attention.cu:266-268).  One CTA per (query
 // head, sequence); its 8 warps take the chunks round-robin, each lane owning 4 (or 8)
-// consecutive dims as float4, and a shared-memory pass adds the 8 partial sums.
-constexpr int kCombineWarps = 8;
-template <typename T>
+// consecutive dims as float4, and a shared-memory pass adds the warps' partial sums.  Eight warps per CTA
+// for batches (a handful of partials per row); 32 for a row with more than 64 partials (one long sequence
+// cut into an item per warp of the grid: 148 partials per head), where eight warps would each walk 19
+// partials in five dependent round trips to L2.
+template <typename T, int kCombineWarps>
 __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const CombineParams p) {
     const int h = blockIdx.x, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1034,8 +1036,12 @@ cudaError_t launch_importance_add(float* scores, const float* new_scores, int n,
 cudaError_t launch_combine(const CombineParams& p, int n_seq, int dtype, cudaStream_t stream) {
     if (n_seq <= 0) return cudaSuccess;
     dim3 grid(p.num_q_heads, n_seq);
-    if (dtype == DRKV_DTYPE_F16) return launch_pdl(combine_kernel<__half>, grid, dim3(kCombineWarps * 32), 0, stream, p);
-    return launch_pdl(combine_kernel<__nv_bfloat16>, grid, dim3(kCombineWarps * 32), 0, stream, p);
+    const bool wide = p.max_chunks + p.tail_chunks * p.tail_split > 64;
+    if (dtype == DRKV_DTYPE_F16)
+        return wide ? launch_pdl(combine_kernel<__half, 32>, grid, dim3(32 * 32), 0, stream, p)
+                    : launch_pdl(combine_kernel<__half, 8>, grid, dim3(8 * 32), 0, stream, p);
+    return wide ? launch_pdl(combine_kernel<__nv_bfloat16, 32>, grid, dim3(32 * 32), 0, stream, p)
+                : launch_pdl(combine_kernel<__nv_bfloat16, 8>, grid, dim3(8 * 32), 0, stream, p);
 }
 
 cudaError_t launch_combine_external(int n_parts, const float* parts, int num_q_heads, int head_dim, void* out,
