@@ -40,11 +40,14 @@ constexpr float kNegBig = -1.0e30f;                            // "no key seen y
 // flight, about bandwidth x loaded latency.  A third slot per warp (19 MB in flight) made the pass over
 // long items 8 % slower: the memory system serves fewer, not more, concurrent streams better.  At 64 and
 // 256 the pass is bound by the instruction stream of the warps, not by the loads in flight (measured:
-// 2 to 6 slots within 1 %), and 256 uses the room of the shallower ring for more warps.
+// 2 to 6 slots within 1 %).  At 256 a ring entry holds ONE plane (kSplit): the K and the V rows of a group
+// are separate 8 KB gathers, three entries per warp, so that eight warps fit (192 KB) where whole groups
+// of 16 KB allowed six; the warp releases a group's K entry after the softmax, sends the next gather and
+// only then waits for the group's V entry.
 template <int D> struct RingShape;
-template <> struct RingShape<64>  { static constexpr int kWarps = 8, kDepth = 6; };
-template <> struct RingShape<128> { static constexpr int kWarps = 8, kDepth = 2; };
-template <> struct RingShape<256> { static constexpr int kWarps = 6, kDepth = 2; };
+template <> struct RingShape<64>  { static constexpr int kWarps = 8, kDepth = 6; static constexpr bool kSplit = false; };
+template <> struct RingShape<128> { static constexpr int kWarps = 8, kDepth = 2; static constexpr bool kSplit = false; };
+template <> struct RingShape<256> { static constexpr int kWarps = 8, kDepth = 3; static constexpr bool kSplit = true; };
 
 enum SlotFlags : int { SLOT_FIRST = 1, SLOT_LAST = 2, SLOT_SKIP = 4, SLOT_DONE = 8 };
 
@@ -122,7 +125,8 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     constexpr int KSTEPS = D / 16;
     constexpr int NT = D / 8;
     constexpr int TILE_BYTES = NH * 2048;            // 16 keys of K (or V)
-    constexpr int SLOT_BYTES = 2 * TILE_BYTES;
+    constexpr bool SPLIT = RingShape<D>::kSplit;     // ring entries hold one plane: K and V of a group travel separately
+    constexpr int SLOT_BYTES = SPLIT ? TILE_BYTES : 2 * TILE_BYTES;
     constexpr int NR = HI ? 2 : 1;
 
     extern __shared__ uint8_t smem_raw[];
@@ -239,6 +243,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     // on the issue path with the latency of a saturated memory system.
     int c_pv = -1, c_pvn = -1, c_pv_base = 0, c_logical = 0, c_off = 0;
     int c_item = 0;             // entry of s_items[w] that describes the item being issued
+    int c_half = 0;             // SPLIT: 0 = the group's K entry is next, 1 = its V entry
     bool zero_filled = false;   // some lane has written zeros into a ring slot since the last proxy fence
     int i_slot = 0, outstanding = 0;
     // ---- compute cursor ----
@@ -315,6 +320,94 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     const int col = (lane & 3) * 2;
     const int qrow = lane >> 2;
 
+    // One ring entry: the gather of the cursor's group (SPLIT: of its K or its V plane), then the cursor moves on.
+    auto issue_entry = [&]() {
+        const int ring = w * DEPTH + i_slot;
+        const int tok0 = c_tok_lo + c_gi * kGroupTokens;
+        if (c_logical - c_pv_base >= 32) {             // next window of page ids (requested 32 pages ago)
+            c_pv = c_pvn;
+            c_pv_base += 32;
+            c_pvn = load_window(c_trow, c_pv_base + 32);
+        }
+        int page = __shfl_sync(0xffffffffu, c_pv, c_logical - c_pv_base);
+        if (page >= p.max_pages) {
+            page = -1;
+            if (lane == 0) atomicExch(p.error_word, (int)KERR_BAD_PAGE);
+        }
+        const bool last = (c_gi == c_ngroups - 1);
+        if (lane == 0) {
+            if (!SPLIT || c_half == 0) {
+                SlotMeta m;
+                m.flags = (c_gi == 0 ? SLOT_FIRST : 0) | (last ? SLOT_LAST : 0) | (page < 0 ? SLOT_SKIP : 0) | (c_item << kItemShift);
+                m.tok0 = tok0;
+                metas[ring] = m;
+            }
+            // Generic-proxy WRITES to the ring (the zero fill of an end group's hidden V rows, made visible
+            // to this lane by the __syncwarp that closed that group) are ordered before the async-proxy
+            // writes of the new gather.  Reads need no fence: the ldmatrix results have been consumed.
+            if (zero_filled) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive_expect_tx(bar_full + 8 * ring, page >= 0 ? SLOT_BYTES : 0);
+            if (page >= 0) {
+                const uint32_t dst = smem_u32(smem + ring * SLOT_BYTES);
+                // head row of the group's first key in the K plane (the descriptor has fewer than 2^31 rows)
+                const int rk = (layer_page0 + page) * plane2 + c_kvh * p.page_size + c_off;
+                // one box: 16 key rows x the whole head dim x the K and the V plane (8 KB at D = 128);
+                // SPLIT: x one plane (8 KB at D = 256)
+                tma_load_4d(dst, &tmap, 0, rk, 0, SPLIT ? c_half : 0, bar_full + 8 * ring);
+            }
+        }
+        zero_filled = false;
+        if (++i_slot == DEPTH) i_slot = 0;
+        outstanding++;
+        if (SPLIT && c_half == 0) {                    // the V entry of the same group comes next
+            c_half = 1;
+            return;
+        }
+        c_half = 0;
+        if (last) {
+            c_valid = false;
+        } else {
+            c_gi++;
+            c_off += kGroupTokens;
+            if (c_off == p.page_size) {
+                c_off = 0;
+                c_logical++;
+            }
+        }
+        // one step of the next-item pipeline per issued group, started near the end of this item
+        if (!exhausted) {
+            if (n_state == 0) {
+                if (!c_valid || c_ngroups - c_gi <= kPrefetchGroups) fetch_raw();
+            } else if (n_state == 1) {
+                decode_next();
+            } else if (n_state == 2) {
+                n_pv = load_window(n_trow, n_tok_lo / p.page_size);
+                n_state = 3;
+            }
+        }
+    };
+
+    // SPLIT: the warp is done with the group's K entry; one more gather goes out (the V plane of the group
+    // whose K plane went out last) and the warp waits for the V entry of the group it is computing.
+    auto next_entry = [&]() -> bool {
+        __syncwarp();
+        outstanding--;
+        if (++slot == DEPTH) { slot = 0; phase ^= 1; }
+        const long long ta = TCLK();
+        if (c_valid && c_half == 1 && outstanding < DEPTH) issue_entry();
+        const long long tb = TCLK();
+        if (!mbar_wait(bar_full + 8 * (w * DEPTH + slot), phase)) {
+            if (lane == 0) atomicExch(p.error_word, (int)KERR_WAIT_FULL);
+            return false;
+        }
+        __syncwarp();
+#ifdef DRKV_WARP_TRACE
+        tr_issue += tb - ta;
+        tr_wait += TCLK() - tb;
+#endif
+        return true;
+    };
+
     // the warp's first item (its own index in the grid: no queue access) and the first window of its page ids
     fetch_raw();
     decode_next();
@@ -355,61 +448,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     s_items[w][c_item] = im;
                 }
             }
-            const int ring = w * DEPTH + i_slot;
-            const int tok0 = c_tok_lo + c_gi * kGroupTokens;
-            if (c_logical - c_pv_base >= 32) {             // next window of page ids (requested 32 pages ago)
-                c_pv = c_pvn;
-                c_pv_base += 32;
-                c_pvn = load_window(c_trow, c_pv_base + 32);
-            }
-            int page = __shfl_sync(0xffffffffu, c_pv, c_logical - c_pv_base);
-            if (page >= p.max_pages) {
-                page = -1;
-                if (lane == 0) atomicExch(p.error_word, (int)KERR_BAD_PAGE);
-            }
-            const bool last = (c_gi == c_ngroups - 1);
-            if (lane == 0) {
-                SlotMeta m;
-                m.flags = (c_gi == 0 ? SLOT_FIRST : 0) | (last ? SLOT_LAST : 0) | (page < 0 ? SLOT_SKIP : 0) | (c_item << kItemShift);
-                m.tok0 = tok0;
-                metas[ring] = m;
-                // Generic-proxy WRITES to the ring (the zero fill of an end group's hidden V rows, made visible
-                // to this lane by the __syncwarp that closed that group) are ordered before the async-proxy
-                // writes of the new gather.  Reads need no fence: the ldmatrix results have been consumed.
-                if (zero_filled) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive_expect_tx(bar_full + 8 * ring, page >= 0 ? SLOT_BYTES : 0);
-                if (page >= 0) {
-                    const uint32_t dst = smem_u32(smem + ring * SLOT_BYTES);
-                    // head row of the group's first key in the K plane (the descriptor has fewer than 2^31 rows)
-                    const int rk = (layer_page0 + page) * plane2 + c_kvh * p.page_size + c_off;
-                    // one box: 16 key rows x the whole head dim x the K and the V plane (8 KB at D = 128)
-                    tma_load_4d(dst, &tmap, 0, 0, rk, 0, bar_full + 8 * ring);
-                }
-            }
-            zero_filled = false;
-            if (++i_slot == DEPTH) i_slot = 0;
-            outstanding++;
-            if (last) {
-                c_valid = false;
-            } else {
-                c_gi++;
-                c_off += kGroupTokens;
-                if (c_off == p.page_size) {
-                    c_off = 0;
-                    c_logical++;
-                }
-            }
-            // one step of the next-item pipeline per issued group, started near the end of this item
-            if (!exhausted) {
-                if (n_state == 0) {
-                    if (!c_valid || c_ngroups - c_gi <= kPrefetchGroups) fetch_raw();
-                } else if (n_state == 1) {
-                    decode_next();
-                } else if (n_state == 2) {
-                    n_pv = load_window(n_trow, n_tok_lo / p.page_size);
-                    n_state = 3;
-                }
-            }
+            issue_entry();
         }
         if (outstanding == 0) break;                   // queue drained and every group consumed
         const long long tc1 = TCLK();
@@ -493,18 +532,21 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 v_hi = min(kGroupTokens, item->tok_hi - meta.tok0);
             }
             uint8_t* kt = smem + ring * SLOT_BYTES;
-            uint8_t* vt = kt + TILE_BYTES;
-            if (v_hi < kGroupTokens || v_lo > 0) {
-                // Slots outside the visible range may hold anything (stale pages): give the
-                // PV product zeros there so that 0 * garbage cannot produce a NaN.
-                for (int i = lane; i < kGroupTokens * NH * 8; i += 32) {
-                    const int r = i / (NH * 8), c = i - r * (NH * 8);
-                    if (r >= v_hi || r < v_lo)
-                        *reinterpret_cast<Vec16*>(vt + swz_rows(r, c, NH * 128)) = Vec16{{0u, 0u, 0u, 0u}};
+            uint8_t* vt = kt + TILE_BYTES;              // SPLIT: set once the V entry has landed
+            auto zero_hidden_rows = [&]() {
+                if (v_hi < kGroupTokens || v_lo > 0) {
+                    // Slots outside the visible range may hold anything (stale pages): give the
+                    // PV product zeros there so that 0 * garbage cannot produce a NaN.
+                    for (int i = lane; i < kGroupTokens * NH * 8; i += 32) {
+                        const int r = i / (NH * 8), c = i - r * (NH * 8);
+                        if (r >= v_hi || r < v_lo)
+                            *reinterpret_cast<Vec16*>(vt + swz_seg16(r, c)) = Vec16{{0u, 0u, 0u, 0u}};
+                    }
+                    __syncwarp();
+                    zero_filled = true;
                 }
-                __syncwarp();
-                zero_filled = true;
-            }
+            };
+            if (!SPLIT) zero_hidden_rows();
             // ---- S = Q K^T : 16 rows x 16 keys ----
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
             {
@@ -515,7 +557,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 for (int kk = 0; kk < KSTEPS; kk++) {
                     const int c = 2 * kk + (mi & 1);
                     uint32_t kb[4];
-                    ldmatrix_x4(kb, kbase + swz_rows(key, c, NH * 128));
+                    ldmatrix_x4(kb, kbase + swz_seg16(key, c));
                     Mma<T>::run(s0[0], s0[1], s0[2], s0[3], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], kb[0], kb[1]);
                     Mma<T>::run(s1[0], s1[1], s1[2], s1[3], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], kb[2], kb[3]);
                 }
@@ -552,6 +594,11 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 split_pack<T>(p8, p9, phi[2 + r], plo[2 + r]);  // a2 / a3
             }
             if (!HI) { phi[1] = phi[3] = plo[1] = plo[3] = 0u; }
+            if (SPLIT) {
+                if (!next_entry()) break;
+                vt = smem + (w * DEPTH + slot) * SLOT_BYTES;
+                zero_hidden_rows();
+            }
             if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
                 for (int i = 0; i < NT; i++) {
@@ -569,7 +616,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 for (int j = 0; j < NT; j += 2) {
                     const int c = j + (mi >> 1);
                     uint32_t vb[4];
-                    ldmatrix_x4_trans(vb, vbase + swz_rows(key, c, NH * 128));
+                    ldmatrix_x4_trans(vb, vbase + swz_seg16(key, c));
                     if (HI) {
                         Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], phi[0], phi[1], phi[2], phi[3], vb[0], vb[1]);
                         Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[0], vb[1]);
@@ -585,10 +632,13 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 }
             }
         }
-        else if (EXT && p.tile_lse != nullptr) {
+        else {
+            if (SPLIT && !next_entry()) break;         // a skipped group still has two (empty) ring entries
+            if (EXT && p.tile_lse != nullptr) {
 #pragma unroll
-            for (int r = 0; r < NR; r++)
-                if (mass_row[r] >= 0) p.tile_lse[mass_row[r] + (meta.tok0 / kGroupTokens) * p.group * 4] = -INFINITY;
+                for (int r = 0; r < NR; r++)
+                    if (mass_row[r] >= 0) p.tile_lse[mass_row[r] + (meta.tok0 / kGroupTokens) * p.group * 4] = -INFINITY;
+            }
         }
         __syncwarp();                                  // every lane is done with the slot's shared memory
         outstanding--;
@@ -847,7 +897,7 @@ combine_external_kernel(int n_parts, const float* parts, int hq, int D, void* ou
 template <typename T, int D, bool HI, bool EXT>
 cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
     constexpr int WARPS = RingShape<D>::kWarps, DEPTH = RingShape<D>::kDepth, NH = D / 64;
-    constexpr size_t smem = 1024 + (size_t)WARPS * DEPTH * (2 * NH * 2048 + sizeof(SlotMeta) + sizeof(uint64_t)) +
+    constexpr size_t smem = 1024 + (size_t)WARPS * DEPTH * ((RingShape<D>::kSplit ? 1 : 2) * NH * 2048 + sizeof(SlotMeta) + sizeof(uint64_t)) +
                             (3 * kMaxDecodeSeqs + 1) * sizeof(int);   // cum[]: family blocks, sequences, their tail pieces
     static bool configured[64] = {};  // per instantiation and device: the attribute belongs to the context
     int dev = 0;
@@ -940,9 +990,13 @@ bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layer
         return false;
     }
     const int nh = head_dim / 64;
-    cuuint64_t gdim[4] = {64, (cuuint64_t)nh, (cuuint64_t)(rows - plane_rows), 2};
-    cuuint64_t gstride[3] = {128, (cuuint64_t)head_dim * 2, (cuuint64_t)plane_rows * head_dim * 2};
-    cuuint32_t box[4] = {64, (cuuint32_t)nh, 16, 2};
+    // dimensions: 64 elements of a 128-byte segment, head row, segment of the row, plane.  The row comes BEFORE
+    // the segment although its stride is the larger one, so that a box lands as [plane][segment][row][128 B]:
+    // rows 128 bytes apart, which is what keeps the ldmatrix reads of the kernel free of bank conflicts.
+    cuuint64_t gdim[4] = {64, (cuuint64_t)(rows - plane_rows), (cuuint64_t)nh, 2};
+    cuuint64_t gstride[3] = {(cuuint64_t)head_dim * 2, 128, (cuuint64_t)plane_rows * head_dim * 2};
+    // head_dim 256: the decode ring holds K and V of a group as separate entries, one plane per box
+    cuuint32_t box[4] = {64, 16, (cuuint32_t)nh, (head_dim == 256 && RingShape<256>::kSplit) ? 1u : 2u};
     cuuint32_t estride[4] = {1, 1, 1, 1};
     CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(pool), gdim, gstride, box, estride,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -124,6 +124,16 @@ __device__ __forceinline__ uint32_t swz_rows(int row, int chunk16, int row_bytes
     return seg + ((((uint32_t)chunk16 & 7u) ^ ((seg >> 7) & 7u)) << 4);
 }
 
+// Byte offset of 16-byte chunk `chunk16` of row `row` in a tile of 16 rows stored as [128-byte segment][row][128 B]
+// (a TMA box whose second dimension is the row and whose third is the segment), 128-byte swizzle, tile base
+// 1024-aligned: rows of one segment are 128 B apart, so the eight rows that an ldmatrix reads at one chunk column
+// fall into eight different 16-byte bank groups.  With full rows side by side ([row][segments], swz_rows) the
+// swizzle key (row * segments + segment) & 7 takes only 8 / segments values over eight rows and the same read
+// is a 2-way (256-byte rows) or 4-way (512-byte rows) bank conflict.
+__device__ __forceinline__ uint32_t swz_seg16(int row, int chunk16) {
+    return (uint32_t)(chunk16 >> 3) * 2048u + (uint32_t)row * 128u + ((((uint32_t)chunk16 ^ (uint32_t)row) & 7u) << 4);
+}
+
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
