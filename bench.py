@@ -260,7 +260,7 @@ def run_ours(args):
     achieved = kv_bytes / (kms / kn_launch * 1e-3) / 1e9 if kn_launch else None
     # DRAM bytes per algorithmic K/V byte of attend_decode_kernel, from the ncu capture summarised in
     # profiles/attend_decode_kernel_c2.md (small case; traffic grows in proportion to the keys processed)
-    traffic_ratio = 1.025
+    traffic_ratio = 1.023
 
     # ---- end to end through the public API with host buffers ----
     e2e = None
