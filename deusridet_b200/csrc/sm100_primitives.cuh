@@ -116,18 +116,10 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk16) {
     return (uint32_t)(row * 128 + ((chunk16 ^ (row & 7)) << 4));
 }
 
-// Byte offset of 16-byte chunk `chunk16` (0 .. row_bytes/16) of row `row` in a tile of full rows
-// ([row][row_bytes], row_bytes a multiple of 128) written by TMA with 128-byte swizzle: within every
-// 128-byte segment the chunk index is XORed with bits 7-9 of the offset (tile base 1024-aligned).
-__device__ __forceinline__ uint32_t swz_rows(int row, int chunk16, int row_bytes) {
-    const uint32_t seg = (uint32_t)(row * row_bytes) + (uint32_t)(chunk16 >> 3) * 128u;
-    return seg + ((((uint32_t)chunk16 & 7u) ^ ((seg >> 7) & 7u)) << 4);
-}
-
 // Byte offset of 16-byte chunk `chunk16` of row `row` in a tile of 16 rows stored as [128-byte segment][row][128 B]
 // (a TMA box whose second dimension is the row and whose third is the segment), 128-byte swizzle, tile base
 // 1024-aligned: rows of one segment are 128 B apart, so the eight rows that an ldmatrix reads at one chunk column
-// fall into eight different 16-byte bank groups.  With full rows side by side ([row][segments], swz_rows) the
+// fall into eight different 16-byte bank groups.  With full rows side by side ([row][segments]) the
 // swizzle key (row * segments + segment) & 7 takes only 8 / segments values over eight rows and the same read
 // is a 2-way (256-byte rows) or 4-way (512-byte rows) bank conflict.
 __device__ __forceinline__ uint32_t swz_seg16(int row, int chunk16) {
