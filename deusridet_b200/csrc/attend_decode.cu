@@ -11,8 +11,10 @@
 //     the tile (the reference re-reads it once per query head);
 //   * pages are gathered by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast): ONE 4-D box per
 //     ring slot brings the K and V rows of 16 keys of one head (8 KB at head_dim 128) into the shared-memory
-//     ring that every warp owns (3 slots, 192 KB in flight per SM, mbarrier-guarded); lane 0 of the warp
-//     walks the block table and issues the copies ahead of the tile being computed, across item boundaries;
+//     ring that every warp owns (two slots: one gather lands while the previous group is computed;
+//     mbarrier-guarded), laid out [plane][128-byte segment][row] so that the fragment loads are free of bank
+//     conflicts; lane 0 of the warp walks the block table, 32 page ids at a time, and issues the copies
+//     ahead of the tile being computed, across item boundaries;
 //   * QK^T and PV run as m16n8k16 tensor-core tiles with fp32 accumulation: the 4..16 query rows of a GQA
 //     group are far from a dense contraction (the tensor pipe is about a quarter busy), they only keep the
 //     SM's issue slots free so that the kernel stays HBM-bound; softmax statistics are reduced with warp
@@ -107,8 +109,8 @@ __device__ __forceinline__ void split_pack(float p0, float p1, uint32_t& hi, uin
 // Persistent kernel, one CTA per SM, every warp on its own.  Work item = (sequence, KV head,
 // chunk of keys); a block-wide prefix sum of the per-sequence chunk counts turns the atomic
 // queue index into (sequence, head, chunk) without empty items.  A warp owns a private ring
-// of DEPTH slots (16 keys of K and V each), its 16-row query fragments and its (m, l, o)
-// state.  Its lane 0 issues the TMA gathers DEPTH - 1 groups ahead of the group being
+// of DEPTH slots (16 keys of K and V each; at head_dim 256 of one plane each), its 16-row query
+// fragments and its (m, l, o) state.  Its lane 0 issues the TMA gathers DEPTH - 1 groups ahead of the group being
 // computed, across item boundaries, and the next item (queue index, length, table row, first
 // 32 page ids) is fetched while the current one is processed, so that neither the atomic nor the
 // table look-ups sit on the critical path.  An item's partial goes straight from the
