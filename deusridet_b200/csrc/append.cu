@@ -21,8 +21,10 @@ template <typename T>
 __global__ void __launch_bounds__(kAppendThreads)
 append_rope_kernel(AppendParams p) {
     const int tok = blockIdx.x;
-    pdl_wait();                     // positions, sources and the pool may come from the preceding kernel
-    pdl_launch_dependents();
+    // Positions, rows, the block table and the frequencies are written by copies or by kernels further back
+    // than the one directly in front (which, when it belongs to this library, released this launch only after
+    // its own wait): the angles and the page id are worked out under that kernel's tail.  The sources and
+    // the pool are touched after the wait.
     int row, pos;
     if (p.rows != nullptr) {
         row = p.rows[tok];
@@ -43,13 +45,12 @@ append_rope_kernel(AppendParams p) {
         s_cos[i] = c;
         s_sin[i] = s;
     }
+    const int logical = pos >= 0 ? pos / P : 0, slot = pos - logical * P;
+    const int page = (pos >= 0 && logical < p.table_stride) ? p.tables[(int64_t)row * p.table_stride + logical] : -1;
     __syncthreads();
-
-    if (pos < 0) return;
-    const int logical = pos / P, slot = pos - logical * P;
-    if (logical >= p.table_stride) return;
-    const int page = p.tables[(int64_t)row * p.table_stride + logical];
-    if (page < 0 || page >= p.layout.max_pages) return;  // hole: nothing to write into
+    pdl_wait();
+    pdl_launch_dependents();
+    if (page < 0 || page >= p.layout.max_pages) return;  // hole or no position: nothing to write into
 
     const T* ksrc = reinterpret_cast<const T*>(p.k_src) + (int64_t)tok * H * D;
     const T* vsrc = reinterpret_cast<const T*>(p.v_src) + (int64_t)tok * H * D;
