@@ -558,7 +558,8 @@ def run_c4(args):
         for s in seqs:
             eng.seq_release(s, discard=True)
 
-    for _ in range(max(1, min(args.warmup, 1))):
+    W = max(1, args.warmup)
+    for _ in range(W):
         release(full_prefill())
     eng.check_kernels()
     sampler = ClockSampler(local)
@@ -588,7 +589,7 @@ def run_c4(args):
             peak = float(json.load(f)["bf16_tflops_sustained"])
         peak_kind = "measured (sustained)"
     return {"metric": "prefill tokens/s (chunked prefill into the paged cache) + tensor TFLOP/s",
-            "value": n_seq * S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": 1,
+            "value": n_seq * S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": {"workload": f"c4: {w['desc']}", "layers": L, "seqs": n_seq},
             "roofline": {"bound": "tensor", "kernel": "attend_prefill_kernel (incl. append)", "achieved": tfs, "peak": peak,
