@@ -449,6 +449,13 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     im.pad0 = im.pad1 = im.pad2 = 0;
                     s_items[w][c_item] = im;
                 }
+                if (!EXT || c_fam == 0) {
+                    // the item's query rows into L1, a group's time before the warp loads them into fragments
+                    const char* qb = reinterpret_cast<const char*>(p.q) +
+                                     ((int64_t)c_b * p.num_q_heads + (int64_t)c_kvh * p.group) * (D * (int)sizeof(T));
+                    if (lane * 128 < p.group * D * (int)sizeof(T))
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(qb + lane * 128));
+                }
             }
             issue_entry();
         }
