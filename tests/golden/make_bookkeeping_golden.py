@@ -1,6 +1,6 @@
 """Records what the reference's own BlockPool / CacheManager objects do (compiled from the
 mounted reference tree into oracle/_ref/ by oracle/ref_build/Makefile) for seeded operation
-sequences, and the text their class-level scenario prints.  Run here, where /root/reference is
+sequences, and the text their class-level scenario prints.  Run where the reference tree is
 mounted; the outputs are committed so that the tests can use them where it is not.
 
     python tests/golden/make_bookkeeping_golden.py

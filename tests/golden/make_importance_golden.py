@@ -2,7 +2,7 @@
 oracle/ref_build/Makefile into oracle/_ref/libref_paged.so) holds after seeded sequences of updates.
 Needs a GPU:
 
-    python tests/golden/make_importance_golden.py gpurun_out/importance_reference.npz
+    python tests/golden/make_importance_golden.py OUTPUT.npz
 
 The result is committed as tests/golden/importance_reference.npz; importance_cases() below is the
 seeded input both the recorder and the tests use."""

@@ -2,7 +2,7 @@
 paged_gqa_decode_attention; compiled by oracle/ref_build/Makefile into oracle/_ref/libref_paged.so with the
 reference's --use_fast_math) return for the seeded cases of tests/golden/paged_cases.py.  Needs a GPU:
 
-    python tests/golden/make_paged_attention_golden.py gpurun_out/paged_attention_reference.npz
+    python tests/golden/make_paged_attention_golden.py OUTPUT.npz
 
 The result is committed as tests/golden/paged_attention_reference.npz.  Flow per case, as in
 full_attention_forward_paged (src/machina/paged_attention.cu:353-367): RoPE on Q and K at the new position,
