@@ -721,8 +721,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
     __shared__ float s_m[kCombineWarps], s_l[kCombineWarps];
     __shared__ float4 s_acc[kCombineWarps][64];         // D <= 256 -> at most 64 float4 per row
 
-    pdl_wait();                                          // partials come from the preceding kernel
-    pdl_launch_dependents();
+    // lengths and plan arrays are older than the kernel in front (see attend_decode_kernel): the slot arithmetic
+    // runs under its tail, the partials are read after the wait
     const int kv_end = p.kv_len != nullptr ? p.kv_len[b] : p.kv_end;
     const int base = (p.kv_begin / kGroupTokens) * kGroupTokens;
     int nch = kv_end > base ? (kv_end - base + p.chunk_tokens - 1) / p.chunk_tokens : 0;
@@ -741,6 +741,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
     const int nchunks = nbig + nsmall;
     const int skip = p.max_chunks - nbig;                // list index i >= nbig lives at slot i + skip
     const int64_t slot0 = ((int64_t)b * p.num_q_heads + h) * (p.max_chunks + tailc * tails);
+    pdl_wait();                                          // partials come from the preceding kernel
+    pdl_launch_dependents();
 
     float mloc = -1.0e20f;
     for (int c = threadIdx.x; c < nchunks; c += kCombineWarps * 32)
