@@ -158,12 +158,7 @@ def run_ours(args):
     from deusridet_b200 import PagedKVEngine, build
     build.build()
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-    torch.cuda.set_device(local)
+    world, rank, local = _dist_setup()
     dev = torch.device(f"cuda:{local}")
 
     w = dict(WORKLOADS[args.workload])
@@ -173,10 +168,7 @@ def run_ours(args):
     L, hq, hkv, d, page = w["layers"], w["hq"], w["hkv"], w["d"], w["page"]
     lens = make_lens(w, 1234 + rank, n_seq)
     K, W = args.steps, args.warmup
-    room = K + W + 8                                   # tokens each sequence may grow in the e2e pass
-    pages_needed = int(sum((int(n) + room + page - 1) // page for n in lens))
-    max_pages = int(np.ceil(1.1 * pages_needed))
-    width = int(max((int(n) + room + page - 1) // page for n in lens)) + 1
+    max_pages, width = c2_pool_pages(lens, page, K, W)
     eng = PagedKVEngine(num_layers=L, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
                         rope_theta=w["theta"], max_pages=max_pages, max_seqs=n_seq, max_pages_per_seq=width,
                         device=local)
@@ -211,7 +203,7 @@ def run_ours(args):
     scale = 1.0 / float(np.sqrt(d))
     max_kv = int(lens.max()) + 1
 
-    def device_step():
+    def device_step(stream=stream):
         for l in range(L):
             eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
             eng.attend_decode(l, n_seq, d_rows, d_len, max_kv, q[l], out[l], scale, stream)
@@ -249,6 +241,30 @@ def run_ours(args):
     if args.scorer:
         launches += K * (L + 1)                        # + page mass per layer, score update per step
 
+    # ---- the same step replayed from a CUDA graph (captured once; the launch shapes depend only on max_kv) ----
+    graph = None
+    if not args.no_graph:
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            device_step(torch.cuda.current_stream())
+        for _ in range(W):
+            cg.replay()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        for _ in range(K):
+            cg.replay()
+        g1.record(stream)
+        barrier()
+        tg = torch.tensor([g0.elapsed_time(g1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        gms = float(tg.item()) / K
+        graph = {"ms_per_step": gms, "value": world * n_seq / (gms * 1e-3), "unit": "tokens/s",
+                 "note": "the timed step replayed from one CUDA graph; `value` above is the stream-launched step (headline)"}
+        del cg
+        eng.check_kernels()
+
     # ---- dominant kernel: per-launch duration from events around each launch ----
     eng.kernel_timing(True)
     for _ in range(min(K, 3)):
@@ -258,8 +274,8 @@ def run_ours(args):
     peak, peak_kind = peaks()
     read_peak = read_stream_gbs(eng, stream)
     achieved = kv_bytes / (kms / kn_launch * 1e-3) / 1e9 if kn_launch else None
-    # DRAM bytes per algorithmic K/V byte of attend_decode_kernel, from the ncu capture summarised in
-    # profiles/attend_decode_kernel_c2.md (small case; traffic grows in proportion to the keys processed)
+    # DRAM bytes per algorithmic K/V byte of attend_decode_kernel, from an ncu capture of a 16-sequence case
+    # (DRAM traffic grows in proportion to the keys processed: one gather per 16 keys, one partial per item)
     traffic_ratio = 1.023
 
     # ---- end to end through the public API with host buffers ----
@@ -345,11 +361,7 @@ def run_ours(args):
             "value": world * n_seq / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {w['desc']}", "layers": L, "seqs_per_gpu": n_seq,
-                       "sum_ctx": int(lens.sum()), "page": page, "pool_pages": max_pages,
-                       "pool_gb": round(eng_bytes(max_pages, w) / 1e9, 2), "parallelism": f"dp{world}",
-                       "importance_scorer": bool(args.scorer),
-                       "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer" % (kv_bytes / 1e9)},
+            "config": c2_config(args, w, lens, world, max_pages, kv_bytes),
             "tokens_per_s_per_gpu": n_seq / (ms_step * 1e-3),
             "hbm_gbs_step": all_bytes * L / (ms_step * 1e-3) / 1e9,
             "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
@@ -361,13 +373,13 @@ def run_ours(args):
             "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
             "cow_copies": stats["cow_copies"],
         }
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        if graph is not None:
+            result["cuda_graph"] = graph
     return result, (w, lens)
 
 
 def _dist_setup():
+    """One process per GPU: the process group is created once (first call) and torn down by main()."""
     import torch
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -379,8 +391,17 @@ def _dist_setup():
     return world, rank, local
 
 
-def run_c5a(args):
-    """Single long sequence, KV pages split by contiguous range across the ranks."""
+def _dist_teardown():
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_c5a(args, collectives=None):
+    """Single long sequence, KV pages split by contiguous range across the ranks.  Returns one result per
+    collective in `collectives` ("peer": partials pushed to every rank by peer stores and merged in the same
+    kernel; "nccl": all-gather of the partials + merge kernel), measured on one engine."""
     import torch
     import torch.distributed as dist
 
@@ -388,6 +409,7 @@ def run_c5a(args):
     build.build()
     world, rank, local = _dist_setup()
     dev = torch.device(f"cuda:{local}")
+    collectives = list(collectives or [args.collective])
     w = dict(WORKLOADS["c5a"])
     if args.layers:
         w["layers"] = args.layers
@@ -426,30 +448,152 @@ def run_c5a(args):
     d_pos = torch.tensor([S - 1], dtype=torch.int32, device=dev)     # the token being decoded sits at S - 1
     owner = sharding.owner_of_position(S - 1, S, page, world)
     scale = 1.0 / float(np.sqrt(d))
-    use_peer = args.collective == "peer"
-    if use_peer:
-        # exchange areas: one CUDA IPC handle per rank, passed around once through the process group
-        handle = torch.frombuffer(bytearray(eng.exchange_create(world, rank)), dtype=torch.uint8).to(dev)
-        handles = torch.empty(world, 64, dtype=torch.uint8, device=dev)
+    kv_rank = float(end - begin) * 2 * hkv * d * 2                   # this rank's K/V bytes per layer
+    peak, peak_kind = peaks()
+
+    def barrier():
         if world > 1:
-            dist.all_gather_into_tensor(handles, handle)
-        else:
-            handles[0] = handle
-        eng.exchange_connect([bytes(h.cpu().numpy().tobytes()) for h in handles])
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    results = {}
+    for coll in collectives:
+        use_peer = coll == "peer"
+        if use_peer:
+            # exchange areas: one CUDA IPC handle per rank, passed around once through the process group
+            handle = torch.frombuffer(bytearray(eng.exchange_create(world, rank)), dtype=torch.uint8).to(dev)
+            handles = torch.empty(world, 64, dtype=torch.uint8, device=dev)
+            if world > 1:
+                dist.all_gather_into_tensor(handles, handle)
+            else:
+                handles[0] = handle
+            eng.exchange_connect([bytes(h.cpu().numpy().tobytes()) for h in handles])
+
+        def step():
+            for l in range(L):
+                if rank == owner:
+                    eng.append_rope(l, 1, d_rows, d_pos, kn[l], vn[l], stream)
+                if use_peer:
+                    eng.attend_exchange(l, s, begin, end, q[l], out[l], scale, stream)   # partial, peer stores, merge
+                    continue
+                eng.attend_partial(l, s, begin, end, q[l], mine, scale, stream)
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered, mine)
+                    eng.combine_partials(world, gathered, out[l], stream)
+                else:
+                    eng.combine_partials(1, mine, out[l], stream)
+
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        for _ in range(W):
+            step()
+        barrier()
+        eng.check_kernels()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        sampler.mark_begin()
+        e0.record(stream)
+        for _ in range(K):
+            step()
+        e1.record(stream)
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        clocks = sampler.stop() if rank == 0 else None
+        ms_step = float(t.item()) / K
+        eng.kernel_timing(True)
+        step()
+        kms, kn_l = eng.kernel_timing(False, read=True)
+        eng.check_kernels()
+        if use_peer:
+            barrier()                                                # nobody tears down while a peer may still push
+            eng.exchange_destroy()
+        achieved = kv_rank / (kms / kn_l * 1e-3) / 1e9
+        results[coll] = {
+            "metric": "decode tokens/s/GPU + achieved HBM GB/s (% of peak) for paged attn+append",
+            "value": 1.0 / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"c5a: {w['desc']}", "layers": L, "keys_per_gpu": end - begin,
+                       "parallelism": f"kv-range-split x{world}",
+                       "collective": ("partials pushed to every rank by peer stores + per-head flags, merged in the same "
+                                      "kernel (no library collective)") if use_peer
+                       else "nccl all_gather of Hq*(D+2) fp32 per layer",
+                       "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer per GPU" % (kv_rank / 1e9)},
+            "hbm_gbs_step": world * kv_rank * L / (ms_step * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "bytes_per_launch": kv_rank, "us_per_launch": kms / kn_l * 1e3},
+            "gpu_launches": K * L * (3 + (1 if owner == 0 else 0)), "clocks": clocks, "e2e": None}
+    eng.close()
+    return results if rank == 0 else None
+
+
+def run_c5b(args):
+    """The 1024-sequence workload: 1024 independent 4096-token sequences, data-parallel with no collective.  A rank
+    owns 1024 / N of them and streams them through ONE resident pool in waves of at most 128 sequences (all 1024
+    together would need 550 GB of K/V): a wave maps the pool's pages to its own sequences through the allocator
+    (create, reserve, table sync), decodes one token per sequence on every layer, and releases them.  A step is
+    one token for all 1024 sequences; tokens/s = 1024 / (slowest rank's time over its waves).  The K/V contents
+    are synthetic and stay resident: no K/V bytes move between waves."""
+    import torch
+    import torch.distributed as dist
+
+    from deusridet_b200 import PagedKVEngine, build
+    build.build()
+    world, rank, local = _dist_setup()
+    dev = torch.device(f"cuda:{local}")
+    w = dict(WORKLOADS["c5b"])
+    if args.layers:
+        w["layers"] = args.layers
+    total = args.seqs or 1024
+    L, hq, hkv, d, page, S = w["layers"], w["hq"], w["hkv"], w["d"], w["page"], w["lo"]
+    K, W = args.steps, args.warmup
+    mine = total // world + (1 if rank < total % world else 0)
+    wave = min(128, max(mine, 1))
+    n_waves = (mine + wave - 1) // wave
+    pages_per_seq = (S + 1 + page - 1) // page
+    max_pages = wave * pages_per_seq + 8
+    eng = PagedKVEngine(num_layers=L, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
+                        rope_theta=w["theta"], max_pages=max_pages, max_seqs=wave, max_pages_per_seq=pages_per_seq + 1,
+                        device=local)
+    rng = np.random.default_rng(31 + rank)
+    pages = [eng.alloc_block() for _ in range(max_pages)]
+    for p in rng.permutation(max_pages):
+        eng.free_block(int(p))
+    stream = torch.cuda.current_stream()
+    torch.manual_seed(13 + rank)
+    pool = eng.pool_tensor().view(torch.bfloat16)
+    for off in range(0, pool.numel(), 1 << 28):
+        pool[off:off + (1 << 28)].normal_()
+    q = torch.randn(L, wave, hq, d, device=dev, dtype=torch.bfloat16)
+    kn = torch.randn(L, wave, hkv, d, device=dev, dtype=torch.bfloat16)
+    vn = torch.randn(L, wave, hkv, d, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(L, wave, hq, d, device=dev, dtype=torch.bfloat16)
+    d_pos = torch.full((wave,), S, dtype=torch.int32, device=dev)
+    d_len = d_pos + 1
+    d_rows = torch.arange(wave, dtype=torch.int32, device=dev)       # rows are handed out lowest-free-first: 0..n-1
+    scale = 1.0 / float(np.sqrt(d))
 
     def step():
-        for l in range(L):
-            if rank == owner:
-                eng.append_rope(l, 1, d_rows, d_pos, kn[l], vn[l], stream)
-            if use_peer:
-                eng.attend_exchange(l, s, begin, end, q[l], out[l], scale, stream)   # partial, peer stores, merge
-                continue
-            eng.attend_partial(l, s, begin, end, q[l], mine, scale, stream)
-            if world > 1:
-                dist.all_gather_into_tensor(gathered, mine)
-                eng.combine_partials(world, gathered, out[l], stream)
-            else:
-                eng.combine_partials(1, mine, out[l], stream)
+        left = mine
+        for _ in range(n_waves):
+            n = min(wave, left)
+            left -= n
+            seqs = [eng.seq_create() for _ in range(n)]
+            assert seqs == list(range(n))
+            for s_ in seqs:
+                assert eng.ensure_blocks_for_range(s_, 0, S + 1)
+                eng.set_seq_len(s_, S)
+            eng.sync_block_table(stream)
+            for l in range(L):
+                eng.append_rope(l, n, d_rows, d_pos, kn[l], vn[l], stream)
+                eng.attend_decode(l, n, d_rows, d_len, S + 1, q[l], out[l], scale, stream)
+            # pages go back to the allocator; the kernels of the next wave are ordered behind these on the stream
+            for s_ in seqs:
+                eng.seq_release(s_, discard=True)
 
     def barrier():
         if world > 1:
@@ -480,34 +624,30 @@ def run_c5a(args):
     step()
     kms, kn_l = eng.kernel_timing(False, read=True)
     eng.check_kernels()
-    if use_peer:
-        barrier()                                                    # nobody tears down while a peer may still push
-        eng.exchange_destroy()
     eng.close()
-    kv_rank = float(end - begin) * 2 * hkv * d * 2                   # this rank's K/V bytes per layer
+    if rank != 0:
+        return None
+    kv_launch = float(min(wave, mine)) * (S + 1) * 2 * hkv * d * 2      # K/V bytes one full-wave launch reads
     peak, peak_kind = peaks()
-    res = None
-    if rank == 0:
-        achieved = kv_rank / (kms / kn_l * 1e-3) / 1e9
-        res = {"metric": "decode tokens/s/GPU + achieved HBM GB/s (% of peak) for paged attn+append",
-               "value": 1.0 / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-               "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-               "dtype": "bf16", "data": "synthetic",
-               "config": {"workload": f"c5a: {w['desc']}", "layers": L, "keys_per_gpu": end - begin,
-                          "parallelism": f"kv-range-split x{world}",
-                          "collective": ("partials pushed to every rank by peer stores + per-head flags, merged in the same "
-                                         "kernel (no library collective)") if use_peer
-                          else "nccl all_gather of Hq*(D+2) fp32 per layer",
-                          "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer per GPU" % (kv_rank / 1e9)},
-               "hbm_gbs_step": world * kv_rank * L / (ms_step * 1e-3) / 1e9,
-               "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
-                            "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                            "bytes_per_launch": kv_rank, "us_per_launch": kms / kn_l * 1e3},
-               "gpu_launches": K * L * (3 + (1 if owner == 0 else 0)), "clocks": clocks, "e2e": None}
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    return res
+    # launches of partial waves are shorter; the per-launch figure is exact when every wave is full
+    achieved = kv_launch / (kms / kn_l * 1e-3) / 1e9 if mine % wave == 0 else None
+    return {"metric": "decode tokens/s/GPU + achieved HBM GB/s (% of peak) for paged attn+append",
+            "value": total / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"c5b: {total} independent {S}-token sequences, {L} layers, {hq}/{hkv} heads, head_dim "
+                                   f"{d}, bf16, page {page}; {mine} per GPU in {n_waves} wave(s) of <= {wave} through one "
+                                   f"resident pool (allocator re-maps the pages per wave; K/V contents synthetic and "
+                                   f"resident); one step = one token for all {total} sequences",
+                       "layers": L, "seqs_total": total, "seqs_per_gpu": mine, "waves_per_gpu": n_waves,
+                       "parallelism": f"dp{world}, no collective",
+                       "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer per wave" % (kv_launch / 1e9)},
+            "tokens_per_s_per_gpu": total / world / (ms_step * 1e-3),
+            "hbm_gbs_step": None if achieved is None else float(mine) * (S + 1) * 2 * hkv * d * 2 * L / (ms_step * 1e-3) / 1e9,
+            "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
+                         "traffic": None, "bytes_per_launch": kv_launch, "us_per_launch": kms / kn_l * 1e3},
+            "gpu_launches": K * n_waves * L * 3, "clocks": clocks, "e2e": None}
 
 
 def run_c4(args):
@@ -748,9 +888,11 @@ def eng_bytes(max_pages, w):
 # --------------------------------------------------------------------------------------------
 # the reference semantics on the host cores (CPU restatement in oracle/, OpenMP over (seq, head))
 # --------------------------------------------------------------------------------------------
-def cpu_pass(w, lens, repeats, seed=5):
-    """One layer x all sequences of the workload on the host: append then attention, repeated;
-    returns seconds per layer-pass and the thread count."""
+def cpu_pass(w, lens, steps, seed=5):
+    """Whole decode steps of the workload on the host: for every layer, append then attention over all
+    sequences.  One layer's pool is resident (1.4 GB for the default workload, far beyond the CPU caches) and
+    is walked once per layer, so a step does the work and the memory traffic of all layers without holding
+    50 GB of synthetic K/V in host memory.  Returns seconds per step (list) and the thread count."""
     from oracle import cbind as ob
     ob.lib()
     ob.use_all_cores()                                   # torchrun exports OMP_NUM_THREADS=1
@@ -775,28 +917,49 @@ def cpu_pass(w, lens, repeats, seed=5):
     rows = np.arange(n_seq, dtype=np.int32)
     scale = 1.0 / float(np.sqrt(d))
     times = []
-    for _ in range(repeats):
+    for _ in range(steps):
         t0 = time.perf_counter()
-        for i in range(n_seq):
-            ob.append(g, pool, max_pages, tables[i], 0, int(lens[i]), 1, k[i], v[i], rope=True)
-        ob.attend_decode(g, pool, max_pages, tables, rows, lens + 1, 0, q, out, scale)
+        for _layer in range(w["layers"]):
+            for i in range(n_seq):
+                ob.append(g, pool, max_pages, tables[i], 0, int(lens[i]), 1, k[i], v[i], rope=True)
+            ob.attend_decode(g, pool, max_pages, tables, rows, lens + 1, 0, q, out, scale)
         times.append(time.perf_counter() - t0)
     return times, ob.num_threads()
 
 
+CPU_SAMPLE = ("whole steps: every layer's append + attention over all {n} sequences ({L} passes over one resident "
+              "layer-sized pool per step), median of {k} steps")
+
+
 def cpu_baseline(w, lens):
-    times, threads = cpu_pass(w, lens, repeats=1)
-    reps = int(min(100, max(1, 12.0 / max(times[0], 1e-3))))
-    if reps > 1:
-        more, _ = cpu_pass(w, lens, repeats=reps)
-        times = more
-    t_layer = float(np.median(times))
-    return {"value": len(lens) / (t_layer * w["layers"]), "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"1 of {w['layers']} layers x all {len(lens)} sequences, {len(times)} passes, median "
-                      f"{t_layer:.3f} s/layer, scaled by the layer count"}
+    """About 10-30 s of host work: one step to size the sample, then up to 8 more; median."""
+    times, threads = cpu_pass(w, lens, steps=1)
+    more = int(min(8, max(2, 20.0 / max(times[0], 1e-3))))
+    times, _ = cpu_pass(w, lens, steps=more)
+    t_step = float(np.median(times))
+    return {"value": len(lens) / t_step, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "ms_per_step": t_step * 1e3,
+            "sample": CPU_SAMPLE.format(n=len(lens), L=w["layers"], k=len(times))}
+
+
+def c2_config(args, w, lens, world, max_pages, kv_bytes):
+    return {"workload": f"{args.workload}: {w['desc']}", "layers": w["layers"], "seqs_per_gpu": len(lens),
+            "sum_ctx": int(lens.sum()), "page": w["page"], "pool_pages": max_pages,
+            "pool_gb": round(eng_bytes(max_pages, w) / 1e9, 2), "parallelism": f"dp{world}",
+            "importance_scorer": bool(args.scorer),
+            "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer" % (kv_bytes / 1e9)}
+
+
+def c2_pool_pages(lens, page, steps, warmup):
+    room = max(64, steps + warmup + 8)                 # tokens each sequence may grow in the end-to-end pass
+    pages_needed = int(sum((int(n) + room + page - 1) // page for n in lens))
+    width = int(max((int(n) + room + page - 1) // page for n in lens)) + 1
+    return int(np.ceil(1.1 * pages_needed)), width
 
 
 def run_reference(args):
+    """The reference arm: the reference's semantics for this path on the host cores (the CPU restatement in
+    oracle/: the reference itself has no CPU implementation of its kernels), same workload, same metric."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
@@ -804,20 +967,21 @@ def run_reference(args):
     if args.layers:
         w["layers"] = args.layers
     lens = make_lens(w, 1234, args.seqs or w["n_seq"])
-    times, threads = cpu_pass(w, lens, repeats=args.warmup + args.steps)
+    times, threads = cpu_pass(w, lens, steps=args.warmup + args.steps)
     times = times[args.warmup:]
-    t_layer = float(np.mean(times))
-    ms_step = t_layer * w["layers"] * 1e3
-    val = len(lens) / (ms_step * 1e-3)
-    sample = (f"each step = 1 of {w['layers']} layers x all {len(lens)} sequences (append + attention), "
-              f"scaled by the layer count")
+    t_step = float(np.median(times))
+    ms_step = t_step * 1e3
+    val = len(lens) / t_step
+    sample = CPU_SAMPLE.format(n=len(lens), L=w["layers"], k=len(times))
+    max_pages, _ = c2_pool_pages(lens, w["page"], args.steps, args.warmup)
+    kv_bytes, _ = algorithmic_bytes_per_layer(w, lens)
     return {
         "impl": "reference",
         "metric": "decode tokens/s/GPU + achieved HBM GB/s (% of peak) for paged attn+append",
         "value": val, "unit": "tokens/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {w['desc']}", "layers": w["layers"], "seqs_per_gpu": len(lens)},
+        "config": c2_config(args, w, lens, int(os.environ.get("WORLD_SIZE", "1")), max_pages, kv_bytes),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -838,6 +1002,9 @@ def main():
                     help="c5a: fused peer-store exchange + merge kernel, or NCCL all-gather + merge")
     ap.add_argument("--scorer", action="store_true", help="c2/c5b: also produce per-page attention mass and scores")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="c2: skip the CUDA-graph replay of the step")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="c2: skip the secondary workloads (long split sequence, 1024 sequences, chunked prefill)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3 and not (args.layers or args.seqs):
@@ -849,22 +1016,85 @@ def main():
         if res is not None:
             print(json.dumps(res), flush=True)
         return
-    if args.workload == "c5a":
-        res = run_c5a(args)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    try:
+        if args.workload == "c5a":
+            res = run_c5a(args)
+            if res is not None:
+                print(json.dumps(res[args.collective]), flush=True)
+            return
+        if args.workload == "c5b":
+            res = run_c5b(args)
+            if res is not None:
+                print(json.dumps(res), flush=True)
+            return
+        if args.workload == "c4":
+            res = run_c4(args)
+            if rank == 0:
+                print(json.dumps(res), flush=True)
+            return
+        if args.workload == "c3":
+            res = run_c3(args)
+            if rank == 0:
+                print(json.dumps(res), flush=True)
+            return
+        res, (w, lens) = run_ours(args)
+        secondary = {}
+        if not args.no_secondary and not (args.layers or args.seqs or args.scorer):
+            secondary = run_secondary(args, world)
         if res is not None:
+            if world == 1 and not args.no_cpu_baseline:
+                res["cpu_baseline"] = cpu_baseline(w, lens)
+            if secondary:
+                res["secondary"] = secondary
             print(json.dumps(res), flush=True)
-        return
-    if args.workload == "c4":
-        print(json.dumps(run_c4(args)), flush=True)
-        return
-    if args.workload == "c3":
-        print(json.dumps(run_c3(args)), flush=True)
-        return
-    res, (w, lens) = run_ours(args)
-    if res is not None:
-        if args.gpus == 1 and not args.no_cpu_baseline:
-            res["cpu_baseline"] = cpu_baseline(w, lens)
-        print(json.dumps(res), flush=True)
+    finally:
+        _dist_teardown()
+
+
+def run_secondary(args, world):
+    """The other workloads of the benchmark list, each on a fresh engine after the headline leg has released its
+    own, with fewer steps: the long sequence split by key range over the ranks (strong scaling; both the
+    peer-store exchange and the NCCL all-gather), the 1024-sequence workload (strong scaling over the ranks, in
+    waves through one pool), and at one GPU the chunked prefill (tensor-core bound).  Every rank takes part;
+    rank 0 gets the results."""
+    import copy
+    import torch
+
+    out = {}
+
+    def leg(name, fn):
+        torch.cuda.empty_cache()
+        t0 = time.perf_counter()
+        try:
+            r = fn()
+        except Exception as ex:   # a secondary leg never takes the headline line down with it
+            r = {"error": f"{type(ex).__name__}: {ex}"}
+        if isinstance(r, dict):
+            r["leg_wall_s"] = round(time.perf_counter() - t0, 1)
+        return r
+
+    a = copy.copy(args)
+    a.steps, a.warmup = min(args.steps, 10), 3
+    r = leg("c5a", lambda: run_c5a(a, collectives=["peer", "nccl"]))
+    if isinstance(r, dict):
+        if "error" in r:
+            out["c5a"] = r
+        else:
+            out["c5a_peer_store_exchange"], out["c5a_nccl_all_gather"] = r["peer"], r["nccl"]
+    b = copy.copy(args)
+    b.steps, b.warmup = min(args.steps, 5), 3
+    r = leg("c5b", lambda: run_c5b(b))
+    if r is not None:
+        out["c5b_1024_sequences"] = r
+    if world == 1:
+        c = copy.copy(args)
+        c.steps, c.warmup = 1, 1
+        r = leg("c4", lambda: run_c4(c))
+        if r is not None:
+            out["c4_chunked_prefill"] = r
+    return out
 
 
 if __name__ == "__main__":

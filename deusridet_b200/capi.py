@@ -132,6 +132,7 @@ SIGNATURES = {
     "drkv_k_extract_kv": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _i, _i, _i, _vp]),
     "drkv_k_inject_kv": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _i, _i, _i, _vp]),
     "drkv_k_decode_scratch_bytes": (_sz, [C.POINTER(Geometry), _i]),
+    "drkv_k_decode_kernel_error": (_i, [_vp, _vp]),
     "drkv_k_decode_attention_noalloc": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
 }
 NOALLOC_SCRATCH_BYTES = 4 << 20

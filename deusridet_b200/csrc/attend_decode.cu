@@ -25,6 +25,9 @@
 //     are a by-product (both compiled only into the EXT instantiation).
 // Holes (table entry < 0) contribute nothing.  All waits are bounded; a wait that gives
 // up records a code in the engine's error word and the CTA retires without trapping.
+#include <atomic>
+#include <mutex>
+
 #include "kernels.hpp"
 #include "kv_common.cuh"
 #include "sm100_primitives.cuh"
@@ -910,14 +913,15 @@ cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int
     constexpr int WARPS = RingShape<D>::kWarps, DEPTH = RingShape<D>::kDepth, NH = D / 64;
     constexpr size_t smem = 1024 + (size_t)WARPS * DEPTH * ((RingShape<D>::kSplit ? 1 : 2) * NH * 2048 + sizeof(SlotMeta) + sizeof(uint64_t)) +
                             (3 * kMaxDecodeSeqs + 1) * sizeof(int);   // cum[]: family blocks, sequences, their tail pieces
-    static bool configured[64] = {};  // per instantiation and device: the attribute belongs to the context
+    // per instantiation and device (the attribute belongs to the context); any thread may be the first caller
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
         e = cudaFuncSetAttribute(attend_decode_kernel<T, D, HI, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     int grid = (p.total_items + WARPS - 1) / WARPS;
     if (grid > num_sms) grid = num_sms;
@@ -987,13 +991,36 @@ bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layer
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) {
-        if (err) *err = "cuTensorMapEncodeTiled is not available from this driver";
-        return false;
+    // One descriptor per (pool, shape) is kept: the raw-pointer entry points are called once per layer and token
+    // with the same pool, and neither the driver look-up nor the encoding belongs on that path.
+    struct Key {
+        const void* pool;
+        int layers, pages, heads, page, dim;
+        bool operator==(const Key& o) const {
+            return pool == o.pool && layers == o.layers && pages == o.pages && heads == o.heads && page == o.page && dim == o.dim;
+        }
+    };
+    struct Entry { Key key; CUtensorMap map; };
+    static std::mutex cache_mu;
+    static Entry cache[8];
+    static int cache_used = 0, cache_next = 0;
+    const Key key{pool, num_layers, max_pages, num_kv_heads, page_size, head_dim};
+    std::lock_guard<std::mutex> lock(cache_mu);
+    for (int i = 0; i < cache_used; i++)
+        if (cache[i].key == key) {
+            *out = cache[i].map;
+            return true;
+        }
+    static EncodeFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) {
+            if (err) *err = "cuTensorMapEncodeTiled is not available from this driver";
+            return false;
+        }
+        encode = reinterpret_cast<EncodeFn>(fn);
     }
-    EncodeFn encode = reinterpret_cast<EncodeFn>(fn);
     const uint64_t plane_rows = (uint64_t)num_kv_heads * page_size;
     const uint64_t rows = (uint64_t)num_layers * max_pages * 2 * plane_rows;
     if (rows >= (1ull << 31)) {
@@ -1016,6 +1043,9 @@ bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layer
         if (err) *err = "cuTensorMapEncodeTiled (decode slot descriptor) failed";
         return false;
     }
+    cache[cache_next] = Entry{key, *out};
+    cache_next = (cache_next + 1) % 8;
+    if (cache_used < 8) cache_used++;
     return true;
 }
 

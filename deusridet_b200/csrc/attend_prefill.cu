@@ -21,6 +21,8 @@
 // fp32 accumulation, out = o / l, rows without a visible key are left unwritten.
 // Block-table holes contribute nothing.  Waits are bounded; a give-up sets the engine's error
 // word, and the CTA still frees its tensor memory before it returns.
+#include <atomic>
+
 #include "kernels.hpp"
 #include "kv_common.cuh"
 #include "sm100_primitives.cuh"
@@ -580,16 +582,16 @@ cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const CUtensorMap* tm
     for (int i = 0; i < p.n_seq; i++) max_m = p.m[i] > max_m ? p.m[i] : max_m;
     if (max_m <= 0 || p.n_seq > kMaxPrefillSeqs) return max_m <= 0 ? cudaSuccess : cudaErrorInvalidValue;
     dim3 grid((max_m + 2 * tok_per_tile - 1) / (2 * tok_per_tile), p.num_kv_heads, p.n_seq);
-    static bool configured[2][64] = {};
+    static std::atomic<bool> configured[2][64];   // any thread may be the first caller
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     const int ti = dtype == DRKV_DTYPE_F16 ? 0 : 1;
-    if (dev < 0 || dev >= 64 || !configured[ti][dev]) {
+    if (dev < 0 || dev >= 64 || !configured[ti][dev].load(std::memory_order_acquire)) {
         e = ti == 0 ? cudaFuncSetAttribute(attend_prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                     : cudaFuncSetAttribute(attend_prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[ti][dev] = true;
+        if (dev >= 0 && dev < 64) configured[ti][dev].store(true, std::memory_order_release);
     }
     if (ti == 0) return launch_pdl(attend_prefill_kernel<__half>, grid, dim3(kPfThreads), smem, stream, tmap, tv, p);
     return launch_pdl(attend_prefill_kernel<__nv_bfloat16>, grid, dim3(kPfThreads), smem, stream, tmap, tv, p);

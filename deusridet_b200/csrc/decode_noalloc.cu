@@ -49,6 +49,10 @@ int builtin_scratch(void** out) {
 
 }  // namespace
 
+namespace drkv {
+int noalloc_scratch_for_current_device(void** out) { return builtin_scratch(out); }
+}  // namespace drkv
+
 extern "C" int drkv_k_decode_attention_noalloc(const drkv_geometry* g, const void* q, const void* kv_pool,
                                                const int32_t* d_block_table, void* out, int layer, int seq_len,
                                                int max_pages, float scale, void* stream) {

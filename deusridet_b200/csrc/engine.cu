@@ -296,8 +296,12 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
         if (!inv.empty() &&
             (ce = cudaMemcpy(e->d_inv_freq, inv.data(), sizeof(float) * inv.size(), cudaMemcpyHostToDevice)) != cudaSuccess)
             return fail(DRKV_ERR_CUDA, "cudaMemcpy(inv_freq)", ce);
-        // split-KV scratch: every sequence at full table length in 256-key chunks, at least 64 MB
-        const size_t row_tokens = (size_t)e->book.row_width() * geom->page_size;
+        // split-KV scratch: every sequence at full length in 256-key chunks, at least 64 MB.  A sequence is
+        // never longer than its table row nor than the pool (the default row is twice the pool, CacheManager's
+        // logical space); a pass that needs more partials than this gets larger chunks (decode_common).
+        size_t row_tokens = (size_t)e->book.row_width() * geom->page_size;
+        const size_t pool_tokens = (size_t)max_pages * geom->page_size;
+        if (row_tokens > pool_tokens) row_tokens = pool_tokens;
         size_t need = (size_t)cfg->max_seqs * geom->num_q_heads * ((row_tokens + 255) / 256) * (geom->head_dim + 2) * 4;
         e->scratch_bytes = need < (64u << 20) ? (64u << 20) : need;
         if ((ce = cudaMalloc(&e->d_scratch, e->scratch_bytes)) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(scratch)", ce);

@@ -3,6 +3,7 @@
 // statics; src/machina/paged_attention.cu:104-115, 155-167, 271-282).  Nothing here owns
 // memory: the decode attention takes its split-KV scratch from the caller.
 #include <climits>
+#include <cstdio>
 #include <string>
 
 #include "../../include/drkv.h"
@@ -70,7 +71,10 @@ int stateless_decode(const drkv_geometry* g, const void* q, const void* kv_pool,
 
     DecodeParams p{};
     p.tables = d_block_table;
-    p.table_stride = INT_MAX;          // the caller's table covers seq_len by contract
+    // The caller's table covers ceil(seq_len / page_size) entries by contract and not one more: the kernel
+    // fetches page ids a window of 32 ahead, and this bound turns every entry past the end into a hole
+    // instead of a read outside the caller's allocation.
+    p.table_stride = (seq_len + g->page_size - 1) / g->page_size;
     p.rows = nullptr;
     p.kv_len = nullptr;
     p.row = 0;
@@ -194,6 +198,29 @@ int drkv_k_extract_kv(const drkv_geometry* g, void* dst, const void* kv_pool, co
 int drkv_k_inject_kv(const drkv_geometry* g, void* kv_pool, const void* src, const int32_t* d_block_table,
                      int start_token, int num_tokens, int max_pages, void* stream) {
     return flat_copy(g, kv_pool, const_cast<void*>(src), d_block_table, start_token, num_tokens, max_pages, false, stream);
+}
+
+int drkv_k_decode_kernel_error(const void* scratch, void* stream) {
+    const void* area = scratch;
+    if (area == nullptr) {
+        void* builtin = nullptr;
+        int rc = noalloc_scratch_for_current_device(&builtin);
+        if (rc != DRKV_OK) return rc;
+        area = builtin;
+    }
+    int code = 0;
+    // header word 1 is the error word of the last call that used this scratch (stateless_decode)
+    if (cudaMemcpyAsync(&code, reinterpret_cast<const int*>(area) + 1, sizeof(int), cudaMemcpyDeviceToHost,
+                        (cudaStream_t)stream) != cudaSuccess ||
+        cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess)
+        return fail(DRKV_ERR_CUDA, "decode_kernel_error: reading the scratch header failed");
+    if (code != 0) {
+        char msg[160];
+        snprintf(msg, sizeof(msg),
+                 "a kernel reported error code %d (1 = load wait, 2 = ring wait, 3 = page id, 4 = peer wait)", code);
+        return fail(DRKV_ERR_CUDA, msg);
+    }
+    return DRKV_OK;
 }
 
 size_t drkv_k_decode_scratch_bytes(const drkv_geometry* g, int seq_len) {

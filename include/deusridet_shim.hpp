@@ -27,7 +27,11 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <functional>
+#include <mutex>
 #include <string>
+#include <unordered_set>
+#include <vector>
 
 #include "drkv.h"
 
@@ -261,29 +265,81 @@ inline void paged_kv_cache_write_batch(const __half* src_k, const __half* src_v,
         std::fprintf(stderr, "[Machina] paged_kv_cache_write_batch: %s\n", drkv_last_error());
 }
 
-// The reference signature has no workspace argument; the shim keeps one device buffer per
-// process, grown on demand (growth synchronises the device, as any cudaMalloc does).
+// The reference signature has no workspace argument; the shim keeps one split-KV scratch buffer per CUDA
+// device, shared by every call on that device: calls must be ordered on one stream (or otherwise not overlap
+// on the GPU).  A buffer grows on demand and is never shrunk; the old buffer of a grown one is kept until the
+// process exits, because kernels already enqueued (or captured in a graph) may still use it.  Growth calls
+// cudaMalloc, which synchronises the device and is illegal during stream capture: call
+// shim_reserve_decode_scratch() for the longest sequence once, before capturing a decode step.
+namespace detail {
+struct DecodeScratch {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+inline std::mutex& decode_scratch_mutex() {
+    static std::mutex m;
+    return m;
+}
+inline DecodeScratch* decode_scratch_slots() {
+    static DecodeScratch slots[64];
+    return slots;
+}
+// Returns the current device's buffer, at least `need` bytes (nullptr on failure).
+inline void* decode_scratch(size_t need, size_t* bytes_out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(decode_scratch_mutex());
+    DecodeScratch& sc = decode_scratch_slots()[dev];
+    if (need > sc.bytes) {
+        void* fresh = nullptr;
+        const size_t bytes = need * 2;
+        if (cudaMalloc(&fresh, bytes) != cudaSuccess) return nullptr;
+        sc.ptr = fresh;       // the previous buffer stays allocated, see above
+        sc.bytes = bytes;
+    }
+    *bytes_out = sc.bytes;
+    return sc.ptr;
+}
+}  // namespace detail
+
+inline bool shim_reserve_decode_scratch(int max_seq_len, int block_size = PagedKVConfig::BLOCK_SIZE) {
+    drkv_geometry g = shim_geometry();
+    g.page_size = block_size;
+    size_t bytes = 0;
+    return detail::decode_scratch(drkv_k_decode_scratch_bytes(&g, max_seq_len > 0 ? max_seq_len : 1), &bytes) != nullptr;
+}
+
 inline void paged_gqa_decode_attention(const __half* Q, __half* kv_pool, const int* d_block_table, __half* out,
                                        int fa_layer_idx, int seq_len, int max_phys_blocks, int block_size,
                                        float scale, cudaStream_t stream = 0) {
-    static void* scratch = nullptr;
-    static size_t scratch_bytes = 0;
     drkv_geometry g = shim_geometry();
     g.page_size = block_size;
-    const size_t need = drkv_k_decode_scratch_bytes(&g, seq_len > 0 ? seq_len : 1);
-    if (need > scratch_bytes) {
-        if (scratch) cudaFree(scratch);
-        scratch_bytes = need * 2;
-        if (cudaMalloc(&scratch, scratch_bytes) != cudaSuccess) {
-            std::fprintf(stderr, "[Machina] paged_gqa_decode_attention: scratch allocation failed\n");
-            scratch = nullptr;
-            scratch_bytes = 0;
-            return;
-        }
+    size_t scratch_bytes = 0;
+    void* scratch = detail::decode_scratch(drkv_k_decode_scratch_bytes(&g, seq_len > 0 ? seq_len : 1), &scratch_bytes);
+    if (scratch == nullptr) {
+        std::fprintf(stderr, "[Machina] paged_gqa_decode_attention: scratch allocation failed\n");
+        return;
     }
     if (drkv_k_decode_attention(&g, Q, kv_pool, d_block_table, out, fa_layer_idx, seq_len, max_phys_blocks, scale,
                                 scratch, scratch_bytes, stream) != DRKV_OK)
         std::fprintf(stderr, "[Machina] paged_gqa_decode_attention: %s\n", drkv_last_error());
+}
+
+// What the kernels of the last paged_gqa_decode_attention call on this device reported (a bounded wait that gave
+// up, a table entry beyond the pool): true = nothing.  Synchronises the stream.  The reference's kernels have no
+// error path (src/machina/paged_attention.cu:219-230 index the pool unchecked).
+inline bool shim_decode_kernels_ok(cudaStream_t stream = 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    void* ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(detail::decode_scratch_mutex());
+        ptr = detail::decode_scratch_slots()[dev].ptr;
+    }
+    if (ptr == nullptr) return true;
+    if (drkv_k_decode_kernel_error(ptr, stream) == DRKV_OK) return true;
+    std::fprintf(stderr, "[Machina] paged_gqa_decode_attention: %s\n", drkv_last_error());
+    return false;
 }
 
 // ---- src/memoria/cache_kernels.h:44-74 -----------------------------------------------------------

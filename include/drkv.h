@@ -336,12 +336,20 @@ DRKV_API int drkv_k_cache_write(const drkv_geometry* g, const void* src_k, const
 DRKV_API int drkv_k_cache_write_batch(const drkv_geometry* g, const void* src_k, const void* src_v,
                                       void* kv_pool, const int32_t* d_block_table, int layer,
                                       int pos_start, int m, int max_pages, void* stream);
-/* `scratch`: device memory of at least drkv_k_decode_scratch_bytes(g, seq_len) bytes. */
+/* `scratch`: device memory of at least drkv_k_decode_scratch_bytes(g, seq_len) bytes, 256-byte aligned.
+ * d_block_table needs ceil(seq_len / page_size) entries and is not read beyond them. */
 DRKV_API int drkv_k_decode_attention(const drkv_geometry* g, const void* q, const void* kv_pool,
                                      const int32_t* d_block_table, void* out, int layer,
                                      int seq_len, int max_pages, float scale, void* scratch,
                                      size_t scratch_bytes, void* stream);
 DRKV_API size_t drkv_k_decode_scratch_bytes(const drkv_geometry* g, int seq_len);
+/* The error word of the last drkv_k_decode_attention call that used `scratch` (NULL: of the last
+ * drkv_k_decode_attention_noalloc call on the current device): DRKV_OK, or DRKV_ERR_CUDA with the
+ * code in drkv_last_error() when a kernel gave up a bounded wait or met a page id >= max_pages (such
+ * an entry is treated as a hole; nothing outside the pool is touched).  Synchronises `stream`.  Each
+ * decode call clears the word when it starts, so ask before the next call on the same scratch.  The
+ * reference's kernels have no counterpart: they index the pool unchecked (paged_attention.cu:219-230). */
+DRKV_API int drkv_k_decode_kernel_error(const void* scratch, void* stream);
 /* invoke_extract_kv_from_pages / invoke_inject_kv_to_pages with raw pointers
  * (src/memoria/cache_kernels.h:44-74); num_layers, heads, dims and block size come from g. */
 DRKV_API int drkv_k_extract_kv(const drkv_geometry* g, void* dst, const void* kv_pool,

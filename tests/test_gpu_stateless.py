@@ -81,3 +81,54 @@ def test_reference_free_functions_model_shape(drkv_lib, oracle):
 
 def test_reference_free_functions_bf16_long(drkv_lib, oracle):
     _run(oracle, drkv_lib, hq=32, hkv=8, d=128, page=16, dtype=oracle.BF16, seq_len=5000, m_batch=17, seed=13)
+
+
+def test_kernel_error_word_of_the_stateless_path(drkv_lib, oracle):
+    """A table entry >= max_pages is refused by the kernel's own range check before any address is formed from it:
+    it counts as a hole, and drkv_k_decode_kernel_error reports code 3 for that call only."""
+    import torch
+    from deusridet_b200 import capi
+
+    ob = oracle
+    layers, hq, hkv, d, page, dtype, seq_len = 1, 16, 4, 128, 16, ob.BF16, 900
+    rng = np.random.default_rng(14)
+    n_pages = (seq_len + page - 1) // page
+    max_pages = n_pages + 3
+    g = ob.geom(layers, hq, hkv, d, page, dtype, 0, 1e4)
+    cg = capi.Geometry(layers, hq, hkv, d, page, dtype, 0, 1e4)
+    table = rng.permutation(max_pages)[:n_pages].astype(np.int32)   # exactly ceil(seq_len / page) entries
+    pool = H.randn_bits(rng, ob.pool_elems(g, max_pages), dtype)
+    d_pool = torch.from_numpy(pool.view(np.int16)).cuda()
+    q = H.randn_bits(rng, (1, hq, d), dtype)
+    d_q = H.to_dev(q, dtype)
+    need = drkv_lib.drkv_k_decode_scratch_bytes(C.byref(cg), seq_len)
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    scale = 1.0 / np.sqrt(d)
+
+    def run(tab, noalloc):
+        d_table = torch.from_numpy(tab).cuda()
+        out = torch.zeros(1, hq, d, dtype=torch.bfloat16, device="cuda")
+        if noalloc:
+            rc = drkv_lib.drkv_k_decode_attention_noalloc(C.byref(cg), d_q.data_ptr(), d_pool.data_ptr(),
+                                                          d_table.data_ptr(), out.data_ptr(), 0, seq_len, max_pages,
+                                                          scale, None)
+        else:
+            rc = drkv_lib.drkv_k_decode_attention(C.byref(cg), d_q.data_ptr(), d_pool.data_ptr(), d_table.data_ptr(),
+                                                  out.data_ptr(), 0, seq_len, max_pages, scale, scratch.data_ptr(),
+                                                  need, None)
+        assert rc == 0, capi.last_error()
+        status = drkv_lib.drkv_k_decode_kernel_error(None if noalloc else scratch.data_ptr(), None)
+        return ob.to_float(H.torch_bits(out), dtype), status
+
+    bad = table.copy()
+    bad[7] = max_pages + 5                                  # not a page of this pool
+    holed = table.copy()
+    holed[7] = -1
+    want = np.zeros((1, hq, d), dtype=np.uint16)
+    ob.attend_decode(g, pool, max_pages, holed[None, :], [0], [seq_len], 0, q, want, scale)
+    for noalloc in (False, True):
+        got, status = run(bad, noalloc)
+        assert status == capi.ERR_CUDA and "code 3" in capi.last_error()
+        assert np.abs(got - ob.to_float(want, dtype)).max() <= 2e-3
+        _, status = run(table, noalloc)                     # the next call starts clean
+        assert status == 0, capi.last_error()

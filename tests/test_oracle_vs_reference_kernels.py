@@ -1,5 +1,6 @@
-"""The CPU checker against outputs of the reference's own CUDA kernels (apply_rope,
-paged_kv_cache_write[_batch], paged_gqa_decode_attention), recorded on a B200 by
+"""The CPU checker against outputs of the reference's own CUDA kernels (apply_rope, paged_rope_batch_kernel,
+paged_kv_cache_write[_batch], paged_gqa_decode_attention, paged_prefill_attention_kernel, the bf16 split-K decode
+and merge, the flat <-> paged copies), recorded on a B200 by
 tests/golden/make_paged_attention_golden.py into tests/golden/paged_attention_reference.npz.
 
 What is pinned, and how tightly:
@@ -70,3 +71,76 @@ def test_importance_update_matches_reference_kernel_record(oracle):
         for k in range(new.shape[0]):
             oracle.importance_update(scores, new[k], decay)
             assert np.array_equal(scores, gold[name][k]), f"{name} step {k}"
+
+
+@pytest.mark.parametrize("name", sorted(paged_cases.PREFILL_CASES))
+def test_checker_reproduces_reference_prefill_kernels(oracle, name):
+    """paged_rope_batch_kernel, paged_kv_cache_write_batch and paged_prefill_attention_kernel
+    (src/machina/paged_attention.cu:412-451, 123-167, 465-554) as recorded on a B200."""
+    import ctypes as C
+    ob = oracle
+    c = paged_cases.build_prefill(name)
+    g, m = c["g"], c["m"]
+    q_r, k_r = c["q"].copy(), c["k"].copy()
+    for t in range(m):                              # the batch kernel rotates token t at pos_start + t
+        ob.lib().okv_rope_rows(q_r[t].ctypes.data, c["hq"], C.byref(g), c["pos_start"] + t)
+        ob.lib().okv_rope_rows(k_r[t].ctypes.data, c["hkv"], C.byref(g), c["pos_start"] + t)
+        assert _rope_close(q_r[t], GOLD[name + "_q_roped"][t], c["q"][t], c, c["pos_start"] + t, ob), t
+        assert _rope_close(k_r[t], GOLD[name + "_k_roped"][t], c["k"][t], c, c["pos_start"] + t, ob), t
+    if c["pos_start"] > 0:
+        assert (GOLD[name + "_k_roped"][:, :, :c["rot"]] != c["k"][:, :, :c["rot"]]).mean() > 0.9
+    assert np.array_equal(GOLD[name + "_q_roped"][:, :, c["rot"]:], c["q"][:, :, c["rot"]:])
+    # the batched write is a copy: with the reference's rotated K the whole pool must hash to the reference's
+    pool = c["pool"].copy()
+    ob.append(g, pool, c["max_pages"], c["table"], c["layer"], c["pos_start"], m, GOLD[name + "_k_roped"], c["v"],
+              rope=False)
+    assert np.array_equal(paged_cases.digest(pool), GOLD[name + "_pool_sha256"])
+    # causal attention of the chunk on that pool with the reference's rotated Q
+    out = np.zeros((m, c["hq"], c["d"]), dtype=np.uint16)
+    ob.attend_prefill(g, pool, c["max_pages"], c["table"], c["layer"], c["pos_start"], m, GOLD[name + "_q_roped"], out,
+                      1.0 / np.sqrt(c["d"]))
+    got, want = ob.to_float(out, ob.F16), ob.to_float(GOLD[name + "_out"], ob.F16)
+    assert np.abs(got - want).max() <= 2e-3
+
+
+@pytest.mark.parametrize("name", sorted(paged_cases.SPLITK_CASES))
+def test_checker_reproduces_reference_split_k_decode(oracle, name):
+    """The reference's only bf16 attention (invoke_causal_gqa_decode, src/sensus/auditus/asr/asr_ops_attn.cu:29-132):
+    per-partition partials (un-normalised o, m, l; 128-key partitions), their merge, and the final output, against
+    the checker's partial / merge / whole-sequence decode on the same values laid out in pages."""
+    ob = oracle
+    c = paged_cases.build_splitk(name)
+    g, hq, d, S, n_parts = c["g"], c["hq"], c["d"], c["seq_len"], c["n_parts"]
+    scale = 1.0 / np.sqrt(d)
+    ref_o, ref_m, ref_l = GOLD[name + "_part_o"], GOLD[name + "_part_m"], GOLD[name + "_part_l"]
+    for p in range(n_parts):
+        part = ob.attend_partial(g, c["pool"], c["max_pages"], c["table"], 0, 128 * p, min(128 * (p + 1), S), c["q"], scale)
+        o, mm, l = part[:hq * d].reshape(hq, d), part[hq * d:hq * d + hq], part[hq * (d + 1):]
+        # (m, l, o) of the two sides may differ by a common factor (running maximum against partition maximum):
+        # the normalised partial and the log-sum-exp do not
+        assert np.abs(o / l[:, None] - ref_o[:, p] / ref_l[:, p, None]).max() <= 2e-4, p
+        assert np.abs((mm + np.log(l)) - (ref_m[:, p] + np.log(ref_l[:, p]))).max() <= 2e-4, p
+    want = ob.to_float(GOLD[name + "_out"], ob.BF16)
+    tol = np.maximum(2e-3, H.ulp(want, ob.BF16))
+    # the checker's merge, fed the reference's own partials, gives the reference's output
+    ext = paged_cases.splitk_parts_external(ref_o, ref_m, ref_l, hq, d, n_parts)
+    merged = np.zeros((hq, d), dtype=np.uint16)
+    ob.combine(g, n_parts, ext, merged)
+    assert (np.abs(ob.to_float(merged, ob.BF16) - want) <= tol).all()
+    # and so does the unsplit decode recurrence
+    whole = np.zeros((1, hq, d), dtype=np.uint16)
+    ob.attend_decode(g, c["pool"], c["max_pages"], c["table"][None, :], [0], [S], 0, c["q"][None], whole, scale)
+    assert (np.abs(ob.to_float(whole[0], ob.BF16) - want) <= tol).all()
+
+
+@pytest.mark.parametrize("name", sorted(paged_cases.FLAT_CASES))
+def test_checker_reproduces_reference_extract_inject(oracle, name):
+    """invoke_extract_kv_from_pages / invoke_inject_kv_to_pages (src/memoria/cache_kernels.cu:30-187), byte-exact:
+    a page missing from the table reads as zeros and is skipped on the way back."""
+    ob = oracle
+    c = paged_cases.build_flat(name)
+    flat = ob.extract(c["g"], c["pool"], c["max_pages"], c["table"], c["start"], c["num"])
+    assert np.array_equal(paged_cases.digest(flat), GOLD[name + "_extract_sha256"])
+    pool = c["pool"].copy()
+    ob.inject(c["g"], pool, c["src"], c["max_pages"], c["table"], c["start"], c["num"])
+    assert np.array_equal(paged_cases.digest(pool), GOLD[name + "_pool_after_inject_sha256"])
