@@ -87,8 +87,8 @@ def test_checker_reproduces_reference_prefill_kernels(oracle, name):
         ob.lib().okv_rope_rows(k_r[t].ctypes.data, c["hkv"], C.byref(g), c["pos_start"] + t)
         assert _rope_close(q_r[t], GOLD[name + "_q_roped"][t], c["q"][t], c, c["pos_start"] + t, ob), t
         assert _rope_close(k_r[t], GOLD[name + "_k_roped"][t], c["k"][t], c, c["pos_start"] + t, ob), t
-    if c["pos_start"] > 0:
-        assert (GOLD[name + "_k_roped"][:, :, :c["rot"]] != c["k"][:, :, :c["rot"]]).mean() > 0.9
+    if c["pos_start"] > 0:     # a rotation did happen (the slowest pairs of a large base barely move at these positions)
+        assert (GOLD[name + "_k_roped"][:, :, :c["rot"]] != c["k"][:, :, :c["rot"]]).mean() > 0.8
     assert np.array_equal(GOLD[name + "_q_roped"][:, :, c["rot"]:], c["q"][:, :, c["rot"]:])
     # the batched write is a copy: with the reference's rotated K the whole pool must hash to the reference's
     pool = c["pool"].copy()
@@ -125,7 +125,7 @@ def test_checker_reproduces_reference_split_k_decode(oracle, name):
     # the checker's merge, fed the reference's own partials, gives the reference's output
     ext = paged_cases.splitk_parts_external(ref_o, ref_m, ref_l, hq, d, n_parts)
     merged = np.zeros((hq, d), dtype=np.uint16)
-    ob.combine(g, n_parts, ext, merged)
+    ob.combine(g, ext, merged)
     assert (np.abs(ob.to_float(merged, ob.BF16) - want) <= tol).all()
     # and so does the unsplit decode recurrence
     whole = np.zeros((1, hq, d), dtype=np.uint16)
