@@ -203,10 +203,18 @@ def run_ours(args):
     scale = 1.0 / float(np.sqrt(d))
     max_kv = int(lens.max()) + 1
 
+    fused = not args.separate_append            # one call per layer: the attention kernel appends the new token itself
+
+    def layer_step(l, k_l, v_l, q_l, mk, stream):
+        if fused:
+            eng.append_attend_decode(l, n_seq, d_rows, d_len, mk, k_l, v_l, q_l, out[l], scale, stream)
+        else:
+            eng.append_rope(l, n_seq, d_rows, d_pos, k_l, v_l, stream)
+            eng.attend_decode(l, n_seq, d_rows, d_len, mk, q_l, out[l], scale, stream)
+
     def device_step(stream=stream):
         for l in range(L):
-            eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
-            eng.attend_decode(l, n_seq, d_rows, d_len, max_kv, q[l], out[l], scale, stream)
+            layer_step(l, kn[l], vn[l], q[l], max_kv, stream)
         if args.scorer:
             eng.scorer_step(stream)
 
@@ -237,7 +245,7 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t.item()) / K
-    launches = K * L * 3                               # append, attention, combine per layer
+    launches = K * L * (2 if fused else 3)             # (append,) attention, combine per layer
     if args.scorer:
         launches += K * (L + 1)                        # + page mass per layer, score update per step
 
@@ -321,8 +329,7 @@ def run_ours(args):
                 if l + AHEAD < L:
                     send(l + AHEAD)
                 stream.wait_event(ev_in[l])
-                eng.append_rope(l, n_seq, d_rows, d_pos, ek[l], evv[l], stream)
-                eng.attend_decode(l, n_seq, d_rows, d_len, mk, eq[l], out[l], scale, stream)
+                layer_step(l, ek[l], evv[l], eq[l], mk, stream)
                 ev_out[l].record(stream)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_out[l])
@@ -471,6 +478,11 @@ def run_c5a(args, collectives=None):
 
         def step():
             for l in range(L):
+                if use_peer and not args.separate_append:
+                    # partial (the owner of the last page appends the new token inside it), peer stores, merge
+                    mine_kv = (kn[l], vn[l]) if rank == owner else (None, None)
+                    eng.append_attend_exchange(l, s, begin, end, mine_kv[0], mine_kv[1], q[l], out[l], scale, stream)
+                    continue
                 if rank == owner:
                     eng.append_rope(l, 1, d_rows, d_pos, kn[l], vn[l], stream)
                 if use_peer:
@@ -526,7 +538,11 @@ def run_c5a(args, collectives=None):
             "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                          "bytes_per_launch": kv_rank, "us_per_launch": kms / kn_l * 1e3},
-            "gpu_launches": K * L * (3 + (1 if owner == 0 else 0)), "clocks": clocks, "e2e": None}
+            # rank 0's own kernels per layer: attention + merge (the merge is also the exchange with peer stores; with
+            # NCCL a second merge follows the all-gather), plus the append kernel where the token is not fused in
+            "gpu_launches": K * L * ((2 if use_peer else 3) +
+                                     (1 if owner == 0 and (args.separate_append or not use_peer) else 0)),
+            "clocks": clocks, "e2e": None}
     eng.close()
     return results if rank == 0 else None
 
@@ -589,8 +605,11 @@ def run_c5b(args):
                 eng.set_seq_len(s_, S)
             eng.sync_block_table(stream)
             for l in range(L):
-                eng.append_rope(l, n, d_rows, d_pos, kn[l], vn[l], stream)
-                eng.attend_decode(l, n, d_rows, d_len, S + 1, q[l], out[l], scale, stream)
+                if args.separate_append:
+                    eng.append_rope(l, n, d_rows, d_pos, kn[l], vn[l], stream)
+                    eng.attend_decode(l, n, d_rows, d_len, S + 1, q[l], out[l], scale, stream)
+                else:
+                    eng.append_attend_decode(l, n, d_rows, d_len, S + 1, kn[l], vn[l], q[l], out[l], scale, stream)
             # pages go back to the allocator; the kernels of the next wave are ordered behind these on the stream
             for s_ in seqs:
                 eng.seq_release(s_, discard=True)
@@ -647,7 +666,7 @@ def run_c5b(args):
             "roofline": {"bound": "hbm", "kernel": "attend_decode_kernel", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
                          "traffic": None, "bytes_per_launch": kv_launch, "us_per_launch": kms / kn_l * 1e3},
-            "gpu_launches": K * n_waves * L * 3, "clocks": clocks, "e2e": None}
+            "gpu_launches": K * n_waves * L * (3 if args.separate_append else 2), "clocks": clocks, "e2e": None}
 
 
 def run_c4(args):
@@ -947,6 +966,7 @@ def c2_config(args, w, lens, world, max_pages, kv_bytes):
             "sum_ctx": int(lens.sum()), "page": w["page"], "pool_pages": max_pages,
             "pool_gb": round(eng_bytes(max_pages, w) / 1e9, 2), "parallelism": f"dp{world}",
             "importance_scorer": bool(args.scorer),
+            "append": "own launch" if getattr(args, "separate_append", False) else "fused into the attention kernel",
             "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer" % (kv_bytes / 1e9)}
 
 
@@ -1003,6 +1023,8 @@ def main():
     ap.add_argument("--scorer", action="store_true", help="c2/c5b: also produce per-page attention mass and scores")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="c2: skip the CUDA-graph replay of the step")
+    ap.add_argument("--separate-append", action="store_true",
+                    help="append the new token with its own kernel launch instead of inside the attention kernel")
     ap.add_argument("--no-secondary", action="store_true",
                     help="c2: skip the secondary workloads (long split sequence, 1024 sequences, chunked prefill)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

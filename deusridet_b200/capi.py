@@ -99,6 +99,7 @@ SIGNATURES = {
     "drkv_append_rope": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "drkv_append_rope_chunk": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp]),
     "drkv_attend_decode": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _vp]),
+    "drkv_append_attend_decode": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _f, _vp]),
     "drkv_plan_decode": (_i, [_vp, _i, _pi32, _pi32, _vp]),
     "drkv_plan_get_info": (_i, [_vp, C.POINTER(PlanInfo)]),
     "drkv_plan_dump": (_i, [_vp, _pi32, _i]),
@@ -120,6 +121,7 @@ SIGNATURES = {
     "drkv_exchange_connect": (_i, [_vp, C.POINTER(C.c_uint8)]),
     "drkv_exchange_destroy": (_i, [_vp]),
     "drkv_attend_exchange": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
+    "drkv_append_attend_exchange": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _vp]),
     "drkv_attend_partial": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_combine_partials": (_i, [_vp, _i, _vp, _vp, _vp]),
     "drkv_probe_read_bandwidth": (_i, [_vp, _sz, _i, _vp, C.POINTER(C.c_double)]),

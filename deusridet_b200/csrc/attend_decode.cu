@@ -58,13 +58,15 @@ enum SlotFlags : int { SLOT_FIRST = 1, SLOT_LAST = 2, SLOT_SKIP = 4, SLOT_DONE =
 
 // What lane 0 leaves for its warp about one ring slot: one 8-byte store per group; everything that is the
 // same for all groups of an item is written once per item.
-struct alignas(8) SlotMeta {
+struct alignas(16) SlotMeta {
     int flags;                      // SlotFlags | (item entry << kItemShift)
     int tok0;                       // first key of the group (a multiple of 16)
+    int page;                       // pool page of the group (< 0: hole)
+    int pad;
 };
 struct alignas(16) ItemMeta {
     int b, kvh, part_slot, fam;     // part_slot: index of the partial of query row 0; fam: family block + 1 or 0
-    int tok_hi, pad0, pad1, pad2;   // keys of the item end here
+    int tok_hi, append, trow, pad2; // keys of the item end here; append: the item ends at the sequence's new token, which it appends; table row
 };
 constexpr int kItemShift = 4, kItemEntries = 8;   // a ring holds at most 6 groups, so at most 7 items are live
 
@@ -107,6 +109,38 @@ __device__ __forceinline__ void split_pack(float p0, float p1, uint32_t& hi, uin
     lo = Elem<T>::pack2(p0 - h.x, p1 - h.y);
 }
 
+// Fused append, the rare path of one work item per (sequence, KV head): the token at `pos` is not in the pool yet.
+// When the item that will reach it STARTS, its warp rotates the K row exactly as append_rope_kernel does (same
+// operations, same rounding: the pool bytes are identical), leaves the K and the V row in a small staging area of
+// its own in shared memory, and writes both to the pool page with 16-byte stores; the item's first gathers are
+// in flight meanwhile.  When the item's last group has landed, the staged rows replace the row of the K and V
+// tiles that the gather brought from the pool (stale there, or racing with the store above).  Kept out of line so
+// that the main loop's register allocation does not see the fp64 sine/cosine evaluation.
+template <typename T, int D>
+__device__ __noinline__ void fused_append_prepare(const T* ksrc, const T* vsrc, T* pool_krow, int64_t plane_elems,
+                                                  const float* inv_freq, int rotary_dim, uint8_t* stage, int pos, int lane) {
+    const int half = rotary_dim >> 1;
+    T* krow = reinterpret_cast<T*>(stage);
+    for (int i = lane; i < half; i += 32) {
+        const float x0 = Elem<T>::to_f(ksrc[i]), x1 = Elem<T>::to_f(ksrc[i + half]);
+        float sn, cs, y0, y1;
+        sincos_det(__fmul_rn((float)pos, __ldg(inv_freq + i)), sn, cs);
+        rope_pair(x0, x1, cs, sn, y0, y1);
+        krow[i] = Elem<T>::from_f(y0);
+        krow[i + half] = Elem<T>::from_f(y1);
+    }
+    for (int d = rotary_dim + lane; d < D; d += 32) krow[d] = ksrc[d];
+    for (int c = lane; c < D / 8; c += 32) *reinterpret_cast<Vec16*>(stage + D * 2 + 16 * c) = ldg16(vsrc + 8 * c);
+    __syncwarp();
+    if (pool_krow != nullptr) {
+        // the token's pool rows: the V plane of a page starts plane_elems after its K plane
+        for (int c = lane; c < 2 * (D / 8); c += 32) {
+            const int pl = c / (D / 8), cc = c - pl * (D / 8);
+            stg16(pool_krow + pl * plane_elems + 8 * cc, *reinterpret_cast<const Vec16*>(stage + pl * (D * 2) + 16 * cc));
+        }
+    }
+}
+
 // Prefix sums of per-sequence chunk counts live in shared memory: kMaxDecodeSeqs + 1 ints.
 
 // Persistent kernel, one CTA per SM, every warp on its own.  Work item = (sequence, KV head,
@@ -141,6 +175,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     int* cum = reinterpret_cast<int*>(bars + WARPS * DEPTH);                           // [n_seq + 1]
     __shared__ int s_warp_tot[WARPS];
     __shared__ ItemMeta s_items[WARPS][kItemEntries];
+    __shared__ __align__(16) uint8_t s_new_kv[SPLIT ? 1 : WARPS][SPLIT ? 16 : 2 * D * 2];   // fused append: a warp's new K row, V row
 
     const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
     const uint32_t bar_full = smem_u32(bars);
@@ -172,7 +207,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     struct SeqShape { int kv_end, first, nbig, nsmall; };
     auto seq_shape = [&](int b) -> SeqShape {
         SeqShape q;
-        q.kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + b) : p.kv_end;
+        q.kv_end = p.kv_len != nullptr ? __ldg(p.kv_len + b) : p.kv_end + b * p.kv_step;
         int nch = q.kv_end > base_tok ? (q.kv_end - base_tok + CT - 1) / CT : 0;
         nch = min(nch, p.max_chunks);
         q.first = n_fb > 0 ? min(__ldg(p.seq_first_chunk + b), nch) : 0;
@@ -239,10 +274,11 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     int raw_next = 0, n_state = 0;
     bool exhausted = false;
     int n_b = 0, n_kvh = 0, n_slot = 0, n_tok_lo = 0, n_tok_hi = 0, n_trow = 0, n_fam = 0;   // n_fam: family block + 1, 0 = plain
+    int n_end = 0;              // the next item ends where its sequence ends (it meets the token a fused append brings)
     int n_pv = -1;              // per lane: page id of logical page (n_tok_lo / page_size) + lane of the next item
     // ---- issue cursor ----
     bool c_valid = false;
-    int c_b = 0, c_kvh = 0, c_slot = 0, c_trow = 0, c_tok_hi = 0, c_tok_lo = 0, c_ngroups = 0, c_gi = 0, c_fam = 0;
+    int c_b = 0, c_kvh = 0, c_slot = 0, c_trow = 0, c_tok_hi = 0, c_tok_lo = 0, c_ngroups = 0, c_gi = 0, c_fam = 0, c_end = 0;
     // Page ids come 32 at a time: lane i holds the id of logical page c_pv_base + i (c_pv) and of the 32 after
     // those (c_pvn), loaded a window ahead; a group's id is a shuffle away.  A table load per group would sit
     // on the issue path with the latency of a saturated memory system.
@@ -288,6 +324,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         const int i = j - n_kvh * per_head;
         if (lo < n_fb) {                               // shared chunks of a family block
             n_fam = lo + 1;
+            n_end = 0;
             n_b = 0;
             n_slot = i;
             n_tok_lo = base_tok + i * CT;
@@ -307,6 +344,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 n_tok_lo = base_tok + (q.nbig + i / TAILS) * CT + (i % TAILS) * SUBK;
                 n_tok_hi = min(n_tok_lo + SUBK, q.kv_end);
             }
+            n_end = n_tok_hi == q.kv_end;
             n_trow = p.rows != nullptr ? __ldg(p.rows + n_b) : p.row;
         }
         n_state = 2;
@@ -345,6 +383,8 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 SlotMeta m;
                 m.flags = (c_gi == 0 ? SLOT_FIRST : 0) | (last ? SLOT_LAST : 0) | (page < 0 ? SLOT_SKIP : 0) | (c_item << kItemShift);
                 m.tok0 = tok0;
+                m.page = page;
+                m.pad = 0;
                 metas[ring] = m;
             }
             // Generic-proxy WRITES to the ring (the zero fill of an end group's hidden V rows, made visible
@@ -432,6 +472,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 if (n_state == 1) decode_next();       // waits for the atomic only if it was just issued
                 if (n_state < 2) break;                // queue drained
                 c_b = n_b; c_kvh = n_kvh; c_slot = n_slot; c_trow = n_trow; c_tok_lo = n_tok_lo; c_tok_hi = n_tok_hi; c_fam = n_fam;
+                c_end = n_end;
                 c_ngroups = (c_tok_hi - c_tok_lo + kGroupTokens - 1) / kGroupTokens;
                 c_gi = 0;
                 c_logical = c_tok_lo / p.page_size;
@@ -449,7 +490,9 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     im.part_slot = (EXT && c_fam) ? c_slot : (c_b * p.num_q_heads + c_kvh * p.group) * slot_stride + c_slot;
                     im.fam = c_fam;
                     im.tok_hi = c_tok_hi;
-                    im.pad0 = im.pad1 = im.pad2 = 0;
+                    im.append = (!SPLIT && c_end && p.k_new != nullptr) ? 1 : 0;
+                    im.trow = c_trow;
+                    im.pad2 = 0;
                     s_items[w][c_item] = im;
                 }
                 if (!EXT || c_fam == 0) {
@@ -458,6 +501,13 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                                      ((int64_t)c_b * p.num_q_heads + (int64_t)c_kvh * p.group) * (D * (int)sizeof(T));
                     if (lane * 128 < p.group * D * (int)sizeof(T))
                         asm volatile("prefetch.global.L1 [%0];" ::"l"(qb + lane * 128));
+                    if (!SPLIT && c_end && p.k_new != nullptr && lane < 2 * (D * (int)sizeof(T) / 128)) {
+                        // the new token's K and V rows, which this item will append when it starts
+                        const int64_t src = ((int64_t)c_b * p.num_kv_heads + c_kvh) * (D * (int)sizeof(T));
+                        const int hl = D * (int)sizeof(T) / 128;                 // 128-byte lines per row
+                        const char* base = reinterpret_cast<const char*>(lane < hl ? p.k_new : p.v_new) + src;
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(base + (lane % hl) * 128));
+                    }
                 }
             }
             issue_entry();
@@ -536,6 +586,21 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
 #pragma unroll
                 for (int j = 0; j < 2 * NR; j++) o[i][j] = 0.f;
         }
+        if (!SPLIT && (meta.flags & SLOT_FIRST) && item->append) {
+            // this item ends at its sequence's new token: rotate and stage the token's rows now, while the item's
+            // first gathers are in flight, and write them into the pool page (nothing if the table has a hole there)
+            const int pos = item->tok_hi - 1;
+            const int logical = pos / p.page_size;
+            int page = logical < p.table_stride ? __ldg(p.tables + (int64_t)item->trow * p.table_stride + logical) : -1;
+            if (page >= p.max_pages) page = -1;
+            const int64_t src = ((int64_t)item->b * p.num_kv_heads + item->kvh) * D;
+            const int64_t plane = rows_per_plane * D;           // elements of one plane of a page
+            // element offset of (layer, page, K plane, kv head, slot of the token, 0)
+            const int64_t krow = ((int64_t)(layer_page0 + page) * 2) * plane + ((int64_t)item->kvh * p.page_size + pos % p.page_size) * D;
+            fused_append_prepare<T, D>(reinterpret_cast<const T*>(p.k_new) + src, reinterpret_cast<const T*>(p.v_new) + src,
+                                       page >= 0 ? reinterpret_cast<T*>(p.pool) + krow : nullptr, plane, p.inv_freq, p.rotary_dim,
+                                       &s_new_kv[SPLIT ? 0 : w][0], pos, lane);
+        }
         if (!(meta.flags & SLOT_SKIP)) {
             // keys [v_lo, v_hi) of the 16 in the slot are visible: all of them except in an item's end groups
             int v_lo = 0, v_hi = kGroupTokens;
@@ -545,6 +610,19 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             }
             uint8_t* kt = smem + ring * SLOT_BYTES;
             uint8_t* vt = kt + TILE_BYTES;              // SPLIT: set once the V entry has landed
+            if (!SPLIT && (meta.flags & SLOT_LAST) && item->append) {
+                // the last key of the item is the sequence's new token: its rows come from the warp's staging area
+                // (see fused_append_prepare), whatever the gather found at that slot of the page
+                const int row = item->tok_hi - 1 - meta.tok0;
+                const uint8_t* stage = &s_new_kv[SPLIT ? 0 : w][0];
+                for (int c = lane; c < 2 * (D / 8); c += 32) {
+                    const int pl = c / (D / 8), cc = c - pl * (D / 8);
+                    *reinterpret_cast<Vec16*>((pl ? vt : kt) + swz_seg16(row, cc)) =
+                        *reinterpret_cast<const Vec16*>(stage + pl * (D * 2) + 16 * cc);
+                }
+                __syncwarp();
+                zero_filled = true;                     // generic-proxy writes to the slot: fence before its next gather
+            }
             auto zero_hidden_rows = [&]() {
                 if (v_hi < kGroupTokens || v_lo > 0) {
                     // Slots outside the visible range may hold anything (stale pages): give the
@@ -726,7 +804,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
 
     // lengths and plan arrays are older than the kernel in front (see attend_decode_kernel): the slot arithmetic
     // runs under its tail, the partials are read after the wait
-    const int kv_end = p.kv_len != nullptr ? p.kv_len[b] : p.kv_end;
+    const int kv_end = p.kv_len != nullptr ? p.kv_len[b] : p.kv_end + b * p.kv_step;
     const int base = (p.kv_begin / kGroupTokens) * kGroupTokens;
     int nch = kv_end > base ? (kv_end - base + p.chunk_tokens - 1) / p.chunk_tokens : 0;
     nch = min(nch, p.max_chunks);

@@ -623,18 +623,39 @@ int drkv_sync_tables(drkv_engine* e, void* stream_) {
     int32_t* stage = e->h_stage[b];
     size_t off = 0;
     const int width = e->book.row_width();
-    for (const DirtyRange& r : dirty) {
-        // A released slot has no Seq to read from any more: its row is all -1.
-        const PageBook::Seq* s = e->book.seq(r.row);
-        const int n = r.hi - r.lo;
-        if (s)
-            memcpy(stage + off, s->table.data() + r.lo, (size_t)n * 4);
-        else
-            memset(stage + off, 0xFF, (size_t)n * 4);
-        CUDA_TRY(cudaMemcpyAsync(e->d_tables + (size_t)r.row * width + r.lo, stage + off, (size_t)n * 4,
-                                 cudaMemcpyHostToDevice, stream));
-        off += n;
-        e->sync_bytes += (int64_t)n * 4;
+    // Many changed rows (a wave of sequences released and another admitted): one copy of the whole rows from the
+    // first to the last changed one costs less than a copy per row, each of which is a few microseconds of stream
+    // time whatever its size.  Unchanged entries in between are re-sent with their current values.
+    long dirty_ints = 0;
+    for (const DirtyRange& r : dirty) dirty_ints += r.hi - r.lo;
+    const int row_lo = dirty.front().row, row_hi = dirty.back().row;      // take_dirty lists rows in ascending order
+    const long span_ints = (long)(row_hi - row_lo + 1) * width;
+    if (dirty.size() > 4 && span_ints <= 8 * dirty_ints && (size_t)span_ints <= e->stage_ints) {
+        for (int row = row_lo; row <= row_hi; row++) {
+            const PageBook::Seq* s = e->book.seq(row);       // a released slot has no Seq any more: all -1
+            if (s)
+                memcpy(stage + off, s->table.data(), (size_t)width * 4);
+            else
+                memset(stage + off, 0xFF, (size_t)width * 4);
+            off += width;
+        }
+        CUDA_TRY(cudaMemcpyAsync(e->d_tables + (size_t)row_lo * width, stage, (size_t)span_ints * 4, cudaMemcpyHostToDevice,
+                                 stream));
+        e->sync_bytes += span_ints * 4;
+    } else {
+        for (const DirtyRange& r : dirty) {
+            // A released slot has no Seq to read from any more: its row is all -1.
+            const PageBook::Seq* s = e->book.seq(r.row);
+            const int n = r.hi - r.lo;
+            if (s)
+                memcpy(stage + off, s->table.data() + r.lo, (size_t)n * 4);
+            else
+                memset(stage + off, 0xFF, (size_t)n * 4);
+            CUDA_TRY(cudaMemcpyAsync(e->d_tables + (size_t)r.row * width + r.lo, stage + off, (size_t)n * 4,
+                                     cudaMemcpyHostToDevice, stream));
+            off += n;
+            e->sync_bytes += (int64_t)n * 4;
+        }
     }
     CUDA_TRY(cudaEventRecord(e->stage_done[b], stream));
     e->stage_busy[b] = true;
@@ -777,7 +798,8 @@ int drkv_seq_inject(drkv_engine* e, int seq, int start_token, int num_tokens, co
 static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows, const int32_t* d_kv_len,
                          int row, int kv_begin, int kv_end, int max_span, const void* q, void* out,
                          float* out_partial, float scale, cudaStream_t stream,
-                         const drkv_engine::Plan* plan = nullptr, const ExchangeParams* xchg = nullptr) {
+                         const drkv_engine::Plan* plan = nullptr, const ExchangeParams* xchg = nullptr,
+                         int kv_step = 0, const void* k_new = nullptr, const void* v_new = nullptr) {
     const drkv_geometry& g = e->geom;
     note_stream(e, stream);
     int chunk = 0;
@@ -829,6 +851,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     p.row = row;
     p.kv_begin = kv_begin;
     p.kv_end = kv_end;
+    p.kv_step = kv_step;
     p.q = q;
     p.part_o = e->d_scratch;
     p.part_m = e->d_scratch + n_slots * g.head_dim;
@@ -864,6 +887,13 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     p.exit_count = e->d_exit;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.error_word = e->d_error;
+    if (k_new != nullptr) {                 // fused append of each entry's new token (see DecodeParams)
+        p.k_new = k_new;
+        p.v_new = v_new;
+        p.pool = e->pool;
+        p.inv_freq = e->d_inv_freq;
+        p.rotary_dim = g.rotary_dim;
+    }
     const bool timed = e->timing && e->tev_used + 2 <= e->tev.size();
     if (timed) CUDA_TRY(cudaEventRecord(e->tev[e->tev_used], stream));
     CUDA_TRY(launch_attend_decode(e->tmap_slot, p, e->num_sms, g.head_dim, g.dtype, stream));
@@ -879,6 +909,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     c.kv_len = d_kv_len;
     c.kv_begin = kv_begin;
     c.kv_end = kv_end;
+    c.kv_step = kv_step;
     c.num_q_heads = g.num_q_heads;
     c.head_dim = g.head_dim;
     c.chunk_tokens = chunk;
@@ -922,6 +953,44 @@ int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_ro
         int rc = decode_common(e, layer, n, d_rows + s0, d_kv_len + s0, 0, 0, 0, max_kv_len,
                                (const char*)q + s0 * row_bytes, (char*)out + s0 * row_bytes, nullptr, scale,
                                (cudaStream_t)stream);
+        if (rc != DRKV_OK) return rc;
+    }
+    return DRKV_OK;
+}
+
+// Head dim 256 keeps K and V of a group in separate ring entries of the decode kernel; there the new token goes
+// through the append kernel first (same bytes, one more launch).
+static bool fused_append_supported(const drkv_engine* e) { return e->geom.head_dim != 256; }
+
+int drkv_append_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows, const int32_t* d_kv_len,
+                              int max_kv_len, const void* k_src, const void* v_src, const void* q, void* out, float scale,
+                              void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (layer < 0 || layer >= e->geom.num_layers || n_seq < 0 || !d_rows || !d_kv_len || !k_src || !v_src || !q || !out ||
+        max_kv_len < 0)
+        return set_err(DRKV_ERR_INVALID, "append_attend_decode: bad argument");
+    if (n_seq == 0 || max_kv_len == 0) return DRKV_OK;
+    const bool fused = fused_append_supported(e);
+    if (!fused) {
+        note_stream(e, (cudaStream_t)stream);
+        AppendParams ap = append_params(e, layer);
+        ap.rows = d_rows;
+        ap.pos = d_kv_len;
+        ap.pos_bias = -1;                   // the new token sits at kv_len - 1
+        ap.k_src = k_src;
+        ap.v_src = v_src;
+        CUDA_TRY(launch_append_rope(ap, n_seq, e->geom.dtype, (cudaStream_t)stream));
+    }
+    const size_t q_bytes = (size_t)e->geom.num_q_heads * e->geom.head_dim * 2;
+    const size_t kv_bytes = (size_t)e->geom.num_kv_heads * e->geom.head_dim * 2;
+    for (int s0 = 0; s0 < n_seq; s0 += kMaxDecodeSeqs) {
+        const int n = n_seq - s0 < kMaxDecodeSeqs ? n_seq - s0 : kMaxDecodeSeqs;
+        int rc = decode_common(e, layer, n, d_rows + s0, d_kv_len + s0, 0, 0, 0, max_kv_len,
+                               (const char*)q + s0 * q_bytes, (char*)out + s0 * q_bytes, nullptr, scale,
+                               (cudaStream_t)stream, nullptr, nullptr, 0,
+                               fused ? (const char*)k_src + s0 * kv_bytes : nullptr,
+                               fused ? (const char*)v_src + s0 * kv_bytes : nullptr);
         if (rc != DRKV_OK) return rc;
     }
     return DRKV_OK;
@@ -1323,8 +1392,23 @@ int drkv_exchange_destroy(drkv_engine* e) {
     return DRKV_OK;
 }
 
+static int attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end, const void* k_src,
+                           const void* v_src, const void* q, void* out, float scale, void* stream);
+
 int drkv_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end, const void* q, void* out,
                          float scale, void* stream) {
+    return attend_exchange(e, layer, seq, kv_begin, kv_end, nullptr, nullptr, q, out, scale, stream);
+}
+
+int drkv_append_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end, const void* k_src,
+                                const void* v_src, const void* q, void* out, float scale, void* stream) {
+    if ((k_src == nullptr) != (v_src == nullptr))
+        return set_err(DRKV_ERR_INVALID, "append_attend_exchange: k_src and v_src come together");
+    return attend_exchange(e, layer, seq, kv_begin, kv_end, k_src, v_src, q, out, scale, stream);
+}
+
+static int attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end, const void* k_src,
+                           const void* v_src, const void* q, void* out, float scale, void* stream) {
     NEED(e);
     NEED_DEVICE(e);
     drkv_engine::Exchange& x = e->xchg;
@@ -1344,9 +1428,23 @@ int drkv_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int k
     p.seq_no = ++x.seq_no;
     p.parity = (int)(p.seq_no & 1u);
     p.error_word = e->d_error;
+    if (k_src != nullptr && (kv_end <= kv_begin || !fused_append_supported(e))) {
+        // nothing of this rank's range to attend, or head dim 256: the token goes through the append kernel
+        if (kv_end < 1) return set_err(DRKV_ERR_INVALID, "append_attend_exchange: no position to append at");
+        note_stream(e, (cudaStream_t)stream);
+        AppendParams ap = append_params(e, layer);
+        ap.rows = nullptr;
+        ap.pos = nullptr;
+        ap.row = seq;
+        ap.pos_start = kv_end - 1;
+        ap.k_src = k_src;
+        ap.v_src = v_src;
+        CUDA_TRY(launch_append_rope(ap, 1, e->geom.dtype, (cudaStream_t)stream));
+        k_src = v_src = nullptr;
+    }
     // the merge kernel's CTA of head h exchanges that head with the peers and writes the final output
     return decode_common(e, layer, 1, nullptr, nullptr, seq, kv_begin, kv_end, span, q, out, nullptr, scale,
-                         (cudaStream_t)stream, nullptr, &p);
+                         (cudaStream_t)stream, nullptr, &p, 0, k_src, v_src);
 }
 
 int drkv_combine_partials(drkv_engine* e, int n_parts, const float* parts, void* out, void* stream) {
@@ -1362,6 +1460,24 @@ size_t drkv_partial_floats(const drkv_engine* e) {
     return e ? (size_t)e->geom.num_q_heads * (e->geom.head_dim + 2) : 0;
 }
 
+// Prefill attention for head dims the tensor-core kernel is not built for (64, 256): the causal rule "token t sees
+// keys [0, pos_start + t]" (paged_attention.cu:465-554) is a batch of m one-token decodes over one block table, which
+// the split-KV decode kernel runs as it stands: batch entry t reads the same table row and sees pos_start + t + 1
+// keys (kv_step = 1), the query rows of a GQA group share each K/V tile, every token re-reads the keys (mostly from
+// L2).  Same arithmetic as decode attention; q/out are [m][Hq][D] in both.
+static int prefill_by_decode(drkv_engine* e, int layer, int seq, int pos_start, int m, const void* q, void* out,
+                             float scale, cudaStream_t stream) {
+    const size_t row_bytes = (size_t)e->geom.num_q_heads * e->geom.head_dim * 2;
+    for (int t0 = 0; t0 < m; t0 += kMaxDecodeSeqs) {
+        const int n = m - t0 < kMaxDecodeSeqs ? m - t0 : kMaxDecodeSeqs;
+        int rc = decode_common(e, layer, n, nullptr, nullptr, seq, 0, pos_start + t0 + 1, pos_start + t0 + n,
+                               (const char*)q + t0 * row_bytes, (char*)out + t0 * row_bytes, nullptr, scale, stream,
+                               nullptr, nullptr, /*kv_step=*/1);
+        if (rc != DRKV_OK) return rc;
+    }
+    return DRKV_OK;
+}
+
 int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_t* seqs, const int32_t* pos_start,
                               const int32_t* m, const void* const* q, void* const* out, float scale, void* stream) {
     NEED(e);
@@ -1369,11 +1485,19 @@ int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_
     const drkv_geometry& g = e->geom;
     if (layer < 0 || layer >= g.num_layers || n_seq < 0 || !seqs || !pos_start || !m || !q || !out)
         return set_err(DRKV_ERR_INVALID, "attend_prefill: bad argument");
-    if (g.head_dim != 128)
-        return set_err(DRKV_ERR_INVALID, "attend_prefill: the tensor-core prefill kernel is built for head_dim 128");
     for (int i = 0; i < n_seq; i++)
         if (seqs[i] < 0 || seqs[i] >= e->book.max_seqs() || pos_start[i] < 0 || m[i] < 0 || (m[i] > 0 && (!q[i] || !out[i])))
             return set_err(DRKV_ERR_INVALID, "attend_prefill: bad sequence entry %d", i);
+    if (g.head_dim != 128) {
+        // the tcgen05 kernel is built for head_dim 128; the other head dims take the split-KV decode kernel
+        note_stream(e, (cudaStream_t)stream);
+        for (int i = 0; i < n_seq; i++) {
+            if (m[i] == 0) continue;
+            int rc = prefill_by_decode(e, layer, seqs[i], pos_start[i], m[i], q[i], out[i], scale, (cudaStream_t)stream);
+            if (rc != DRKV_OK) return rc;
+        }
+        return DRKV_OK;
+    }
     for (int s0 = 0; s0 < n_seq; s0 += kMaxPrefillSeqs) {
         PrefillParams p{};
         p.tables = e->d_tables;

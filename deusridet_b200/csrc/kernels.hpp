@@ -16,6 +16,7 @@ struct AppendParams {
     int table_stride;
     const int32_t* rows;     // per token table row, or nullptr: all tokens use `row`
     const int32_t* pos;      // per token position (rows != nullptr) or one device int (rows == nullptr)
+    int pos_bias;            // added to every position read from `pos` (-1: `pos` holds lengths that include the token)
     int row, pos_start;      // used when rows == nullptr (pos_start only if pos == nullptr)
     int layer;
     int rotary_dim;          // 0 = plain copy
@@ -45,8 +46,9 @@ struct DecodeParams {
     const int32_t* tables;
     int table_stride;
     const int32_t* rows;      // [n_seq] table row per batch entry, nullptr = `row` for all
-    const int32_t* kv_len;    // [n_seq] keys visible, nullptr = `kv_end`
+    const int32_t* kv_len;    // [n_seq] keys visible, nullptr = `kv_end` + batch index * `kv_step`
     int row, kv_begin, kv_end;
+    int kv_step;              // kv_len == nullptr: entry b sees kv_end + b * kv_step keys (1: the tokens of a prefill chunk)
     const void* q;            // [n_seq][Hq][D]
     float* part_o;            // [n_seq][Hq][max_chunks][D]   un-normalised
     float* part_m;            // [n_seq][Hq][max_chunks]      natural-log domain
@@ -71,6 +73,14 @@ struct DecodeParams {
     int* exit_count;          // device int, 0 at launch: warps that have left
     float scale_log2;         // scale * log2(e)
     int* error_word;
+    // Fused append (all null / 0: off): the new token of batch entry b, at position kv_len[b] - 1, comes from
+    // k_new / v_new [n_seq][Hkv][D] instead of the pool.  The work item that reaches that position rotates K,
+    // puts both rows into its shared-memory tile and writes them to the pool page (head dims 64 and 128).
+    const void* k_new;
+    const void* v_new;
+    void* pool;
+    const float* inv_freq;    // [rotary_dim / 2]
+    int rotary_dim;
 };
 
 // Chunked-prefill attention: for each of n_seq sequences, chunk tokens [0, m) at positions pos_start + t.
@@ -104,7 +114,7 @@ struct CombineParams {
     const float* part_m;
     const float* part_l;
     const int32_t* kv_len;    // [n_seq] or nullptr
-    int kv_begin, kv_end;
+    int kv_begin, kv_end, kv_step;        // as in DecodeParams
     int num_q_heads, head_dim, chunk_tokens, max_chunks;
     int tail_chunks, tail_split;          // as in DecodeParams
     const int32_t* seq_first_chunk;       // shared-prefix plan's first own chunk per sequence, or nullptr

@@ -161,6 +161,10 @@ class PagedKVEngine:
     def attend_decode(self, layer, n_seq, d_rows, d_kv_len, max_kv_len, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_decode(self.h, layer, n_seq, _ptr(d_rows), _ptr(d_kv_len), max_kv_len, _ptr(q),
                                           _ptr(out), scale, _stream(stream)))
+    def append_attend_decode(self, layer, n_seq, d_rows, d_kv_len, max_kv_len, k_src, v_src, q, out, scale, stream=None) -> None:
+        """Append of each entry's new token (at kv_len - 1) and decode attention over kv_len keys, one call."""
+        check(self.lib.drkv_append_attend_decode(self.h, layer, n_seq, _ptr(d_rows), _ptr(d_kv_len), max_kv_len,
+                                                 _ptr(k_src), _ptr(v_src), _ptr(q), _ptr(out), scale, _stream(stream)))
     def plan_decode(self, seqs, kv_len, stream=None) -> dict:
         """Shared-prefix plan for a decode batch (host lists); returns the plan's summary."""
         n = len(seqs)
@@ -241,6 +245,10 @@ class PagedKVEngine:
     def attend_exchange(self, layer, seq, kv_begin, kv_end, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_exchange(self.h, layer, seq, kv_begin, kv_end, _ptr(q), _ptr(out), scale,
                                             _stream(stream)))
+
+    def append_attend_exchange(self, layer, seq, kv_begin, kv_end, k_src, v_src, q, out, scale, stream=None) -> None:
+        check(self.lib.drkv_append_attend_exchange(self.h, layer, seq, kv_begin, kv_end, _ptr(k_src), _ptr(v_src),
+                                                   _ptr(q), _ptr(out), scale, _stream(stream)))
 
     def attend_partial(self, layer, seq, kv_begin, kv_end, q, part, scale, stream=None) -> None:
         check(self.lib.drkv_attend_partial(self.h, layer, seq, kv_begin, kv_end, _ptr(q), _ptr(part), scale,

@@ -223,6 +223,16 @@ DRKV_API int drkv_seq_inject(drkv_engine* e, int seq, int start_token, int num_t
 DRKV_API int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows,
                                 const int32_t* d_kv_len, int max_kv_len, const void* q, void* out,
                                 float scale, void* stream);
+/* The decode step of one layer in one call: paged_kv_cache_write + rope_kernel's K half + paged_gqa_decode_attention
+ * (paged_attention.cu:353-367 runs them as three launches).  d_kv_len[i] counts the new token: it is appended at
+ * position d_kv_len[i] - 1 of table row d_rows[i] from k_src / v_src [n_seq][num_kv_heads][head_dim] and attended
+ * to with the rest.  For head dims 64 and 128 there is no append launch: the work item of the attention kernel that
+ * reaches the new position rotates K, uses both rows from the caller's buffers and writes them into the page (the
+ * same bytes drkv_append_rope writes); head dim 256 runs the append kernel first.  A hole at the new position
+ * writes nothing, as in drkv_append_rope. */
+DRKV_API int drkv_append_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows,
+                                       const int32_t* d_kv_len, int max_kv_len, const void* k_src, const void* v_src,
+                                       const void* q, void* out, float scale, void* stream);
 /* Shared-prefix decode.  The reference's decode kernel (paged_attention.cu:179-282) walks every
  * sequence's whole block table, so branches forked from one prompt (CacheManager block tables that
  * start with the same page ids) each read the shared pages again.  A plan finds, among CONSECUTIVE
@@ -292,7 +302,9 @@ DRKV_API int drkv_scorer_sync(drkv_engine* e, void* stream);
 DRKV_API int drkv_scorer_scores(const drkv_engine* e, int seq, float* out, int cap);
 
 /* paged_prefill_attention_kernel (paged_attention.cu:465-554): q/out
- * [m][num_q_heads][head_dim]; token t attends keys 0..pos_start+t. */
+ * [m][num_q_heads][head_dim]; token t attends keys 0..pos_start+t.  head_dim 128 runs on the tensor-core
+ * (tcgen05) kernel; head_dim 64 and 256 (the reference model's own, block_pool.h:34-40) run the chunk as a
+ * batch of one-token decodes on the split-KV decode kernel: same results, every token re-reads its keys. */
 DRKV_API int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m,
                                        const void* q, void* out, float scale, void* stream);
 /* The same for several sequences in one launch (host arrays of n_seq entries; q[i] / out[i] are
@@ -321,6 +333,12 @@ DRKV_API int drkv_exchange_connect(drkv_engine* e, const uint8_t* handles /* [wo
 DRKV_API int drkv_exchange_destroy(drkv_engine* e);   /* after a host-side barrier: peers must be done */
 DRKV_API int drkv_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end,
                                   const void* q, void* out, float scale, void* stream);
+/* drkv_attend_exchange with the new token's append fused as in drkv_append_attend_decode: the rank whose range ends
+ * at the sequence's end (kv_end = length including the new token) passes the token's k_src / v_src
+ * [num_kv_heads][head_dim]; every other rank passes NULL for both. */
+DRKV_API int drkv_append_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end,
+                                         const void* k_src, const void* v_src, const void* q, void* out, float scale,
+                                         void* stream);
 /* contiguous_split_k_merge_kernel (asr_ops_attn.cu:88-108): merges n_parts partials laid
  * out as drkv_attend_partial writes them (parts[p] at p * (Hq*(D+2)) floats). */
 DRKV_API int drkv_combine_partials(drkv_engine* e, int n_parts, const float* parts, void* out,

@@ -11,7 +11,9 @@ TOL = 2e-3  # max-abs on attention outputs: fp16/bf16 out, fp32 accumulate
 
 
 def _decode_case(oracle, *, layers, hq, hkv, d, page, dtype, theta, lens, seed, pool_slack=1.1, rot=None,
-                 chunk=0, holes=0):
+                 chunk=0, holes=0, fused=False, holes_first_only=False):
+    """fused: the step goes through drkv_append_attend_decode (the new token is appended by the attention kernel's
+    own work item, or by the append kernel in front of it at head_dim 256) instead of the two separate calls."""
     import torch
     from deusridet_b200 import PagedKVEngine
 
@@ -41,10 +43,10 @@ def _decode_case(oracle, *, layers, hq, hkv, d, page, dtype, theta, lens, seed, 
         tables = np.stack([eng.table(s) for s in seqs])
         if holes:
             # evicted pages: the table entry becomes -1 and attention must skip it
-            for s in seqs:
+            for s in (seqs[:1] if holes_first_only else seqs):
                 eng.evict_blocks(s, holes)
             tables = np.stack([eng.table(s) for s in seqs])
-            assert (tables[:, :holes] == -1).all()
+            assert (tables[:1 if holes_first_only else None, :holes] == -1).all()
         eng.sync_block_table()
 
         # pool contents: N(0,1) everywhere (also in slots no sequence owns)
@@ -63,8 +65,12 @@ def _decode_case(oracle, *, layers, hq, hkv, d, page, dtype, theta, lens, seed, 
             q = H.randn_bits(rng, (n_seq, hq, d), dtype)
             out_dev = torch.full((n_seq, hq, d), 7.0, device="cuda",
                                  dtype=torch.float16 if dtype == ob.F16 else torch.bfloat16)
-            eng.append_rope(layer, n_seq, d_rows, d_pos, H.to_dev(k_new, dtype), H.to_dev(v_new, dtype))
-            eng.attend_decode(layer, n_seq, d_rows, d_len, int(pos.max()) + 1, H.to_dev(q, dtype), out_dev, scale)
+            if fused:
+                eng.append_attend_decode(layer, n_seq, d_rows, d_len, int(pos.max()) + 1, H.to_dev(k_new, dtype),
+                                         H.to_dev(v_new, dtype), H.to_dev(q, dtype), out_dev, scale)
+            else:
+                eng.append_rope(layer, n_seq, d_rows, d_pos, H.to_dev(k_new, dtype), H.to_dev(v_new, dtype))
+                eng.attend_decode(layer, n_seq, d_rows, d_len, int(pos.max()) + 1, H.to_dev(q, dtype), out_dev, scale)
             torch.cuda.synchronize()
             eng.check_kernels()
 
@@ -140,3 +146,52 @@ def test_decode_with_evicted_pages(drkv_lib, oracle):
     """Holes in the table (evicted pages) contribute nothing."""
     _decode_case(oracle, layers=1, hq=16, hkv=4, d=128, page=16, dtype=oracle.BF16, theta=1e4, lens=[600, 900],
                  seed=8, holes=3)
+
+
+# ---- the same step through the fused entry point: pool bytes and outputs must not change ----
+def test_fused_append_toy_fp16(drkv_lib, oracle):
+    _decode_case(oracle, layers=1, hq=16, hkv=4, d=128, page=16, dtype=oracle.F16, theta=1e4, lens=[512], seed=1,
+                 pool_slack=64 / 33, fused=True)
+
+
+def test_fused_append_batched_bf16_ragged(drkv_lib, oracle):
+    """Lengths around page and chunk boundaries: the new token is the first slot of a fresh page (16, 1024, 2048),
+    the last slot of one (15, 4095), the only key of its sequence (0)."""
+    _decode_case(oracle, layers=2, hq=32, hkv=8, d=128, page=16, dtype=oracle.BF16, theta=1e6,
+                 lens=[1024, 1531, 4095, 2048, 777, 3000, 0, 1, 15, 16, 17], seed=2, fused=True)
+
+
+@pytest.mark.parametrize("chunk", [16, 64, 2048])
+def test_fused_append_chunk_sizes(drkv_lib, oracle, chunk):
+    _decode_case(oracle, layers=2, hq=32, hkv=8, d=128, page=16, dtype=oracle.BF16, theta=1e6,
+                 lens=[1200, 63, 64, 65, 2500], seed=3, chunk=chunk, fused=True)
+
+
+def test_fused_append_deep_batch_with_tail_pieces(drkv_lib, oracle):
+    """A batch deep enough for 512-key items with the last chunk of every sequence in 64-key pieces: the piece
+    that ends the sequence does the append."""
+    lens = np.random.default_rng(9).integers(3600, 4400, size=64)
+    _decode_case(oracle, layers=1, hq=32, hkv=8, d=128, page=16, dtype=oracle.BF16, theta=1e6, lens=lens, seed=9,
+                 fused=True)
+
+
+def test_fused_append_group8_page64_partial_rotary(drkv_lib, oracle):
+    _decode_case(oracle, layers=1, hq=64, hkv=8, d=128, page=64, dtype=oracle.BF16, theta=1e6, lens=[3000, 64, 129],
+                 seed=4, rot=64, fused=True)
+
+
+def test_fused_append_head_dim_64(drkv_lib, oracle):
+    _decode_case(oracle, layers=1, hq=8, hkv=2, d=64, page=32, dtype=oracle.BF16, theta=1e4, lens=[500, 100], seed=7,
+                 fused=True)
+
+
+def test_fused_append_head_dim_256_takes_the_append_kernel(drkv_lib, oracle):
+    _decode_case(oracle, layers=1, hq=24, hkv=4, d=256, page=256, dtype=oracle.F16, theta=1e7, lens=[1000, 300],
+                 seed=6, rot=64, fused=True)
+
+
+def test_fused_append_into_a_hole_writes_nothing(drkv_lib, oracle):
+    """The first sequence's only page is evicted: its token has no page to go to, nothing is written and its output
+    rows stay as they were; the other sequence is unaffected."""
+    _decode_case(oracle, layers=1, hq=16, hkv=4, d=128, page=16, dtype=oracle.BF16, theta=1e4, lens=[5, 900], seed=10,
+                 holes=1, holes_first_only=True, fused=True)

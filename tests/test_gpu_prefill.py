@@ -94,6 +94,17 @@ def test_prefill_with_evicted_pages(drkv_lib, oracle):
                   holes=4)
 
 
+def test_prefill_reference_model_shape_head_dim_256(drkv_lib, oracle):
+    """24 query / 4 KV heads, head_dim 256, 256-key pages, partial rotary 64: the reference's own attention shape
+    (src/memoria/block_pool.h:34-40).  Head dims other than 128 run the chunk on the split-KV decode kernel."""
+    _prefill_case(oracle, layers=2, hq=24, hkv=4, page=256, dtype=oracle.F16, theta=1e7, chunks=[300, 77, 1], seed=27,
+                  d=256)
+
+
+def test_prefill_head_dim_64_bf16(drkv_lib, oracle):
+    _prefill_case(oracle, layers=1, hq=16, hkv=2, page=32, dtype=oracle.BF16, theta=1e4, chunks=[130, 260], seed=28, d=64)
+
+
 def test_prefill_batch_of_sequences(drkv_lib, oracle):
     """Three sequences at different depths and chunk lengths in one launch."""
     import torch
