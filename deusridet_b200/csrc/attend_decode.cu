@@ -1024,41 +1024,6 @@ extern "C" __attribute__((visibility("default"))) int drkv_debug_warp_trace(unsi
 }
 #endif
 
-bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages, int num_kv_heads,
-                          int page_size, int head_dim, const char** err) {
-    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static EncodeFn encode = nullptr;
-    if (encode == nullptr) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
-            fn == nullptr) {
-            if (err) *err = "cuTensorMapEncodeTiled is not available from this driver";
-            return false;
-        }
-        encode = reinterpret_cast<EncodeFn>(fn);
-    }
-    const uint64_t rows = (uint64_t)num_layers * max_pages * 2 * num_kv_heads * page_size;
-    if (rows >= (1ull << 31)) {
-        if (err) *err = "pool has more than 2^31 head rows: not addressable by one TMA descriptor";
-        return false;
-    }
-    cuuint64_t gdim[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
-    cuuint64_t gstride[1] = {(cuuint64_t)head_dim * 2};
-    cuuint32_t box[2] = {64, 16};
-    cuuint32_t estride[2] = {1, 1};
-    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(pool), gdim, gstride, box, estride,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        if (err) *err = "cuTensorMapEncodeTiled failed";
-        return false;
-    }
-    return true;
-}
-
 // Decode's descriptor: the pool as [plane offset 0/1][head row][64-dim half][64 elements], so that one box
 // of {64, D/64, 16, 2} brings 16 key rows of one head, all dims, K and V (the V plane of a page starts
 // num_kv_heads * page_size rows after its K plane).  The row dimension stops one plane short of the end so
@@ -1127,34 +1092,44 @@ bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layer
     return true;
 }
 
-// The prefill kernel's V descriptor for head_dim 128: [64-dim half (stride 128 B)][head row (stride 256 B)][64],
-// box {64, 16, 2}: one copy brings both halves of 16 value rows as [half][row][128 B], the MN-major layout
-// the PV MMA reads.  The half dimension has the smaller stride; a driver that refuses such a view makes the
-// caller keep two boxes per group.
-bool make_pool_vhalves_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages, int num_kv_heads,
-                                  int page_size, int head_dim, const char** err) {
+// The prefill kernel's descriptor for head_dim 128: the pool as
+//   [octet of 8 head rows (stride 2 KB)][plane K/V (stride Hkv * page rows)][64-dim half (stride 128 B)][row in octet (stride 256 B)][64 elements],
+// box {64, 8, 2, 2, 2}: one copy brings the K and the V rows of 16 keys of one head, all dims (8 KB), as sixteen 8-row
+// groups of 128 bytes ordered [octet][plane][half], 128-byte swizzle.  The 8-row groups of one (plane, half) are then
+// 4 KB apart over a whole block of keys, so a single MMA operand descriptor (one stride between 8-row groups) walks
+// them: K-major for K, MN-major for V.  The octet dimension stops one plane short of the end so that plane 1 stays
+// inside the pool.
+bool make_pool_kv16_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages, int num_kv_heads,
+                               int page_size, int head_dim, const char** err) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
-    if (head_dim != 128 || cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
-        fn == nullptr) {
-        if (err) *err = "no V-halves descriptor";
+    if (head_dim != 128) {
+        if (err) *err = "the tensor-core prefill kernel is built for head_dim 128";
+        return false;
+    }
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) {
+        if (err) *err = "cuTensorMapEncodeTiled is not available from this driver";
         return false;
     }
     EncodeFn encode = reinterpret_cast<EncodeFn>(fn);
-    const uint64_t rows = (uint64_t)num_layers * max_pages * 2 * num_kv_heads * page_size;
-    if (rows >= (1ull << 31)) return false;
-    cuuint64_t gdim[3] = {64, (cuuint64_t)rows, 2};
-    cuuint64_t gstride[2] = {(cuuint64_t)head_dim * 2, 128};
-    cuuint32_t box[3] = {64, 16, 2};
-    cuuint32_t estride[3] = {1, 1, 1};
-    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(pool), gdim, gstride, box, estride,
+    const uint64_t plane_rows = (uint64_t)num_kv_heads * page_size;
+    const uint64_t rows = (uint64_t)num_layers * max_pages * 2 * plane_rows;
+    if (rows >= (1ull << 31)) {
+        if (err) *err = "pool has more than 2^31 head rows: not addressable by one TMA descriptor";
+        return false;
+    }
+    cuuint64_t gdim[5] = {64, 8, 2, 2, (cuuint64_t)((rows - plane_rows) / 8)};
+    cuuint64_t gstride[4] = {(cuuint64_t)head_dim * 2, 128, (cuuint64_t)plane_rows * head_dim * 2, (cuuint64_t)8 * head_dim * 2};
+    cuuint32_t box[5] = {64, 8, 2, 2, 2};
+    cuuint32_t estride[5] = {1, 1, 1, 1, 1};
+    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 5, const_cast<void*>(pool), gdim, gstride, box, estride,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-        if (err) *err = "cuTensorMapEncodeTiled refused the V-halves view";
+        if (err) *err = "cuTensorMapEncodeTiled refused the 16-key K/V view of the pool";
         return false;
     }
     return true;

@@ -12,8 +12,10 @@
 // only by CTAs whose rows see at most 1024 keys, where single-term 16-bit weights would cost more
 // than the 2e-3 bound on rows dominated by a handful of keys.  One thread per tile
 // issues that tile's MMAs (a lone issuing thread is a serial stream of waits, instructions and
-// commits: two of them overlap), one warp issues the box loads of a key block from as many lanes as
-// there are boxes, eight softmax warps (four per tile, one row per thread) do the arithmetic; the
+// commits: two of them overlap), one warp issues the box loads of a key block (ONE 5-D box per 16 keys
+// brings their K and V rows, all dims: the issue rate of copy instructions, not HBM, bounds a producer that
+// sends twelve 2-4 KB boxes per block), eight softmax warps (four per tile, one row per thread) do the
+// arithmetic, the two warps that share a scheduler taking turns at the exponential unit; the
 // K/V block fetched by TMA is used by 256 query rows.  O stays in
 // TMEM across key blocks and is rescaled there only when a row's running maximum has grown by
 // more than 2^8 since the scale in use was chosen; the final division by l undoes the stale
@@ -40,7 +42,12 @@ constexpr int kPfMmaWarp = 9;
 constexpr int kPfThreads = 11 * 32;           // 8 softmax warps, TMA producer, one MMA issuer per tile
 constexpr int kPfTmemCols = 512;
 constexpr int kPfQBytes = 128 * kPfD * 2;      // one Q tile: [2 halves][128 rows][128 B]
-constexpr int kPfKBytes = kPfBlockN * kPfD * 2;   // K (or V) of one block: [2 halves][64 keys][128 B]
+constexpr int kPfKBytes = kPfBlockN * kPfD * 2;   // K (or V) bytes of one block
+// A stage holds a block as eight "octets" of 8 keys, each [K half 0][K half 1][V half 0][V half 1] x [8 rows][128 B]
+// (4 KB): the image of the 5-D box {64 elements, 8 rows, 2 halves, 2 planes, 2 octets} that brings 16 keys.  The
+// 8-row groups of any one (plane, half) are then 4 KB apart throughout the block, which is what one stride field
+// of an MMA operand descriptor can express.
+constexpr int kPfOctetBytes = 4096;
 constexpr int kPfLoTermMaxKeys = 1024;         // CTAs that see at most this many keys add the lo term of P
 constexpr int kPfMaxTableSlice = 4096;         // block-table entries staged in shared memory
 constexpr float kPfRescaleThreshold = 8.0f;    // log2 units
@@ -53,19 +60,21 @@ struct PfSmem {
     static constexpr int pages = kv + kPfStages * 2 * kPfKBytes;       // int[kPfMaxTableSlice]
     static constexpr int holes = pages + kPfMaxTableSlice * 4;         // int[kPfStages]
     static constexpr int bars = holes + 16;                            // uint64[...]
-    static constexpr int n_bars = 2 * kPfStages + 8;
+    static constexpr int n_bars = 2 * kPfStages + 8 + 8;
     static constexpr int tmem = bars + n_bars * 8;                     // uint32 holder
     static constexpr int total = tmem + 16;
 };
 
 // barrier indices
 enum { BAR_KV_FULL = 0, BAR_KV_EMPTY = kPfStages, BAR_S_READY = 2 * kPfStages, BAR_S_FREE = BAR_S_READY + 2,
-       BAR_P_READY = BAR_S_FREE + 2, BAR_O_READY = BAR_P_READY + 2 };
+       BAR_P_READY = BAR_S_FREE + 2, BAR_O_READY = BAR_P_READY + 2,
+       BAR_XU = BAR_O_READY + 2 };   // [warp of the tile 0..3][tile]: that warp may run its exponentials
 
 #ifdef DRKV_PF_TRACE
 // Debug build only: clock cycles the first softmax warp of each tile of CTA 0 spent per phase, summed over
 // the key blocks of the last launch: wait S, load S, math, wait O, store P; then the block count.
 __device__ long long g_pf_trace[2][6];
+__device__ long long g_pf_trace_xu[2][2];   // per tile: cycles waiting for the turn at the exponential unit, cycles in the exponential loop
 __device__ long long g_pf_trace_prod[4];  // producer lane 0: wait empty, set-up, issue, blocks
 __device__ long long g_pf_trace_mma[8];
 __device__ long long g_pf_trace_fine[4];
@@ -84,6 +93,10 @@ __device__ long long g_pf_trace_each[16];   // cycles per instruction of one QK 
 #ifndef DRKV_PF_POLY
 #define DRKV_PF_POLY 0
 #endif
+#ifndef DRKV_PF_XU_TURNS
+#define DRKV_PF_XU_TURNS 1
+#endif
+
 __device__ __forceinline__ float poly_exp2(float x) {
     x = fmaxf(x, -126.f);
     const float t = x + 12582912.f;                       // 1.5 * 2^23: the low mantissa bits hold round(x)
@@ -96,8 +109,7 @@ __device__ __forceinline__ float poly_exp2(float x) {
 
 template <typename T>
 __global__ void __launch_bounds__(kPfThreads, 1)
-attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_v,
-                      const __grid_constant__ PrefillParams p) {
+attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ PrefillParams p) {
     // one sequence of the batch per grid.z; sequences with fewer tiles than grid.x leave the extra CTAs idle
     const int p_m = p.m[blockIdx.z], p_pos_start = p.pos_start[blockIdx.z], p_row = p.row[blockIdx.z];
     if ((int)blockIdx.x * 2 * (128 / p.group) >= p_m) return;
@@ -139,9 +151,9 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             mbar_init(bars + 8 * (BAR_P_READY + x), 128);
             mbar_init(bars + 8 * (BAR_O_READY + x), 1);
         }
+        for (int i = 0; i < 8; i++) mbar_init(bars + 8 * (BAR_XU + i), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_v) : "memory");
     }
     if (warp == kPfMmaWarp) tmem_alloc(sbase + PfSmem::tmem, kPfTmemCols);
     pdl_wait();                                  // Q, the pool and the table may come from the preceding kernel
@@ -196,13 +208,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 break;
             }
             const long long b1 = PF_CLK();
-            uint8_t* kdst = smem + PfSmem::kv + s * 2 * kPfKBytes;
-            uint8_t* vdst = kdst + kPfKBytes;
-            // Box loads of a block of 4 groups of 16 keys.  K: one box per group and 64-dim half (the K-major
-            // operand layout keeps the halves 8 KB apart).  V: one box per group with the V-halves view
-            // ([half][16 rows][128 B] is exactly what the PV MMA of that group reads), else two like K.  Every
-            // box is issued by its own lane: a single thread needs ~135 cycles per load.
-            const bool vh = p.v_halves != 0;
+            uint8_t* stage = smem + PfSmem::kv + s * 2 * kPfKBytes;
+            // One box per group of 16 keys: K and V rows, both 64-dim halves (8 KB), issued by lanes 0..3.
             const int my_gi = lane & 3;
             int page = -1;
             {
@@ -222,12 +229,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 // nothing will be loaded there: give the MMAs zeros instead of stale shared memory
                 for (int g4 = 0; g4 < 4; g4++) {
                     if (!((holes >> g4) & 1)) continue;
-                    for (int i = lane; i < 2 * 2 * 16 * 8; i += 32) {       // K and V, 2 halves, 16 rows, 8 chunks
-                        const int ks = i >> 8, hh = (i >> 7) & 1, r = (i >> 3) & 15, c = i & 7;
-                        uint8_t* base = (ks && vh) ? vdst + g4 * 4096 + hh * 2048 + r * 128 + c * 16
-                                                   : (ks ? vdst : kdst) + hh * (kPfBlockN * 128) + (g4 * 16 + r) * 128 + c * 16;
-                        *reinterpret_cast<Vec16*>(base) = Vec16{{0u, 0u, 0u, 0u}};
-                    }
+                    for (int i = lane; i < 2 * kPfOctetBytes / 16; i += 32)
+                        *reinterpret_cast<Vec16*>(stage + g4 * 2 * kPfOctetBytes + 16 * i) = Vec16{{0u, 0u, 0u, 0u}};
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
@@ -238,21 +241,13 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 mbar_arrive_expect_tx(bars + 8 * (BAR_KV_FULL + s), bytes);
             }
             __syncwarp();
-            // box of this lane: 0..7 K (group, half); then V: 8..11 (group) with the halves view, else 8..15 (group, half)
-            const bool is_k = lane < 8;
-            const int gi = is_k ? (lane >> 1) : (vh ? lane - 8 : (lane - 8) >> 1);
-            const int h = lane & 1;
-            const bool active = lane < (vh ? 12 : 16);
-            const int bpage = __shfl_sync(0xffffffffu, page, gi & 3);
-            if (active && bpage >= 0) {
-                const int tok = (j * 4 + gi) * 16;
-                const int64_t row = (((int64_t)p.layer * p.max_pages + bpage) * 2 + (is_k ? 0 : 1)) * rows_per_plane +
+            if (lane < 4 && page >= 0) {
+                const int tok = (j * 4 + lane) * 16;
+                // K-plane row of the group's first key, in octets of 8 rows (a multiple of 8: pages hold multiples of 16)
+                const int64_t row = (((int64_t)p.layer * p.max_pages + page) * 2) * rows_per_plane +
                                     (int64_t)kvh * p.page_size + (tok % p.page_size);
-                if (is_k || !vh)
-                    tma_load_2d(smem_u32(is_k ? kdst : vdst) + h * (kPfBlockN * 128) + gi * 2048, &tmap, h * 64, (int)row,
-                                bars + 8 * (BAR_KV_FULL + s));
-                else
-                    tma_load_3d(smem_u32(vdst) + gi * 4096, &tmap_v, 0, (int)row, 0, bars + 8 * (BAR_KV_FULL + s));
+                tma_load_5d(smem_u32(stage) + lane * 2 * kPfOctetBytes, &tmap, 0, 0, 0, 0, (int)(row >> 3),
+                            bars + 8 * (BAR_KV_FULL + s));
             }
             pt[0] += b1 - b0; pt[1] += b2 - b1; pt[2] += PF_CLK() - b2;
         }
@@ -277,11 +272,12 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             // [0,14)): one add per MMA.  Between two MMAs the issuing thread executes nothing else: a run-time
             // predicate or branch per instruction costs this lone thread 20-80 cycles, more than the 32-64
             // cycles of tensor work an instruction carries.
-            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);     // SBO 1024, version 1, 128-byte swizzle
+            constexpr uint32_t kDescHiQ = (1024u >> 4) | (1u << 14) | (2u << 29);    // Q: 8-row groups 1 KB apart, version 1, 128-byte swizzle
+            constexpr uint32_t kDescHi = ((uint32_t)kPfOctetBytes >> 4) | (1u << 14) | (2u << 29);   // K, V: 8-row groups one octet apart
             constexpr uint32_t kLboK = (16u >> 4) << 16;                            // K-major operands
-            // V, MN-major: the next 64-dim run is 8 KB on with two boxes per group, 2 KB with the halves view
-            const uint32_t kLboV = (p.v_halves ? (2048u >> 4) : ((uint32_t)(kPfBlockN * 128) >> 4)) << 16;
-            const uint32_t v_step = p.v_halves ? (4096u >> 4) : (2048u >> 4);        // from one group of 16 keys to the next
+            // V, MN-major: the next 64-dim run (the other half) is 1 KB on; 16 keys = two octets
+            constexpr uint32_t kLboV = (1024u >> 4) << 16;
+            constexpr uint32_t v_step = (2u * kPfOctetBytes) >> 4;                   // from one group of 16 keys to the next
             auto mk = [](uint32_t lo, uint32_t hi) -> uint64_t { return ((uint64_t)hi << 32) | lo; };
             const uint32_t qa = ((((sbase + PfSmem::q) & 0x3FFFFu) >> 4) | kLboK) + x * (kPfQBytes >> 4);
             const uint32_t kv_lo0 = ((sbase + PfSmem::kv) & 0x3FFFFu) >> 4;
@@ -294,8 +290,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
 #pragma unroll
                 for (int kk = 0; kk < kPfD / 16; kk++) {
                     const uint32_t off_q = ((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4;
-                    const uint32_t off_k = ((kk >> 2) * (kPfBlockN * 128) + (kk & 3) * 32) >> 4;
-                    umma_f16(d_s, mk(qa + off_q, kDescHi), mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
+                    const uint32_t off_k = ((kk >> 2) * 1024 + (kk & 3) * 32) >> 4;     // half, then 16 dims = 32 bytes
+                    umma_f16(d_s, mk(qa + off_q, kDescHiQ), mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
                 }
                 const long long f1 = PF_CLK();
                 umma_commit(bars + 8 * (BAR_S_READY + x));
@@ -303,7 +299,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             };
             auto issue_pv = [&](int s, bool first_block) {
                 const long long f0 = PF_CLK();
-                const uint32_t vb = (kv_lo0 + s * (2 * kPfKBytes >> 4) + (kPfKBytes >> 4)) | kLboV;
+                const uint32_t vb = (kv_lo0 + s * (2 * kPfKBytes >> 4) + (2048u >> 4)) | kLboV;   // V half 0 of octet 0
                 const uint32_t acc0 = first_block ? 0u : 1u;
                 if (!use_lo) {
                     umma_f16_ts(d_o, pa, mk(vb, kDescHi), idesc_pv, acc0);
@@ -379,7 +375,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             const uint32_t t_p = tmem_base + lane_base + kPfColP + x * 64;
             float m_used = kNegBigPf, l = 0.f;
             bool dead = false;
-            long long ph[5] = {0, 0, 0, 0, 0};
+            const bool xu_turns = tile_b_active && DRKV_PF_XU_TURNS;
+            long long ph[5] = {0, 0, 0, 0, 0}, xu[2] = {0, 0};
             for (int j = 0; j < n_blocks; j++) {
                 const long long c0 = PF_CLK();
                 if (!mbar_wait(bars + 8 * (BAR_S_READY + x), j & 1)) { dead = true; break; }
@@ -425,6 +422,17 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                     m_used = mx;
                     need = j > 0;
                 }
+                // The exponential unit delivers 16 results per clock and SM, which makes a block's exponentials as
+                // long as its MMAs; warp k of tile 0 and warp k of tile 1 share a scheduler and its quarter of that
+                // unit.  Left alone, both run their exponentials at the same time, each at half rate, and then leave
+                // the unit idle together while they load, take maxima and store.  They take turns instead: a warp
+                // starts its exponentials when its partner has finished the partner's, so that one's loads, maxima
+                // and stores run under the other's exponentials.
+                const long long x0c = PF_CLK();
+                if (xu_turns) {
+                    if (!mbar_wait(bars + 8 * (BAR_XU + 2 * (warp & 3) + x), (uint32_t)((j & 1) ^ (x ^ 1)))) { dead = true; break; }
+                }
+                const long long x1c = PF_CLK();
                 // p = 2^(s * scale_log2 - m): one FMA and one EX2 per score
                 const float neg_m = -m_used;
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};                    // independent partial sums
@@ -462,7 +470,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                         for (int c = 0; c < 32; c += 2) {
                             float a0, a1;
                             unpack_f32x2(fma_f32x2(pack_f32x2(sv[h][c], sv[h][c + 1]), scale2, negm2), a0, a1);
-                            const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+                            const float p0 = fast_exp2_ordered(a0), p1 = fast_exp2_ordered(a1);
                             sum2[(c >> 1) & 3] = add_f32x2(sum2[(c >> 1) & 3], pack_f32x2(p0, p1));
                             phi[h * 16 + (c >> 1)] = Elem<T>::pack2(p0, p1);
                         }
@@ -477,8 +485,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                     for (int h = 0; h < 2; h++)
 #pragma unroll
                         for (int c = 0; c < 32; c += 2) {
-                            const float p0 = fast_exp2(fmaf(sv[h][c], p.scale_log2, neg_m));
-                            const float p1 = fast_exp2(fmaf(sv[h][c + 1], p.scale_log2, neg_m));
+                            const float p0 = fast_exp2_ordered(fmaf(sv[h][c], p.scale_log2, neg_m));
+                            const float p1 = fast_exp2_ordered(fmaf(sv[h][c + 1], p.scale_log2, neg_m));
                             sum4[(c >> 1) & 3] += p0 + p1;
                             const uint32_t hi = Elem<T>::pack2(p0, p1);
                             const float2 hf = Elem<T>::unpack2(hi);
@@ -486,6 +494,11 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                             plo[h * 16 + (c >> 1)] = Elem<T>::pack2(p0 - hf.x, p1 - hf.y);
                         }
                 }
+                if (xu_turns) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bars + 8 * (BAR_XU + 2 * (warp & 3) + (x ^ 1)));   // the partner's turn
+                }
+                xu[0] += x1c - x0c; xu[1] += PF_CLK() - x1c;
                 l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
                 const long long c3 = PF_CLK();
                 if (j > 0) {
@@ -519,6 +532,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp & 3) == 0 && lane == 0) {
                 for (int i = 0; i < 5; i++) g_pf_trace[x][i] = ph[i];
                 g_pf_trace[x][5] = n_blocks;
+                g_pf_trace_xu[x][0] = xu[0];
+                g_pf_trace_xu[x][1] = xu[1];
             }
 #endif
             if (!dead && !mbar_wait(bars + 8 * (BAR_O_READY + x), (n_blocks - 1) & 1)) dead = true;
@@ -565,15 +580,13 @@ extern "C" __attribute__((visibility("default"))) int drkv_debug_prefill_trace(l
     if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 20, g_pf_trace_prod, sizeof(g_pf_trace_prod));
     if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 24, g_pf_trace_fine, sizeof(g_pf_trace_fine));
     if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 28, g_pf_trace_each, sizeof(g_pf_trace_each));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 44, g_pf_trace_xu, sizeof(g_pf_trace_xu));
     return (int)e;
 }
 #endif
 
-cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const CUtensorMap* tmap_v, const PrefillParams& p_in,
-                                  int head_dim, int dtype, cudaStream_t stream) {
-    PrefillParams p = p_in;
-    p.v_halves = tmap_v != nullptr ? 1 : 0;
-    const CUtensorMap& tv = tmap_v != nullptr ? *tmap_v : tmap;
+cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
+                                  cudaStream_t stream) {
     if (p.n_seq <= 0) return cudaSuccess;
     if (head_dim != kPfD || p.group < 1 || p.group > 16 || p.page_size % 16 != 0) return cudaErrorInvalidValue;
     constexpr size_t smem = 1024 + PfSmem::total;
@@ -593,8 +606,8 @@ cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const CUtensorMap* tm
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[ti][dev].store(true, std::memory_order_release);
     }
-    if (ti == 0) return launch_pdl(attend_prefill_kernel<__half>, grid, dim3(kPfThreads), smem, stream, tmap, tv, p);
-    return launch_pdl(attend_prefill_kernel<__nv_bfloat16>, grid, dim3(kPfThreads), smem, stream, tmap, tv, p);
+    if (ti == 0) return launch_pdl(attend_prefill_kernel<__half>, grid, dim3(kPfThreads), smem, stream, tmap, p);
+    return launch_pdl(attend_prefill_kernel<__nv_bfloat16>, grid, dim3(kPfThreads), smem, stream, tmap, p);
 }
 
 }  // namespace drkv

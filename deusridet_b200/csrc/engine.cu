@@ -115,9 +115,9 @@ struct drkv_engine {
     int* d_error = nullptr;
     float* d_scratch = nullptr;
     size_t scratch_bytes = 0;
-    CUtensorMap tmap{};        // 2-D view, 16-row x 64-element boxes: the prefill kernel's
-    CUtensorMap tmap_v{};      // 3-D view of both 64-dim halves of 16 rows: the prefill kernel's V loads (optional)
-    bool has_tmap_v = false;
+    CUtensorMap tmap_pf{};     // 5-D view, one box per 16 keys x 128 dims x (K, V): the prefill kernel's (head_dim 128)
+    bool has_tmap_pf = false;
+    std::string tmap_pf_err;
     CUtensorMap tmap_slot{};   // 4-D view, one box per 16 keys x head_dim x (K, V): the decode kernel's
     PoolLayout layout{};
     int forced_chunk = 0;
@@ -306,15 +306,12 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
         e->scratch_bytes = need < (64u << 20) ? (64u << 20) : need;
         if ((ce = cudaMalloc(&e->d_scratch, e->scratch_bytes)) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(scratch)", ce);
         const char* terr = nullptr;
-        if (!make_pool_tensor_map(&e->tmap, e->pool, geom->num_layers, (int)max_pages, geom->num_kv_heads,
-                                  geom->page_size, geom->head_dim, &terr)) {
-            set_err(DRKV_ERR_CUDA, "%s", terr ? terr : "tensor map");
-            drkv_destroy(e);
-            return DRKV_ERR_CUDA;
+        if (geom->head_dim == 128) {
+            const char* perr = nullptr;
+            e->has_tmap_pf = make_pool_kv16_tensor_map(&e->tmap_pf, e->pool, geom->num_layers, (int)max_pages,
+                                                       geom->num_kv_heads, geom->page_size, geom->head_dim, &perr);
+            if (!e->has_tmap_pf) e->tmap_pf_err = perr ? perr : "tensor map";   // reported by the first prefill call
         }
-        e->has_tmap_v = make_pool_vhalves_tensor_map(&e->tmap_v, e->pool, geom->num_layers, (int)max_pages, geom->num_kv_heads,
-                                                     geom->page_size, geom->head_dim, nullptr) &&
-                        getenv("DRKV_NO_VHALVES") == nullptr;
         if (!make_pool_slot_tensor_map(&e->tmap_slot, e->pool, geom->num_layers, (int)max_pages, geom->num_kv_heads,
                                        geom->page_size, geom->head_dim, &terr)) {
             set_err(DRKV_ERR_CUDA, "%s", terr ? terr : "tensor map");
@@ -1498,6 +1495,7 @@ int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_
         }
         return DRKV_OK;
     }
+    if (!e->has_tmap_pf) return set_err(DRKV_ERR_CUDA, "attend_prefill: %s", e->tmap_pf_err.c_str());
     for (int s0 = 0; s0 < n_seq; s0 += kMaxPrefillSeqs) {
         PrefillParams p{};
         p.tables = e->d_tables;
@@ -1518,8 +1516,7 @@ int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_
         p.page_size = g.page_size;
         p.scale_log2 = scale * 1.4426950408889634f;
         p.error_word = e->d_error;
-        CUDA_TRY(launch_attend_prefill(e->tmap, e->has_tmap_v ? &e->tmap_v : nullptr, p, g.head_dim, g.dtype,
-                                       (cudaStream_t)stream));
+        CUDA_TRY(launch_attend_prefill(e->tmap_pf, p, g.head_dim, g.dtype, (cudaStream_t)stream));
     }
     return DRKV_OK;
 }

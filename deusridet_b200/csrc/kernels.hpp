@@ -95,7 +95,6 @@ struct PrefillParams {
     int layer, max_pages, num_q_heads, num_kv_heads, group, page_size;
     float scale_log2;
     int* error_word;
-    int v_halves;             // set by the launcher: V comes through the V-halves view, one box per 16 keys
 };
 
 // Cross-GPU merge of one sequence's split-KV partials by peer stores, the tail of the merge kernel
@@ -142,11 +141,6 @@ cudaError_t launch_append_rope(const AppendParams& p, int n_tokens, int dtype, c
 cudaError_t launch_cow_copy(const CowParams& p, int num_layers, cudaStream_t stream);
 cudaError_t launch_flat_paged_copy(const FlatCopyParams& p, bool to_flat, int num_sms, cudaStream_t stream);
 
-// Builds the TMA descriptor of a pool: a 2-D tensor [rows][head_dim] of 2-byte elements with
-// a {64 x 16} box and 128-byte swizzle.  Returns false if the driver entry point is missing.
-bool make_pool_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
-                          int num_kv_heads, int page_size, int head_dim, const char** err);
-
 // The decode kernel's descriptor: 4-D view whose one box is 16 key rows x head_dim x (K, V).
 bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
                                int num_kv_heads, int page_size, int head_dim, const char** err);
@@ -155,11 +149,11 @@ cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p,
                                  int dtype, cudaStream_t stream);
 constexpr int kMaxDecodeSeqs = 2048;   // sequences one decode-attention launch can take
 int decode_warps_per_cta(int head_dim);  // warps of one decode CTA, each with its own queue of items
-bool make_pool_vhalves_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
-                                  int num_kv_heads, int page_size, int head_dim, const char** err);
-// tmap_v: the V-halves view, or nullptr (then V is loaded with the 2-D boxes of tmap as K is).
-cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const CUtensorMap* tmap_v, const PrefillParams& p, int head_dim,
-                                  int dtype,
+// The prefill kernel's descriptor (head_dim 128): 5-D view whose one box is 16 key rows x both 64-dim halves x (K, V),
+// landing in 8-row groups of 128 bytes ordered [octet of 8 keys][plane][half].
+bool make_pool_kv16_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
+                               int num_kv_heads, int page_size, int head_dim, const char** err);
+cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
                                   cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, int n_seq, int dtype, cudaStream_t stream);
 
