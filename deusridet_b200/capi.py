@@ -120,6 +120,9 @@ SIGNATURES = {
     "drkv_exchange_create": (_i, [_vp, _i, _i, C.POINTER(C.c_uint8)]),
     "drkv_exchange_connect": (_i, [_vp, C.POINTER(C.c_uint8)]),
     "drkv_exchange_destroy": (_i, [_vp]),
+    "drkv_exchange_connect_local": (_i, [_vp, C.POINTER(C.c_void_p)]),
+    "drkv_exchange_area": (_vp, [_vp]),
+    "drkv_exchange_set_wait_ms": (_i, [_vp, _i]),
     "drkv_attend_exchange": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_append_attend_exchange": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _vp]),
     "drkv_attend_partial": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
@@ -133,6 +136,10 @@ SIGNATURES = {
     "drkv_seq_inject": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "drkv_k_extract_kv": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _i, _i, _i, _vp]),
     "drkv_k_inject_kv": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "drkv_shard_page_range": (_i, [_i, _i, _i, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "drkv_shard_key_range": (_i, [_i, _i, _i, _i, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "drkv_shard_owner_of_position": (_i, [_i, _i, _i, _i]),
+    "drkv_shard_sequences": (_i, [_i, C.POINTER(C.c_int64), _pi32, _i, _pi32]),
     "drkv_k_decode_scratch_bytes": (_sz, [C.POINTER(Geometry), _i]),
     "drkv_k_decode_kernel_error": (_i, [_vp, _vp]),
     "drkv_k_decode_attention_noalloc": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),

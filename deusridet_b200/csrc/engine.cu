@@ -175,6 +175,8 @@ struct drkv_engine {
         size_t flags_offset = 0;
         void* peer_area[kMaxExchangeRanks] = {};     // every rank's area as mapped here (own = area)
         bool connected = false;
+        bool local = false;                          // peers' areas were given as pointers, not opened through IPC
+        unsigned long long wait_ns = 2000000000ull;  // bounded wait for a peer's flag
     } xchg;
 
     // storage tier behind the pool (off until drkv_tier_enable)
@@ -1332,9 +1334,11 @@ int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begin, int kv
 static void exchange_release(drkv_engine* e) {
     drkv_engine::Exchange& x = e->xchg;
     for (int r = 0; r < x.world; r++)
-        if (x.connected && r != x.rank && x.peer_area[r]) cudaIpcCloseMemHandle(x.peer_area[r]);
+        if (x.connected && !x.local && r != x.rank && x.peer_area[r]) cudaIpcCloseMemHandle(x.peer_area[r]);
     if (x.area) cudaFree(x.area);
+    const unsigned long long keep = x.wait_ns;
     x = drkv_engine::Exchange();
+    x.wait_ns = keep;
 }
 
 int drkv_exchange_create(drkv_engine* e, int world, int rank, uint8_t* handle_out) {
@@ -1376,6 +1380,31 @@ int drkv_exchange_connect(drkv_engine* e, const uint8_t* handles) {
         CUDA_TRY(cudaIpcOpenMemHandle(&x.peer_area[r], h, cudaIpcMemLazyEnablePeerAccess));
     }
     x.connected = true;
+    return DRKV_OK;
+}
+
+int drkv_exchange_connect_local(drkv_engine* e, void* const* areas) {
+    NEED(e);
+    NEED_DEVICE(e);
+    LOCK(e);
+    drkv_engine::Exchange& x = e->xchg;
+    if (x.world == 0 || !areas) return set_err(DRKV_ERR_STATE, "exchange_connect_local: no exchange area / null areas");
+    for (int r = 0; r < x.world; r++) {
+        if (r == x.rank) continue;
+        if (areas[r] == nullptr) return set_err(DRKV_ERR_INVALID, "exchange_connect_local: rank %d has no area", r);
+        x.peer_area[r] = areas[r];
+    }
+    x.connected = true;
+    x.local = true;
+    return DRKV_OK;
+}
+
+void* drkv_exchange_area(const drkv_engine* e) { return e ? e->xchg.area : nullptr; }
+
+int drkv_exchange_set_wait_ms(drkv_engine* e, int ms) {
+    NEED(e);
+    if (ms < 1 || ms > 60000) return set_err(DRKV_ERR_INVALID, "exchange wait limit: 1 .. 60000 ms");
+    e->xchg.wait_ns = (unsigned long long)ms * 1000000ull;
     return DRKV_OK;
 }
 
@@ -1424,6 +1453,7 @@ static int attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int
     p.rank = x.rank;
     p.seq_no = ++x.seq_no;
     p.parity = (int)(p.seq_no & 1u);
+    p.wait_ns = x.wait_ns;
     p.error_word = e->d_error;
     if (k_src != nullptr && (kv_end <= kv_begin || !fused_append_supported(e))) {
         // nothing of this rank's range to attend, or head dim 256: the token goes through the append kernel

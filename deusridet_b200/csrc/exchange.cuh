@@ -62,7 +62,7 @@ __device__ void exchange_and_merge(const ExchangeParams& x, int h, int hq, int D
         uint32_t spins = 0;
         // sequence numbers only grow; the signed difference copes with wrap-around
         while ((int32_t)(ld_acquire_sys(f) - x.seq_no) < 0) {
-            if ((++spins & 63u) == 0 && global_timer() - t0 > kWaitLimitNs) {
+            if ((++spins & 63u) == 0 && global_timer() - t0 > x.wait_ns) {
                 *s_ok = 0;
                 break;
             }

@@ -105,6 +105,7 @@ struct ExchangeParams {
     uint32_t* peer_flags[kMaxExchangeRanks];    // every rank's flag array
     int world, rank, parity;
     uint32_t seq_no;
+    unsigned long long wait_ns;                 // how long a rank waits for a peer's flag before it gives up
     int* error_word;
 };
 

@@ -241,6 +241,12 @@ class PagedKVEngine:
         blob = b"".join(handles)
         arr = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
         check(self.lib.drkv_exchange_connect(self.h, arr))
+    def exchange_connect_local(self, areas: Sequence[int]) -> None:
+        """Ranks in one process: every rank's exchange_area() as a device pointer."""
+        arr = (C.c_void_p * len(areas))(*[int(a) for a in areas])
+        check(self.lib.drkv_exchange_connect_local(self.h, arr))
+    def exchange_area(self) -> int: return self.lib.drkv_exchange_area(self.h) or 0
+    def exchange_set_wait_ms(self, ms: int) -> None: check(self.lib.drkv_exchange_set_wait_ms(self.h, ms))
     def exchange_destroy(self) -> None: check(self.lib.drkv_exchange_destroy(self.h))
     def attend_exchange(self, layer, seq, kv_begin, kv_end, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_exchange(self.h, layer, seq, kv_begin, kv_end, _ptr(q), _ptr(out), scale,

@@ -330,6 +330,12 @@ DRKV_API int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begi
 #define DRKV_IPC_HANDLE_BYTES 64
 DRKV_API int drkv_exchange_create(drkv_engine* e, int world, int rank, uint8_t* handle_out /* [64] */);
 DRKV_API int drkv_exchange_connect(drkv_engine* e, const uint8_t* handles /* [world][64] */);
+/* Ranks that live in ONE process (one engine per GPU, peer access enabled by the host) connect with plain device
+ * pointers instead of IPC handles: areas[r] = drkv_exchange_area() of rank r's engine. */
+DRKV_API int drkv_exchange_connect_local(drkv_engine* e, void* const* areas /* [world] */);
+DRKV_API void* drkv_exchange_area(const drkv_engine* e);
+/* How long the merge kernel waits for a peer's flag before it gives up with kernel error 4 (default 2000 ms). */
+DRKV_API int drkv_exchange_set_wait_ms(drkv_engine* e, int ms);
 DRKV_API int drkv_exchange_destroy(drkv_engine* e);   /* after a host-side barrier: peers must be done */
 DRKV_API int drkv_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end,
                                   const void* q, void* out, float scale, void* stream);
@@ -344,6 +350,18 @@ DRKV_API int drkv_append_attend_exchange(drkv_engine* e, int layer, int seq, int
 DRKV_API int drkv_combine_partials(drkv_engine* e, int n_parts, const float* parts, void* out,
                                    void* stream);
 DRKV_API size_t drkv_partial_floats(const drkv_engine* e);   /* Hq * (D + 2) */
+
+/* ---- partitioning across the GPUs of one box (one process per GPU) ---------------------------
+ * No counterpart in the reference, which is single-GPU.  One long sequence is split by contiguous page range:
+ * rank r owns pages [lo, hi) (sizes differ by at most one, earlier ranks take the larger shares), attends keys
+ * [begin, end) = that range clipped to the sequence, and the rank whose range holds a position appends it.
+ * Independent sequences are placed by greedy balance of their cost (context length), largest unit first;
+ * families[i] (NULL: none) groups forks that share pages: a family goes to one rank as a unit.
+ * rank_of[i] receives the rank of sequence i. */
+DRKV_API int drkv_shard_page_range(int n_pages, int rank, int world, int* lo, int* hi);
+DRKV_API int drkv_shard_key_range(int seq_len, int page_size, int rank, int world, int* begin, int* end);
+DRKV_API int drkv_shard_owner_of_position(int pos, int seq_len_after, int page_size, int world);   /* rank, or < 0 */
+DRKV_API int drkv_shard_sequences(int n, const int64_t* costs, const int32_t* families, int world, int32_t* rank_of);
 
 /* ---- stateless kernel entry points: the reference's free functions -------------------
  * Same argument meaning as src/machina/paged_attention.h:27-71 plus the geometry the

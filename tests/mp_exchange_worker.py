@@ -44,6 +44,7 @@ def main():
         handles = [None] * world
         dist.all_gather_object(handles, handle)
         eng.exchange_connect(handles)
+        eng.exchange_set_wait_ms(200)                    # a peer that stays away is given up on after 0.2 s
         dist.barrier()
         begin, end = sharding.key_range_for_rank(n_tok, page, rank, world)
         scale = 1.0 / np.sqrt(d)

@@ -97,3 +97,78 @@ def test_split_sequence_allgather_combine(oracle, world, seq_len):
     ob.attend_decode(g, pool, pages, table[None, :], [0], [seq_len], 0, q[None], whole, scale)
     got = ob.to_float(result.numpy().view(np.uint16), ob.BF16)
     assert np.abs(got - ob.to_float(whole[0], ob.BF16)).max() <= 2e-3
+
+
+def _rank_with_departure(rank, world, ports, seq_len, q_bits, pool, table, geom_args, scale, result, status):
+    """Step 0 with every rank; then the last rank leaves between steps (no collective in flight).  The survivors'
+    next gather must end with an error they can turn into a status, not hang; they re-form a smaller world,
+    re-split the page ranges over it and the step gives the whole-sequence answer again."""
+    import datetime
+    from oracle import cbind as ob
+    g = ob.geom(*geom_args)
+    pages = pool.size // (geom_args[0] * 2 * geom_args[2] * geom_args[4] * geom_args[3])
+
+    def step(r, w):
+        begin, end = sharding.key_range_for_rank(seq_len, geom_args[4], r, w)
+        mine = torch.from_numpy(ob.attend_partial(g, pool, pages, table, 0, begin, end, q_bits, scale))
+        gathered = [torch.empty_like(mine) for _ in range(w)]
+        dist.all_gather(gathered, mine)
+        out = np.zeros((geom_args[1], geom_args[3]), dtype=np.uint16)
+        ob.combine(g, np.stack([t.numpy() for t in gathered]), out)
+        return out
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{ports[0]}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=20))
+    first = step(rank, world)
+    if rank == 0:
+        result[0].copy_(torch.from_numpy(first.view(np.int16)))
+    dist.barrier()
+    if rank == world - 1:                    # leaves between steps, with none of its collectives in flight
+        dist.destroy_process_group()
+        return
+    lost = 0
+    try:
+        step(rank, world)
+    except Exception:                        # RuntimeError / DistBackendError: the peer is gone or the gather timed out
+        lost = 1
+    status[rank] = lost
+    try:
+        dist.destroy_process_group()
+    except Exception:
+        pass
+    survivors = world - 1
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{ports[1]}", rank=rank, world_size=survivors,
+                            timeout=datetime.timedelta(seconds=20))
+    again = step(rank, survivors)
+    if rank == 0:
+        result[1].copy_(torch.from_numpy(again.view(np.int16)))
+    dist.destroy_process_group()
+
+
+def test_rank_leaves_between_steps_and_the_world_is_reformed(oracle):
+    """Failure detection on the host, without a GPU: what is under test is the protocol around the collective
+    (an error status instead of a hang, re-partition by sharding.key_range_for_rank over the survivors, the same
+    answer afterwards).  Every rank holds the whole cache here; bringing a lost rank's pages back (storage tier,
+    re-prefill) is the caller's business."""
+    ob = oracle
+    rng = np.random.default_rng(77)
+    world, seq_len = 3, 900
+    layers, hq, hkv, d, page = 1, 8, 2, 128, 64
+    pages = (seq_len + page - 1) // page + 2
+    geom_args = (layers, hq, hkv, d, page, ob.BF16, d, 1e6)
+    g = ob.geom(*geom_args)
+    pool = ob.from_float(rng.standard_normal(ob.pool_elems(g, pages), dtype=np.float32), ob.BF16)
+    table = rng.permutation(pages).astype(np.int32)
+    q = ob.from_float(rng.standard_normal((hq, d), dtype=np.float32), ob.BF16)
+    scale = 1.0 / np.sqrt(d)
+    result = torch.zeros((2, hq, d), dtype=torch.int16).share_memory_()
+    status = torch.full((world,), -1, dtype=torch.int32).share_memory_()
+    mp.spawn(_rank_with_departure, args=(world, (_free_port(), _free_port()), seq_len, q, pool, table, geom_args, scale,
+                                         result, status), nprocs=world, join=True)
+    assert status[:world - 1].tolist() == [1] * (world - 1), "the survivors did not see the departure as an error"
+    whole = np.zeros((1, hq, d), dtype=np.uint16)
+    ob.attend_decode(g, pool, pages, table[None, :], [0], [seq_len], 0, q[None], whole, scale)
+    want = ob.to_float(whole[0], ob.BF16)
+    for k in range(2):                       # before the departure (3 ranks) and after it (2 ranks)
+        got = ob.to_float(result[k].numpy().view(np.uint16), ob.BF16)
+        assert np.abs(got - want).max() <= 2e-3, k
