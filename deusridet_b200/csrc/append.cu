@@ -25,6 +25,7 @@ append_rope_kernel(AppendParams p) {
     // than the one directly in front (which, when it belongs to this library, released this launch only after
     // its own wait): the angles and the page id are worked out under that kernel's tail.  The sources and
     // the pool are touched after the wait.
+    if (p.wait_first) pdl_wait();    // a foreign caller's kernel in front may have written the position or the table
     int row, pos;
     if (p.rows != nullptr) {
         row = p.rows[tok];

@@ -187,6 +187,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
     }
+    if (p.wait_first) pdl_wait();   // raw-pointer entry points: the table may come from the caller's kernel in front
     // What runs before pdl_wait() overlaps the tail of the preceding kernel.  That kernel may still be writing
     // the pool (an append), the query or the scratch; everything launched before it has completed, because a
     // kernel of this library releases its dependents only after its own wait, and any other kernel releases

@@ -20,6 +20,8 @@ struct AppendParams {
     int row, pos_start;      // used when rows == nullptr (pos_start only if pos == nullptr)
     int layer;
     int rotary_dim;          // 0 = plain copy
+    int wait_first;          // 1: read nothing before the programmatic-launch wait (positions and tables may come
+                             // from the caller's kernel directly in front: the raw-pointer entry points)
     const float* inv_freq;   // [rotary_dim / 2] device
     const void* k_src;
     const void* v_src;
@@ -73,6 +75,8 @@ struct DecodeParams {
     int* exit_count;          // device int, 0 at launch: warps that have left
     float scale_log2;         // scale * log2(e)
     int* error_word;
+    int wait_first;           // 1: read nothing before the programmatic-launch wait (raw-pointer entry points, whose
+                              // block table may be written by the caller's kernel directly in front)
     // Fused append (all null / 0: off): the new token of batch entry b, at position kv_len[b] - 1, comes from
     // k_new / v_new [n_seq][Hkv][D] instead of the pool.  The work item that reaches that position rotates K,
     // puts both rows into its shared-memory tile and writes them to the pool page (head dims 64 and 128).

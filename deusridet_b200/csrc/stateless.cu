@@ -98,6 +98,7 @@ int stateless_decode(const drkv_geometry* g, const void* q, const void* kv_pool,
     p.exit_count = header + 2;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.error_word = header + 1;
+    p.wait_first = 1;                  // the caller's own kernel may have written the table directly in front
     if (launch_attend_decode(tmap, p, num_sms, g->head_dim, g->dtype, stream) != cudaSuccess)
         return fail(DRKV_ERR_CUDA, "decode attention launch failed");
 
@@ -137,6 +138,7 @@ int drkv_k_cache_write(const drkv_geometry* g, const void* src_k, const void* sr
     p.row = 0;
     p.layer = layer;
     p.rotary_dim = 0;              // the reference rotates K before this call
+    p.wait_first = 1;              // d_pos and the table may come from the caller's kernel directly in front
     p.inv_freq = nullptr;
     p.k_src = src_k;
     p.v_src = src_v;
@@ -162,6 +164,7 @@ int drkv_k_cache_write_batch(const drkv_geometry* g, const void* src_k, const vo
     p.pos_start = pos_start;
     p.layer = layer;
     p.rotary_dim = 0;
+    p.wait_first = 1;
     p.inv_freq = nullptr;
     p.k_src = src_k;
     p.v_src = src_v;

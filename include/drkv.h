@@ -191,7 +191,10 @@ DRKV_API int drkv_kernel_timing(drkv_engine* e, int enable, double* total_ms, in
 /* paged_kv_cache_write + rope_kernel's K half (paged_attention.cu:73-115,
  * layer_attention.cu:32-69), batched over sequences: sequence i of the batch uses table
  * row d_rows[i] and writes its token at d_pos[i] (both device int32 arrays).
- * k_src/v_src: [n_seq][num_kv_heads][head_dim] device, storage type. */
+ * k_src/v_src: [n_seq][num_kv_heads][head_dim] device, storage type.
+ * As with drkv_attend_decode, d_rows, d_pos and the block table are read while the launch directly in
+ * front may still be running: a caller's kernel that writes them and signals programmatic completion
+ * early must not be that launch. */
 DRKV_API int drkv_append_rope(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows,
                               const int32_t* d_pos, const void* k_src, const void* v_src,
                               void* stream);
@@ -365,7 +368,10 @@ DRKV_API int drkv_shard_sequences(int n, const int64_t* costs, const int32_t* fa
 
 /* ---- stateless kernel entry points: the reference's free functions -------------------
  * Same argument meaning as src/machina/paged_attention.h:27-71 plus the geometry the
- * reference reads from ModelConfig statics.  One sequence, one table. */
+ * reference reads from ModelConfig statics.  One sequence, one table.  These kernels read nothing
+ * (positions, block table, sources) before every earlier launch on the stream has completed: a caller's
+ * own kernel may write d_pos or the table directly in front of them, as with the reference's launches.
+ * (The engine's batched calls above read lengths and tables early; see drkv_attend_decode.) */
 DRKV_API int drkv_k_cache_write(const drkv_geometry* g, const void* src_k, const void* src_v,
                                 void* kv_pool, const int32_t* d_block_table, int layer,
                                 const int32_t* d_pos, int max_pages, void* stream);

@@ -132,3 +132,40 @@ def test_kernel_error_word_of_the_stateless_path(drkv_lib, oracle):
         assert np.abs(got - ob.to_float(want, dtype)).max() <= 2e-3
         _, status = run(table, noalloc)                     # the next call starts clean
         assert status == 0, capi.last_error()
+
+
+def test_position_written_by_the_kernel_in_front(drkv_lib, oracle):
+    """The reference's decode loop uploads / computes d_pos right before paged_kv_cache_write
+    (src/conscientia/stream.cpp:304-309): the raw-pointer entry points read the position and the table only after
+    every earlier launch on the stream has completed.  A device kernel rewrites both directly in front of each call."""
+    import torch
+    from deusridet_b200 import capi
+
+    ob = oracle
+    layers, hq, hkv, d, page, dtype = 1, 8, 2, 128, 16, ob.BF16
+    rng = np.random.default_rng(15)
+    max_pages = 12
+    g = ob.geom(layers, hq, hkv, d, page, dtype, 0, 1e4)
+    cg = capi.Geometry(layers, hq, hkv, d, page, dtype, 0, 1e4)
+    pool = H.randn_bits(rng, ob.pool_elems(g, max_pages), dtype)
+    d_pool = torch.from_numpy(pool.view(np.int16)).cuda()
+    base_table = rng.permutation(max_pages).astype(np.int32)
+    d_base = torch.from_numpy(base_table).cuda()
+    d_table = torch.full((max_pages,), -1, dtype=torch.int32, device="cuda")
+    d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    step = torch.ones(1, dtype=torch.int32, device="cuda")
+    table = np.full(max_pages, -1, dtype=np.int32)
+    for it in range(40):
+        pos = 7 * it % (max_pages * page)
+        k1, v1 = H.randn_bits(rng, (1, hkv, d), dtype), H.randn_bits(rng, (1, hkv, d), dtype)
+        dk, dv = H.to_dev(k1, dtype), H.to_dev(v1, dtype)
+        d_pos.zero_()
+        torch.mul(step, pos, out=d_pos)                       # device kernels write the position ...
+        d_table.copy_(torch.roll(d_base, it))                 # ... and the table, directly in front of the call
+        table = np.roll(base_table, it)
+        rc = drkv_lib.drkv_k_cache_write(C.byref(cg), dk.data_ptr(), dv.data_ptr(), d_pool.data_ptr(), d_table.data_ptr(),
+                                         0, d_pos.data_ptr(), max_pages, None)
+        assert rc == 0, capi.last_error()
+        ob.append(g, pool, max_pages, table, 0, pos, 1, k1, v1, rope=False)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_pool.cpu().numpy().view(np.uint16), pool)
