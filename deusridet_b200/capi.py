@@ -43,7 +43,8 @@ class PlanInfo(C.Structure):
 
 class TierStats(C.Structure):
     _fields_ = [(n, C.c_int64) for n in (
-        "pages_stored", "swap_outs", "swap_ins", "bytes_out", "bytes_in", "prefetch_hits", "page_file_bytes")]
+        "pages_stored", "swap_outs", "swap_ins", "bytes_out", "bytes_in", "prefetch_hits", "page_file_bytes",
+        "writes_deferred", "write_failures")]
 
 
 class EvictRecord(C.Structure):
@@ -108,6 +109,11 @@ SIGNATURES = {
     "drkv_tier_disable": (_i, [_vp]),
     "drkv_tier_prefetch": (_i, [_vp, _i, _i]),
     "drkv_tier_drain": (_i, [_vp]),
+    "drkv_tier_set_write_behind": (_i, [_vp, _i]),
+    "drkv_tier_is_prefetched": (_i, [_vp, _i, _i]),
+    "drkv_tier_drop_prefetch": (_i, [_vp, _i, _i]),
+    "drkv_tier_page_to_file": (_i, [_vp, _i, C.c_char_p]),
+    "drkv_tier_file_to_page": (_i, [_vp, C.c_char_p, _i]),
     "drkv_tier_get_stats": (_i, [_vp, C.POINTER(TierStats)]),
     "drkv_seq_locations": (_i, [_vp, _i, C.POINTER(C.c_int8), _i]),
     "drkv_scorer_enable": (_i, [_vp, _f]),

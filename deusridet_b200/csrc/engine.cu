@@ -1200,6 +1200,46 @@ int drkv_tier_prefetch(drkv_engine* e, int seq, int logical) {
     return e->store->prefetch(seq, logical) ? 1 : 0;
 }
 
+int drkv_tier_set_write_behind(drkv_engine* e, int on) {
+    NEED(e);
+    LOCK(e);
+    if (!e->store) return set_err(DRKV_ERR_STATE, "tier_set_write_behind: no storage tier");
+    if (!on) e->store->drain();
+    e->store->set_write_behind(on != 0);
+    return DRKV_OK;
+}
+
+int drkv_tier_is_prefetched(drkv_engine* e, int seq, int logical) {
+    NEED(e);
+    if (!e->store) return set_err(DRKV_ERR_STATE, "tier_is_prefetched: no storage tier");
+    return e->store->is_prefetched(seq, logical) ? 1 : 0;
+}
+
+int drkv_tier_drop_prefetch(drkv_engine* e, int seq, int logical) {
+    NEED(e);
+    if (!e->store) return set_err(DRKV_ERR_STATE, "tier_drop_prefetch: no storage tier");
+    e->store->drop_prefetch(seq, logical);
+    return DRKV_OK;
+}
+
+int drkv_tier_page_to_file(drkv_engine* e, int page, const char* path) {
+    NEED(e);
+    LOCK(e);
+    if (!e->store) return set_err(DRKV_ERR_STATE, "tier_page_to_file: no storage tier");
+    if (!path || page < 0 || page >= e->book.max_pages()) return set_err(DRKV_ERR_INVALID, "tier_page_to_file: bad argument");
+    if (!e->store->page_to_file(page, path)) return set_err(DRKV_ERR_STATE, "tier_page_to_file: copy or write failed (%s)", path);
+    return DRKV_OK;
+}
+
+int drkv_tier_file_to_page(drkv_engine* e, const char* path, int page) {
+    NEED(e);
+    LOCK(e);
+    if (!e->store) return set_err(DRKV_ERR_STATE, "tier_file_to_page: no storage tier");
+    if (!path || page < 0 || page >= e->book.max_pages()) return set_err(DRKV_ERR_INVALID, "tier_file_to_page: bad argument");
+    if (!e->store->file_to_page(path, page)) return set_err(DRKV_ERR_STATE, "tier_file_to_page: read or copy failed (%s)", path);
+    return DRKV_OK;
+}
+
 int drkv_tier_drain(drkv_engine* e) {
     NEED(e);
     if (!e->store) return set_err(DRKV_ERR_STATE, "tier_drain: no storage tier");
@@ -1221,6 +1261,8 @@ int drkv_tier_get_stats(const drkv_engine* ce, drkv_tier_stats* out) {
         out->bytes_in = e->store->bytes_in;
         out->prefetch_hits = e->store->prefetch_hits;
         out->page_file_bytes = (int64_t)e->store->file_bytes();
+        out->writes_deferred = e->store->writes_deferred;
+        out->write_failures = e->store->write_failures;
     }
     return DRKV_OK;
 }

@@ -46,6 +46,20 @@ public:
     bool swap_in(int seq, int logical, int page) override;
     void drop(int seq, int logical) override;
 
+    // Write-behind (off by default: both moves are synchronous, as CacheManager drives its swapper,
+    // cache_manager.cpp:215-241).  When on, swap_out returns as soon as the page's bytes have landed in one of a few
+    // pinned buffers (the pool page is free from then on) and the worker thread writes the file
+    // (kv_swapper.cpp:154-177 moves pages on an I/O thread the same way); a swap-in, drop or prefetch of that page
+    // waits for its write.  A write that fails is counted; the page then cannot be read back.
+    void set_write_behind(bool on) { write_behind_ = on; }
+    bool write_behind() const { return write_behind_; }
+
+    // One pool page to / from a file of the caller's choosing: what a KVSwapper::submit request asks for
+    // (kv_swapper.h:36-44).  Synchronous.
+    bool page_to_file(int page, const std::string& path);
+    bool file_to_page(const std::string& path, int page);
+    void drop_prefetch(int seq, int logical);       // kv_swapper.h:88
+
     // Reads a stored page into host memory in the background; the next swap_in of it skips the file
     // (kv_swapper.h:78-88).  Returns false if it is not stored.
     bool prefetch(int seq, int logical);
@@ -54,7 +68,7 @@ public:
 
     std::string path_for(int seq, int logical) const;
     size_t file_bytes() const { return (size_t)num_layers_ * page_bytes_; }
-    int64_t bytes_out = 0, bytes_in = 0, prefetch_hits = 0;
+    int64_t bytes_out = 0, bytes_in = 0, prefetch_hits = 0, writes_deferred = 0, write_failures = 0;
 
 private:
     std::string dir_;
@@ -68,8 +82,20 @@ private:
     static int64_t key(int seq, int logical) { return ((int64_t)seq << 32) | (uint32_t)logical; }
     std::mutex mu_;
     std::condition_variable cv_;
-    std::deque<int64_t> queue_;
-    std::unordered_set<int64_t> pending_;
+    struct Job {
+        int64_t key;
+        int wb_buf;                                 // >= 0: write this buffer to the page's file; -1: prefetch read
+    };
+    std::deque<Job> queue_;
+    std::unordered_set<int64_t> pending_;           // prefetch reads queued or running
+    static constexpr int kWriteBehindBuffers = 4;
+    bool write_behind_ = false;
+    void* wb_bufs_[kWriteBehindBuffers] = {};       // pinned, one page file each (allocated on first use)
+    std::vector<int> wb_free_;
+    std::unordered_map<int64_t, int> wb_pending_;   // page -> buffer whose file write is queued or running
+    bool copy_out(int page, void* host);            // pool page -> pinned host buffer, complete on return
+    bool copy_in(const void* host, int page);
+    bool write_file(const std::string& path, const void* src);
     std::unordered_map<int64_t, std::vector<char>> cache_;
     std::thread worker_;
     bool running_ = false;

@@ -191,6 +191,11 @@ class PagedKVEngine:
     def tier_disable(self) -> None: check(self.lib.drkv_tier_disable(self.h))
     def prefetch_block(self, seq: int, logical: int) -> int: return check(self.lib.drkv_tier_prefetch(self.h, seq, logical))
     def tier_drain(self) -> None: check(self.lib.drkv_tier_drain(self.h))
+    def tier_set_write_behind(self, on: bool) -> None: check(self.lib.drkv_tier_set_write_behind(self.h, 1 if on else 0))
+    def is_prefetched(self, seq: int, logical: int) -> bool: return check(self.lib.drkv_tier_is_prefetched(self.h, seq, logical)) == 1
+    def drop_prefetch(self, seq: int, logical: int) -> None: check(self.lib.drkv_tier_drop_prefetch(self.h, seq, logical))
+    def page_to_file(self, page: int, path: str) -> None: check(self.lib.drkv_tier_page_to_file(self.h, page, path.encode()))
+    def file_to_page(self, path: str, page: int) -> None: check(self.lib.drkv_tier_file_to_page(self.h, path.encode(), page))
     def tier_stats(self) -> dict:
         st = capi.TierStats()
         check(self.lib.drkv_tier_get_stats(self.h, C.byref(st)))

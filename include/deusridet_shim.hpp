@@ -8,8 +8,9 @@
 //
 //   BlockPool      src/memoria/block_pool.h:58-123
 //   CacheManager   src/memoria/cache_manager.h:52-169
-//   KVSwapper      src/memoria/kv_swapper.h:52-120: a token here; a non-null swapper together with a
-//                  cache_dir switches the engine's storage tier on (cache_manager.cpp:132, 56-66)
+//   KVSwapper      src/memoria/kv_swapper.h:36-120 (SwapRequest, submit, drain, prefetch, is_prefetched, drop_prefetch):
+//                  a non-null swapper together with a cache_dir switches the engine's storage tier on
+//                  (cache_manager.cpp:132, 56-66); its calls forward to that tier
 //   ImportanceScorer src/memoria/importance_scorer.h:25-67: init / update / sync_to_host / score /
 //                  least_important forward to the engine's scorer once a CacheManager has adopted it
 //   paged_kv_cache_write / _batch, paged_gqa_decode_attention
@@ -58,20 +59,52 @@ struct PagedKVConfig {
 
 class BlockPool;
 
-// The engine moves pages itself; what remains of the swapper is the fact that one was configured.
+// src/memoria/kv_swapper.h:36-44
+enum class SwapDirection { GPU_TO_SSD, SSD_TO_GPU };
+struct SwapRequest {
+    SwapDirection direction;
+    int logical_block_idx;
+    int physical_block_id;                 // pool page (source for out, target for in)
+    std::string ssd_path;                  // file path
+    std::function<void(bool)> callback;    // completion callback (success)
+};
+
+// src/memoria/kv_swapper.h:52-120.  The engine moves evicted pages itself once a CacheManager has adopted the
+// swapper (cache_manager.cpp:132, 215-292); the swapper's own calls forward to the engine's storage tier.  A
+// request is carried out before submit() returns (the reference queues it for its I/O thread and its only caller
+// drains at once, cache_manager.cpp:226-229); drkv_tier_set_write_behind is how file writes leave the caller's thread.
 class KVSwapper {
 public:
-    bool init(BlockPool&, const std::string& ssd_dir, int /*staging_blocks*/ = 2) {
-        dir_ = ssd_dir;
-        return true;
+    bool init(BlockPool& pool, const std::string& ssd_dir, int /*staging_blocks*/ = 2);
+    void submit(SwapRequest req) {
+        bool ok = false;
+        if (e_ != nullptr)
+            ok = (req.direction == SwapDirection::GPU_TO_SSD
+                      ? drkv_tier_page_to_file(e_, req.physical_block_id, req.ssd_path.c_str())
+                      : drkv_tier_file_to_page(e_, req.ssd_path.c_str(), req.physical_block_id)) == DRKV_OK;
+        if (!ok) std::fprintf(stderr, "[Memoria] KVSwapper: %s\n", e_ ? drkv_last_error() : "not initialised");
+        if (req.callback) req.callback(ok);
     }
-    void drain() {}
-    void shutdown() {}
+    void drain() {
+        if (e_) drkv_tier_drain(e_);
+    }
+    void shutdown() { drain(); }
     int pending() const { return 0; }
+    // the file of a logical block is the engine's own (cache_manager.cpp:211-213): the path argument is not needed
+    void prefetch(int logical_block_idx, const std::string& /*ssd_path*/) {
+        if (e_) drkv_tier_prefetch(e_, seq_, logical_block_idx);
+    }
+    bool is_prefetched(int logical_block_idx) const { return e_ && drkv_tier_is_prefetched(e_, seq_, logical_block_idx) == 1; }
+    void drop_prefetch(int logical_block_idx) {
+        if (e_) drkv_tier_drop_prefetch(e_, seq_, logical_block_idx);
+    }
     const std::string& dir() const { return dir_; }
 
 private:
+    friend class CacheManager;
     std::string dir_;
+    drkv_engine* e_ = nullptr;
+    int seq_ = 0;
 };
 
 class ImportanceScorer {
@@ -178,6 +211,16 @@ private:
     int block_size_ = PagedKVConfig::BLOCK_SIZE;
 };
 
+inline bool KVSwapper::init(BlockPool& pool, const std::string& ssd_dir, int) {
+    dir_ = ssd_dir;
+    e_ = pool.engine();                    // null until the pool is initialised; a CacheManager sets it when it adopts the swapper
+    if (e_ != nullptr && !ssd_dir.empty() && drkv_tier_enable(e_, ssd_dir.c_str()) != DRKV_OK) {
+        std::fprintf(stderr, "[Memoria] KVSwapper: %s\n", drkv_last_error());
+        return false;
+    }
+    return true;
+}
+
 class CacheManager {
 public:
     CacheManager() = default;
@@ -199,6 +242,10 @@ public:
         // cannot be created switches the tier off with a warning
         if (seq_ >= 0 && swapper != nullptr && !cache_dir.empty() && drkv_tier_enable(pool_.e_, cache_dir.c_str()) != DRKV_OK)
             std::fprintf(stderr, "[Memoria] Cannot create SSD cache dir: %s\n", cache_dir.c_str());
+        if (swapper != nullptr) {
+            swapper->e_ = pool_.e_;
+            swapper->seq_ = seq_;
+        }
         return seq_ >= 0;
     }
     bool ensure_blocks_for(int pos) { return ok(drkv_seq_ensure_pos(pool_.e_, seq_, pos, nullptr)); }

@@ -267,17 +267,32 @@ DRKV_API int drkv_attend_decode_planned(drkv_engine* e, int layer, const void* q
  * seq<row>_block_<logical>.kv) instead of discarded, and drkv_seq_ensure_pos / _range / _reserve on a
  * stored page allocates a pool page (discarding, never storing, a victim if the pool is empty) and
  * reads it back.  File = for every layer the K plane then the V plane of the page, sized from the
- * engine's geometry (the reference sizes it from compile-time constants).  Both moves are synchronous,
- * as in the reference.  On an engine without a device the files are empty markers. */
+ * engine's geometry (the reference sizes it from compile-time constants).  Both moves are synchronous
+ * unless drkv_tier_set_write_behind turns deferred file writes on.  On an engine without a device the files
+ * are empty markers. */
 typedef struct drkv_tier_stats {
     int64_t pages_stored, swap_outs, swap_ins, bytes_out, bytes_in, prefetch_hits, page_file_bytes;
+    int64_t writes_deferred, write_failures;   /* write-behind: file writes handed to the worker thread / that failed there */
 } drkv_tier_stats;
 DRKV_API int drkv_tier_enable(drkv_engine* e, const char* dir);
 DRKV_API int drkv_tier_disable(drkv_engine* e);       /* refused while pages are stored */
 /* CacheManager::prefetch_block (cache_manager.cpp:166-180): background read of a stored page into host
  * memory, so that the swap-in skips the file.  Returns 1 if queued, 0 if the page is not stored. */
 DRKV_API int drkv_tier_prefetch(drkv_engine* e, int seq, int logical);
-DRKV_API int drkv_tier_drain(drkv_engine* e);          /* waits for queued prefetches */
+DRKV_API int drkv_tier_drain(drkv_engine* e);          /* waits for queued prefetches and deferred file writes */
+/* Write-behind (off by default).  The reference moves pages on an I/O thread with its own stream
+ * (kv_swapper.cpp:154-177) but CacheManager waits for it (submit + drain, cache_manager.cpp:215-241), so its moves
+ * are synchronous in effect.  With write-behind on, a swap-out returns once the page's bytes are in pinned host
+ * memory (the pool page is free from then on) and a worker thread writes the file; whatever touches that page
+ * next (swap-in, prefetch, release) waits for its write.  Up to four pages may wait for their files. */
+DRKV_API int drkv_tier_set_write_behind(drkv_engine* e, int on);
+/* KVSwapper::is_prefetched / drop_prefetch (kv_swapper.h:85-88): 1 if a background read of the page has landed. */
+DRKV_API int drkv_tier_is_prefetched(drkv_engine* e, int seq, int logical);
+DRKV_API int drkv_tier_drop_prefetch(drkv_engine* e, int seq, int logical);
+/* What one KVSwapper::submit request does (SwapRequest, kv_swapper.h:36-44): pool page `page` to the file `path`
+ * (GPU_TO_SSD) or back (SSD_TO_GPU), file layout as above.  Synchronous; the bookkeeping is the caller's. */
+DRKV_API int drkv_tier_page_to_file(drkv_engine* e, int page, const char* path);
+DRKV_API int drkv_tier_file_to_page(drkv_engine* e, const char* path, int page);
 DRKV_API int drkv_tier_get_stats(const drkv_engine* e, drkv_tier_stats* out);
 /* BlockLocation per logical page of a sequence (cache_manager.h:42-46): 0 invalid, 1 in the pool, 2 stored. */
 DRKV_API int drkv_seq_locations(const drkv_engine* e, int seq, int8_t* out, int cap);

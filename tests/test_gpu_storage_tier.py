@@ -128,3 +128,69 @@ def test_swap_out_waits_for_kernels_in_flight(drkv_lib, oracle, tmp_path):
         eng.check_kernels()
     finally:
         eng.close()
+
+
+def test_write_behind_round_trip_and_swapper_requests(drkv_lib, oracle, tmp_path):
+    """With deferred file writes on: pages evicted in a burst (more than the four pinned buffers) come back with
+    their bytes whether their file has been written yet or not, the freed pool pages may be overwritten at once,
+    the files are complete after a drain, and nothing is left behind after the swap-ins.  Then the two moves a
+    KVSwapper::submit request asks for (kv_swapper.h:36-44): one pool page to a file of the caller's choosing and
+    back into another page."""
+    import torch
+    from deusridet_b200 import PagedKVEngine
+
+    ob = oracle
+    layers, hq, hkv, d, page, dtype = 3, 16, 4, 128, 16, ob.BF16
+    max_pages, n_pages = 24, 16
+    rng = np.random.default_rng(61)
+    eng = PagedKVEngine(num_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
+                        rope_theta=1e6, max_pages=max_pages, max_seqs=1, max_pages_per_seq=32, device=0,
+                        stream_evict=True)
+    g = ob.geom(layers, hq, hkv, d, page, dtype, d, 1e6)
+    try:
+        eng.tier_enable(str(tmp_path))
+        eng.tier_set_write_behind(True)
+        H.shuffled_free_stack(eng, rng)
+        s = eng.seq_create()
+        n_tok = n_pages * page
+        eng.reserve(s, n_tok)
+        eng.set_seq_len(s, n_tok)
+        pool_host = H.randn_bits(rng, ob.pool_elems(g, max_pages), dtype)
+        pool_dev = eng.pool_tensor()
+        pool_dev.copy_(torch.from_numpy(pool_host.view(np.int16)))
+        eng.sync_block_table()
+        before = eng.table(s).copy()
+        per_layer = 2 * hkv * page * d
+        by_layer = pool_host.reshape(layers, max_pages, per_layer)
+        k = 10
+        assert eng.evict_blocks(s, k) == k                          # a burst: ten pages through four buffers
+        for j in range(k):                                          # the pool pages are free: scribble over them at once
+            pool_dev.view(layers, max_pages, per_layer)[:, int(before[j]), :] = 0x7F7F
+        assert eng.prefetch_block(s, 2) == 1                        # queued behind the page's own file write
+        assert eng.ensure_blocks_for_range(s, 0, 4 * page)          # four come back straight away
+        eng.tier_drain()
+        st = eng.tier_stats()
+        assert st["writes_deferred"] == k and st["write_failures"] == 0 and st["swap_ins"] == 4
+        for j in range(4, k):                                       # the others' files are complete
+            with open(os.path.join(tmp_path, f"block_{j}.kv"), "rb") as f:
+                got = np.frombuffer(f.read(), dtype=np.uint16)
+            assert np.array_equal(got, by_layer[:, before[j], :].reshape(-1)), f"file of logical page {j}"
+        assert eng.ensure_blocks_for_range(s, 0, k * page)
+        assert sorted(os.listdir(tmp_path)) == []
+        eng.sync_block_table()
+        after = eng.table(s)
+        now = pool_dev.cpu().numpy().view(np.uint16).reshape(layers, max_pages, per_layer)
+        for j in range(n_pages):
+            assert np.array_equal(now[:, after[j], :], by_layer[:, before[j], :]), f"logical page {j}"
+
+        # one SwapRequest each way: pool page -> file -> another pool page
+        src, dst = int(after[0]), eng.alloc_block()
+        assert dst >= 0
+        path = str(tmp_path / "request.kv")
+        eng.page_to_file(src, path)
+        eng.file_to_page(path, dst)
+        torch.cuda.synchronize()
+        now = pool_dev.cpu().numpy().view(np.uint16).reshape(layers, max_pages, per_layer)
+        assert np.array_equal(now[:, dst, :], now[:, src, :]) and os.path.getsize(path) == layers * per_layer * 2
+    finally:
+        eng.close()
