@@ -60,6 +60,21 @@ def peaks():
     return 6650.0, "fallback"
 
 
+READ_STREAM_SRC = os.path.join(ROOT, "bench_read_stream.cu")
+READ_STREAM_LIB = os.path.join(ROOT, "libbench_read_stream.so")
+
+
+def build_read_stream(force: bool = False) -> str:
+    """The read-only streaming probe (a measurement helper, kept out of libdrkv.so), built next to this file."""
+    import shutil
+    if force or not os.path.exists(READ_STREAM_LIB) or os.path.getmtime(READ_STREAM_LIB) < os.path.getmtime(READ_STREAM_SRC):
+        nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+        subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-shared", "-Xcompiler",
+                        "-fPIC,-fvisibility=hidden", READ_STREAM_SRC, "-o", READ_STREAM_LIB + ".tmp"], check=True)
+        os.replace(READ_STREAM_LIB + ".tmp", READ_STREAM_LIB)
+    return READ_STREAM_LIB
+
+
 def read_stream_gbs(eng, stream):
     """Read-only streaming bandwidth of this GPU over the first 8 GiB of the engine's pool (the reference's own
     ceiling method, tools/probe_bw.cu): the second denominator beside the measured copy peak."""
@@ -68,8 +83,13 @@ def read_stream_gbs(eng, stream):
     nbytes = min(pool.numel() * pool.element_size(), 8 << 30)
     if nbytes < (256 << 20):
         return None
+    try:
+        lib = C.CDLL(build_read_stream())
+    except (OSError, subprocess.CalledProcessError):
+        return None
+    lib.bench_read_stream_gbs.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.POINTER(C.c_double)]
     out = C.c_double()
-    rc = eng.lib.drkv_probe_read_bandwidth(pool.data_ptr(), nbytes, 10, stream.cuda_stream, C.byref(out))
+    rc = lib.bench_read_stream_gbs(pool.data_ptr(), nbytes, 10, stream.cuda_stream, C.byref(out))
     return float(out.value) if rc == 0 else None
 
 

@@ -1,14 +1,12 @@
-// probe.cu — read-only streaming bandwidth of the device the caller is on, the second denominator the
-// decode roofline is quoted against (the reference measures its ceiling the same way: a kernel that only
-// reads and sums, tools/probe_bw.cu:18-28, timed with events over repeated launches, :99-113).  A copy
-// (read + write) understates what a read-mostly kernel can reach.
+// bench_read_stream.cu — measurement helper of bench.py, not part of the library: read-only streaming bandwidth
+// of the device the caller is on, the second denominator the decode roofline is quoted against (the reference
+// measures its ceiling the same way: a kernel that only reads and sums, tools/probe_bw.cu:18-28, timed with
+// events over repeated launches, :99-113).  A copy (read + write) understates what a read-mostly kernel can
+// reach.  bench.py builds this file into libbench_read_stream.so next to itself.
 #include <cuda_runtime.h>
+#include <cstddef>
 #include <cstdint>
 
-#include "../../include/drkv.h"
-#include "stateless.hpp"
-
-namespace drkv {
 namespace {
 
 // 4 independent 16-byte loads in flight per thread and trip, grid-stride over the buffer.
@@ -28,14 +26,12 @@ __global__ void __launch_bounds__(512) read_stream_kernel(const uint4* __restric
 }
 
 }  // namespace
-}  // namespace drkv
 
-extern "C" int drkv_probe_read_bandwidth(const void* buf, size_t bytes, int iters, void* stream_, double* gb_per_s) {
-    using namespace drkv;
-    if (!buf || bytes < (1u << 20) || iters < 1 || !gb_per_s) {
-        set_last_error("probe_read_bandwidth: bad argument (at least 1 MiB, one iteration)");
-        return DRKV_ERR_INVALID;
-    }
+// GB/s over `bytes` of device memory at `buf` (use more than the L2 holds): CUDA events around `iters` launches after
+// two warm-ups.  Returns 0, or a negative number / a cudaError_t value on failure.
+extern "C" __attribute__((visibility("default"))) int bench_read_stream_gbs(const void* buf, size_t bytes, int iters,
+                                                                            void* stream_, double* gb_per_s) {
+    if (!buf || bytes < (1u << 20) || iters < 1 || !gb_per_s) return -1;
     cudaStream_t stream = (cudaStream_t)stream_;
     int dev = 0, sms = 0;
     uint32_t* sink = nullptr;
@@ -60,10 +56,7 @@ extern "C" int drkv_probe_read_bandwidth(const void* buf, size_t bytes, int iter
     if (e0) cudaEventDestroy(e0);
     if (e1) cudaEventDestroy(e1);
     if (sink) cudaFree(sink);
-    if (ce != cudaSuccess) {
-        set_last_error(cudaGetErrorString(ce));
-        return DRKV_ERR_CUDA;
-    }
+    if (ce != cudaSuccess) return (int)ce;
     *gb_per_s = (double)(bytes / sizeof(uint4) * sizeof(uint4)) * iters / (ms * 1e-3) / 1e9;
-    return DRKV_OK;
+    return 0;
 }

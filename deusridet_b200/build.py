@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdrkv.so")
 
-CUDA_SOURCES = ["engine.cu", "append.cu", "attend_decode.cu", "stateless.cu", "decode_noalloc.cu", "attend_prefill.cu", "gather_scatter.cu", "probe.cu"]
+CUDA_SOURCES = ["engine.cu", "append.cu", "attend_decode.cu", "stateless.cu", "decode_noalloc.cu", "attend_prefill.cu", "gather_scatter.cu"]
 CXX_SOURCES = ["page_book.cpp", "page_store.cpp", "sharding.cpp"]
 HEADERS = ["kernels.hpp", "kv_common.cuh", "page_book.hpp", "page_store.hpp", "exchange.cuh", "stateless.hpp", "sm100_primitives.cuh", os.path.join("..", "..", "include", "drkv.h")]
 

@@ -133,7 +133,6 @@ SIGNATURES = {
     "drkv_append_attend_exchange": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _vp]),
     "drkv_attend_partial": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp]),
     "drkv_combine_partials": (_i, [_vp, _i, _vp, _vp, _vp]),
-    "drkv_probe_read_bandwidth": (_i, [_vp, _sz, _i, _vp, C.POINTER(C.c_double)]),
     "drkv_partial_floats": (_sz, [_vp]),
     "drkv_k_cache_write": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "drkv_k_cache_write_batch": (_i, [C.POINTER(Geometry), _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),

@@ -435,12 +435,6 @@ DRKV_API int drkv_k_decode_attention_noalloc(const drkv_geometry* g, const void*
                                              const int32_t* d_block_table, void* out, int layer,
                                              int seq_len, int max_pages, float scale, void* stream);
 
-/* ---- measurement aid ------------------------------------------------------------------------
- * Read-only streaming bandwidth over `bytes` of device memory at `buf` (GB/s, CUDA events around `iters`
- * launches after two warm-ups): the reference's own way of finding its ceiling (tools/probe_bw.cu:18-28,
- * 99-113: a kernel that only reads and sums).  Use a buffer larger than L2. */
-DRKV_API int drkv_probe_read_bandwidth(const void* buf, size_t bytes, int iters, void* stream, double* gb_per_s);
-
 #ifdef __cplusplus
 }
 #endif

@@ -42,4 +42,6 @@ def main(out_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "importance_reference.npz"))
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    main(sys.argv[1])
