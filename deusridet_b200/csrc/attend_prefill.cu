@@ -96,6 +96,9 @@ __device__ long long g_pf_trace_each[16];   // cycles per instruction of one QK 
 #ifndef DRKV_PF_XU_TURNS
 #define DRKV_PF_XU_TURNS 1
 #endif
+#ifndef DRKV_PF_WARP_ARRIVE
+#define DRKV_PF_WARP_ARRIVE 1
+#endif
 
 __device__ __forceinline__ float poly_exp2(float x) {
     x = fmaxf(x, -126.f);
@@ -147,8 +150,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         }
         for (int x = 0; x < 2; x++) {
             mbar_init(bars + 8 * (BAR_S_READY + x), 1);
-            mbar_init(bars + 8 * (BAR_S_FREE + x), 128);
-            mbar_init(bars + 8 * (BAR_P_READY + x), 128);
+            mbar_init(bars + 8 * (BAR_S_FREE + x), DRKV_PF_WARP_ARRIVE ? 4 : 128);     // one arrival per softmax warp of the tile
+            mbar_init(bars + 8 * (BAR_P_READY + x), DRKV_PF_WARP_ARRIVE ? 4 : 128);
             mbar_init(bars + 8 * (BAR_O_READY + x), 1);
         }
         for (int i = 0; i < 8; i++) mbar_init(bars + 8 * (BAR_XU + i), 1);
@@ -388,7 +391,12 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 tmem_wait_ld();
                 const long long c2 = PF_CLK();
                 tcgen05_fence_before();
-                mbar_arrive(bars + 8 * (BAR_S_FREE + x));               // S(j+1) may overwrite the columns now
+                if (DRKV_PF_WARP_ARRIVE) {                              // S(j+1) may overwrite the columns now
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bars + 8 * (BAR_S_FREE + x));
+                } else {
+                    mbar_arrive(bars + 8 * (BAR_S_FREE + x));
+                }
                 const int key0 = j * kPfBlockN;
                 const int holes = s_holes[j % kPfStages];
                 // Blocks left of the diagonal with all pages present need no mask: that is almost all of them.
@@ -465,7 +473,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                     // two scores per multiply-add and per add (packed fp32 pairs), one exponential each, one
                     // conversion per pair
 #pragma unroll
-                    for (int h = 0; h < 2; h++)
+                    for (int h = 0; h < 2; h++) {
 #pragma unroll
                         for (int c = 0; c < 32; c += 2) {
                             float a0, a1;
@@ -474,6 +482,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                             sum2[(c >> 1) & 3] = add_f32x2(sum2[(c >> 1) & 3], pack_f32x2(p0, p1));
                             phi[h * 16 + (c >> 1)] = Elem<T>::pack2(p0, p1);
                         }
+                    }
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         float s0, s1;
@@ -524,7 +533,12 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 if (use_lo) tmem_st32(t_p + 32, plo);
                 tmem_wait_st();
                 tcgen05_fence_before();
-                mbar_arrive(bars + 8 * (BAR_P_READY + x));
+                if (DRKV_PF_WARP_ARRIVE) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bars + 8 * (BAR_P_READY + x));
+                } else {
+                    mbar_arrive(bars + 8 * (BAR_P_READY + x));
+                }
                 const long long c5 = PF_CLK();
                 ph[0] += c1 - c0; ph[1] += c2 - c1; ph[2] += c3 - c2; ph[3] += c4 - c3; ph[4] += c5 - c4;
             }
