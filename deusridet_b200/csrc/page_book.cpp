@@ -26,6 +26,7 @@ bool PageBook::init(int max_pages, int page_size, int max_seqs, int max_pages_pe
     for (int i = 0; i < max_pages; i++) free_stack_[i] = max_pages - 1 - i;  // block_pool.cpp:52-55
     refcount_.assign(max_pages, 0);
     state_.assign(max_pages, PageState::FREE);
+    caller_owned_.assign(max_pages, 0);
     lru_.clear();
     lru_pos_.assign(max_pages, lru_.end());
     seqs_.assign(max_seqs, Seq());
@@ -39,7 +40,7 @@ bool PageBook::init(int max_pages, int page_size, int max_seqs, int max_pages_pe
 // pool
 // ---------------------------------------------------------------------------------------
 
-int PageBook::pool_alloc() {
+int PageBook::alloc_raw() {
     if (free_stack_.empty()) return -1;  // block_pool.cpp:63-69
     int id = free_stack_.back();
     free_stack_.pop_back();
@@ -48,11 +49,21 @@ int PageBook::pool_alloc() {
     return id;
 }
 
+int PageBook::pool_alloc() {
+    const int id = alloc_raw();
+    if (id >= 0) caller_owned_[id] = 1;
+    return id;
+}
+
 int PageBook::pool_free(int page) {
     if (page < 0 || page >= max_pages_) return fail(DRKV_ERR_INVALID, "free: page id out of range");
     if (state_[page] != PageState::ACTIVE)
         return fail(DRKV_ERR_STATE, "free: page is not allocated (double free?)");
+    // The reference's free_block pushes whatever id it is given (block_pool.cpp:71-74); a page that a block table
+    // still points to must not come back through this door.
+    if (!caller_owned_[page]) return fail(DRKV_ERR_STATE, "free: page belongs to a sequence, not to the caller");
     if (refcount_[page] != 1) return fail(DRKV_ERR_STATE, "free: page is still shared");
+    caller_owned_[page] = 0;
     refcount_[page] = 0;
     state_[page] = PageState::FREE;
     free_stack_.push_back(page);  // block_pool.cpp:71-74
@@ -147,13 +158,13 @@ bool PageBook::evict_one_of(int seq, bool may_store) {
 }
 
 int PageBook::take_page(int seq, bool may_store) {
-    int id = pool_alloc();
+    int id = alloc_raw();
     if (id >= 0) return id;
     if (!lru_.empty()) {
         evict_cached(1);
-        return pool_alloc();
+        return alloc_raw();
     }
-    if (stream_evict_ && seq_live(seq) && evict_one_of(seq, may_store)) return pool_alloc();  // cache_manager.cpp:310-319
+    if (stream_evict_ && seq_live(seq) && evict_one_of(seq, may_store)) return alloc_raw();  // cache_manager.cpp:310-319
     return -1;
 }
 

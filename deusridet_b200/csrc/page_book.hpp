@@ -127,6 +127,7 @@ private:
     std::vector<int32_t> free_stack_;
     std::vector<int32_t> refcount_;
     std::vector<PageState> state_;
+    std::vector<uint8_t> caller_owned_;                // taken by pool_alloc(): only those go back through pool_free()
     std::list<int> lru_;                               // cached pages, head = oldest release
     std::vector<std::list<int>::iterator> lru_pos_;    // valid while state == CACHED
     std::vector<Seq> seqs_;
@@ -151,6 +152,7 @@ private:
     }
     // A page for `seq`: free stack, else the LRU head of the cached pages, else (stream
     // mode) after the sequence has discarded one of its own pages.  -1 when none.
+    int alloc_raw();                                   // pops the free stack: the page is ACTIVE with one reference
     int take_page(int seq, bool may_store = true);
     bool evict_one_of(int seq, bool may_store = true);
     void retire(int seq, std::deque<int>::iterator it, bool may_store);

@@ -40,6 +40,7 @@ class BookModel:
         self.stream_evict = stream_evict
         self.free = list(range(max_pages - 1, -1, -1))          # block_pool.cpp:52-55
         self.ref = [0] * max_pages
+        self.caller_owned = set()                               # pages handed out by pool_alloc(): only those go back by pool_free()
         self.state = [FREE] * max_pages
         self.lru = deque()                                      # cached pages, oldest release first
         self.seqs: List[Optional[Seq]] = [None] * max_seqs
@@ -52,18 +53,25 @@ class BookModel:
         self.files = set()                                      # (seq, logical) files the tier holds
 
     # ---- pool ---------------------------------------------------------------------------
-    def pool_alloc(self) -> int:
+    def _alloc_raw(self) -> int:
         if not self.free:
             return -1                                           # block_pool.cpp:63-69
         p = self.free.pop()
         self.state[p], self.ref[p] = ACTIVE, 1
         return p
 
+    def pool_alloc(self) -> int:
+        p = self._alloc_raw()
+        if p >= 0:
+            self.caller_owned.add(p)
+        return p
+
     def pool_free(self, p: int) -> int:
         if p < 0 or p >= self.n:
             return ERR_INVALID
-        if self.state[p] != ACTIVE or self.ref[p] != 1:
-            return ERR_STATE
+        if self.state[p] != ACTIVE or p not in self.caller_owned or self.ref[p] != 1:
+            return ERR_STATE                                    # not allocated, a sequence's page, or still shared
+        self.caller_owned.discard(p)
         self.state[p], self.ref[p] = FREE, 0
         self.free.append(p)                                     # block_pool.cpp:71-74
         return OK
@@ -143,14 +151,14 @@ class BookModel:
         return 0 <= s < len(self.seqs) and self.seqs[s] is not None
 
     def _take(self, s: int, may_store: bool = True) -> int:
-        p = self.pool_alloc()
+        p = self._alloc_raw()
         if p >= 0:
             return p
         if self.lru:
             self.evict_cached(1)
-            return self.pool_alloc()
+            return self._alloc_raw()
         if self.stream_evict and self._live(s) and self._evict_one_of(s, may_store):   # cache_manager.cpp:310-319
-            return self.pool_alloc()
+            return self._alloc_raw()
         return -1
 
     def seq_evict(self, s: int, n: int) -> int:

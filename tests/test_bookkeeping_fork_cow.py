@@ -306,3 +306,19 @@ def test_prefix_sharing_full_size(drkv_lib):
     # eviction order is release order of the fillers' pages
     assert [p for _, _, _, p in mod.log] == [p for _, _, _, p in eng.evict_log(clear=False)]
     eng.close()
+
+
+def test_host_bookkeeping_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+    """tests/cpp/page_book_fuzz.cpp drives csrc/page_book.cpp (no CUDA in it) with seeded operation mixes (valid calls,
+    unknown sequences, double frees, frees of pages a block table still owns) and checks reference counts, free
+    stack, cached list and stored-page counts after every operation, built with -fsanitize=address,undefined."""
+    import os
+    import subprocess
+    ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "page_book_fuzz")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined",
+                    f"-I{ROOT}/deusridet_b200/csrc", f"-I{ROOT}/include", f"{ROOT}/tests/cpp/page_book_fuzz.cpp",
+                    f"{ROOT}/deusridet_b200/csrc/page_book.cpp", "-o", exe], check=True)
+    for seed in (11, 12, 13, 14):
+        res = subprocess.run([exe, str(seed), "15000"], capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0 and "PAGE_BOOK_FUZZ OK" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
