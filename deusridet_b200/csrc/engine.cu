@@ -172,7 +172,6 @@ struct drkv_engine {
         int world = 0, rank = 0;
         uint32_t seq_no = 0;
         void* area = nullptr;                        // this rank's slots + flags, one allocation
-        size_t flags_offset = 0;
         void* peer_area[kMaxExchangeRanks] = {};     // every rank's area as mapped here (own = area)
         bool connected = false;
         bool local = false;                          // peers' areas were given as pointers, not opened through IPC
@@ -1393,9 +1392,9 @@ int drkv_exchange_create(drkv_engine* e, int world, int rank, uint8_t* handle_ou
     CUDA_TRY(cudaSetDevice(e->device));
     exchange_release(e);
     drkv_engine::Exchange& x = e->xchg;
-    const size_t per_rank = (size_t)e->geom.num_q_heads * (e->geom.head_dim + 2) * sizeof(float);
-    x.flags_offset = (2 * (size_t)world * per_rank + 255) / 256 * 256;
-    const size_t bytes = x.flags_offset + (size_t)world * e->geom.num_q_heads * sizeof(uint32_t);
+    // {value, sequence number} words: 2 parities x world ranks x Hq * (D + 2)
+    const size_t per_rank = (size_t)e->geom.num_q_heads * (e->geom.head_dim + 2) * sizeof(float2);
+    const size_t bytes = (2 * (size_t)world * per_rank + 255) / 256 * 256;
     CUDA_TRY(cudaMalloc(&x.area, bytes));
     CUDA_TRY(cudaMemset(x.area, 0, bytes));
     CUDA_TRY(cudaDeviceSynchronize());
@@ -1488,8 +1487,7 @@ static int attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int
     if (span < 1) span = 1;
     ExchangeParams p{};
     for (int r = 0; r < x.world; r++) {
-        p.peer_slots[r] = static_cast<float*>(x.peer_area[r]);
-        p.peer_flags[r] = reinterpret_cast<uint32_t*>(static_cast<char*>(x.peer_area[r]) + x.flags_offset);
+        p.peer_slots[r] = static_cast<float2*>(x.peer_area[r]);
     }
     p.world = x.world;
     p.rank = x.rank;

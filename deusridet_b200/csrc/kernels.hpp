@@ -105,8 +105,7 @@ struct PrefillParams {
 // (exchange.cuh); world == 0: off.
 constexpr int kMaxExchangeRanks = 16;
 struct ExchangeParams {
-    float* peer_slots[kMaxExchangeRanks];       // every rank's slot area, as mapped into this process
-    uint32_t* peer_flags[kMaxExchangeRanks];    // every rank's flag array
+    float2* peer_slots[kMaxExchangeRanks];      // every rank's area of {value, sequence number} words, as mapped into this process
     int world, rank, parity;
     uint32_t seq_no;
     unsigned long long wait_ns;                 // how long a rank waits for a peer's flag before it gives up
