@@ -550,7 +550,7 @@ def run_c5a(args, collectives=None):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"c5a: {w['desc']}", "layers": L, "keys_per_gpu": end - begin,
                        "parallelism": f"kv-range-split x{world}",
-                       "collective": ("partials pushed to every rank by peer stores + per-head flags, merged in the same "
+                       "collective": ("partials pushed to every rank by peer stores as {value, call number} words, merged in the same "
                                       "kernel (no library collective)") if use_peer
                        else "nccl all_gather of Hq*(D+2) fp32 per layer",
                        "cold_cache": "inputs larger than L2: %.2f GB of K/V per layer per GPU" % (kv_rank / 1e9)},

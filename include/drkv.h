@@ -339,9 +339,9 @@ DRKV_API int drkv_attend_partial(drkv_engine* e, int layer, int seq, int kv_begi
                                  const void* q, float* part, float scale, void* stream);
 /* The same split across GPUs with the merge fused with the exchange: drkv_attend_exchange computes this
  * rank's partial over [kv_begin, kv_end) and then ONE kernel pushes it into every rank's exchange area
- * with peer stores over NVLink, raises a per-(rank, head) flag, waits (bounded: a rank that never arrives
- * ends the wait after 2 s with kernel error 4, nothing traps) for the peers' flags and writes the merged
- * output; no library collective is called.  Every rank makes the same sequence of drkv_attend_exchange
+ * with peer stores over NVLink, every value as one 64-bit {fp32 value, call number} word, polls the words the
+ * peers push (bounded: a rank that never arrives ends the wait after 2 s with kernel error 4, the outputs are
+ * left as they were, nothing traps) and writes the merged output; no library collective is called.  Every rank makes the same sequence of drkv_attend_exchange
  * calls.  Set-up: each rank (one process per GPU, same node) creates its area and gets a 64-byte CUDA IPC
  * handle, the ranks exchange handles by any host-side means, each connects to all.  No counterpart in the
  * reference, which is single-GPU. */
@@ -352,7 +352,7 @@ DRKV_API int drkv_exchange_connect(drkv_engine* e, const uint8_t* handles /* [wo
  * pointers instead of IPC handles: areas[r] = drkv_exchange_area() of rank r's engine. */
 DRKV_API int drkv_exchange_connect_local(drkv_engine* e, void* const* areas /* [world] */);
 DRKV_API void* drkv_exchange_area(const drkv_engine* e);
-/* How long the merge kernel waits for a peer's flag before it gives up with kernel error 4 (default 2000 ms). */
+/* How long the merge kernel waits for a peer's words before it gives up with kernel error 4 (default 2000 ms). */
 DRKV_API int drkv_exchange_set_wait_ms(drkv_engine* e, int ms);
 DRKV_API int drkv_exchange_destroy(drkv_engine* e);   /* after a host-side barrier: peers must be done */
 DRKV_API int drkv_attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int kv_end,
