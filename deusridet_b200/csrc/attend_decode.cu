@@ -70,13 +70,6 @@ struct alignas(16) ItemMeta {
 };
 constexpr int kItemShift = 4, kItemEntries = 8;   // a ring holds at most 6 groups, so at most 7 items are live
 
-#ifdef DRKV_WARP_TRACE
-// Debug build only: per-warp timestamps (ns) of the last launch: start, first data, last item start, end, items.
-__device__ unsigned long long g_warp_trace[148 * 8][8];   // start, first data, last item start, end, items, cycles waiting for data, cycles in item start, cycles in the issue path
-#define TRACE(i, v) do { if (lane == 0) g_warp_trace[blockIdx.x * WARPS + w][i] = (v); } while (0)
-#else
-#define TRACE(i, v) do { } while (0)
-#endif
 
 template <typename T>
 struct Mma;
@@ -253,15 +246,6 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     }
     __syncthreads();
     const int total_items = cum[n_ent];
-    TRACE(0, global_timer());
-#ifdef DRKV_WARP_TRACE
-    unsigned long long trace_items = 0;
-    bool trace_first = true;
-    long long tr_wait = 0, tr_first = 0, tr_issue = 0;
-#define TCLK() clock64()
-#else
-#define TCLK() 0ll
-#endif
 
     // ---- next-item prefetch state (warp-uniform except raw_next, which lane 0 owns) ----
     // n_state: 0 nothing requested, 1 queue index requested (atomic in flight), 2 decoded (length and
@@ -439,18 +423,12 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
         __syncwarp();
         outstanding--;
         if (++slot == DEPTH) { slot = 0; phase ^= 1; }
-        const long long ta = TCLK();
         if (c_valid && c_half == 1 && outstanding < DEPTH) issue_entry();
-        const long long tb = TCLK();
         if (!mbar_wait(bar_full + 8 * (w * DEPTH + slot), phase)) {
             if (lane == 0) atomicExch(p.error_word, (int)KERR_WAIT_FULL);
             return false;
         }
         __syncwarp();
-#ifdef DRKV_WARP_TRACE
-        tr_issue += tb - ta;
-        tr_wait += TCLK() - tb;
-#endif
         return true;
     };
 
@@ -466,7 +444,6 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
 
     while (true) {
         // ------------- issue: keep DEPTH groups in flight, across item boundaries -------------
-        const long long tc0 = TCLK();
         while (outstanding < DEPTH) {
             if (!c_valid) {
                 if (n_state == 0 && !exhausted) fetch_raw();
@@ -514,7 +491,6 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             issue_entry();
         }
         if (outstanding == 0) break;                   // queue drained and every group consumed
-        const long long tc1 = TCLK();
 
         // ------------- compute the oldest group in flight -------------
         const int ring = w * DEPTH + slot;
@@ -523,15 +499,8 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             break;
         }
         __syncwarp();
-        const long long tc2 = TCLK();
         const SlotMeta meta = metas[ring];
         const ItemMeta* item = &s_items[w][(meta.flags >> kItemShift) & (kItemEntries - 1)];
-#ifdef DRKV_WARP_TRACE
-        tr_issue += tc1 - tc0;
-        tr_wait += tc2 - tc1;
-        if (trace_first) { TRACE(1, global_timer()); trace_first = false; }
-        if (meta.flags & SLOT_FIRST) { TRACE(2, global_timer()); trace_items++; }
-#endif
         if (meta.flags & SLOT_FIRST) {
             // query rows straight into m16k16 A fragments.  Plain item: row r is query head r of the group;
             // family block: row r is head r % g of member r / g (several forked sequences share the keys).
@@ -571,15 +540,6 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                 qf[kk][1] = qr1 ? __ldg(q1 + 8 * kk) : 0u;
                 qf[kk][3] = qr1 ? __ldg(q1 + 8 * kk + 4) : 0u;
             }
-#ifdef DRKV_WARP_TRACE
-            {   // force the query loads to land here so that their latency is attributed to the item start
-                uint32_t x = 0;
-#pragma unroll
-                for (int kk = 0; kk < KSTEPS; kk++) x ^= qf[kk][0] ^ qf[kk][1] ^ qf[kk][2] ^ qf[kk][3];
-                if (x == 0x12345678u) tr_first += 1;
-                tr_first += TCLK() - tc2;
-            }
-#endif
             m2[0] = m2[1] = kNegBig;
             lsum[0] = lsum[1] = 0.f;
 #pragma unroll
@@ -769,13 +729,6 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             }
         }
     }
-#ifdef DRKV_WARP_TRACE
-    TRACE(3, global_timer());
-    TRACE(4, trace_items);
-    TRACE(5, tr_wait);
-    TRACE(6, tr_first);
-    TRACE(7, tr_issue);
-#endif
     // The last warp of the grid to leave rewinds the work queue for the next launch on this stream.
     if (lane == 0) {
         __threadfence();
@@ -1019,11 +972,6 @@ cudaError_t launch_decode_t(const CUtensorMap& tmap, const DecodeParams& p, int 
 
 }  // namespace
 
-#ifdef DRKV_WARP_TRACE
-extern "C" __attribute__((visibility("default"))) int drkv_debug_warp_trace(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_warp_trace, sizeof(g_warp_trace));
-}
-#endif
 
 // Decode's descriptor: the pool as [plane offset 0/1][head row][64-dim half][64 elements], so that one box
 // of {64, D/64, 16, 2} brings 16 key rows of one head, all dims, K and V (the V plane of a page starts

@@ -70,45 +70,6 @@ enum { BAR_KV_FULL = 0, BAR_KV_EMPTY = kPfStages, BAR_S_READY = 2 * kPfStages, B
        BAR_P_READY = BAR_S_FREE + 2, BAR_O_READY = BAR_P_READY + 2,
        BAR_XU = BAR_O_READY + 2 };   // [warp of the tile 0..3][tile]: that warp may run its exponentials
 
-#ifdef DRKV_PF_TRACE
-// Debug build only: clock cycles the first softmax warp of each tile of CTA 0 spent per phase, summed over
-// the key blocks of the last launch: wait S, load S, math, wait O, store P; then the block count.
-__device__ long long g_pf_trace[2][6];
-__device__ long long g_pf_trace_xu[2][2];   // per tile: cycles waiting for the turn at the exponential unit, cycles in the exponential loop
-__device__ long long g_pf_trace_prod[4];  // producer lane 0: wait empty, set-up, issue, blocks
-__device__ long long g_pf_trace_mma[8];
-__device__ long long g_pf_trace_fine[4];
-__device__ long long g_pf_trace_each[16];   // cycles per instruction of one QK group (8) and one PV group (4+)   // MMA thread: wait KV, wait S free 0/1, wait P 0/1, issue, blocks
-#define PF_CLK() clock64()
-#else
-#define PF_CLK() 0ll
-#endif
-
-// 2^x on the FMA pipe for x in [-126, ~9]: nearest integer by the magic-number add, degree-3 minimax of
-// 2^f on [-0.5, 0.5] (relative error 7.6e-5, below half an ulp of a bf16 or fp16 probability), exponent
-// added as an integer.  The exponential unit (16 results per clock per SM) is as loaded as the tensor
-// pipe on paper; DRKV_PF_POLY of every four pairs take this route instead.  Measured on c4: 0 -> 514,
-// 1 -> 495, 2 -> 469, 3 -> 448 TFLOP/s, i.e. the exponential unit is not what the softmax warps wait
-// for, so the default is 0.
-#ifndef DRKV_PF_POLY
-#define DRKV_PF_POLY 0
-#endif
-#ifndef DRKV_PF_XU_TURNS
-#define DRKV_PF_XU_TURNS 1
-#endif
-#ifndef DRKV_PF_WARP_ARRIVE
-#define DRKV_PF_WARP_ARRIVE 1
-#endif
-
-__device__ __forceinline__ float poly_exp2(float x) {
-    x = fmaxf(x, -126.f);
-    const float t = x + 12582912.f;                       // 1.5 * 2^23: the low mantissa bits hold round(x)
-    const float f = x - (t - 12582912.f);
-    float r = fmaf(f, 0.055205513f, 0.24261390f);
-    r = fmaf(r, f, 0.69325477f);
-    r = fmaf(r, f, 0.99992770f);
-    return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
-}
 
 template <typename T>
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -150,8 +111,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         }
         for (int x = 0; x < 2; x++) {
             mbar_init(bars + 8 * (BAR_S_READY + x), 1);
-            mbar_init(bars + 8 * (BAR_S_FREE + x), DRKV_PF_WARP_ARRIVE ? 4 : 128);     // one arrival per softmax warp of the tile
-            mbar_init(bars + 8 * (BAR_P_READY + x), DRKV_PF_WARP_ARRIVE ? 4 : 128);
+            mbar_init(bars + 8 * (BAR_S_FREE + x), 4);       // one arrival per softmax warp of the tile
+            mbar_init(bars + 8 * (BAR_P_READY + x), 4);
             mbar_init(bars + 8 * (BAR_O_READY + x), 1);
         }
         for (int i = 0; i < 8; i++) mbar_init(bars + 8 * (BAR_XU + i), 1);
@@ -199,18 +160,15 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
     if (warp == kPfProducerWarp) {
         // ------------------------------- TMA producer -------------------------------
         const int64_t rows_per_plane = (int64_t)p.num_kv_heads * p.page_size;
-        long long pt[3] = {0, 0, 0};
         for (int j = 0; j < n_blocks; j++) {
             const int s = j % kPfStages, u = j / kPfStages;
             bool ok = true;
-            const long long b0 = PF_CLK();
             if (lane == 0) ok = mbar_wait(bars + 8 * (BAR_KV_EMPTY + s), (u & 1) ^ 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) {
                 if (lane == 0) { atomicExch(p.error_word, (int)KERR_WAIT_EMPTY); s_dead = 1; }
                 break;
             }
-            const long long b1 = PF_CLK();
             uint8_t* stage = smem + PfSmem::kv + s * 2 * kPfKBytes;
             // One box per group of 16 keys: K and V rows, both 64-dim halves (8 KB), issued by lanes 0..3.
             const int my_gi = lane & 3;
@@ -238,7 +196,6 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             __syncwarp();
-            const long long b2 = PF_CLK();
             if (lane == 0) {
                 s_holes[s] = holes;
                 mbar_arrive_expect_tx(bars + 8 * (BAR_KV_FULL + s), bytes);
@@ -252,14 +209,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 tma_load_5d(smem_u32(stage) + lane * 2 * kPfOctetBytes, &tmap, 0, 0, 0, 0, (int)(row >> 3),
                             bars + 8 * (BAR_KV_FULL + s));
             }
-            pt[0] += b1 - b0; pt[1] += b2 - b1; pt[2] += PF_CLK() - b2;
         }
-#ifdef DRKV_PF_TRACE
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) {
-            for (int i = 0; i < 3; i++) g_pf_trace_prod[i] = pt[i];
-            g_pf_trace_prod[3] = n_blocks;
-        }
-#endif
     } else if (warp >= kPfMmaWarp) {
         // ------------------------------- MMA issuers -------------------------------
         // One thread per tile: warp kPfMmaWarp + x issues S = Q K^T and O += P V of tile x.  Each thread is
@@ -270,7 +220,6 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, 128, kPfBlockN, 0, 0);
             constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 128, kPfD, 0, 1);
             bool dead = false;
-            long long fine[4] = {0, 0, 0, 0};   // debug builds: cycles in QK MMAs, QK commit, PV MMAs, PV commit
             // Descriptors differ only in the start-address field of their low word (address >> 4 in bits
             // [0,14)): one add per MMA.  Between two MMAs the issuing thread executes nothing else: a run-time
             // predicate or branch per instruction costs this lone thread 20-80 cycles, more than the 32-64
@@ -288,7 +237,6 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             const uint32_t d_o = tmem_base + kPfColO + x * kPfD;
             const uint32_t pa = tmem_base + kPfColP + x * 64;           // hi at +0, lo at +32; 8 columns per 16 keys
             auto issue_qk = [&](int s) {
-                const long long f0 = PF_CLK();
                 const uint32_t kb = (kv_lo0 + s * (2 * kPfKBytes >> 4)) | kLboK;
 #pragma unroll
                 for (int kk = 0; kk < kPfD / 16; kk++) {
@@ -296,12 +244,9 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                     const uint32_t off_k = ((kk >> 2) * 1024 + (kk & 3) * 32) >> 4;     // half, then 16 dims = 32 bytes
                     umma_f16(d_s, mk(qa + off_q, kDescHiQ), mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
                 }
-                const long long f1 = PF_CLK();
                 umma_commit(bars + 8 * (BAR_S_READY + x));
-                fine[0] += f1 - f0; fine[1] += PF_CLK() - f1;
             };
             auto issue_pv = [&](int s, bool first_block) {
-                const long long f0 = PF_CLK();
                 const uint32_t vb = (kv_lo0 + s * (2 * kPfKBytes >> 4) + (2048u >> 4)) | kLboV;   // V half 0 of octet 0
                 const uint32_t acc0 = first_block ? 0u : 1u;
                 if (!use_lo) {
@@ -317,9 +262,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                         umma_f16_ts(d_o, pa + 32 + kk * 8, vdesc, idesc_pv, 1u);
                     }
                 }
-                const long long f1 = PF_CLK();
                 umma_commit(bars + 8 * (BAR_O_READY + x));
-                fine[2] += f1 - f0; fine[3] += PF_CLK() - f1;
             };
             // S(0)
             if (!mbar_wait(bars + 8 * (BAR_KV_FULL + 0), 0)) dead = true;
@@ -327,37 +270,22 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 tcgen05_fence_after();
                 issue_qk(0);
             }
-            long long mt[6] = {0, 0, 0, 0, 0, 0};
             for (int j = 0; j < n_blocks && !dead; j++) {
                 const int s = j % kPfStages;
                 // S(j+1): as soon as the softmax warps have pulled S(j) out of tensor memory
                 if (j + 1 < n_blocks) {
                     const int s1 = (j + 1) % kPfStages;
-                    const long long a0 = PF_CLK();
                     if (!mbar_wait(bars + 8 * (BAR_KV_FULL + s1), ((j + 1) / kPfStages) & 1)) { dead = true; break; }
-                    const long long a1 = PF_CLK();
                     if (!mbar_wait(bars + 8 * (BAR_S_FREE + x), j & 1)) { dead = true; break; }
-                    const long long a2 = PF_CLK();
                     tcgen05_fence_after();
                     issue_qk(s1);
-                    mt[0] += a1 - a0; mt[1] += a2 - a1; mt[5] += PF_CLK() - a2;
                 }
                 // O += P(j) V(j)
-                const long long a1 = PF_CLK();
                 if (!mbar_wait(bars + 8 * (BAR_P_READY + x), j & 1)) { dead = true; break; }
-                const long long a2 = PF_CLK();
                 tcgen05_fence_after();
                 issue_pv(s, j == 0);
-                mt[3] += a2 - a1; mt[5] += PF_CLK() - a2;
                 umma_commit(bars + 8 * (BAR_KV_EMPTY + s));        // this tile's MMAs that read the stage are done
             }
-#ifdef DRKV_PF_TRACE
-            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && x == 0) {
-                for (int i = 0; i < 6; i++) g_pf_trace_mma[i] = mt[i];
-                g_pf_trace_mma[6] = n_blocks;
-                for (int i = 0; i < 4; i++) g_pf_trace_fine[i] = fine[i];
-            }
-#endif
             if (dead) {
                 atomicExch(p.error_word, (int)KERR_WAIT_FULL);
                 s_dead = 1;
@@ -378,25 +306,17 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             const uint32_t t_p = tmem_base + lane_base + kPfColP + x * 64;
             float m_used = kNegBigPf, l = 0.f;
             bool dead = false;
-            const bool xu_turns = tile_b_active && DRKV_PF_XU_TURNS;
-            long long ph[5] = {0, 0, 0, 0, 0}, xu[2] = {0, 0};
+            const bool xu_turns = tile_b_active;
             for (int j = 0; j < n_blocks; j++) {
-                const long long c0 = PF_CLK();
                 if (!mbar_wait(bars + 8 * (BAR_S_READY + x), j & 1)) { dead = true; break; }
-                const long long c1 = PF_CLK();
                 tcgen05_fence_after();
                 float sv[2][32];
                 tmem_ld32(t_s, sv[0]);
                 tmem_ld32(t_s + 32, sv[1]);
                 tmem_wait_ld();
-                const long long c2 = PF_CLK();
                 tcgen05_fence_before();
-                if (DRKV_PF_WARP_ARRIVE) {                              // S(j+1) may overwrite the columns now
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bars + 8 * (BAR_S_FREE + x));
-                } else {
-                    mbar_arrive(bars + 8 * (BAR_S_FREE + x));
-                }
+                __syncwarp();                                           // S(j+1) may overwrite the columns now
+                if (lane == 0) mbar_arrive(bars + 8 * (BAR_S_FREE + x));
                 const int key0 = j * kPfBlockN;
                 const int holes = s_holes[j % kPfStages];
                 // Blocks left of the diagonal with all pages present need no mask: that is almost all of them.
@@ -436,11 +356,9 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 // the unit idle together while they load, take maxima and store.  They take turns instead: a warp
                 // starts its exponentials when its partner has finished the partner's, so that one's loads, maxima
                 // and stores run under the other's exponentials.
-                const long long x0c = PF_CLK();
                 if (xu_turns) {
                     if (!mbar_wait(bars + 8 * (BAR_XU + 2 * (warp & 3) + x), (uint32_t)((j & 1) ^ (x ^ 1)))) { dead = true; break; }
                 }
-                const long long x1c = PF_CLK();
                 // p = 2^(s * scale_log2 - m): one FMA and one EX2 per score
                 const float neg_m = -m_used;
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};                    // independent partial sums
@@ -448,28 +366,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 const unsigned long long negm2 = pack_f32x2(neg_m, neg_m);
                 unsigned long long sum2[4] = {0ull, 0ull, 0ull, 0ull};    // packed pairs of partial sums (+0.f, +0.f)
                 uint32_t phi[32], plo[32];
-                if (DRKV_PF_POLY > 0 && !use_lo && unmasked) {
-                    // the common block (no -inf among the scores), with DRKV_PF_POLY of every four pairs taking
-                    // their exponentials from the FMA-pipe polynomial instead of the exponential unit
-#pragma unroll
-                    for (int h = 0; h < 2; h++)
-#pragma unroll
-                        for (int c = 0; c < 32; c += 2) {
-                            float a0, a1;
-                            unpack_f32x2(fma_f32x2(pack_f32x2(sv[h][c], sv[h][c + 1]), scale2, negm2), a0, a1);
-                            const bool poly = ((c >> 1) & 3) < DRKV_PF_POLY;
-                            const float p0 = poly ? poly_exp2(a0) : fast_exp2(a0);
-                            const float p1 = poly ? poly_exp2(a1) : fast_exp2(a1);
-                            sum2[(c >> 1) & 3] = add_f32x2(sum2[(c >> 1) & 3], pack_f32x2(p0, p1));
-                            phi[h * 16 + (c >> 1)] = Elem<T>::pack2(p0, p1);
-                        }
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        float s0, s1;
-                        unpack_f32x2(sum2[i], s0, s1);
-                        sum4[i] = s0 + s1;
-                    }
-                } else if (!use_lo) {
+                if (!use_lo) {
                     // two scores per multiply-add and per add (packed fp32 pairs), one exponential each, one
                     // conversion per pair
 #pragma unroll
@@ -507,9 +404,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bars + 8 * (BAR_XU + 2 * (warp & 3) + (x ^ 1)));   // the partner's turn
                 }
-                xu[0] += x1c - x0c; xu[1] += PF_CLK() - x1c;
                 l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-                const long long c3 = PF_CLK();
                 if (j > 0) {
                     // PV(j-1) must have landed before O is touched or P is overwritten
                     if (!mbar_wait(bars + 8 * (BAR_O_READY + x), (j - 1) & 1)) { dead = true; break; }
@@ -527,29 +422,14 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                         tmem_wait_st();
                     }
                 }
-                const long long c4 = PF_CLK();
                 // P(j) into tensor memory: 64 keys = 32 packed columns (hi), then the lo term
                 tmem_st32(t_p, phi);
                 if (use_lo) tmem_st32(t_p + 32, plo);
                 tmem_wait_st();
                 tcgen05_fence_before();
-                if (DRKV_PF_WARP_ARRIVE) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bars + 8 * (BAR_P_READY + x));
-                } else {
-                    mbar_arrive(bars + 8 * (BAR_P_READY + x));
-                }
-                const long long c5 = PF_CLK();
-                ph[0] += c1 - c0; ph[1] += c2 - c1; ph[2] += c3 - c2; ph[3] += c4 - c3; ph[4] += c5 - c4;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bars + 8 * (BAR_P_READY + x));
             }
-#ifdef DRKV_PF_TRACE
-            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp & 3) == 0 && lane == 0) {
-                for (int i = 0; i < 5; i++) g_pf_trace[x][i] = ph[i];
-                g_pf_trace[x][5] = n_blocks;
-                g_pf_trace_xu[x][0] = xu[0];
-                g_pf_trace_xu[x][1] = xu[1];
-            }
-#endif
             if (!dead && !mbar_wait(bars + 8 * (BAR_O_READY + x), (n_blocks - 1) & 1)) dead = true;
             if (dead) {
                 atomicExch(p.error_word, (int)KERR_WAIT_FULL);
@@ -587,17 +467,6 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
 
 }  // namespace
 
-#ifdef DRKV_PF_TRACE
-extern "C" __attribute__((visibility("default"))) int drkv_debug_prefill_trace(long long* out) {
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_pf_trace, sizeof(g_pf_trace));
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 12, g_pf_trace_mma, sizeof(g_pf_trace_mma));
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 20, g_pf_trace_prod, sizeof(g_pf_trace_prod));
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 24, g_pf_trace_fine, sizeof(g_pf_trace_fine));
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 28, g_pf_trace_each, sizeof(g_pf_trace_each));
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 44, g_pf_trace_xu, sizeof(g_pf_trace_xu));
-    return (int)e;
-}
-#endif
 
 cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
                                   cudaStream_t stream) {
