@@ -920,6 +920,122 @@ def run_c3(args):
             "cow_copies": stats["cow_copies"]}
 
 
+def run_aux(args):
+    """The path's other kernels on one GPU, each timed alone with CUDA events on its stream over buffers larger
+    than L2: the chunk append (RoPE on K + scatter of K and V into pages), the decode append as its own launch, the
+    flat <-> paged copies, and the copy-on-write page copy.  Bytes are the algorithmic ones (read + written)."""
+    import torch
+
+    from deusridet_b200 import PagedKVEngine, build
+    build.build()
+    world, rank, local = _dist_setup()
+    dev = torch.device(f"cuda:{local}")
+    w = dict(WORKLOADS["c2"])
+    if args.layers:
+        w["layers"] = args.layers
+    L, hq, hkv, d, page = w["layers"], w["hq"], w["hkv"], w["d"], w["page"]
+    T = 8192                                                  # tokens of the one long sequence
+    n_fork = 32
+    K, W = args.steps, max(args.warmup, 1)
+    max_pages = T // page + 2 * n_fork + 72
+    eng = PagedKVEngine(num_layers=L, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
+                        rope_theta=w["theta"], max_pages=max_pages, max_seqs=n_fork + 70,
+                        max_pages_per_seq=T // page + 4, device=local)
+    stream = torch.cuda.current_stream()
+    rng = np.random.default_rng(5)
+    for p_ in [eng.alloc_block() for _ in range(max_pages)]:
+        pass
+    for p_ in rng.permutation(max_pages):
+        eng.free_block(int(p_))
+    s = eng.seq_create()
+    assert eng.ensure_blocks_for_range(s, 0, T)
+    eng.set_seq_len(s, T)
+    eng.sync_block_table(stream)
+    peak, peak_kind = peaks()
+    out = {}
+
+    def timed(fn, n_inner):
+        for _ in range(W):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(K):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (K * n_inner) * 1e3      # us per launch
+
+    def entry(kernel, us, nbytes, note):
+        gbs = nbytes / (us * 1e-6) / 1e9
+        return {"kernel": kernel, "us_per_launch": us, "bytes_per_launch": nbytes, "achieved": gbs, "unit": "GB/s",
+                "peak": peak, "peak_kind": peak_kind, "frac": gbs / peak, "note": note}
+
+    # chunk append: T tokens of one layer per launch, a different layer (source and pages) every launch
+    kn = torch.randn(L, T, hkv, d, device=dev, dtype=torch.bfloat16)
+    vn = torch.randn(L, T, hkv, d, device=dev, dtype=torch.bfloat16)
+    us = timed(lambda: [eng.append_rope_chunk(l, s, 0, T, kn[l], vn[l], stream) for l in range(L)], L)
+    out["append_chunk"] = entry("append_rope_kernel", us, 2.0 * 2 * T * hkv * d * 2,
+                                f"{T} tokens of one layer per launch: K and V rows read, rotated K and V written")
+    # flat <-> paged copies of the whole sequence, all layers in one launch each
+    flat = torch.empty(L, 2, T, hkv, d, device=dev, dtype=torch.bfloat16)
+    us = timed(lambda: eng.extract(s, 0, T, flat, stream), 1)
+    out["extract"] = entry("flat_paged_copy_kernel (pages -> flat)", us, 2.0 * flat.numel() * 2,
+                           f"{T} tokens x {L} layers, K and V, one launch")
+    us = timed(lambda: eng.inject(s, 0, T, flat, stream), 1)
+    out["inject"] = entry("flat_paged_copy_kernel (flat -> pages)", us, 2.0 * flat.numel() * 2,
+                          f"{T} tokens x {L} layers, K and V, one launch")
+    del flat, kn, vn
+    # decode append as its own launch: one token for each of 64 sequences
+    seqs = [eng.seq_create() for _ in range(64)]
+    for q_ in seqs:
+        eng.reserve(q_, 1, stream)
+    eng.sync_block_table(stream)
+    d_rows = torch.tensor(seqs, dtype=torch.int32, device=dev)
+    d_pos = torch.zeros(64, dtype=torch.int32, device=dev)
+    k1 = torch.randn(L, 64, hkv, d, device=dev, dtype=torch.bfloat16)
+    v1 = torch.randn(L, 64, hkv, d, device=dev, dtype=torch.bfloat16)
+    us = timed(lambda: [eng.append_rope(l, 64, d_rows, d_pos, k1[l], v1[l], stream) for l in range(L)], L)
+    out["append_decode"] = entry("append_rope_kernel", us, 2.0 * 2 * 64 * hkv * d * 2,
+                                 "one token for each of 64 sequences: 0.5 MB, launches issued from Python one after the other: launch-bound")
+    # copy-on-write of a shared partial tail page: all layers of one page per copy
+    root = eng.seq_create()
+    eng.reserve(root, page // 2, stream)
+    eng.set_seq_len(root, page // 2)
+    page_bytes = float(L * 2 * hkv * page * d * 2)
+    cow_us = []
+    for _ in range(W + K):
+        kids = [eng.seq_fork(root) for _ in range(n_fork)]
+        torch.cuda.synchronize()
+        c0 = eng.stats()["cow_copies"]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for k_ in kids:
+            eng.reserve(k_, 1, stream)                        # the child's write position is in the shared page
+        e1.record(stream)
+        torch.cuda.synchronize()
+        n_cow = eng.stats()["cow_copies"] - c0
+        cow_us.append(e0.elapsed_time(e1) * 1e3 / max(n_cow, 1))
+        for k_ in kids:
+            eng.seq_release(k_, True)
+    us = float(np.median(cow_us[W:]))
+    out["cow_copy"] = entry("cow_copy_kernel", us, 2.0 * page_bytes / 2,
+                            f"the filled half of one page across {L} layers per copy ({page_bytes / 2e6:.2f} MB), one "
+                            "launch per forked sequence, issued from the host one after the other: launch-bound")
+    eng.check_kernels()
+    eng.close()
+    if rank != 0:
+        return None
+    return {"metric": "achieved HBM GB/s of the secondary kernels (append, flat copies, copy-on-write)",
+            "value": out["extract"]["achieved"], "unit": "GB/s", "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": out["extract"]["us_per_launch"] / 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"aux: {L} layers, {hq}/{hkv} heads, head_dim {d}, bf16, page {page}; one "
+                                   f"{T}-token sequence, 64 one-token appends, {n_fork} forks of a half-full page",
+                       "cold_cache": "buffers larger than L2 except where a note says otherwise"},
+            "kernels": out, "gpu_launches": K * (2 * L + 2 + n_fork)}
+
+
 def eng_bytes(max_pages, w):
     return max_pages * w["layers"] * 2 * w["hkv"] * w["page"] * w["d"] * 2
 
@@ -1034,7 +1150,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["aux"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling a small case)")
     ap.add_argument("--seqs", type=int, default=0, help="override sequences per GPU (profiling a small case)")
     ap.add_argument("--chunk", type=int, default=0, help="keys per split-KV chunk (0 = automatic)")
@@ -1079,6 +1195,11 @@ def main():
         if args.workload == "c3":
             res = run_c3(args)
             if rank == 0:
+                print(json.dumps(res), flush=True)
+            return
+        if args.workload == "aux":
+            res = run_aux(args)
+            if res is not None:
                 print(json.dumps(res), flush=True)
             return
         res, (w, lens) = run_ours(args)
