@@ -830,15 +830,23 @@ def run_c3(args):
     info = eng.plan_decode(seqs, (cur + 1).tolist(), stream)
     max_kv = int(cur.max()) + 1
 
+    fused = not args.separate_append          # the new token is appended by the attention kernel's own item
+
     def planned_step():
         for l in range(L):
-            eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
-            eng.attend_decode_planned(l, q[l], out[l], scale, stream)
+            if fused:
+                eng.append_attend_decode_planned(l, kn[l], vn[l], q[l], out[l], scale, stream)
+            else:
+                eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
+                eng.attend_decode_planned(l, q[l], out[l], scale, stream)
 
     def plain_step():
         for l in range(L):
-            eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
-            eng.attend_decode(l, n_seq, d_rows, d_len, max_kv, q[l], out[l], scale, stream)
+            if fused:
+                eng.append_attend_decode(l, n_seq, d_rows, d_len, max_kv, kn[l], vn[l], q[l], out[l], scale, stream)
+            else:
+                eng.append_rope(l, n_seq, d_rows, d_pos, kn[l], vn[l], stream)
+                eng.attend_decode(l, n_seq, d_rows, d_len, max_kv, q[l], out[l], scale, stream)
 
     def timed(fn):
         for _ in range(W):
@@ -877,9 +885,12 @@ def run_c3(args):
         d_pos.copy_(h_pos, non_blocking=True)
         d_in.copy_(h_in, non_blocking=True)
         for l in range(L):
-            eng.append_rope(l, n_seq, d_rows, d_pos, d_in[l, nq:nq + nk].view(n_seq, hkv, d),
-                            d_in[l, nq + nk:].view(n_seq, hkv, d), stream)
-            eng.attend_decode_planned(l, d_in[l, :nq].view(n_seq, hq, d), out[l], scale, stream)
+            k_l, v_l = d_in[l, nq:nq + nk].view(n_seq, hkv, d), d_in[l, nq + nk:].view(n_seq, hkv, d)
+            if fused:
+                eng.append_attend_decode_planned(l, k_l, v_l, d_in[l, :nq].view(n_seq, hq, d), out[l], scale, stream)
+            else:
+                eng.append_rope(l, n_seq, d_rows, d_pos, k_l, v_l, stream)
+                eng.attend_decode_planned(l, d_in[l, :nq].view(n_seq, hq, d), out[l], scale, stream)
         h_out.copy_(out, non_blocking=True)
         stream.synchronize()
         cur[:] = cur + 1
@@ -905,6 +916,7 @@ def run_c3(args):
             "ms_per_step": plan_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"c3: {w['desc']}", "layers": L, "branches": n_seq, "plan": info,
+                       "append": "fused into the attention kernel" if fused else "its own launch",
                        "cold_cache": "the shared prefix (%.0f MB per layer) fits L2; all layers together do not"
                                      % (prefix * kv_tok / 1e6)},
             "per_sequence_pass": {"ms_per_step": plain_ms, "tokens_per_s": n_seq / (plain_ms * 1e-3),
@@ -914,7 +926,7 @@ def run_c3(args):
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                          "bytes_per_launch": unique, "bytes_read_per_launch": float(info["keys_planned_pass"]) * kv_tok,
                          "us_per_launch": plan_us},
-            "gpu_launches": K * L * 3, "clocks": clocks,
+            "gpu_launches": K * L * (2 if fused else 3), "clocks": clocks,
             "e2e": {"value": n_seq / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(h_in.numel() * 2 + n_seq * 4), "d2h_bytes_per_step": int(h_out.numel() * 2)},
             "cow_copies": stats["cow_copies"]}

@@ -105,6 +105,7 @@ SIGNATURES = {
     "drkv_plan_get_info": (_i, [_vp, C.POINTER(PlanInfo)]),
     "drkv_plan_dump": (_i, [_vp, _pi32, _i]),
     "drkv_attend_decode_planned": (_i, [_vp, _i, _vp, _vp, _f, _vp]),
+    "drkv_append_attend_decode_planned": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _f, _vp]),
     "drkv_tier_enable": (_i, [_vp, C.c_char_p]),
     "drkv_tier_disable": (_i, [_vp]),
     "drkv_tier_prefetch": (_i, [_vp, _i, _i]),

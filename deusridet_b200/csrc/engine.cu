@@ -1165,6 +1165,30 @@ int drkv_attend_decode_planned(drkv_engine* e, int layer, const void* q, void* o
                          scale, (cudaStream_t)stream, &pl);
 }
 
+int drkv_append_attend_decode_planned(drkv_engine* e, int layer, const void* k_src, const void* v_src, const void* q,
+                                      void* out, float scale, void* stream) {
+    NEED(e);
+    NEED_DEVICE(e);
+    if (layer < 0 || layer >= e->geom.num_layers || !k_src || !v_src || !q || !out)
+        return set_err(DRKV_ERR_INVALID, "append_attend_decode_planned: bad argument");
+    const drkv_engine::Plan& pl = e->plan;
+    if (!pl.valid) return set_err(DRKV_ERR_INVALID, "append_attend_decode_planned: no decode plan");
+    if (pl.n_seq == 0 || pl.max_chunks == 0) return DRKV_OK;
+    const bool fused = fused_append_supported(e);
+    if (!fused) {
+        note_stream(e, (cudaStream_t)stream);
+        AppendParams ap = append_params(e, layer);
+        ap.rows = pl.rows;
+        ap.pos = pl.kv_len;
+        ap.pos_bias = -1;                   // the new token sits at kv_len - 1
+        ap.k_src = k_src;
+        ap.v_src = v_src;
+        CUDA_TRY(launch_append_rope(ap, pl.n_seq, e->geom.dtype, (cudaStream_t)stream));
+    }
+    return decode_common(e, layer, pl.n_seq, pl.rows, pl.kv_len, 0, 0, 0, pl.max_chunks * pl.chunk, q, out, nullptr,
+                         scale, (cudaStream_t)stream, &pl, nullptr, 0, fused ? k_src : nullptr, fused ? v_src : nullptr);
+}
+
 // ---- storage tier --------------------------------------------------------------------------
 int drkv_tier_enable(drkv_engine* e, const char* dir) {
     NEED(e);

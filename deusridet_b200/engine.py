@@ -186,6 +186,10 @@ class PagedKVEngine:
                 "fb_members": buf[3 * ns + 2 * nb:].reshape(nb, 16)}
     def attend_decode_planned(self, layer, q, out, scale, stream=None) -> None:
         check(self.lib.drkv_attend_decode_planned(self.h, layer, _ptr(q), _ptr(out), scale, _stream(stream)))
+    def append_attend_decode_planned(self, layer, k_src, v_src, q, out, scale, stream=None) -> None:
+        """The planned pass with each entry's new token (position kv_len - 1 of the plan) appended in the same call."""
+        check(self.lib.drkv_append_attend_decode_planned(self.h, layer, _ptr(k_src), _ptr(v_src), _ptr(q), _ptr(out),
+                                                         scale, _stream(stream)))
     # ---- storage tier (KVSwapper + CacheManager swap paths) -----------------------------------
     def tier_enable(self, directory: str) -> None: check(self.lib.drkv_tier_enable(self.h, directory.encode()))
     def tier_disable(self) -> None: check(self.lib.drkv_tier_disable(self.h))

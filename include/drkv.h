@@ -260,6 +260,13 @@ DRKV_API int drkv_plan_dump(const drkv_engine* e, int32_t* out, int cap);
 /* q/out [n_seq][num_q_heads][head_dim] in the plan's batch order. */
 DRKV_API int drkv_attend_decode_planned(drkv_engine* e, int layer, const void* q, void* out,
                                         float scale, void* stream);
+/* The planned pass with the append of each entry's new token in the same call, as drkv_append_attend_decode does
+ * for the per-sequence pass: the plan's lengths count the token, whose position is kv_len - 1; k_src / v_src
+ * [n_seq][num_kv_heads][head_dim] in the plan's batch order.  The token always falls into an item of its own
+ * sequence (the chunks a family shares are whole chunks of cached keys), which rotates K, writes both rows into the
+ * page and attends over them. */
+DRKV_API int drkv_append_attend_decode_planned(drkv_engine* e, int layer, const void* k_src, const void* v_src,
+                                               const void* q, void* out, float scale, void* stream);
 /* ---- storage tier behind the pool --------------------------------------------------------------
  * KVSwapper (kv_swapper.h:52-120, kv_swapper.cpp:179-300) and CacheManager's swap paths
  * (cache_manager.cpp:132-141, 215-292): with a tier enabled, a page that a sequence evicts from

@@ -122,6 +122,67 @@ def test_planned_pass_matches_checker_and_per_sequence_pass(drkv_lib, oracle, ca
         eng.close()
 
 
+@pytest.mark.parametrize("case", [CASES[0], CASES[1], CASES[3], CASES[4], CASES[5]],
+                         ids=lambda c: f"hq{c[0]}kv{c[1]}d{c[2]}p{c[3]}{c[4]}c{c[7]}")
+def test_planned_pass_with_the_append_in_the_same_call(drkv_lib, oracle, case):
+    """Every branch decodes one token: room is reserved (copy-on-write of a shared partial tail page), the plan
+    counts the token, and one call per layer appends it and attends.  Pool bytes must equal the checker's append
+    bit for bit and the outputs its attention within 2e-3; head_dim 256 takes the append kernel in front."""
+    import torch
+    from deusridet_b200 import PagedKVEngine
+
+    ob = oracle
+    hq, hkv, d, page, dt, families, singles, chunk = case
+    dtype = ob.BF16 if dt == "bf16" else ob.F16
+    tdt = torch.bfloat16 if dt == "bf16" else torch.float16
+    layers, max_pages, width = 2, 400, 64
+    rng = np.random.default_rng(hq * 1000 + d + page + 1)
+    eng = PagedKVEngine(num_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype=dt,
+                        rope_theta=1e6, max_pages=max_pages, max_seqs=64, max_pages_per_seq=width, device=0)
+    g = ob.geom(layers, hq, hkv, d, page, dtype, d, 1e6)
+    try:
+        H.shuffled_free_stack(eng, rng)
+        seqs, lens = _build_batch(eng, rng, page, families, singles)
+        n = len(seqs)
+        for sq in seqs:
+            eng.reserve(sq, 1)                                   # a page of its own where the token lands
+        torch.cuda.synchronize()
+        pool_host = H.randn_bits(rng, ob.pool_elems(g, max_pages), dtype)
+        eng.pool_tensor().copy_(torch.from_numpy(pool_host.view(np.int16)))
+        eng.sync_block_table()
+        tables = np.full((n, eng.table_stride()), -1, dtype=np.int32)
+        for i, sq in enumerate(seqs):
+            t = eng.table(sq)
+            tables[i, :len(t)] = t
+        if chunk:
+            eng.set_chunk_tokens(chunk)
+        new_lens = [x + 1 for x in lens]
+        info = eng.plan_decode(seqs, new_lens)
+        assert info["n_families"] == len(families)
+        scale = 1.0 / np.sqrt(d)
+        for layer in range(layers):
+            q = H.randn_bits(rng, (n, hq, d), dtype)
+            k_new = H.randn_bits(rng, (n, hkv, d), dtype)
+            v_new = H.randn_bits(rng, (n, hkv, d), dtype)
+            got = torch.zeros(n, hq, d, dtype=tdt, device="cuda")
+            eng.append_attend_decode_planned(layer, H.to_dev(k_new, dtype), H.to_dev(v_new, dtype), H.to_dev(q, dtype),
+                                             got, scale)
+            torch.cuda.synchronize()
+            eng.check_kernels()
+            for i in range(n):
+                ob.append(g, pool_host, max_pages, tables[i], layer, lens[i], 1, k_new[i], v_new[i], rope=True)
+            want = np.zeros((n, hq, d), dtype=np.uint16)
+            ob.attend_decode(g, pool_host, max_pages, tables, np.arange(n), np.array(new_lens, dtype=np.int32), layer,
+                             q, want, scale)
+            got_pool = eng.pool_tensor().cpu().numpy().view(np.uint16)
+            assert np.array_equal(got_pool, pool_host), f"layer {layer}: pool bytes differ after the append"
+            ref = ob.to_float(want, dtype)
+            err = np.abs(ob.to_float(H.torch_bits(got), dtype) - ref)
+            assert (err <= np.maximum(2e-3, H.ulp(ref, dtype))).all(), f"layer {layer}: {err.max()}"
+    finally:
+        eng.close()
+
+
 def test_plan_without_families_is_the_per_sequence_pass(drkv_lib, oracle):
     import torch
     from deusridet_b200 import PagedKVEngine
