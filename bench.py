@@ -336,12 +336,17 @@ def run_ours(args):
                 d_in[l].copy_(h_in[l], non_blocking=True)
                 ev_in[l].record(s_in)
 
-        def e2e_step():
-            eng.reserve_batch(seq_arr, 1, stream)       # allocate (copy-on-write aware) room for one token each
+        def prepare_next():
+            # Room for the next token of every sequence (copy-on-write aware), the changed table rows and the
+            # positions: none of it depends on the token being sampled, so it is issued behind the running step
+            # (stream order keeps it after that step's kernels) instead of in front of the next one.
+            eng.reserve_batch(seq_arr, 1, stream)
             eng.sync_block_table(stream)
             h_pos.copy_(torch.from_numpy(cur))
             d_pos.copy_(h_pos, non_blocking=True)
             torch.add(d_pos, 1, out=d_len)
+
+        def e2e_step():
             mk = int(cur.max()) + 1
             for l in range(min(AHEAD, L)):
                 send(l)
@@ -355,11 +360,13 @@ def run_ours(args):
                     s_out.wait_event(ev_out[l])
                     h_out[l].copy_(out[l], non_blocking=True)
             ev_done.record(s_out)
-            ev_done.synchronize()                       # the caller samples from the outputs before the next token
-            stream.synchronize()
             cur[:] = cur + 1
             eng.advance_batch(seq_arr, 1)
+            prepare_next()
+            ev_done.synchronize()                       # the caller samples from the outputs before the next token
+            stream.synchronize()
 
+        prepare_next()
         for _ in range(W):
             e2e_step()
         barrier()
@@ -877,12 +884,16 @@ def run_c3(args):
     h_out = torch.empty(out.shape, dtype=torch.bfloat16).pin_memory()
     h_pos = torch.empty(n_seq, dtype=torch.int32).pin_memory()
 
-    def e2e_step():
+    def prepare_next():
+        # room for every branch's next token (copy-on-write of a shared tail page), changed table rows, the plan
+        # and the positions: independent of the token being sampled, so issued behind the running step
         eng.reserve_batch(seq_arr, 1, stream)
         eng.sync_block_table(stream)
         eng.plan_decode(seqs, (cur + 1).tolist(), stream)
         h_pos.copy_(torch.from_numpy(cur))
         d_pos.copy_(h_pos, non_blocking=True)
+
+    def e2e_step():
         d_in.copy_(h_in, non_blocking=True)
         for l in range(L):
             k_l, v_l = d_in[l, nq:nq + nk].view(n_seq, hkv, d), d_in[l, nq + nk:].view(n_seq, hkv, d)
@@ -892,10 +903,12 @@ def run_c3(args):
                 eng.append_rope(l, n_seq, d_rows, d_pos, k_l, v_l, stream)
                 eng.attend_decode_planned(l, d_in[l, :nq].view(n_seq, hq, d), out[l], scale, stream)
         h_out.copy_(out, non_blocking=True)
-        stream.synchronize()
         cur[:] = cur + 1
         eng.advance_batch(seq_arr, 1)
+        prepare_next()
+        stream.synchronize()
 
+    prepare_next()
     for _ in range(W):
         e2e_step()
     torch.cuda.synchronize()
