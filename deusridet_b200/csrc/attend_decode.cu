@@ -43,14 +43,17 @@ constexpr float kNegBig = -1.0e30f;                            // "no key seen y
 // Ring geometry per head_dim: consumer warps per CTA and slots per warp ring.  At head_dim 128 a warp
 // has one 8 KB gather landing while it computes the previous one: 148 SMs x 8 warps x 8 KB = 9.7 MB in
 // flight, about bandwidth x loaded latency.  A third slot per warp (19 MB in flight) made the pass over
-// long items 8 % slower: the memory system serves fewer, not more, concurrent streams better.  At 64 and
-// 256 the pass is bound by the instruction stream of the warps, not by the loads in flight (measured:
-// 2 to 6 slots within 1 %).  At 256 a ring entry holds ONE plane (kSplit): the K and the V rows of a group
+// long items 8 % slower, and so do more warps with two slots each (12 warps: c2 +4 %, one long sequence +12 %;
+// only a short launch over few items gains, c3 -13 %): the memory system serves fewer, not more, concurrent
+// streams better.  At 64 and 256 the pass is bound by the instruction stream of the warps, not by the loads in
+// flight (2 to 6 slots within 1 %): at 64, where a slot is 4 KB and the registers allow it, sixteen warps with two
+// slots each run 45 % faster than eight with six (4.0 -> 5.8 TB/s on a 64-sequence batch, 4.3 -> 6.3 on one long
+// sequence).  At 256 a ring entry holds ONE plane (kSplit): the K and the V rows of a group
 // are separate 8 KB gathers, three entries per warp, so that eight warps fit (192 KB) where whole groups
 // of 16 KB allowed six; the warp releases a group's K entry after the softmax, sends the next gather and
 // only then waits for the group's V entry.
 template <int D> struct RingShape;
-template <> struct RingShape<64>  { static constexpr int kWarps = 8, kDepth = 6; static constexpr bool kSplit = false; };
+template <> struct RingShape<64>  { static constexpr int kWarps = 16, kDepth = 2; static constexpr bool kSplit = false; };
 template <> struct RingShape<128> { static constexpr int kWarps = 8, kDepth = 2; static constexpr bool kSplit = false; };
 template <> struct RingShape<256> { static constexpr int kWarps = 8, kDepth = 3; static constexpr bool kSplit = true; };
 
