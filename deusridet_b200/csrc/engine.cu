@@ -825,7 +825,7 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     // queued last and in 64-key pieces, so that the warps finish within a piece of one another.
     int tail_chunks = 0, tail_split = 1;
     {
-        const long warps = (long)e->num_sms * decode_warps_per_cta(g.head_dim), streams = (long)n_seq * g.num_kv_heads;
+        const long warps = (long)e->num_sms * decode_warps_per_cta(g.head_dim, plan && plan->n_fb > 0), streams = (long)n_seq * g.num_kv_heads;
         const long items = streams * max_chunks;
         const bool forced = e->tail_mode > 0 && chunk >= 32 && chunk % 32 == 0;
         const bool automatic = e->tail_mode < 0 && chunk >= 128 && chunk % 64 == 0 && items >= 3 * warps;
@@ -1059,7 +1059,16 @@ int drkv_plan_decode(drkv_engine* e, int n_seq, const int32_t* seqs, const int32
     };
     int chunk = e->forced_chunk;
     if (!chunk) {
-        chunk = pick_chunk_by_cost(group, (long)e->num_sms * decode_warps_per_cta(e->geom.head_dim), true, [&](int c) { return (long)planned_items(c, nullptr); });
+        auto items = [&](int c) { return (long)planned_items(c, nullptr); };
+        auto blocks_at = [&](int c) {
+            for (const Fam& f : fams)
+                if (f.shared_tokens / c > 0) return true;
+            return false;
+        };
+        // a pass with family blocks runs on more warps per CTA (head_dim 128): pick the chunk for the CTA it will get
+        chunk = pick_chunk_by_cost(group, (long)e->num_sms * decode_warps_per_cta(e->geom.head_dim, !fams.empty()), true, items);
+        if (!fams.empty() && !blocks_at(chunk))
+            chunk = pick_chunk_by_cost(group, (long)e->num_sms * decode_warps_per_cta(e->geom.head_dim, false), true, items);
     }
     if (e->has_device) {
         auto need_bytes = [&](int c) {

@@ -152,7 +152,8 @@ bool make_pool_slot_tensor_map(CUtensorMap* out, const void* pool, int num_layer
 cudaError_t launch_attend_decode(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, int head_dim,
                                  int dtype, cudaStream_t stream);
 constexpr int kMaxDecodeSeqs = 2048;   // sequences one decode-attention launch can take
-int decode_warps_per_cta(int head_dim);  // warps of one decode CTA, each with its own queue of items
+// warps of one decode CTA, each with its own queue of items; family_blocks: the pass has shared-prefix family blocks
+int decode_warps_per_cta(int head_dim, bool family_blocks = false);
 // The prefill kernel's descriptor (head_dim 128): 5-D view whose one box is 16 key rows x both 64-dim halves x (K, V),
 // landing in 8-row groups of 128 bytes ordered [octet of 8 keys][plane][half].
 bool make_pool_kv16_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
