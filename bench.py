@@ -893,15 +893,19 @@ def run_c3(args):
         h_pos.copy_(torch.from_numpy(cur))
         d_pos.copy_(h_pos, non_blocking=True)
 
+    eq = [d_in[l, :nq].view(n_seq, hq, d) for l in range(L)]                 # views made once, not per step
+    ek = [d_in[l, nq:nq + nk].view(n_seq, hkv, d) for l in range(L)]
+    ev = [d_in[l, nq + nk:].view(n_seq, hkv, d) for l in range(L)]
+    eo = [out[l] for l in range(L)]
+
     def e2e_step():
         d_in.copy_(h_in, non_blocking=True)
         for l in range(L):
-            k_l, v_l = d_in[l, nq:nq + nk].view(n_seq, hkv, d), d_in[l, nq + nk:].view(n_seq, hkv, d)
             if fused:
-                eng.append_attend_decode_planned(l, k_l, v_l, d_in[l, :nq].view(n_seq, hq, d), out[l], scale, stream)
+                eng.append_attend_decode_planned(l, ek[l], ev[l], eq[l], eo[l], scale, stream)
             else:
-                eng.append_rope(l, n_seq, d_rows, d_pos, k_l, v_l, stream)
-                eng.attend_decode_planned(l, d_in[l, :nq].view(n_seq, hq, d), out[l], scale, stream)
+                eng.append_rope(l, n_seq, d_rows, d_pos, ek[l], ev[l], stream)
+                eng.attend_decode_planned(l, eq[l], eo[l], scale, stream)
         h_out.copy_(out, non_blocking=True)
         cur[:] = cur + 1
         eng.advance_batch(seq_arr, 1)
