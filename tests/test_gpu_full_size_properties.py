@@ -216,3 +216,67 @@ def test_chunked_prefill_at_full_size(drkv_lib, oracle):
         eng.check_kernels()
     finally:
         eng.close()
+
+
+def test_forked_branches_at_full_size(drkv_lib, oracle):
+    """Eight decode branches forked from one 16 384-token prompt (minus five tokens, so that the shared tail page is
+    partial and every branch copies it on its first write), private tails of U[0, 2048] tokens, 32/8 heads, head_dim
+    128, bf16, page 16 (the prefix-sharing configuration), 2 of its 32 identical layers: the planned pass, which reads
+    the shared pages once per 16 query rows, with the append inside it, must give what the per-sequence pass gives,
+    and the CPU checker agrees on the shortest and the longest branch."""
+    import torch
+    from deusridet_b200 import PagedKVEngine
+
+    ob = oracle
+    layers, hq, hkv, d, page, dtype, prefix, n = 2, 32, 8, 128, 16, ob.BF16, 16384 - 5, 8
+    rng = np.random.default_rng(79)
+    private = rng.integers(0, 2049, size=n)
+    max_pages = (prefix + page - 1) // page + int(sum((int(x) + 2 * page + 16) // page for x in private)) + 16
+    width = (prefix + int(private.max())) // page + 4
+    eng = PagedKVEngine(num_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
+                        rope_theta=1e6, max_pages=max_pages, max_seqs=n, max_pages_per_seq=width, device=0)
+    g = ob.geom(layers, hq, hkv, d, page, dtype, d, 1e6)
+    try:
+        H.shuffled_free_stack(eng, rng)
+        root = eng.seq_create()
+        eng.reserve(root, prefix)
+        eng.set_seq_len(root, prefix)
+        seqs = [root] + [eng.seq_fork(root) for _ in range(n - 1)]
+        assert int(eng.refcounts().max()) == n                         # the prompt's pages are shared by all eight
+        lens = []
+        for s, x in zip(seqs, private):
+            eng.reserve(s, int(x) + 1)                                  # private tail + room for the token being decoded
+            eng.set_seq_len(s, prefix + int(x))
+            lens.append(prefix + int(x))
+        assert eng.stats()["cow_copies"] >= n - 1                       # every branch but the last holder copied the tail page
+        torch.cuda.synchronize()
+        eng.sync_block_table()
+        torch.manual_seed(8)
+        eng.pool_tensor().view(torch.bfloat16).normal_()
+        lens = np.asarray(lens, dtype=np.int32)
+        info = eng.plan_decode(seqs, (lens + 1).tolist())
+        assert info["n_families"] == 1 and info["keys_planned_pass"] < info["keys_per_sequence_pass"] // 3
+        rows = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+        d_len = torch.from_numpy(lens + 1).cuda()
+        scale = 1.0 / np.sqrt(d)
+        layer = 1
+        q = torch.randn(n, hq, d, dtype=torch.bfloat16, device="cuda")
+        k_new = torch.randn(n, hkv, d, dtype=torch.bfloat16, device="cuda")
+        v_new = torch.randn(n, hkv, d, dtype=torch.bfloat16, device="cuda")
+        planned = torch.zeros(n, hq, d, dtype=torch.bfloat16, device="cuda")
+        eng.append_attend_decode_planned(layer, k_new, v_new, q, planned, scale)
+        plain = torch.zeros_like(planned)
+        eng.attend_decode(layer, n, rows, d_len, int(lens.max()) + 1, q, plain, scale)   # the token is in the pool by now
+        torch.cuda.synchronize()
+        eng.check_kernels()
+        assert (planned.float() - plain.float()).abs().max().item() <= TOL
+        pool_host = H.torch_bits(eng.pool_tensor())
+        sample = sorted({int(np.argmin(lens)), int(np.argmax(lens))})
+        tables = np.stack([eng.table(seqs[i]) for i in sample])
+        want = np.zeros((len(sample), hq, d), dtype=np.uint16)
+        ob.attend_decode(g, pool_host, max_pages, tables, np.arange(len(sample)), (lens[sample] + 1).astype(np.int32), layer,
+                         H.torch_bits(q[sample]), want, scale)
+        err = np.abs(ob.to_float(H.torch_bits(planned[sample]), dtype) - ob.to_float(want, dtype)).max()
+        assert err <= TOL, err
+    finally:
+        eng.close()
