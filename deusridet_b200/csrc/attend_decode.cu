@@ -152,7 +152,12 @@ __device__ __noinline__ void fused_append_prepare(const T* ksrc, const T* vsrc, 
 // EXT compiles in the two extensions that cost the plain pass time when merely present: shared-prefix
 // family blocks and the per-tile masses of the importance scorer.
 // WARPS: consumer warps per CTA; RingShape<D>::kWarps except for passes over family blocks at head_dim 128.
-template <typename T, int D, bool HI, bool EXT, int WARPS>
+// LO: P enters PV as two terms, its value rounded to the storage type and the residue of that rounding (about 16
+// significant bits together).  Without it P has the storage type's precision, as in the prefill kernel: enough
+// once a row sees more than kLoTermMaxKeys keys, whose residues average out far below the tolerance.  Only the
+// head_dim 256 pass, which is bound by its warps' instruction stream, has the variant without (9 % faster); the
+// host asks for it when it knows that every row of the launch sees more keys than that.
+template <typename T, int D, bool HI, bool EXT, int WARPS, bool LO = true>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams p) {
     constexpr int DEPTH = RingShape<D>::kDepth;
@@ -645,8 +650,14 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     if (mass_row[r] >= 0)
                         p.tile_lse[mass_row[r] + (meta.tok0 / kGroupTokens) * p.group * 4] = ts > 0.f ? mnew + __log2f(ts) : -INFINITY;
                 }
-                split_pack<T>(p0, p1, phi[r], plo[r]);          // a0 (r=0) / a1 (r=1)
-                split_pack<T>(p8, p9, phi[2 + r], plo[2 + r]);  // a2 / a3
+                if (LO) {
+                    split_pack<T>(p0, p1, phi[r], plo[r]);          // a0 (r=0) / a1 (r=1)
+                    split_pack<T>(p8, p9, phi[2 + r], plo[2 + r]);  // a2 / a3
+                } else {
+                    phi[r] = Elem<T>::pack2(p0, p1);
+                    phi[2 + r] = Elem<T>::pack2(p8, p9);
+                    plo[r] = plo[2 + r] = 0u;
+                }
             }
             if (!HI) { phi[1] = phi[3] = plo[1] = plo[3] = 0u; }
             if (SPLIT) {
@@ -674,15 +685,15 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     ldmatrix_x4_trans(vb, vbase + swz_seg16(key, c));
                     if (HI) {
                         Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], phi[0], phi[1], phi[2], phi[3], vb[0], vb[1]);
-                        Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[0], vb[1]);
+                        if (LO) Mma<T>::run(o[j][0], o[j][1], o[j][2 * NR - 2], o[j][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[0], vb[1]);
                         Mma<T>::run(o[j + 1][0], o[j + 1][1], o[j + 1][2 * NR - 2], o[j + 1][2 * NR - 1], phi[0], phi[1], phi[2], phi[3], vb[2], vb[3]);
-                        Mma<T>::run(o[j + 1][0], o[j + 1][1], o[j + 1][2 * NR - 2], o[j + 1][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[2], vb[3]);
+                        if (LO) Mma<T>::run(o[j + 1][0], o[j + 1][1], o[j + 1][2 * NR - 2], o[j + 1][2 * NR - 1], plo[0], plo[1], plo[2], plo[3], vb[2], vb[3]);
                     } else {
                         float z0 = 0.f, z1 = 0.f;   // rows 8..15 are padding: their sums are discarded
                         Mma<T>::run(o[j][0], o[j][1], z0, z1, phi[0], 0u, phi[2], 0u, vb[0], vb[1]);
-                        Mma<T>::run(o[j][0], o[j][1], z0, z1, plo[0], 0u, plo[2], 0u, vb[0], vb[1]);
+                        if (LO) Mma<T>::run(o[j][0], o[j][1], z0, z1, plo[0], 0u, plo[2], 0u, vb[0], vb[1]);
                         Mma<T>::run(o[j + 1][0], o[j + 1][1], z0, z1, phi[0], 0u, phi[2], 0u, vb[2], vb[3]);
-                        Mma<T>::run(o[j + 1][0], o[j + 1][1], z0, z1, plo[0], 0u, plo[2], 0u, vb[2], vb[3]);
+                        if (LO) Mma<T>::run(o[j + 1][0], o[j + 1][1], z0, z1, plo[0], 0u, plo[2], 0u, vb[2], vb[3]);
                     }
                 }
             }
@@ -944,7 +955,7 @@ combine_external_kernel(int n_parts, const float* parts, int hq, int D, void* ou
     }
 }
 
-template <typename T, int D, bool HI, bool EXT, int WARPS = RingShape<D>::kWarps>
+template <typename T, int D, bool HI, bool EXT, int WARPS = RingShape<D>::kWarps, bool LO = true>
 cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
     constexpr int DEPTH = RingShape<D>::kDepth, NH = D / 64;
     constexpr size_t smem = 1024 + (size_t)WARPS * DEPTH * ((RingShape<D>::kSplit ? 1 : 2) * NH * 2048 + sizeof(SlotMeta) + sizeof(uint64_t)) +
@@ -955,13 +966,13 @@ cudaError_t launch_decode_hi(const CUtensorMap& tmap, const DecodeParams& p, int
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-        e = cudaFuncSetAttribute(attend_decode_kernel<T, D, HI, EXT, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(attend_decode_kernel<T, D, HI, EXT, WARPS, LO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     int grid = (p.total_items + WARPS - 1) / WARPS;
     if (grid > num_sms) grid = num_sms;
-    return launch_pdl(attend_decode_kernel<T, D, HI, EXT, WARPS>, dim3(grid), dim3(WARPS * 32), smem, stream, tmap, p);
+    return launch_pdl(attend_decode_kernel<T, D, HI, EXT, WARPS, LO>, dim3(grid), dim3(WARPS * 32), smem, stream, tmap, p);
 }
 
 // A pass over family blocks (branches of one prompt: a short launch over few items, its shared pages partly read
@@ -972,6 +983,12 @@ constexpr int kFamilyWarps128 = 12;
 template <typename T, int D>
 cudaError_t launch_decode_t(const CUtensorMap& tmap, const DecodeParams& p, int num_sms, cudaStream_t stream) {
     const bool ext = p.n_fb > 0 || p.tile_lse != nullptr;
+    if constexpr (D == 256) {
+        if (p.few_keys_possible == 0 && !ext)
+            return (p.group > 8 || p.rows_per_item > 8)
+                       ? launch_decode_hi<T, D, true, false, RingShape<D>::kWarps, false>(tmap, p, num_sms, stream)
+                       : launch_decode_hi<T, D, false, false, RingShape<D>::kWarps, false>(tmap, p, num_sms, stream);
+    }
     if constexpr (D == 128) {
         if (p.n_fb > 0)
             return (p.group > 8 || p.rows_per_item > 8)

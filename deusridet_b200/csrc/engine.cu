@@ -142,7 +142,7 @@ struct drkv_engine {
     // shared-prefix decode plan: device arrays in one allocation, uploaded from two pinned buffers
     struct Plan {
         bool valid = false;
-        int n_seq = 0, n_fb = 0, n_fam = 0, chunk = 0, max_chunks = 0, rows_per_item = 0;
+        int n_seq = 0, n_fb = 0, n_fam = 0, chunk = 0, max_chunks = 0, rows_per_item = 0, min_kv = 0;
         int64_t keys_seq = 0, keys_plan = 0;
         const int32_t *rows = nullptr, *kv_len = nullptr, *first_chunk = nullptr;
         const int32_t *fb_row = nullptr, *fb_chunks = nullptr, *fb_members = nullptr;
@@ -865,6 +865,11 @@ static int decode_common(drkv_engine* e, int layer, int n_seq, const int32_t* d_
     p.tail_chunks = tail_chunks;
     p.tail_split = tail_split;
     p.n_seq = n_seq;
+    // Lengths given on the host (one sequence, a range of it, the tokens of a chunk: every entry sees at least kv_end
+    // keys once its partials are merged) or known from the plan: the pass may leave out the residue term of P.
+    p.few_keys_possible = 1;
+    if (d_kv_len == nullptr && kv_end > 1024) p.few_keys_possible = 0;
+    if (plan && plan->min_kv > 1024) p.few_keys_possible = 0;
     p.total_items = n_seq * g.num_kv_heads * max_chunks;
     if (plan && plan->n_fb > 0) {
         p.n_fb = plan->n_fb;
@@ -1128,6 +1133,8 @@ int drkv_plan_decode(drkv_engine* e, int n_seq, const int32_t* seqs, const int32
     pl.n_fam = n_fam;
     pl.chunk = chunk;
     pl.max_chunks = (max_kv + chunk - 1) / chunk;
+    pl.min_kv = n_seq > 0 ? kv_len[0] : 0;
+    for (int i = 1; i < n_seq; i++) pl.min_kv = kv_len[i] < pl.min_kv ? kv_len[i] : pl.min_kv;
     pl.rows_per_item = max_members * group;
     pl.keys_seq = keys_seq;
     planned_items(chunk, &pl.keys_plan);

@@ -59,6 +59,7 @@ struct DecodeParams {
     int chunk_tokens, max_chunks;
     int tail_chunks, tail_split;   // last tail_chunks chunks of a sequence go as tail_split pieces each (0: off)
     int n_seq;
+    int few_keys_possible;    // 0: the host knows that every row of the launch sees more than 1 024 keys; else 1
     // shared-prefix plan (all null / 0 without one): family block k covers chunks [0, fb_chunks[k]) of table
     // row fb_row[k] for the batch entries fb_members[16 k + i] (-1 = none); sequence b starts at chunk
     // seq_first_chunk[b].  rows_per_item: query rows a family block fills (members * group), else 0.

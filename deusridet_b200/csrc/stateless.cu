@@ -93,6 +93,7 @@ int stateless_decode(const drkv_geometry* g, const void* q, const void* kv_pool,
     p.chunk_tokens = chunk;
     p.max_chunks = max_chunks;
     p.n_seq = 1;
+    p.few_keys_possible = seq_len > 1024 ? 0 : 1;       // the length comes from the host: see DecodeParams
     p.total_items = g->num_kv_heads * max_chunks;
     p.work_counter = header;
     p.exit_count = header + 2;

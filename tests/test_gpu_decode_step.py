@@ -195,3 +195,53 @@ def test_fused_append_into_a_hole_writes_nothing(drkv_lib, oracle):
     rows stay as they were; the other sequence is unaffected."""
     _decode_case(oracle, layers=1, hq=16, hkv=4, d=128, page=16, dtype=oracle.BF16, theta=1e4, lens=[5, 900], seed=10,
                  holes=1, holes_first_only=True, fused=True)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+def test_head_dim_256_with_lengths_known_on_the_host(drkv_lib, oracle, dt):
+    """A plan gives the lengths on the host; when every sequence has more than 1 024 keys the head_dim 256 pass
+    feeds P to the PV product in the storage type alone (no residue term).  Same bound against the CPU checker, and
+    within it of the pass that takes its lengths from the device and keeps the term."""
+    import torch
+    from deusridet_b200 import PagedKVEngine
+
+    ob = oracle
+    dtype = ob.BF16 if dt == "bf16" else ob.F16
+    tdt = torch.bfloat16 if dt == "bf16" else torch.float16
+    layers, hq, hkv, d, page = 1, 24, 4, 256, 256
+    lens = np.array([1500, 3000, 1025, 5000], dtype=np.int32)
+    n = len(lens)
+    rng = np.random.default_rng(256)
+    max_pages = int(sum((int(x) + page - 1) // page for x in lens)) + 4
+    eng = PagedKVEngine(num_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype=dt,
+                        rotary_dim=64, rope_theta=1e7, max_pages=max_pages, max_seqs=n, max_pages_per_seq=24, device=0)
+    g = ob.geom(layers, hq, hkv, d, page, dtype, 64, 1e7)
+    try:
+        H.shuffled_free_stack(eng, rng)
+        seqs = [eng.seq_create() for _ in range(n)]
+        for s, x in zip(seqs, lens):
+            assert eng.ensure_blocks_for_range(s, 0, int(x))
+            eng.set_seq_len(s, int(x))
+        eng.sync_block_table()
+        pool_host = H.randn_bits(rng, ob.pool_elems(g, max_pages), dtype)
+        eng.pool_tensor().copy_(torch.from_numpy(pool_host.view(np.int16)))
+        tables = np.stack([eng.table(s) for s in seqs])
+        q = H.randn_bits(rng, (n, hq, d), dtype)
+        scale = 1.0 / np.sqrt(d)
+        eng.plan_decode(seqs, lens.tolist())
+        planned = torch.zeros(n, hq, d, dtype=tdt, device="cuda")
+        eng.attend_decode_planned(0, H.to_dev(q, dtype), planned, scale)
+        rows = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+        d_len = torch.from_numpy(lens).cuda()
+        plain = torch.zeros_like(planned)
+        eng.attend_decode(0, n, rows, d_len, int(lens.max()), H.to_dev(q, dtype), plain, scale)
+        torch.cuda.synchronize()
+        eng.check_kernels()
+        want = np.zeros((n, hq, d), dtype=np.uint16)
+        ob.attend_decode(g, pool_host, max_pages, tables, np.arange(n), lens, 0, q, want, scale)
+        ref = ob.to_float(want, dtype)
+        assert np.abs(ob.to_float(H.torch_bits(planned), dtype) - ref).max() <= TOL
+        assert np.abs(ob.to_float(H.torch_bits(plain), dtype) - ref).max() <= TOL
+        assert (planned.float() - plain.float()).abs().max().item() <= TOL
+    finally:
+        eng.close()
