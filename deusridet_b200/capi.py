@@ -95,6 +95,7 @@ SIGNATURES = {
     "drkv_table_stride": (_i, [_vp]),
     "drkv_kernel_error": (_i, [_vp]),
     "drkv_set_tail_split": (_i, [_vp, _i]),
+    "drkv_set_prefill_on_decode_kernel": (_i, [_vp, _i]),
     "drkv_set_chunk_tokens": (_i, [_vp, _i]),
     "drkv_kernel_timing": (_i, [_vp, _i, C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "drkv_append_rope": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),

@@ -1087,8 +1087,8 @@ bool make_pool_kv16_tensor_map(CUtensorMap* out, const void* pool, int num_layer
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
-    if (head_dim != 128) {
-        if (err) *err = "the tensor-core prefill kernel is built for head_dim 128";
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) {
+        if (err) *err = "the tensor-core prefill kernel is built for head_dim 64, 128 and 256";
         return false;
     }
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr) {
@@ -1102,9 +1102,10 @@ bool make_pool_kv16_tensor_map(CUtensorMap* out, const void* pool, int num_layer
         if (err) *err = "pool has more than 2^31 head rows: not addressable by one TMA descriptor";
         return false;
     }
-    cuuint64_t gdim[5] = {64, 8, 2, 2, (cuuint64_t)((rows - plane_rows) / 8)};
+    const cuuint32_t halves = (cuuint32_t)(head_dim / 64);          // 64-element (128-byte) runs of a head row
+    cuuint64_t gdim[5] = {64, 8, halves, 2, (cuuint64_t)((rows - plane_rows) / 8)};
     cuuint64_t gstride[4] = {(cuuint64_t)head_dim * 2, 128, (cuuint64_t)plane_rows * head_dim * 2, (cuuint64_t)8 * head_dim * 2};
-    cuuint32_t box[5] = {64, 8, 2, 2, 2};
+    cuuint32_t box[5] = {64, 8, halves, 2, 2};
     cuuint32_t estride[5] = {1, 1, 1, 1, 1};
     CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 5, const_cast<void*>(pool), gdim, gstride, box, estride,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

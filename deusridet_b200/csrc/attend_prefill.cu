@@ -3,11 +3,13 @@
 // Replaces paged_prefill_attention_kernel (src/machina/paged_attention.cu:465-554): one CTA per
 // (query head, query token), each re-streaming every earlier key with scalar loads.  Here the
 // m tokens of a chunk times the g query heads of a GQA group form the rows of 128-row tiles; a
-// CTA owns two such tiles of one KV head and walks the keys 0 .. pos_start + t in blocks of 64:
-//     S = Q K^T   tcgen05.mma  M128 x N64  x K128   (A = Q tile, B = K block, both K-major in smem)
+// CTA owns two such tiles of one KV head (one at head_dim 256) and walks the keys 0 .. pos_start + t in
+// blocks of 64, for head dims D = 64, 128 and 256 (the reference's own model is 24/4 heads x 256):
+//     S = Q K^T   tcgen05.mma  M128 x N64 x K=D   (A = Q tile, B = K block, both K-major in smem)
 //     P = softmax piece (fp32 in registers, one row per thread, read from TMEM with tcgen05.ld)
-//     O += P V    tcgen05.mma  M128 x N128 x K64    (A = P in tensor memory, B = V block, MN-major)
-// with the S and O accumulators and P in tensor memory (2 x (64 + 128 + 64) = all 512 columns).
+//     O += P V    tcgen05.mma  M128 x N=D x K64   (A = P in tensor memory, B = V block, MN-major)
+// with the S and O accumulators and P in tensor memory (D = 128: 2 x (64 + 128 + 64) = all 512 columns;
+// D = 256: 64 + 256 + 64 of one tile).
 // P is stored as a two-term split (hi + lo, 32 packed columns each); the lo term is multiplied in
 // only by CTAs whose rows see at most 1024 keys, where single-term 16-bit weights would cost more
 // than the 2e-3 bound on rows dominated by a handful of keys.  One thread per tile
@@ -16,7 +18,7 @@
 // brings their K and V rows, all dims: the issue rate of copy instructions, not HBM, bounds a producer that
 // sends twelve 2-4 KB boxes per block), eight softmax warps (four per tile, one row per thread) do the
 // arithmetic, the two warps that share a scheduler taking turns at the exponential unit; the
-// K/V block fetched by TMA is used by 256 query rows.  O stays in
+// K/V block fetched by TMA is used by 256 query rows (128 at head_dim 256).  O stays in
 // TMEM across key blocks and is rescaled there only when a row's running maximum has grown by
 // more than 2^8 since the scale in use was chosen; the final division by l undoes the stale
 // scale.  Same recurrence and mask as the reference: token t sees keys [0, pos_start + t],
@@ -33,93 +35,97 @@ namespace drkv {
 
 namespace {
 
-constexpr int kPfD = 128;                      // head_dim handled by this kernel
 constexpr int kPfBlockN = 64;                  // keys per block
-constexpr int kPfStages = 4;                   // K/V blocks in flight
 constexpr int kPfSoftmaxWarps = 8;             // 4 per tile
 constexpr int kPfProducerWarp = 8;
 constexpr int kPfMmaWarp = 9;
 constexpr int kPfThreads = 11 * 32;           // 8 softmax warps, TMA producer, one MMA issuer per tile
 constexpr int kPfTmemCols = 512;
-constexpr int kPfQBytes = 128 * kPfD * 2;      // one Q tile: [2 halves][128 rows][128 B]
-constexpr int kPfKBytes = kPfBlockN * kPfD * 2;   // K (or V) bytes of one block
-// A stage holds a block as eight "octets" of 8 keys, each [K half 0][K half 1][V half 0][V half 1] x [8 rows][128 B]
-// (4 KB): the image of the 5-D box {64 elements, 8 rows, 2 halves, 2 planes, 2 octets} that brings 16 keys.  The
-// 8-row groups of any one (plane, half) are then 4 KB apart throughout the block, which is what one stride field
-// of an MMA operand descriptor can express.
-constexpr int kPfOctetBytes = 4096;
 constexpr int kPfLoTermMaxKeys = 1024;         // CTAs that see at most this many keys add the lo term of P
 constexpr int kPfMaxTableSlice = 4096;         // block-table entries staged in shared memory
 constexpr float kPfRescaleThreshold = 8.0f;    // log2 units
 constexpr float kNegBigPf = -1.0e30f;          // "no key seen yet"
 
-struct PfSmem {
-    // byte offsets from the 1024-aligned base
-    static constexpr int q = 0;                                        // 2 tiles
-    static constexpr int kv = q + 2 * kPfQBytes;                       // stages x (K | V)
-    static constexpr int pages = kv + kPfStages * 2 * kPfKBytes;       // int[kPfMaxTableSlice]
-    static constexpr int holes = pages + kPfMaxTableSlice * 4;         // int[kPfStages]
-    static constexpr int bars = holes + 16;                            // uint64[...]
-    static constexpr int n_bars = 2 * kPfStages + 8 + 8;
-    static constexpr int tmem = bars + n_bars * 8;                     // uint32 holder
+// What depends on the head dim D (64, 128, 256).  Two 128-row tiles per CTA up to D = 128; at 256 the O accumulator
+// of one tile takes 256 of the 512 tensor-memory columns and a CTA has one tile.
+template <int D>
+struct PfShape {
+    static constexpr int kTiles = D <= 128 ? 2 : 1;
+    static constexpr int kHalves = D / 64;                              // 64-dim (128-byte) runs of a head row
+    static constexpr int kStages = D <= 128 ? 4 : 2;                    // K/V blocks in flight
+    static constexpr int kQBytes = 128 * D * 2;                         // one Q tile: [halves][128 rows][128 B]
+    static constexpr int kKBytes = kPfBlockN * D * 2;                   // K (or V) bytes of one block
+    // A stage holds a block as eight "octets" of 8 keys, each [K half 0 ..][V half 0 ..] x [8 rows][128 B]: the image
+    // of the 5-D box {64 elements, 8 rows, halves, 2 planes, 2 octets} that brings 16 keys.  The 8-row groups of any
+    // one (plane, half) are then one octet apart throughout the block, which is what one stride field of an MMA
+    // operand descriptor can express.
+    static constexpr int kOctetBytes = 2 * kHalves * 1024;
+    // shared memory: byte offsets from the 1024-aligned base
+    static constexpr int q = 0;                                         // the tiles
+    static constexpr int kv = q + kTiles * kQBytes;                     // stages x (K | V)
+    static constexpr int pages = kv + kStages * 2 * kKBytes;            // int[kPfMaxTableSlice]
+    static constexpr int holes = pages + kPfMaxTableSlice * 4;          // int[kStages]
+    static constexpr int bars = holes + 16;                             // uint64[...]
+    static constexpr int n_bars = 2 * kStages + 8 + 8;
+    static constexpr int tmem = bars + n_bars * 8;                      // uint32 holder
     static constexpr int total = tmem + 16;
+    // barrier indices
+    static constexpr int BAR_KV_FULL = 0, BAR_KV_EMPTY = kStages, BAR_S_READY = 2 * kStages, BAR_S_FREE = BAR_S_READY + 2,
+                         BAR_P_READY = BAR_S_FREE + 2, BAR_O_READY = BAR_P_READY + 2,
+                         BAR_XU = BAR_O_READY + 2;   // [warp of the tile 0..3][tile]: that warp may run its exponentials
+    // tensor-memory columns: S of the tiles, O of the tiles, P (hi | lo) of the tiles
+    static constexpr uint32_t kColS = 0, kColO = 2 * kPfBlockN, kColP = 2 * kPfBlockN + kTiles * D;
 };
 
-// barrier indices
-enum { BAR_KV_FULL = 0, BAR_KV_EMPTY = kPfStages, BAR_S_READY = 2 * kPfStages, BAR_S_FREE = BAR_S_READY + 2,
-       BAR_P_READY = BAR_S_FREE + 2, BAR_O_READY = BAR_P_READY + 2,
-       BAR_XU = BAR_O_READY + 2 };   // [warp of the tile 0..3][tile]: that warp may run its exponentials
 
-
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(kPfThreads, 1)
 attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ PrefillParams p) {
+    using Sh = PfShape<D>;
     // one sequence of the batch per grid.z; sequences with fewer tiles than grid.x leave the extra CTAs idle
     const int p_m = p.m[blockIdx.z], p_pos_start = p.pos_start[blockIdx.z], p_row = p.row[blockIdx.z];
-    if ((int)blockIdx.x * 2 * (128 / p.group) >= p_m) return;
+    if ((int)blockIdx.x * Sh::kTiles * (128 / p.group) >= p_m) return;
     const void* const p_q = p.q[blockIdx.z];
     void* const p_out = p.out[blockIdx.z];
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
-    int* s_pages = reinterpret_cast<int*>(smem + PfSmem::pages);
-    volatile int* s_holes = reinterpret_cast<volatile int*>(smem + PfSmem::holes);
-    const uint32_t bars = sbase + PfSmem::bars;
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + PfSmem::tmem);
+    int* s_pages = reinterpret_cast<int*>(smem + Sh::pages);
+    volatile int* s_holes = reinterpret_cast<volatile int*>(smem + Sh::holes);
+    const uint32_t bars = sbase + Sh::bars;
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + Sh::tmem);
     __shared__ int s_dead;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = p.group, kvh = blockIdx.y;
     const int tok_per_tile = 128 / g;
     const int rows_used = tok_per_tile * g;
-    const int t0 = blockIdx.x * 2 * tok_per_tile;                       // first chunk token of tile A
-    const int t_end = min(t0 + 2 * tok_per_tile, p_m);                  // one past the last token of the CTA
-    const bool tile_b_active = t0 + tok_per_tile < p_m;
+    const int t0 = blockIdx.x * Sh::kTiles * tok_per_tile;              // first chunk token of tile A
+    const int t_end = min(t0 + Sh::kTiles * tok_per_tile, p_m);         // one past the last token of the CTA
+    const bool tile_b_active = Sh::kTiles == 2 && t0 + tok_per_tile < p_m;
     const int kv_hi = p_pos_start + t_end;                              // keys any row of this CTA may see
     const int n_blocks = (kv_hi + kPfBlockN - 1) / kPfBlockN;
     const int n_groups = (kv_hi + 15) / 16;
     constexpr int fmt = Elem<T>::kUmmaFormat;
     const bool use_lo = kv_hi <= kPfLoTermMaxKeys;
-    // tensor-memory columns: S of both tiles, O of both tiles, P (hi | lo) of both tiles
-    constexpr uint32_t kPfColS = 0, kPfColO = 2 * kPfBlockN, kPfColP = 2 * kPfBlockN + 2 * kPfD;
 
     if (tid == 0) {
         s_dead = 0;
-        for (int s = 0; s < kPfStages; s++) {
-            mbar_init(bars + 8 * (BAR_KV_FULL + s), 1);
-            mbar_init(bars + 8 * (BAR_KV_EMPTY + s), tile_b_active ? 2 : 1);   // one commit per issuing thread
+        for (int s = 0; s < Sh::kStages; s++) {
+            mbar_init(bars + 8 * (Sh::BAR_KV_FULL + s), 1);
+            mbar_init(bars + 8 * (Sh::BAR_KV_EMPTY + s), tile_b_active ? 2 : 1);   // one commit per issuing thread
         }
         for (int x = 0; x < 2; x++) {
-            mbar_init(bars + 8 * (BAR_S_READY + x), 1);
-            mbar_init(bars + 8 * (BAR_S_FREE + x), 4);       // one arrival per softmax warp of the tile
-            mbar_init(bars + 8 * (BAR_P_READY + x), 4);
-            mbar_init(bars + 8 * (BAR_O_READY + x), 1);
+            mbar_init(bars + 8 * (Sh::BAR_S_READY + x), 1);
+            mbar_init(bars + 8 * (Sh::BAR_S_FREE + x), 4);       // one arrival per softmax warp of the tile
+            mbar_init(bars + 8 * (Sh::BAR_P_READY + x), 4);
+            mbar_init(bars + 8 * (Sh::BAR_O_READY + x), 1);
         }
-        for (int i = 0; i < 8; i++) mbar_init(bars + 8 * (BAR_XU + i), 1);
+        for (int i = 0; i < 8; i++) mbar_init(bars + 8 * (Sh::BAR_XU + i), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
     }
-    if (warp == kPfMmaWarp) tmem_alloc(sbase + PfSmem::tmem, kPfTmemCols);
+    if (warp == kPfMmaWarp) tmem_alloc(sbase + Sh::tmem, kPfTmemCols);
     pdl_wait();                                  // Q, the pool and the table may come from the preceding kernel
     pdl_launch_dependents();
 
@@ -142,10 +148,10 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         const int x = warp >> 2, r = (warp & 3) * 32 + lane;
         const int t = t0 + x * tok_per_tile + r / g;
         const bool valid = r < rows_used && t < p_m;
-        const T* src = reinterpret_cast<const T*>(p_q) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * kPfD;
-        uint8_t* dst = smem + PfSmem::q + x * kPfQBytes;
+        const T* src = reinterpret_cast<const T*>(p_q) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * D;
+        uint8_t* dst = smem + Sh::q + x * Sh::kQBytes;
 #pragma unroll
-        for (int c = 0; c < kPfD / 8; c++) {
+        for (int c = 0; c < D / 8; c++) {
             Vec16 v = {{0u, 0u, 0u, 0u}};
             if (valid) v = ldg16(src + 8 * c);
             *reinterpret_cast<Vec16*>(dst + (c >> 3) * (128 * 128) + swz(r, c & 7)) = v;
@@ -161,15 +167,15 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         // ------------------------------- TMA producer -------------------------------
         const int64_t rows_per_plane = (int64_t)p.num_kv_heads * p.page_size;
         for (int j = 0; j < n_blocks; j++) {
-            const int s = j % kPfStages, u = j / kPfStages;
+            const int s = j % Sh::kStages, u = j / Sh::kStages;
             bool ok = true;
-            if (lane == 0) ok = mbar_wait(bars + 8 * (BAR_KV_EMPTY + s), (u & 1) ^ 1);
+            if (lane == 0) ok = mbar_wait(bars + 8 * (Sh::BAR_KV_EMPTY + s), (u & 1) ^ 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) {
                 if (lane == 0) { atomicExch(p.error_word, (int)KERR_WAIT_EMPTY); s_dead = 1; }
                 break;
             }
-            uint8_t* stage = smem + PfSmem::kv + s * 2 * kPfKBytes;
+            uint8_t* stage = smem + Sh::kv + s * 2 * Sh::kKBytes;
             // One box per group of 16 keys: K and V rows, both 64-dim halves (8 KB), issued by lanes 0..3.
             const int my_gi = lane & 3;
             int page = -1;
@@ -185,20 +191,20 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 }
             }
             const int holes = (int)(__ballot_sync(0xffffffffu, page < 0) & 0xfu);      // lanes 0..3 hold groups 0..3
-            const uint32_t bytes = (uint32_t)(4 - __popc(holes)) * (2u * kPfKBytes / 4u);
+            const uint32_t bytes = (uint32_t)(4 - __popc(holes)) * (2u * Sh::kKBytes / 4u);
             if (holes) {
                 // nothing will be loaded there: give the MMAs zeros instead of stale shared memory
                 for (int g4 = 0; g4 < 4; g4++) {
                     if (!((holes >> g4) & 1)) continue;
-                    for (int i = lane; i < 2 * kPfOctetBytes / 16; i += 32)
-                        *reinterpret_cast<Vec16*>(stage + g4 * 2 * kPfOctetBytes + 16 * i) = Vec16{{0u, 0u, 0u, 0u}};
+                    for (int i = lane; i < 2 * Sh::kOctetBytes / 16; i += 32)
+                        *reinterpret_cast<Vec16*>(stage + g4 * 2 * Sh::kOctetBytes + 16 * i) = Vec16{{0u, 0u, 0u, 0u}};
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             __syncwarp();
             if (lane == 0) {
                 s_holes[s] = holes;
-                mbar_arrive_expect_tx(bars + 8 * (BAR_KV_FULL + s), bytes);
+                mbar_arrive_expect_tx(bars + 8 * (Sh::BAR_KV_FULL + s), bytes);
             }
             __syncwarp();
             if (lane < 4 && page >= 0) {
@@ -206,8 +212,8 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 // K-plane row of the group's first key, in octets of 8 rows (a multiple of 8: pages hold multiples of 16)
                 const int64_t row = (((int64_t)p.layer * p.max_pages + page) * 2) * rows_per_plane +
                                     (int64_t)kvh * p.page_size + (tok % p.page_size);
-                tma_load_5d(smem_u32(stage) + lane * 2 * kPfOctetBytes, &tmap, 0, 0, 0, 0, (int)(row >> 3),
-                            bars + 8 * (BAR_KV_FULL + s));
+                tma_load_5d(smem_u32(stage) + lane * 2 * Sh::kOctetBytes, &tmap, 0, 0, 0, 0, (int)(row >> 3),
+                            bars + 8 * (Sh::BAR_KV_FULL + s));
             }
         }
     } else if (warp >= kPfMmaWarp) {
@@ -218,36 +224,36 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
         const int x = warp - kPfMmaWarp;
         if (lane == 0 && (x == 0 || tile_b_active)) {
             constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, 128, kPfBlockN, 0, 0);
-            constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 128, kPfD, 0, 1);
+            constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, 128, D, 0, 1);
             bool dead = false;
             // Descriptors differ only in the start-address field of their low word (address >> 4 in bits
             // [0,14)): one add per MMA.  Between two MMAs the issuing thread executes nothing else: a run-time
             // predicate or branch per instruction costs this lone thread 20-80 cycles, more than the 32-64
             // cycles of tensor work an instruction carries.
             constexpr uint32_t kDescHiQ = (1024u >> 4) | (1u << 14) | (2u << 29);    // Q: 8-row groups 1 KB apart, version 1, 128-byte swizzle
-            constexpr uint32_t kDescHi = ((uint32_t)kPfOctetBytes >> 4) | (1u << 14) | (2u << 29);   // K, V: 8-row groups one octet apart
+            constexpr uint32_t kDescHi = ((uint32_t)Sh::kOctetBytes >> 4) | (1u << 14) | (2u << 29);   // K, V: 8-row groups one octet apart
             constexpr uint32_t kLboK = (16u >> 4) << 16;                            // K-major operands
             // V, MN-major: the next 64-dim run (the other half) is 1 KB on; 16 keys = two octets
             constexpr uint32_t kLboV = (1024u >> 4) << 16;
-            constexpr uint32_t v_step = (2u * kPfOctetBytes) >> 4;                   // from one group of 16 keys to the next
+            constexpr uint32_t v_step = (2u * Sh::kOctetBytes) >> 4;                   // from one group of 16 keys to the next
             auto mk = [](uint32_t lo, uint32_t hi) -> uint64_t { return ((uint64_t)hi << 32) | lo; };
-            const uint32_t qa = ((((sbase + PfSmem::q) & 0x3FFFFu) >> 4) | kLboK) + x * (kPfQBytes >> 4);
-            const uint32_t kv_lo0 = ((sbase + PfSmem::kv) & 0x3FFFFu) >> 4;
-            const uint32_t d_s = tmem_base + kPfColS + x * kPfBlockN;
-            const uint32_t d_o = tmem_base + kPfColO + x * kPfD;
-            const uint32_t pa = tmem_base + kPfColP + x * 64;           // hi at +0, lo at +32; 8 columns per 16 keys
+            const uint32_t qa = ((((sbase + Sh::q) & 0x3FFFFu) >> 4) | kLboK) + x * (Sh::kQBytes >> 4);
+            const uint32_t kv_lo0 = ((sbase + Sh::kv) & 0x3FFFFu) >> 4;
+            const uint32_t d_s = tmem_base + Sh::kColS + x * kPfBlockN;
+            const uint32_t d_o = tmem_base + Sh::kColO + x * D;
+            const uint32_t pa = tmem_base + Sh::kColP + x * 64;           // hi at +0, lo at +32; 8 columns per 16 keys
             auto issue_qk = [&](int s) {
-                const uint32_t kb = (kv_lo0 + s * (2 * kPfKBytes >> 4)) | kLboK;
+                const uint32_t kb = (kv_lo0 + s * (2 * Sh::kKBytes >> 4)) | kLboK;
 #pragma unroll
-                for (int kk = 0; kk < kPfD / 16; kk++) {
+                for (int kk = 0; kk < D / 16; kk++) {
                     const uint32_t off_q = ((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4;
                     const uint32_t off_k = ((kk >> 2) * 1024 + (kk & 3) * 32) >> 4;     // half, then 16 dims = 32 bytes
                     umma_f16(d_s, mk(qa + off_q, kDescHiQ), mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
                 }
-                umma_commit(bars + 8 * (BAR_S_READY + x));
+                umma_commit(bars + 8 * (Sh::BAR_S_READY + x));
             };
             auto issue_pv = [&](int s, bool first_block) {
-                const uint32_t vb = (kv_lo0 + s * (2 * kPfKBytes >> 4) + (2048u >> 4)) | kLboV;   // V half 0 of octet 0
+                const uint32_t vb = (kv_lo0 + s * (2 * Sh::kKBytes >> 4) + ((Sh::kHalves * 1024u) >> 4)) | kLboV;   // V half 0 of octet 0
                 const uint32_t acc0 = first_block ? 0u : 1u;
                 if (!use_lo) {
                     umma_f16_ts(d_o, pa, mk(vb, kDescHi), idesc_pv, acc0);
@@ -262,29 +268,29 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                         umma_f16_ts(d_o, pa + 32 + kk * 8, vdesc, idesc_pv, 1u);
                     }
                 }
-                umma_commit(bars + 8 * (BAR_O_READY + x));
+                umma_commit(bars + 8 * (Sh::BAR_O_READY + x));
             };
             // S(0)
-            if (!mbar_wait(bars + 8 * (BAR_KV_FULL + 0), 0)) dead = true;
+            if (!mbar_wait(bars + 8 * (Sh::BAR_KV_FULL + 0), 0)) dead = true;
             if (!dead) {
                 tcgen05_fence_after();
                 issue_qk(0);
             }
             for (int j = 0; j < n_blocks && !dead; j++) {
-                const int s = j % kPfStages;
+                const int s = j % Sh::kStages;
                 // S(j+1): as soon as the softmax warps have pulled S(j) out of tensor memory
                 if (j + 1 < n_blocks) {
-                    const int s1 = (j + 1) % kPfStages;
-                    if (!mbar_wait(bars + 8 * (BAR_KV_FULL + s1), ((j + 1) / kPfStages) & 1)) { dead = true; break; }
-                    if (!mbar_wait(bars + 8 * (BAR_S_FREE + x), j & 1)) { dead = true; break; }
+                    const int s1 = (j + 1) % Sh::kStages;
+                    if (!mbar_wait(bars + 8 * (Sh::BAR_KV_FULL + s1), ((j + 1) / Sh::kStages) & 1)) { dead = true; break; }
+                    if (!mbar_wait(bars + 8 * (Sh::BAR_S_FREE + x), j & 1)) { dead = true; break; }
                     tcgen05_fence_after();
                     issue_qk(s1);
                 }
                 // O += P(j) V(j)
-                if (!mbar_wait(bars + 8 * (BAR_P_READY + x), j & 1)) { dead = true; break; }
+                if (!mbar_wait(bars + 8 * (Sh::BAR_P_READY + x), j & 1)) { dead = true; break; }
                 tcgen05_fence_after();
                 issue_pv(s, j == 0);
-                umma_commit(bars + 8 * (BAR_KV_EMPTY + s));        // this tile's MMAs that read the stage are done
+                umma_commit(bars + 8 * (Sh::BAR_KV_EMPTY + s));        // this tile's MMAs that read the stage are done
             }
             if (dead) {
                 atomicExch(p.error_word, (int)KERR_WAIT_FULL);
@@ -301,14 +307,14 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             const int limit = valid ? p_pos_start + t + 1 : 0;          // keys [0, limit) are visible to this row
             const int tile_min_limit = p_pos_start + t0 + x * tok_per_tile + 1;
             const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-            const uint32_t t_s = tmem_base + lane_base + kPfColS + x * kPfBlockN;
-            const uint32_t t_o = tmem_base + lane_base + kPfColO + x * kPfD;
-            const uint32_t t_p = tmem_base + lane_base + kPfColP + x * 64;
+            const uint32_t t_s = tmem_base + lane_base + Sh::kColS + x * kPfBlockN;
+            const uint32_t t_o = tmem_base + lane_base + Sh::kColO + x * D;
+            const uint32_t t_p = tmem_base + lane_base + Sh::kColP + x * 64;
             float m_used = kNegBigPf, l = 0.f;
             bool dead = false;
             const bool xu_turns = tile_b_active;
             for (int j = 0; j < n_blocks; j++) {
-                if (!mbar_wait(bars + 8 * (BAR_S_READY + x), j & 1)) { dead = true; break; }
+                if (!mbar_wait(bars + 8 * (Sh::BAR_S_READY + x), j & 1)) { dead = true; break; }
                 tcgen05_fence_after();
                 float sv[2][32];
                 tmem_ld32(t_s, sv[0]);
@@ -316,9 +322,9 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 tmem_wait_ld();
                 tcgen05_fence_before();
                 __syncwarp();                                           // S(j+1) may overwrite the columns now
-                if (lane == 0) mbar_arrive(bars + 8 * (BAR_S_FREE + x));
+                if (lane == 0) mbar_arrive(bars + 8 * (Sh::BAR_S_FREE + x));
                 const int key0 = j * kPfBlockN;
-                const int holes = s_holes[j % kPfStages];
+                const int holes = s_holes[j % Sh::kStages];
                 // Blocks left of the diagonal with all pages present need no mask: that is almost all of them.
                 const bool unmasked = (key0 + kPfBlockN <= tile_min_limit) && holes == 0;
                 if (!unmasked) {
@@ -357,7 +363,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 // starts its exponentials when its partner has finished the partner's, so that one's loads, maxima
                 // and stores run under the other's exponentials.
                 if (xu_turns) {
-                    if (!mbar_wait(bars + 8 * (BAR_XU + 2 * (warp & 3) + x), (uint32_t)((j & 1) ^ (x ^ 1)))) { dead = true; break; }
+                    if (!mbar_wait(bars + 8 * (Sh::BAR_XU + 2 * (warp & 3) + x), (uint32_t)((j & 1) ^ (x ^ 1)))) { dead = true; break; }
                 }
                 // p = 2^(s * scale_log2 - m): one FMA and one EX2 per score
                 const float neg_m = -m_used;
@@ -402,16 +408,16 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 }
                 if (xu_turns) {
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bars + 8 * (BAR_XU + 2 * (warp & 3) + (x ^ 1)));   // the partner's turn
+                    if (lane == 0) mbar_arrive(bars + 8 * (Sh::BAR_XU + 2 * (warp & 3) + (x ^ 1)));   // the partner's turn
                 }
                 l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
                 if (j > 0) {
                     // PV(j-1) must have landed before O is touched or P is overwritten
-                    if (!mbar_wait(bars + 8 * (BAR_O_READY + x), (j - 1) & 1)) { dead = true; break; }
+                    if (!mbar_wait(bars + 8 * (Sh::BAR_O_READY + x), (j - 1) & 1)) { dead = true; break; }
                     tcgen05_fence_after();
                     if (__any_sync(0xffffffffu, need)) {
 #pragma unroll 1
-                        for (int c0 = 0; c0 < kPfD; c0 += 32) {
+                        for (int c0 = 0; c0 < D; c0 += 32) {
                             float ov[32];
                             tmem_ld32(t_o + c0, ov);
                             tmem_wait_ld();
@@ -428,18 +434,18 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 tmem_wait_st();
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bars + 8 * (BAR_P_READY + x));
+                if (lane == 0) mbar_arrive(bars + 8 * (Sh::BAR_P_READY + x));
             }
-            if (!dead && !mbar_wait(bars + 8 * (BAR_O_READY + x), (n_blocks - 1) & 1)) dead = true;
+            if (!dead && !mbar_wait(bars + 8 * (Sh::BAR_O_READY + x), (n_blocks - 1) & 1)) dead = true;
             if (dead) {
                 atomicExch(p.error_word, (int)KERR_WAIT_FULL);
                 s_dead = 1;
             } else {
                 tcgen05_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
-                T* orow = reinterpret_cast<T*>(p_out) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * kPfD;
+                T* orow = reinterpret_cast<T*>(p_out) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * D;
 #pragma unroll 1
-                for (int c0 = 0; c0 < kPfD; c0 += 32) {
+                for (int c0 = 0; c0 < D; c0 += 32) {
                     float ov[32];
                     tmem_ld32(t_o + c0, ov);
                     tmem_wait_ld();
@@ -468,29 +474,46 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
 }  // namespace
 
 
-cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
-                                  cudaStream_t stream) {
-    if (p.n_seq <= 0) return cudaSuccess;
-    if (head_dim != kPfD || p.group < 1 || p.group > 16 || p.page_size % 16 != 0) return cudaErrorInvalidValue;
-    constexpr size_t smem = 1024 + PfSmem::total;
-    const int tok_per_tile = 128 / p.group;
-    int max_m = 0;
-    for (int i = 0; i < p.n_seq; i++) max_m = p.m[i] > max_m ? p.m[i] : max_m;
-    if (max_m <= 0 || p.n_seq > kMaxPrefillSeqs) return max_m <= 0 ? cudaSuccess : cudaErrorInvalidValue;
-    dim3 grid((max_m + 2 * tok_per_tile - 1) / (2 * tok_per_tile), p.num_kv_heads, p.n_seq);
-    static std::atomic<bool> configured[2][64];   // any thread may be the first caller
+namespace {
+
+template <typename T, int D>
+cudaError_t launch_prefill_d(const CUtensorMap& tmap, const PrefillParams& p, int max_m, cudaStream_t stream) {
+    using Sh = PfShape<D>;
+    constexpr size_t smem = 1024 + Sh::total;
+    const int tok_per_cta = Sh::kTiles * (128 / p.group);
+    dim3 grid((max_m + tok_per_cta - 1) / tok_per_cta, p.num_kv_heads, p.n_seq);
+    static std::atomic<bool> configured[64];      // per instantiation and device; any thread may be the first caller
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    const int ti = dtype == DRKV_DTYPE_F16 ? 0 : 1;
-    if (dev < 0 || dev >= 64 || !configured[ti][dev].load(std::memory_order_acquire)) {
-        e = ti == 0 ? cudaFuncSetAttribute(attend_prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                    : cudaFuncSetAttribute(attend_prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+        e = cudaFuncSetAttribute(attend_prefill_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[ti][dev].store(true, std::memory_order_release);
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
-    if (ti == 0) return launch_pdl(attend_prefill_kernel<__half>, grid, dim3(kPfThreads), smem, stream, tmap, p);
-    return launch_pdl(attend_prefill_kernel<__nv_bfloat16>, grid, dim3(kPfThreads), smem, stream, tmap, p);
+    return launch_pdl(attend_prefill_kernel<T, D>, grid, dim3(kPfThreads), smem, stream, tmap, p);
+}
+
+}  // namespace
+
+cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
+                                  cudaStream_t stream) {
+    if (p.n_seq <= 0) return cudaSuccess;
+    if (p.group < 1 || p.group > 16 || p.page_size % 16 != 0) return cudaErrorInvalidValue;
+    int max_m = 0;
+    for (int i = 0; i < p.n_seq; i++) max_m = p.m[i] > max_m ? p.m[i] : max_m;
+    if (max_m <= 0 || p.n_seq > kMaxPrefillSeqs) return max_m <= 0 ? cudaSuccess : cudaErrorInvalidValue;
+    const bool f16 = dtype == DRKV_DTYPE_F16;
+    switch (head_dim) {
+        case 64:
+            return f16 ? launch_prefill_d<__half, 64>(tmap, p, max_m, stream) : launch_prefill_d<__nv_bfloat16, 64>(tmap, p, max_m, stream);
+        case 128:
+            return f16 ? launch_prefill_d<__half, 128>(tmap, p, max_m, stream) : launch_prefill_d<__nv_bfloat16, 128>(tmap, p, max_m, stream);
+        case 256:
+            return f16 ? launch_prefill_d<__half, 256>(tmap, p, max_m, stream) : launch_prefill_d<__nv_bfloat16, 256>(tmap, p, max_m, stream);
+        default:
+            return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace drkv

@@ -121,6 +121,7 @@ struct drkv_engine {
     CUtensorMap tmap_slot{};   // 4-D view, one box per 16 keys x head_dim x (K, V): the decode kernel's
     PoolLayout layout{};
     int forced_chunk = 0;
+    bool prefill_on_decode = false;   // chunk attention as one-token decodes even where the tensor-memory kernel could run
     int tail_mode = -1;        // tail split of the decode pass: -1 automatic (default), 0 off, n > 0: the last n chunks
     int num_sms = 148;
     int* d_work = nullptr;   // decode kernel's work-queue head
@@ -307,11 +308,11 @@ int drkv_create(const drkv_geometry* geom, const drkv_config* cfg, drkv_engine**
         e->scratch_bytes = need < (64u << 20) ? (64u << 20) : need;
         if ((ce = cudaMalloc(&e->d_scratch, e->scratch_bytes)) != cudaSuccess) return fail(DRKV_ERR_CUDA, "cudaMalloc(scratch)", ce);
         const char* terr = nullptr;
-        if (geom->head_dim == 128) {
+        {
             const char* perr = nullptr;
             e->has_tmap_pf = make_pool_kv16_tensor_map(&e->tmap_pf, e->pool, geom->num_layers, (int)max_pages,
                                                        geom->num_kv_heads, geom->page_size, geom->head_dim, &perr);
-            if (!e->has_tmap_pf) e->tmap_pf_err = perr ? perr : "tensor map";   // reported by the first prefill call
+            if (!e->has_tmap_pf) e->tmap_pf_err = perr ? perr : "tensor map";   // prefill then runs on the decode kernel
         }
         if (!make_pool_slot_tensor_map(&e->tmap_slot, e->pool, geom->num_layers, (int)max_pages, geom->num_kv_heads,
                                        geom->page_size, geom->head_dim, &terr)) {
@@ -680,6 +681,12 @@ int drkv_set_tail_split(drkv_engine* e, int mode) {
     NEED(e);
     if (mode < -1 || mode > 4) return set_err(DRKV_ERR_INVALID, "tail split: -1 (automatic), 0 (off) or 1..4 chunks");
     e->tail_mode = mode;
+    return DRKV_OK;
+}
+
+int drkv_set_prefill_on_decode_kernel(drkv_engine* e, int on) {
+    NEED(e);
+    e->prefill_on_decode = on != 0;
     return DRKV_OK;
 }
 
@@ -1567,7 +1574,8 @@ size_t drkv_partial_floats(const drkv_engine* e) {
     return e ? (size_t)e->geom.num_q_heads * (e->geom.head_dim + 2) : 0;
 }
 
-// Prefill attention for head dims the tensor-core kernel is not built for (64, 256): the causal rule "token t sees
+// Prefill attention without the tensor-memory kernel (a pool that one TMA descriptor cannot address, or on request:
+// drkv_set_prefill_on_decode_kernel): the causal rule "token t sees
 // keys [0, pos_start + t]" (paged_attention.cu:465-554) is a batch of m one-token decodes over one block table, which
 // the split-KV decode kernel runs as it stands: batch entry t reads the same table row and sees pos_start + t + 1
 // keys (kv_step = 1), the query rows of a GQA group share each K/V tile, every token re-reads the keys (mostly from
@@ -1595,8 +1603,10 @@ int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_
     for (int i = 0; i < n_seq; i++)
         if (seqs[i] < 0 || seqs[i] >= e->book.max_seqs() || pos_start[i] < 0 || m[i] < 0 || (m[i] > 0 && (!q[i] || !out[i])))
             return set_err(DRKV_ERR_INVALID, "attend_prefill: bad sequence entry %d", i);
-    if (g.head_dim != 128) {
-        // the tcgen05 kernel is built for head_dim 128; the other head dims take the split-KV decode kernel
+    if (!e->has_tmap_pf || e->prefill_on_decode) {
+        // no 16-key view of this pool for the tensor-memory kernel (a pool beyond what one TMA descriptor addresses),
+        // or the caller asked for it: the chunk runs on the split-KV decode kernel, a batch of one-token decodes over
+        // one block table
         note_stream(e, (cudaStream_t)stream);
         for (int i = 0; i < n_seq; i++) {
             if (m[i] == 0) continue;
@@ -1605,7 +1615,6 @@ int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_
         }
         return DRKV_OK;
     }
-    if (!e->has_tmap_pf) return set_err(DRKV_ERR_CUDA, "attend_prefill: %s", e->tmap_pf_err.c_str());
     for (int s0 = 0; s0 < n_seq; s0 += kMaxPrefillSeqs) {
         PrefillParams p{};
         p.tables = e->d_tables;

@@ -139,6 +139,8 @@ class PagedKVEngine:
     def table_stride(self) -> int: return self.lib.drkv_table_stride(self.h)
     def check_kernels(self) -> None: check(self.lib.drkv_kernel_error(self.h))
     def set_tail_split(self, mode: int) -> None: check(self.lib.drkv_set_tail_split(self.h, mode))
+    def set_prefill_on_decode_kernel(self, on: bool) -> None:
+        check(self.lib.drkv_set_prefill_on_decode_kernel(self.h, 1 if on else 0))
     def set_chunk_tokens(self, n: int) -> None: check(self.lib.drkv_set_chunk_tokens(self.h, n))
 
     def kernel_timing(self, enable: bool, read: bool = False):

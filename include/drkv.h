@@ -327,9 +327,12 @@ DRKV_API int drkv_scorer_sync(drkv_engine* e, void* stream);
 DRKV_API int drkv_scorer_scores(const drkv_engine* e, int seq, float* out, int cap);
 
 /* paged_prefill_attention_kernel (paged_attention.cu:465-554): q/out
- * [m][num_q_heads][head_dim]; token t attends keys 0..pos_start+t.  head_dim 128 runs on the tensor-core
- * (tcgen05) kernel; head_dim 64 and 256 (the reference model's own, block_pool.h:34-40) run the chunk as a
- * batch of one-token decodes on the split-KV decode kernel: same results, every token re-reads its keys. */
+ * [m][num_q_heads][head_dim]; token t attends keys 0..pos_start+t.  Runs on the tensor-core (tcgen05) kernel at
+ * head_dim 64, 128 and 256 (the reference model's own, block_pool.h:34-40).  A pool with more than 2^31 head rows,
+ * which one TMA descriptor cannot address, or an engine told so by drkv_set_prefill_on_decode_kernel(e, 1), runs
+ * the chunk as a batch of one-token decodes on the split-KV decode kernel: same results within the tolerance, every
+ * token re-reads its keys (about ten times slower). */
+DRKV_API int drkv_set_prefill_on_decode_kernel(drkv_engine* e, int on);
 DRKV_API int drkv_attend_prefill_chunk(drkv_engine* e, int layer, int seq, int pos_start, int m,
                                        const void* q, void* out, float scale, void* stream);
 /* The same for several sequences in one launch (host arrays of n_seq entries; q[i] / out[i] are

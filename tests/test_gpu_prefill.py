@@ -11,8 +11,9 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-3
 
 
-def _prefill_case(oracle, *, layers, hq, hkv, page, dtype, theta, chunks, seed, d=128, holes=0):
-    """chunks: list of chunk lengths processed in order from position 0."""
+def _prefill_case(oracle, *, layers, hq, hkv, page, dtype, theta, chunks, seed, d=128, holes=0, on_decode_kernel=False):
+    """chunks: list of chunk lengths processed in order from position 0.  on_decode_kernel: the engine is told to run
+    chunk attention as one-token decodes on the split-KV decode kernel instead of the tensor-memory kernel."""
     import torch
     from deusridet_b200 import PagedKVEngine
 
@@ -27,6 +28,7 @@ def _prefill_case(oracle, *, layers, hq, hkv, page, dtype, theta, chunks, seed, 
     g = ob.geom(layers, hq, hkv, d, page, dtype, d, theta)
     tdt = torch.float16 if dtype == ob.F16 else torch.bfloat16
     try:
+        eng.set_prefill_on_decode_kernel(on_decode_kernel)
         H.shuffled_free_stack(eng, rng)
         filler = eng.seq_create()            # so that the sequence under test is not table row 0
         seq = eng.seq_create()
@@ -96,7 +98,7 @@ def test_prefill_with_evicted_pages(drkv_lib, oracle):
 
 def test_prefill_reference_model_shape_head_dim_256(drkv_lib, oracle):
     """24 query / 4 KV heads, head_dim 256, 256-key pages, partial rotary 64: the reference's own attention shape
-    (src/memoria/block_pool.h:34-40).  Head dims other than 128 run the chunk on the split-KV decode kernel."""
+    (src/memoria/block_pool.h:34-40): one 128-row tile per CTA, O in 256 of the 512 tensor-memory columns."""
     _prefill_case(oracle, layers=2, hq=24, hkv=4, page=256, dtype=oracle.F16, theta=1e7, chunks=[300, 77, 1], seed=27,
                   d=256)
 
@@ -141,3 +143,11 @@ def test_prefill_batch_of_sequences(drkv_lib, oracle):
             assert (np.abs(got_f - want_f) <= np.maximum(TOL, H.ulp(want_f, dtype))).all(), f"sequence {i}"
     finally:
         eng.close()
+
+
+@pytest.mark.parametrize("d,hq,hkv,page", [(256, 24, 4, 256), (128, 8, 2, 16), (64, 16, 2, 32)])
+def test_prefill_on_the_decode_kernel(drkv_lib, oracle, d, hq, hkv, page):
+    """The path a pool takes that one TMA descriptor cannot address (more than 2^31 head rows), selected here by the
+    engine switch: the chunk as a batch of one-token decodes over one block table."""
+    _prefill_case(oracle, layers=1, hq=hq, hkv=hkv, page=page, dtype=oracle.BF16, theta=1e6, chunks=[200, 77, 1], seed=41,
+                  d=d, on_decode_kernel=True)
