@@ -9,7 +9,7 @@
 //     P = softmax piece (fp32 in registers, one row per thread, read from TMEM with tcgen05.ld)
 //     O += P V    tcgen05.mma  M128 x N=D x K64   (A = P in tensor memory, B = V block, MN-major)
 // with the S and O accumulators and P in tensor memory (D = 128: 2 x (64 + 128 + 64) = all 512 columns;
-// D = 256: 64 + 256 + 64 of one tile).
+// D = 256: 64 + 256 + 64 of one tile, and the tile's Q as the A operand of Q K^T in the remaining 128).
 // P is stored as a two-term split (hi + lo, 32 packed columns each); the lo term is multiplied in
 // only by CTAs whose rows see at most 1024 keys, where single-term 16-bit weights would cost more
 // than the 2e-3 bound on rows dominated by a handful of keys.  One thread per tile
@@ -52,7 +52,10 @@ template <int D>
 struct PfShape {
     static constexpr int kTiles = D <= 128 ? 2 : 1;
     static constexpr int kHalves = D / 64;                              // 64-dim (128-byte) runs of a head row
-    static constexpr int kStages = D <= 128 ? 4 : 2;                    // K/V blocks in flight
+    // At D = 256 the Q tile (64 KB) lives in tensor memory, in the 128 columns that S, O and P of the single tile leave
+    // free, as the A operand of Q K^T; shared memory then holds three 64 KB K/V stages instead of two.
+    static constexpr bool kQInTmem = D == 256;
+    static constexpr int kStages = D <= 128 ? 4 : 3;                    // K/V blocks in flight
     static constexpr int kQBytes = 128 * D * 2;                         // one Q tile: [halves][128 rows][128 B]
     static constexpr int kKBytes = kPfBlockN * D * 2;                   // K (or V) bytes of one block
     // A stage holds a block as eight "octets" of 8 keys, each [K half 0 ..][V half 0 ..] x [8 rows][128 B]: the image
@@ -62,19 +65,22 @@ struct PfShape {
     static constexpr int kOctetBytes = 2 * kHalves * 1024;
     // shared memory: byte offsets from the 1024-aligned base
     static constexpr int q = 0;                                         // the tiles
-    static constexpr int kv = q + kTiles * kQBytes;                     // stages x (K | V)
+    static constexpr int kv = q + (kQInTmem ? 0 : kTiles * kQBytes);    // stages x (K | V)
     static constexpr int pages = kv + kStages * 2 * kKBytes;            // int[kPfMaxTableSlice]
     static constexpr int holes = pages + kPfMaxTableSlice * 4;          // int[kStages]
     static constexpr int bars = holes + 16;                             // uint64[...]
-    static constexpr int n_bars = 2 * kStages + 8 + 8;
+    static constexpr int n_bars = 2 * kStages + 8 + 8 + 2;
     static constexpr int tmem = bars + n_bars * 8;                      // uint32 holder
     static constexpr int total = tmem + 16;
     // barrier indices
     static constexpr int BAR_KV_FULL = 0, BAR_KV_EMPTY = kStages, BAR_S_READY = 2 * kStages, BAR_S_FREE = BAR_S_READY + 2,
                          BAR_P_READY = BAR_S_FREE + 2, BAR_O_READY = BAR_P_READY + 2,
-                         BAR_XU = BAR_O_READY + 2;   // [warp of the tile 0..3][tile]: that warp may run its exponentials
+                         BAR_XU = BAR_O_READY + 2,   // [warp of the tile 0..3][tile]: that warp may run its exponentials
+                         BAR_Q_READY = BAR_XU + 8;   // kQInTmem: the tile's Q rows are in tensor memory
     // tensor-memory columns: S of the tiles, O of the tiles, P (hi | lo) of the tiles
     static constexpr uint32_t kColS = 0, kColO = 2 * kPfBlockN, kColP = 2 * kPfBlockN + kTiles * D;
+    // kQInTmem: dims [0, 128) of Q in columns 64..127 (beside S), dims [128, 256) in 448..511 (behind P)
+    static constexpr uint32_t kColQ0 = kPfBlockN, kColQ1 = kColP + 64;
 };
 
 
@@ -122,6 +128,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             mbar_init(bars + 8 * (Sh::BAR_O_READY + x), 1);
         }
         for (int i = 0; i < 8; i++) mbar_init(bars + 8 * (Sh::BAR_XU + i), 1);
+        mbar_init(bars + 8 * Sh::BAR_Q_READY, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap) : "memory");
     }
@@ -144,7 +151,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
     }
     // Q tiles: row r = (token t0 + X * tok_per_tile + r / g, query head kvh * g + r % g), written in the
     // K-major 128-byte-swizzled layout the MMA descriptor expects; unused rows are zero.
-    if (warp < kPfSoftmaxWarps) {
+    if (!Sh::kQInTmem && warp < kPfSoftmaxWarps) {
         const int x = warp >> 2, r = (warp & 3) * 32 + lane;
         const int t = t0 + x * tok_per_tile + r / g;
         const bool valid = r < rows_used && t < p_m;
@@ -248,7 +255,10 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 for (int kk = 0; kk < D / 16; kk++) {
                     const uint32_t off_q = ((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4;
                     const uint32_t off_k = ((kk >> 2) * 1024 + (kk & 3) * 32) >> 4;     // half, then 16 dims = 32 bytes
-                    umma_f16(d_s, mk(qa + off_q, kDescHiQ), mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
+                    if (Sh::kQInTmem)       // A = Q in tensor memory: 16 dims are 8 packed columns
+                        umma_f16_ts(d_s, tmem_base + (kk < 8 ? Sh::kColQ0 : Sh::kColQ1) + (kk & 7) * 8, mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
+                    else
+                        umma_f16(d_s, mk(qa + off_q, kDescHiQ), mk(kb + off_k, kDescHi), idesc_qk, kk > 0);
                 }
                 umma_commit(bars + 8 * (Sh::BAR_S_READY + x));
             };
@@ -272,6 +282,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             };
             // S(0)
             if (!mbar_wait(bars + 8 * (Sh::BAR_KV_FULL + 0), 0)) dead = true;
+            if (Sh::kQInTmem && !dead && !mbar_wait(bars + 8 * Sh::BAR_Q_READY, 0)) dead = true;
             if (!dead) {
                 tcgen05_fence_after();
                 issue_qk(0);
@@ -313,6 +324,27 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             float m_used = kNegBigPf, l = 0.f;
             bool dead = false;
             const bool xu_turns = tile_b_active;
+            if (Sh::kQInTmem) {
+                // this thread's Q row into tensor memory, 64 dims (32 packed columns) at a time: column c holds dims
+                // 2c and 2c + 1, as the MMA reads an A operand there; rows past the tile's tokens are zero
+                const T* src = reinterpret_cast<const T*>(p_q) + ((int64_t)t * p.num_q_heads + kvh * g + r % g) * D;
+#pragma unroll 1
+                for (int piece = 0; piece < D / 64; piece++) {
+                    uint32_t qw[32];
+#pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        Vec16 v = {{0u, 0u, 0u, 0u}};
+                        if (valid) v = ldg16(src + piece * 64 + 8 * c);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) qw[4 * c + e] = v.w[e];
+                    }
+                    tmem_st32(tmem_base + lane_base + (piece < 2 ? Sh::kColQ0 : Sh::kColQ1) + (piece & 1) * 32, qw);
+                }
+                tmem_wait_st();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bars + 8 * Sh::BAR_Q_READY);
+            }
             for (int j = 0; j < n_blocks; j++) {
                 if (!mbar_wait(bars + 8 * (Sh::BAR_S_READY + x), j & 1)) { dead = true; break; }
                 tcgen05_fence_after();
