@@ -49,6 +49,11 @@ WORKLOADS = {
     "c4": dict(layers=28, hq=28, hkv=4, d=128, page=16, n_seq=4, seq_len=32768, chunk=2048, theta=1e6,
                desc="chunked prefill: 28 layers, 28/4 heads, head_dim 128, bf16, page 16, 4 sequences x 32768 "
                     "tokens in 2048-token chunks (RoPE + scatter, then causal attention over all prior pages)"),
+    # the same at the reference's own attention shape (src/memoria/block_pool.h:34-40): 24/4 heads, head_dim 256,
+    # 256-key pages, partial rotary 64, one sequence, 16 full-attention layers
+    "c4r": dict(layers=16, hq=24, hkv=4, d=256, page=256, n_seq=1, seq_len=32768, chunk=2048, theta=1e7, rot=64,
+                desc="chunked prefill at the reference model's attention shape: 16 layers, 24/4 heads, head_dim 256, "
+                     "bf16, page 256, partial rotary 64, 1 sequence x 32768 tokens in 2048-token chunks"),
 }
 
 
@@ -696,22 +701,22 @@ def run_c5b(args):
             "gpu_launches": K * n_waves * L * (3 if args.separate_append else 2), "clocks": clocks, "e2e": None}
 
 
-def run_c4(args):
-    """Chunked prefill of 4 sequences into the paged cache (one GPU)."""
+def run_c4(args, name="c4"):
+    """Chunked prefill of the workload's sequences into the paged cache (one GPU)."""
     import torch
 
     from deusridet_b200 import PagedKVEngine, build
     build.build()
     world, rank, local = _dist_setup()
     dev = torch.device(f"cuda:{local}")
-    w = dict(WORKLOADS["c4"])
+    w = dict(WORKLOADS[name])
     if args.layers:
         w["layers"] = args.layers
     n_seq = args.seqs or w["n_seq"]
     L, hq, hkv, d, page, S, C = w["layers"], w["hq"], w["hkv"], w["d"], w["page"], w["seq_len"], w["chunk"]
     pages_per_seq = S // page
     eng = PagedKVEngine(num_layers=L, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
-                        rope_theta=w["theta"], max_pages=n_seq * pages_per_seq + 16, max_seqs=n_seq,
+                        rotary_dim=w.get("rot", d), rope_theta=w["theta"], max_pages=n_seq * pages_per_seq + 16, max_seqs=n_seq,
                         max_pages_per_seq=pages_per_seq + 1, device=local)
     rng = np.random.default_rng(17 + rank)
     pages = [eng.alloc_block() for _ in range(eng.max_blocks())]
@@ -729,7 +734,7 @@ def run_c4(args):
         seqs = [eng.seq_create() for _ in range(n_seq)]
         for pos in range(0, S, C):
             for s in seqs:
-                assert eng.ensure_blocks_for_range(s, pos, C)       # 128 new pages per sequence and chunk
+                assert eng.ensure_blocks_for_range(s, pos, C)       # C / page new pages per sequence and chunk
             eng.sync_block_table(stream)
             for l in range(L):
                 for s in seqs:
@@ -777,7 +782,7 @@ def run_c4(args):
     return {"metric": "prefill tokens/s (chunked prefill into the paged cache) + tensor TFLOP/s",
             "value": n_seq * S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": {"workload": f"c4: {w['desc']}", "layers": L, "seqs": n_seq},
+            "data": "synthetic", "config": {"workload": f"{name}: {w['desc']}", "layers": L, "seqs": n_seq},
             "roofline": {"bound": "tensor", "kernel": "attend_prefill_kernel (incl. append)", "achieved": tfs, "peak": peak,
                          "peak_kind": peak_kind, "unit": "TFLOP/s", "frac": tfs / peak, "traffic": None},
             "gpu_launches": K * n_seq * (S // C) * L * 2, "clocks": clocks, "e2e": None}
@@ -1216,8 +1221,8 @@ def main():
             if res is not None:
                 print(json.dumps(res), flush=True)
             return
-        if args.workload == "c4":
-            res = run_c4(args)
+        if args.workload in ("c4", "c4r"):
+            res = run_c4(args, args.workload)
             if rank == 0:
                 print(json.dumps(res), flush=True)
             return
