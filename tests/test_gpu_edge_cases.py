@@ -73,3 +73,20 @@ def test_prefill_group_that_does_not_divide_a_tile(drkv_lib, oracle):
     """Group 6 (24/4 heads as the reference's model, head_dim 128): 21 tokens per tile, 2 of its 128 rows unused."""
     _prefill_case(oracle, layers=1, hq=24, hkv=4, page=32, dtype=oracle.BF16, theta=1e6, chunks=[100, 43, 21, 22],
                   seed=33)
+
+
+def test_prefill_head_dim_256_across_tile_boundaries(drkv_lib, oracle):
+    """The reference's head shape (24/4 heads x 256, 256-key pages): one tile of 21 tokens per CTA; chunk lengths one
+    short of, equal to and one past a tile and a few tiles, single tokens, and starts inside a page."""
+    _prefill_case(oracle, layers=1, hq=24, hkv=4, page=256, dtype=oracle.BF16, theta=1e7, d=256,
+                  chunks=[1, 20, 21, 22, 43, 1, 127, 129, 300], seed=34)
+
+
+def test_prefill_head_dim_256_with_evicted_pages(drkv_lib, oracle):
+    _prefill_case(oracle, layers=1, hq=24, hkv=4, page=64, dtype=oracle.F16, theta=1e7, d=256, chunks=[200, 150, 90],
+                  seed=35, holes=2)
+
+
+def test_prefill_head_dim_64_across_tile_boundaries(drkv_lib, oracle):
+    _prefill_case(oracle, layers=1, hq=32, hkv=8, page=16, dtype=oracle.BF16, theta=1e4, d=64,
+                  chunks=[1, 31, 32, 33, 63, 65, 200], seed=36, holes=1)
