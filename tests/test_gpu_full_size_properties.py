@@ -166,15 +166,17 @@ def test_long_sequence_split_at_full_size(drkv_lib, oracle):
         eng.close()
 
 
-def test_chunked_prefill_at_full_size(drkv_lib, oracle):
+@pytest.mark.parametrize("hq,hkv,d,page", [(28, 4, 128, 16), (24, 4, 256, 256)], ids=["c4_shape", "reference_model_shape"])
+def test_chunked_prefill_at_full_size(drkv_lib, oracle, hq, hkv, d, page):
     """A 32 768-token sequence prefilled in 2 048-token chunks, 28/4 heads, head_dim 128, bf16, page 16 (the chunked
-    prefill configuration), one of its 28 identical layers: every chunk is appended and attended; tokens of the first,
-    a middle and the last chunk must see exactly what a decode call with that many keys sees."""
+    prefill configuration) and 24/4 heads, head_dim 256, 256-key pages (the reference model's own attention shape), one
+    of the identical layers: every chunk is appended and attended; tokens of the first, a middle and the last chunk
+    must see exactly what a decode call with that many keys sees."""
     import torch
     from deusridet_b200 import PagedKVEngine
 
     ob = oracle
-    layers, hq, hkv, d, page, S, C = 1, 28, 4, 128, 16, 32768, 2048
+    layers, S, C = 1, 32768, 2048
     n_pages = S // page
     eng = PagedKVEngine(num_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
                         rope_theta=1e6, max_pages=n_pages + 8, max_seqs=1, max_pages_per_seq=n_pages + 1, device=0)
