@@ -49,6 +49,10 @@ WORKLOADS = {
     "c4": dict(layers=28, hq=28, hkv=4, d=128, page=16, n_seq=4, seq_len=32768, chunk=2048, theta=1e6,
                desc="chunked prefill: 28 layers, 28/4 heads, head_dim 128, bf16, page 16, 4 sequences x 32768 "
                     "tokens in 2048-token chunks (RoPE + scatter, then causal attention over all prior pages)"),
+    # single-stream decode at the reference's own attention shape (src/memoria/block_pool.h:34-40)
+    "c2r": dict(layers=16, hq=24, hkv=4, d=256, page=256, n_seq=1, lo=32768, hi=32768, theta=1e7, rot=64,
+                desc="single-stream decode at the reference model's attention shape: 16 layers, 24/4 heads, head_dim "
+                     "256, bf16, page 256, partial rotary 64, one sequence of 32768 cached tokens"),
     # the same at the reference's own attention shape (src/memoria/block_pool.h:34-40): 24/4 heads, head_dim 256,
     # 256-key pages, partial rotary 64, one sequence, 16 full-attention layers
     "c4r": dict(layers=16, hq=24, hkv=4, d=256, page=256, n_seq=1, seq_len=32768, chunk=2048, theta=1e7, rot=64,
@@ -195,8 +199,8 @@ def run_ours(args):
     K, W = args.steps, args.warmup
     max_pages, width = c2_pool_pages(lens, page, K, W)
     eng = PagedKVEngine(num_layers=L, num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=page, dtype="bf16",
-                        rope_theta=w["theta"], max_pages=max_pages, max_seqs=n_seq, max_pages_per_seq=width,
-                        device=local)
+                        rotary_dim=w.get("rot", d), rope_theta=w["theta"], max_pages=max_pages, max_seqs=n_seq,
+                        max_pages_per_seq=width, device=local)
     rng = np.random.default_rng(99 + rank)
     # seeded shuffle of the pool through the public pool calls
     pages = [eng.alloc_block() for _ in range(max_pages)]
@@ -1087,7 +1091,7 @@ def cpu_pass(w, lens, steps, seed=5):
     ob.use_all_cores()                                   # torchrun exports OMP_NUM_THREADS=1
     hq, hkv, d, page = w["hq"], w["hkv"], w["d"], w["page"]
     n_seq = len(lens)
-    g = ob.geom(1, hq, hkv, d, page, ob.BF16, d, w["theta"])
+    g = ob.geom(1, hq, hkv, d, page, ob.BF16, w.get("rot", d), w["theta"])
     rng = np.random.default_rng(seed)
     pages = [(int(n) + 1 + page - 1) // page for n in lens]
     max_pages = int(np.ceil(1.1 * sum(pages)))

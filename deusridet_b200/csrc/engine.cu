@@ -85,11 +85,12 @@ int pick_chunk_by_cost(int group, long warps, bool exact, ItemsFn items) {
 
 int pick_chunk(int n_seq, int hkv, int group, int max_kv_span, long warps) {
     auto items = [&](int c) { return (long)n_seq * hkv * ((max_kv_span + c - 1) / c); };
-    if (n_seq == 1 && items(group > 4 ? 512 : 256) > warps) {
-        // One long sequence: equal items, one per warp, is a perfect partition with the fewest partials.
+    if (n_seq == 1) {
+        // One sequence: equal items, one per warp, is a perfect partition with the fewest partials, as long as an item
+        // is not shorter than the smallest chunk the cost model would pick.
         const long per_head = warps / hkv > 0 ? warps / hkv : 1;
-        const long c = (max_kv_span + per_head - 1) / per_head;
-        return (int)((c + 15) / 16 * 16);
+        const long c = ((max_kv_span + per_head - 1) / per_head + 15) / 16 * 16;
+        if (c >= 64) return (int)c;
     }
     return pick_chunk_by_cost(group, warps, false, items);
 }
