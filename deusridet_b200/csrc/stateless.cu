@@ -32,13 +32,13 @@ bool stateless_geometry_ok(const drkv_geometry* g) {
 int stateless_pick_chunk(const drkv_geometry* g, int seq_len, int num_sms) {
     const int group = g->num_q_heads / g->num_kv_heads;
     int chunk = group > 4 ? 512 : 256;
-    const long warps = (long)num_sms * 8;
+    const long warps = (long)num_sms * decode_warps_per_cta(g->head_dim);
     const long hkv = g->num_kv_heads;
-    if (hkv * ((seq_len + chunk - 1) / chunk) > warps) {
-        // long sequence: one equal item per warp, the fewest partials
+    {
+        // one equal item per warp, the fewest partials, whenever such an item keeps at least 64 keys
         const long per_head = warps / hkv > 0 ? warps / hkv : 1;
-        const long c = (seq_len + per_head - 1) / per_head;
-        return (int)((c + 15) / 16 * 16);
+        const long c = ((seq_len + per_head - 1) / per_head + 15) / 16 * 16;
+        if (c >= 64) return (int)c;
     }
     while (chunk > 64 && hkv * ((seq_len + chunk - 1) / chunk) < warps) chunk >>= 1;
     return chunk;
