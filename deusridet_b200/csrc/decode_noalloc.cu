@@ -70,7 +70,8 @@ extern "C" int drkv_k_decode_attention_noalloc(const drkv_geometry* g, const voi
     // Same chunking rule as the caller-scratch entry point; a longer sequence gets larger chunks
     // (fewer partials) until it fits, and is refused once even 4096-key chunks do not.
     int chunk = stateless_pick_chunk(g, seq_len, num_sms);
-    while (stateless_scratch_bytes(g, seq_len, chunk) > DRKV_NOALLOC_SCRATCH_BYTES && chunk < 4096) chunk <<= 1;
+    while (stateless_scratch_bytes(g, seq_len, chunk) > DRKV_NOALLOC_SCRATCH_BYTES && chunk < 4096)
+        chunk = chunk * 2 < 4096 ? chunk * 2 : 4096;
     if (stateless_scratch_bytes(g, seq_len, chunk) > DRKV_NOALLOC_SCRATCH_BYTES) {
         set_last_error("decode_attention_noalloc: seq_len x heads needs more than the built-in scratch "
                        "(DRKV_NOALLOC_SCRATCH_BYTES); use drkv_k_decode_attention with caller memory");
