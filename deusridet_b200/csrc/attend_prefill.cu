@@ -88,11 +88,21 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kPfThreads, 1)
 attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ PrefillParams p) {
     using Sh = PfShape<D>;
-    // one sequence of the batch per grid.z; sequences with fewer tiles than grid.x leave the extra CTAs idle
-    const int p_m = p.m[blockIdx.z], p_pos_start = p.pos_start[blockIdx.z], p_row = p.row[blockIdx.z];
-    if ((int)blockIdx.x * Sh::kTiles * (128 / p.group) >= p_m) return;
-    const void* const p_q = p.q[blockIdx.z];
-    void* const p_out = p.out[blockIdx.z];
+    // CTA -> work unit (tile group, KV head, sequence) and, in the split tail of the launch, the piece of its keys
+    int unit = blockIdx.x, piece = 0, pieces = 1;
+    if (unit >= p.full_units) {
+        const int tail = unit - p.full_units;
+        pieces = p.tail_pieces;
+        unit = p.full_units + tail / pieces;
+        piece = tail - (tail / pieces) * pieces;
+    }
+    const int bx = unit % p.grid_x, by = (unit / p.grid_x) % p.grid_y, bz = unit / (p.grid_x * p.grid_y);
+    // sequences with fewer tiles than grid_x leave their extra units idle
+    const int p_m = p.m[bz], p_pos_start = p.pos_start[bz], p_row = p.row[bz];
+    if (bx * Sh::kTiles * (128 / p.group) >= p_m) return;
+    const void* const p_q = p.q[bz];
+    void* const p_out = p.out[bz];
+    float* const partial = pieces > 1 ? p.partials + (size_t)(blockIdx.x - p.full_units) * Sh::kTiles * 128 * (D + 4) : nullptr;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
@@ -103,14 +113,22 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
     __shared__ int s_dead;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = p.group, kvh = blockIdx.y;
+    const int g = p.group, kvh = by;
     const int tok_per_tile = 128 / g;
     const int rows_used = tok_per_tile * g;
-    const int t0 = blockIdx.x * Sh::kTiles * tok_per_tile;              // first chunk token of tile A
+    const int t0 = bx * Sh::kTiles * tok_per_tile;                      // first chunk token of tile A
     const int t_end = min(t0 + Sh::kTiles * tok_per_tile, p_m);         // one past the last token of the CTA
     const bool tile_b_active = Sh::kTiles == 2 && t0 + tok_per_tile < p_m;
     const int kv_hi = p_pos_start + t_end;                              // keys any row of this CTA may see
-    const int n_blocks = (kv_hi + kPfBlockN - 1) / kPfBlockN;
+    const int n_blocks_all = (kv_hi + kPfBlockN - 1) / kPfBlockN;
+    // this CTA's share of the key blocks: all of them, or piece `piece` of `pieces` (the last piece gets the diagonal)
+    const int jb0 = (int)((long long)n_blocks_all * piece / pieces);
+    const int n_blocks = (int)((long long)n_blocks_all * (piece + 1) / pieces) - jb0;
+    if (n_blocks == 0) {
+        // more pieces than key blocks: nothing to do here; the merge reads l = 0 for every row of this piece
+        if (partial != nullptr && threadIdx.x < Sh::kTiles * 128) partial[(size_t)threadIdx.x * (D + 4) + D + 1] = 0.f;
+        return;
+    }
     const int n_groups = (kv_hi + 15) / 16;
     constexpr int fmt = Elem<T>::kUmmaFormat;
     const bool use_lo = kv_hi <= kPfLoTermMaxKeys;
@@ -187,7 +205,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             const int my_gi = lane & 3;
             int page = -1;
             {
-                const int grp = j * 4 + my_gi;
+                const int grp = (jb0 + j) * 4 + my_gi;
                 if (grp < n_groups) {
                     if (pages_staged) page = s_pages[grp];
                     else {
@@ -215,7 +233,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             }
             __syncwarp();
             if (lane < 4 && page >= 0) {
-                const int tok = (j * 4 + lane) * 16;
+                const int tok = ((jb0 + j) * 4 + lane) * 16;
                 // K-plane row of the group's first key, in octets of 8 rows (a multiple of 8: pages hold multiples of 16)
                 const int64_t row = (((int64_t)p.layer * p.max_pages + page) * 2) * rows_per_plane +
                                     (int64_t)kvh * p.page_size + (tok % p.page_size);
@@ -355,7 +373,7 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
                 tcgen05_fence_before();
                 __syncwarp();                                           // S(j+1) may overwrite the columns now
                 if (lane == 0) mbar_arrive(bars + 8 * (Sh::BAR_S_FREE + x));
-                const int key0 = j * kPfBlockN;
+                const int key0 = (jb0 + j) * kPfBlockN;
                 const int holes = s_holes[j % Sh::kStages];
                 // Blocks left of the diagonal with all pages present need no mask: that is almost all of them.
                 const bool unmasked = (key0 + kPfBlockN <= tile_min_limit) && holes == 0;
@@ -472,6 +490,23 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
             if (dead) {
                 atomicExch(p.error_word, (int)KERR_WAIT_FULL);
                 s_dead = 1;
+            } else if (partial != nullptr) {
+                // a piece of a split unit: the row's un-normalised O, its scale in use (log2 domain) and its sum
+                tcgen05_fence_after();
+                float* prow = partial + ((size_t)x * 128 + r) * (D + 4);
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    float ov[32];
+                    tmem_ld32(t_o + c0, ov);
+                    tmem_wait_ld();
+                    if (valid && l > 0.f) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4)
+                            *reinterpret_cast<float4*>(prow + c0 + c) = make_float4(ov[c], ov[c + 1], ov[c + 2], ov[c + 3]);
+                    }
+                }
+                prow[D] = m_used;
+                prow[D + 1] = valid ? l : 0.f;
             } else {
                 tcgen05_fence_after();
                 const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -508,12 +543,93 @@ attend_prefill_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_con
 
 namespace {
 
+// Merge of the pieces of the split tail: one warp per query row of a split unit.  out = sum_p o_p 2^(m_p - M) /
+// sum_p l_p 2^(m_p - M) with M the largest scale among the pieces that saw a key; a row no piece saw a key for is
+// left unwritten, as in the unsplit kernel.
 template <typename T, int D>
-cudaError_t launch_prefill_d(const CUtensorMap& tmap, const PrefillParams& p, int max_m, cudaStream_t stream) {
+__global__ void __launch_bounds__(128) prefill_merge_kernel(const __grid_constant__ PrefillParams p) {
+    using Sh = PfShape<D>;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int row_id = blockIdx.x * 4 + (threadIdx.x >> 5);            // (tail unit, tile, row)
+    const int r = row_id % 128, x = (row_id / 128) % Sh::kTiles, tail_unit = row_id / (128 * Sh::kTiles);
+    const int unit = p.full_units + tail_unit;
+    if (unit >= p.n_units) return;
+    const int bx = unit % p.grid_x, by = (unit / p.grid_x) % p.grid_y, bz = unit / (p.grid_x * p.grid_y);
+    const int g = p.group, tok_per_tile = 128 / g;
+    const int t = (bx * Sh::kTiles + x) * tok_per_tile + r / g;
+    if (r >= tok_per_tile * g || t >= p.m[bz]) return;
+    const float* base = p.partials + ((size_t)tail_unit * p.tail_pieces * Sh::kTiles + x) * 128 * (D + 4) + (size_t)r * (D + 4);
+    const size_t piece_stride = (size_t)Sh::kTiles * 128 * (D + 4);
+    float M = -INFINITY;
+    for (int q = 0; q < p.tail_pieces; q++) {
+        const float* pr = base + q * piece_stride;
+        if (pr[D + 1] > 0.f) M = fmaxf(M, pr[D]);
+    }
+    if (M == -INFINITY) return;
+    constexpr int PER = D / 32;                                        // dims per lane
+    float acc[PER], L = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; i++) acc[i] = 0.f;
+    for (int q = 0; q < p.tail_pieces; q++) {
+        const float* pr = base + q * piece_stride;
+        const float lq = pr[D + 1];
+        if (!(lq > 0.f)) continue;
+        const float w = fast_exp2(pr[D] - M);
+        L += lq * w;
+#pragma unroll
+        for (int i = 0; i < PER; i++) acc[i] += pr[lane * PER + i] * w;
+    }
+    T* orow = reinterpret_cast<T*>(p.out[bz]) + ((int64_t)t * p.num_q_heads + by * g + r % g) * D + lane * PER;
+    const float inv = 1.f / L;
+#pragma unroll
+    for (int i = 0; i < PER; i += 2) *reinterpret_cast<uint32_t*>(orow + i) = Elem<T>::pack2(acc[i] * inv, acc[i + 1] * inv);
+}
+
+}  // namespace
+
+namespace {
+
+// Pieces per unit of the tail (1: no split): the choice that makes the tail's CTAs fill whole waves of `sms` best,
+// with a small charge per piece for its start-up, its partial and the merge.
+int pick_tail_pieces(int tail_units, int sms) {
+    if (tail_units <= 0) return 1;
+    int best = 1;
+    double best_cost = 1e30;
+    for (int pc = 1; pc <= 8; pc++) {
+        const int ctas = tail_units * pc;
+        const double cost = (double)((ctas + sms - 1) / sms) / pc + (pc > 1 ? 0.03 + 0.01 * pc : 0.0);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = pc;
+        }
+    }
+    return best;
+}
+
+template <typename T, int D>
+cudaError_t launch_prefill_d(const CUtensorMap& tmap, PrefillParams p, int max_m, int num_sms, float* scratch,
+                             size_t scratch_bytes, cudaStream_t stream) {
     using Sh = PfShape<D>;
     constexpr size_t smem = 1024 + Sh::total;
     const int tok_per_cta = Sh::kTiles * (128 / p.group);
-    dim3 grid((max_m + tok_per_cta - 1) / tok_per_cta, p.num_kv_heads, p.n_seq);
+    p.grid_x = (max_m + tok_per_cta - 1) / tok_per_cta;
+    p.grid_y = p.num_kv_heads;
+    p.n_units = p.grid_x * p.grid_y * p.n_seq;
+    // whole waves of one CTA per unit, then the remainder cut into pieces along the keys
+    const int sms = num_sms > 0 ? num_sms : 1;
+    int tail_units = p.n_units % sms;
+    p.tail_pieces = scratch != nullptr ? pick_tail_pieces(tail_units, sms) : 1;
+    const size_t per_cta = (size_t)Sh::kTiles * 128 * (D + 4) * sizeof(float);
+    while (p.tail_pieces > 1 && (size_t)tail_units * p.tail_pieces * per_cta > scratch_bytes) p.tail_pieces--;
+    if (p.tail_pieces <= 1) {
+        p.tail_pieces = 1;
+        tail_units = 0;
+    }
+    p.full_units = p.n_units - tail_units;
+    p.partials = scratch;
+    const int ctas = p.full_units + tail_units * p.tail_pieces;
     static std::atomic<bool> configured[64];      // per instantiation and device; any thread may be the first caller
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -523,29 +639,34 @@ cudaError_t launch_prefill_d(const CUtensorMap& tmap, const PrefillParams& p, in
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
-    return launch_pdl(attend_prefill_kernel<T, D>, grid, dim3(kPfThreads), smem, stream, tmap, p);
+    e = launch_pdl(attend_prefill_kernel<T, D>, dim3(ctas), dim3(kPfThreads), smem, stream, tmap, p);
+    if (e != cudaSuccess || tail_units == 0) return e;
+    const int rows = tail_units * Sh::kTiles * 128;
+    return launch_pdl(prefill_merge_kernel<T, D>, dim3((rows + 3) / 4), dim3(128), 0, stream, p);
 }
 
 }  // namespace
 
-cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
-                                  cudaStream_t stream) {
+cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype, int num_sms,
+                                  float* scratch, size_t scratch_bytes, cudaStream_t stream) {
     if (p.n_seq <= 0) return cudaSuccess;
     if (p.group < 1 || p.group > 16 || p.page_size % 16 != 0) return cudaErrorInvalidValue;
     int max_m = 0;
     for (int i = 0; i < p.n_seq; i++) max_m = p.m[i] > max_m ? p.m[i] : max_m;
     if (max_m <= 0 || p.n_seq > kMaxPrefillSeqs) return max_m <= 0 ? cudaSuccess : cudaErrorInvalidValue;
     const bool f16 = dtype == DRKV_DTYPE_F16;
+#define DRKV_PF_CASE(DIM)                                                                                             \
+    case DIM:                                                                                                          \
+        return f16 ? launch_prefill_d<__half, DIM>(tmap, p, max_m, num_sms, scratch, scratch_bytes, stream)            \
+                   : launch_prefill_d<__nv_bfloat16, DIM>(tmap, p, max_m, num_sms, scratch, scratch_bytes, stream);
     switch (head_dim) {
-        case 64:
-            return f16 ? launch_prefill_d<__half, 64>(tmap, p, max_m, stream) : launch_prefill_d<__nv_bfloat16, 64>(tmap, p, max_m, stream);
-        case 128:
-            return f16 ? launch_prefill_d<__half, 128>(tmap, p, max_m, stream) : launch_prefill_d<__nv_bfloat16, 128>(tmap, p, max_m, stream);
-        case 256:
-            return f16 ? launch_prefill_d<__half, 256>(tmap, p, max_m, stream) : launch_prefill_d<__nv_bfloat16, 256>(tmap, p, max_m, stream);
+        DRKV_PF_CASE(64)
+        DRKV_PF_CASE(128)
+        DRKV_PF_CASE(256)
         default:
             return cudaErrorInvalidValue;
     }
+#undef DRKV_PF_CASE
 }
 
 }  // namespace drkv

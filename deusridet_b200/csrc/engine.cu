@@ -1636,7 +1636,8 @@ int drkv_attend_prefill_batch(drkv_engine* e, int layer, int n_seq, const int32_
         p.page_size = g.page_size;
         p.scale_log2 = scale * 1.4426950408889634f;
         p.error_word = e->d_error;
-        CUDA_TRY(launch_attend_prefill(e->tmap_pf, p, g.head_dim, g.dtype, (cudaStream_t)stream));
+        CUDA_TRY(launch_attend_prefill(e->tmap_pf, p, g.head_dim, g.dtype, e->num_sms, e->d_scratch, e->scratch_bytes,
+                                       (cudaStream_t)stream));
     }
     return DRKV_OK;
 }

@@ -100,6 +100,11 @@ struct PrefillParams {
     int layer, max_pages, num_q_heads, num_kv_heads, group, page_size;
     float scale_log2;
     int* error_word;
+    // Work units are (tile group of tokens, KV head, sequence), numbered x fastest.  The launch has one CTA per unit
+    // for the first full_units of them; each of the remaining ones (what would be a partly filled last wave of CTAs)
+    // is cut along the keys into tail_pieces CTAs that write un-normalised partials, merged by a second kernel.
+    int grid_x, grid_y, n_units, full_units, tail_pieces;
+    float* partials;          // [(unit - full_units) * tail_pieces + piece][tile][128 rows][head_dim + 4]: o, m (log2), l, 2 unused (rows stay 16-byte aligned)
 };
 
 // Cross-GPU merge of one sequence's split-KV partials by peer stores, the tail of the merge kernel
@@ -159,8 +164,9 @@ int decode_warps_per_cta(int head_dim, bool family_blocks = false);
 // landing in 8-row groups of 128 bytes ordered [octet of 8 keys][plane][half].
 bool make_pool_kv16_tensor_map(CUtensorMap* out, const void* pool, int num_layers, int max_pages,
                                int num_kv_heads, int page_size, int head_dim, const char** err);
-cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype,
-                                  cudaStream_t stream);
+// scratch / scratch_bytes: device memory for the partials of a split tail (none: no split); num_sms sizes the waves
+cudaError_t launch_attend_prefill(const CUtensorMap& tmap, const PrefillParams& p, int head_dim, int dtype, int num_sms,
+                                  float* scratch, size_t scratch_bytes, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& p, int n_seq, int dtype, cudaStream_t stream);
 
 // Merges partials that already sit in the external layout (drkv_attend_partial).
