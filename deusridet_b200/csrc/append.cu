@@ -29,7 +29,7 @@ append_rope_kernel(AppendParams p) {
     int row, pos;
     if (p.rows != nullptr) {
         row = p.rows[tok];
-        pos = p.pos[tok] + p.pos_bias;
+        pos = p.pos[tok];
     } else {
         row = p.row;
         pos = (p.pos != nullptr ? p.pos[0] : p.pos_start) + tok;

@@ -112,7 +112,9 @@ __device__ __forceinline__ void split_pack(float p0, float p1, uint32_t& hi, uin
 // in flight meanwhile.  When the item's last group has landed, the staged rows replace the row of the K and V
 // tiles that the gather brought from the pool (stale there, or racing with the store above).  Kept out of line so
 // that the main loop's register allocation does not see the fp64 sine/cosine evaluation.
-template <typename T, int D>
+// STAGE_V = false (head_dim 256, where shared memory has room for the K row only): the V row is not staged; it goes
+// from its source to the pool here and from its source into the V tile later (it is not rotated, so both are copies).
+template <typename T, int D, bool STAGE_V>
 __device__ __noinline__ void fused_append_prepare(const T* ksrc, const T* vsrc, T* pool_krow, int64_t plane_elems,
                                                   const float* inv_freq, int rotary_dim, uint8_t* stage, int pos, int lane) {
     const int half = rotary_dim >> 1;
@@ -126,13 +128,15 @@ __device__ __noinline__ void fused_append_prepare(const T* ksrc, const T* vsrc, 
         krow[i + half] = Elem<T>::from_f(y1);
     }
     for (int d = rotary_dim + lane; d < D; d += 32) krow[d] = ksrc[d];
-    for (int c = lane; c < D / 8; c += 32) *reinterpret_cast<Vec16*>(stage + D * 2 + 16 * c) = ldg16(vsrc + 8 * c);
+    if (STAGE_V)
+        for (int c = lane; c < D / 8; c += 32) *reinterpret_cast<Vec16*>(stage + D * 2 + 16 * c) = ldg16(vsrc + 8 * c);
     __syncwarp();
     if (pool_krow != nullptr) {
         // the token's pool rows: the V plane of a page starts plane_elems after its K plane
         for (int c = lane; c < 2 * (D / 8); c += 32) {
             const int pl = c / (D / 8), cc = c - pl * (D / 8);
-            stg16(pool_krow + pl * plane_elems + 8 * cc, *reinterpret_cast<const Vec16*>(stage + pl * (D * 2) + 16 * cc));
+            const Vec16 v = (pl && !STAGE_V) ? ldg16(vsrc + 8 * cc) : *reinterpret_cast<const Vec16*>(stage + pl * (D * 2) + 16 * cc);
+            stg16(pool_krow + pl * plane_elems + 8 * cc, v);
         }
     }
 }
@@ -177,7 +181,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
     int* cum = reinterpret_cast<int*>(bars + WARPS * DEPTH);                           // [n_seq + 1]
     __shared__ int s_warp_tot[WARPS];
     __shared__ ItemMeta s_items[WARPS][kItemEntries];
-    __shared__ __align__(16) uint8_t s_new_kv[SPLIT ? 1 : WARPS][SPLIT ? 16 : 2 * D * 2];   // fused append: a warp's new K row, V row
+    __shared__ __align__(16) uint8_t s_new_kv[WARPS][SPLIT ? D * 2 : 2 * D * 2];   // fused append: a warp's new K row (and V row)
 
     const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
     const uint32_t bar_full = smem_u32(bars);
@@ -477,7 +481,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                     im.part_slot = (EXT && c_fam) ? c_slot : (c_b * p.num_q_heads + c_kvh * p.group) * slot_stride + c_slot;
                     im.fam = c_fam;
                     im.tok_hi = c_tok_hi;
-                    im.append = (!SPLIT && c_end && p.k_new != nullptr) ? 1 : 0;
+                    im.append = (c_end && p.k_new != nullptr) ? 1 : 0;
                     im.trow = c_trow;
                     im.pad2 = 0;
                     s_items[w][c_item] = im;
@@ -488,7 +492,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
                                      ((int64_t)c_b * p.num_q_heads + (int64_t)c_kvh * p.group) * (D * (int)sizeof(T));
                     if (lane * 128 < p.group * D * (int)sizeof(T))
                         asm volatile("prefetch.global.L1 [%0];" ::"l"(qb + lane * 128));
-                    if (!SPLIT && c_end && p.k_new != nullptr && lane < 2 * (D * (int)sizeof(T) / 128)) {
+                    if (c_end && p.k_new != nullptr && lane < 2 * (D * (int)sizeof(T) / 128)) {
                         // the new token's K and V rows, which this item will append when it starts
                         const int64_t src = ((int64_t)c_b * p.num_kv_heads + c_kvh) * (D * (int)sizeof(T));
                         const int hl = D * (int)sizeof(T) / 128;                 // 128-byte lines per row
@@ -556,7 +560,7 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
 #pragma unroll
                 for (int j = 0; j < 2 * NR; j++) o[i][j] = 0.f;
         }
-        if (!SPLIT && (meta.flags & SLOT_FIRST) && item->append) {
+        if ((meta.flags & SLOT_FIRST) && item->append) {
             // this item ends at its sequence's new token: rotate and stage the token's rows now, while the item's
             // first gathers are in flight, and write them into the pool page (nothing if the table has a hole there)
             const int pos = item->tok_hi - 1;
@@ -567,9 +571,9 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             const int64_t plane = rows_per_plane * D;           // elements of one plane of a page
             // element offset of (layer, page, K plane, kv head, slot of the token, 0)
             const int64_t krow = ((int64_t)(layer_page0 + page) * 2) * plane + ((int64_t)item->kvh * p.page_size + pos % p.page_size) * D;
-            fused_append_prepare<T, D>(reinterpret_cast<const T*>(p.k_new) + src, reinterpret_cast<const T*>(p.v_new) + src,
-                                       page >= 0 ? reinterpret_cast<T*>(p.pool) + krow : nullptr, plane, p.inv_freq, p.rotary_dim,
-                                       &s_new_kv[SPLIT ? 0 : w][0], pos, lane);
+            fused_append_prepare<T, D, !SPLIT>(reinterpret_cast<const T*>(p.k_new) + src, reinterpret_cast<const T*>(p.v_new) + src,
+                                               page >= 0 ? reinterpret_cast<T*>(p.pool) + krow : nullptr, plane, p.inv_freq,
+                                               p.rotary_dim, &s_new_kv[w][0], pos, lane);
         }
         if (!(meta.flags & SLOT_SKIP)) {
             // keys [v_lo, v_hi) of the 16 in the slot are visible: all of them except in an item's end groups
@@ -580,12 +584,15 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             }
             uint8_t* kt = smem + ring * SLOT_BYTES;
             uint8_t* vt = kt + TILE_BYTES;              // SPLIT: set once the V entry has landed
-            if (!SPLIT && (meta.flags & SLOT_LAST) && item->append) {
+            const bool patch_new = (meta.flags & SLOT_LAST) && item->append;
+            if (patch_new) {
                 // the last key of the item is the sequence's new token: its rows come from the warp's staging area
-                // (see fused_append_prepare), whatever the gather found at that slot of the page
+                // (see fused_append_prepare), whatever the gather found at that slot of the page.  With K and V in
+                // separate ring entries only the K row is staged and patched here; the V row follows once its entry
+                // has landed.
                 const int row = item->tok_hi - 1 - meta.tok0;
-                const uint8_t* stage = &s_new_kv[SPLIT ? 0 : w][0];
-                for (int c = lane; c < 2 * (D / 8); c += 32) {
+                const uint8_t* stage = &s_new_kv[w][0];
+                for (int c = lane; c < (SPLIT ? 1 : 2) * (D / 8); c += 32) {
                     const int pl = c / (D / 8), cc = c - pl * (D / 8);
                     *reinterpret_cast<Vec16*>((pl ? vt : kt) + swz_seg16(row, cc)) =
                         *reinterpret_cast<const Vec16*>(stage + pl * (D * 2) + 16 * cc);
@@ -663,6 +670,14 @@ attend_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParam
             if (SPLIT) {
                 if (!next_entry()) break;
                 vt = smem + (w * DEPTH + slot) * SLOT_BYTES;
+                if (patch_new) {
+                    // the new token's V row, straight from its source (it is not rotated)
+                    const int row = item->tok_hi - 1 - meta.tok0;
+                    const T* vsrc = reinterpret_cast<const T*>(p.v_new) + ((int64_t)item->b * p.num_kv_heads + item->kvh) * D;
+                    for (int c = lane; c < D / 8; c += 32) *reinterpret_cast<Vec16*>(vt + swz_seg16(row, c)) = ldg16(vsrc + 8 * c);
+                    __syncwarp();
+                    zero_filled = true;
+                }
                 zero_hidden_rows();
             }
             if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {

@@ -969,10 +969,6 @@ int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_ro
     return DRKV_OK;
 }
 
-// Head dim 256 keeps K and V of a group in separate ring entries of the decode kernel; there the new token goes
-// through the append kernel first (same bytes, one more launch).
-static bool fused_append_supported(const drkv_engine* e) { return e->geom.head_dim != 256; }
-
 int drkv_append_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows, const int32_t* d_kv_len,
                               int max_kv_len, const void* k_src, const void* v_src, const void* q, void* out, float scale,
                               void* stream) {
@@ -982,17 +978,8 @@ int drkv_append_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_
         max_kv_len < 0)
         return set_err(DRKV_ERR_INVALID, "append_attend_decode: bad argument");
     if (n_seq == 0 || max_kv_len == 0) return DRKV_OK;
-    const bool fused = fused_append_supported(e);
-    if (!fused) {
-        note_stream(e, (cudaStream_t)stream);
-        AppendParams ap = append_params(e, layer);
-        ap.rows = d_rows;
-        ap.pos = d_kv_len;
-        ap.pos_bias = -1;                   // the new token sits at kv_len - 1
-        ap.k_src = k_src;
-        ap.v_src = v_src;
-        CUDA_TRY(launch_append_rope(ap, n_seq, e->geom.dtype, (cudaStream_t)stream));
-    }
+    // every head dim appends inside the decode kernel (at head dim 256, whose ring holds K and V of a group in separate
+    // entries, the K row is staged and the V row taken from its source)
     const size_t q_bytes = (size_t)e->geom.num_q_heads * e->geom.head_dim * 2;
     const size_t kv_bytes = (size_t)e->geom.num_kv_heads * e->geom.head_dim * 2;
     for (int s0 = 0; s0 < n_seq; s0 += kMaxDecodeSeqs) {
@@ -1000,8 +987,7 @@ int drkv_append_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_
         int rc = decode_common(e, layer, n, d_rows + s0, d_kv_len + s0, 0, 0, 0, max_kv_len,
                                (const char*)q + s0 * q_bytes, (char*)out + s0 * q_bytes, nullptr, scale,
                                (cudaStream_t)stream, nullptr, nullptr, 0,
-                               fused ? (const char*)k_src + s0 * kv_bytes : nullptr,
-                               fused ? (const char*)v_src + s0 * kv_bytes : nullptr);
+                               (const char*)k_src + s0 * kv_bytes, (const char*)v_src + s0 * kv_bytes);
         if (rc != DRKV_OK) return rc;
     }
     return DRKV_OK;
@@ -1198,19 +1184,8 @@ int drkv_append_attend_decode_planned(drkv_engine* e, int layer, const void* k_s
     const drkv_engine::Plan& pl = e->plan;
     if (!pl.valid) return set_err(DRKV_ERR_INVALID, "append_attend_decode_planned: no decode plan");
     if (pl.n_seq == 0 || pl.max_chunks == 0) return DRKV_OK;
-    const bool fused = fused_append_supported(e);
-    if (!fused) {
-        note_stream(e, (cudaStream_t)stream);
-        AppendParams ap = append_params(e, layer);
-        ap.rows = pl.rows;
-        ap.pos = pl.kv_len;
-        ap.pos_bias = -1;                   // the new token sits at kv_len - 1
-        ap.k_src = k_src;
-        ap.v_src = v_src;
-        CUDA_TRY(launch_append_rope(ap, pl.n_seq, e->geom.dtype, (cudaStream_t)stream));
-    }
     return decode_common(e, layer, pl.n_seq, pl.rows, pl.kv_len, 0, 0, 0, pl.max_chunks * pl.chunk, q, out, nullptr,
-                         scale, (cudaStream_t)stream, &pl, nullptr, 0, fused ? k_src : nullptr, fused ? v_src : nullptr);
+                         scale, (cudaStream_t)stream, &pl, nullptr, 0, k_src, v_src);
 }
 
 // ---- storage tier --------------------------------------------------------------------------
@@ -1543,8 +1518,8 @@ static int attend_exchange(drkv_engine* e, int layer, int seq, int kv_begin, int
     p.parity = (int)(p.seq_no & 1u);
     p.wait_ns = x.wait_ns;
     p.error_word = e->d_error;
-    if (k_src != nullptr && (kv_end <= kv_begin || !fused_append_supported(e))) {
-        // nothing of this rank's range to attend, or head dim 256: the token goes through the append kernel
+    if (k_src != nullptr && kv_end <= kv_begin) {
+        // nothing of this rank's range to attend: the token goes through the append kernel
         if (kv_end < 1) return set_err(DRKV_ERR_INVALID, "append_attend_exchange: no position to append at");
         note_stream(e, (cudaStream_t)stream);
         AppendParams ap = append_params(e, layer);

@@ -16,7 +16,6 @@ struct AppendParams {
     int table_stride;
     const int32_t* rows;     // per token table row, or nullptr: all tokens use `row`
     const int32_t* pos;      // per token position (rows != nullptr) or one device int (rows == nullptr)
-    int pos_bias;            // added to every position read from `pos` (-1: `pos` holds lengths that include the token)
     int row, pos_start;      // used when rows == nullptr (pos_start only if pos == nullptr)
     int layer;
     int rotary_dim;          // 0 = plain copy

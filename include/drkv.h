@@ -229,9 +229,9 @@ DRKV_API int drkv_attend_decode(drkv_engine* e, int layer, int n_seq, const int3
 /* The decode step of one layer in one call: paged_kv_cache_write + rope_kernel's K half + paged_gqa_decode_attention
  * (paged_attention.cu:353-367 runs them as three launches).  d_kv_len[i] counts the new token: it is appended at
  * position d_kv_len[i] - 1 of table row d_rows[i] from k_src / v_src [n_seq][num_kv_heads][head_dim] and attended
- * to with the rest.  For head dims 64 and 128 there is no append launch: the work item of the attention kernel that
+ * to with the rest.  There is no append launch: the work item of the attention kernel that
  * reaches the new position rotates K, uses both rows from the caller's buffers and writes them into the page (the
- * same bytes drkv_append_rope writes); head dim 256 runs the append kernel first.  A hole at the new position
+ * same bytes drkv_append_rope writes).  A hole at the new position
  * writes nothing, as in drkv_append_rope. */
 DRKV_API int drkv_append_attend_decode(drkv_engine* e, int layer, int n_seq, const int32_t* d_rows,
                                        const int32_t* d_kv_len, int max_kv_len, const void* k_src, const void* v_src,

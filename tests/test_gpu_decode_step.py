@@ -13,7 +13,7 @@ TOL = 2e-3  # max-abs on attention outputs: fp16/bf16 out, fp32 accumulate
 def _decode_case(oracle, *, layers, hq, hkv, d, page, dtype, theta, lens, seed, pool_slack=1.1, rot=None,
                  chunk=0, holes=0, fused=False, holes_first_only=False):
     """fused: the step goes through drkv_append_attend_decode (the new token is appended by the attention kernel's
-    own work item, or by the append kernel in front of it at head_dim 256) instead of the two separate calls."""
+    own work item) instead of the two separate calls."""
     import torch
     from deusridet_b200 import PagedKVEngine
 
@@ -185,7 +185,7 @@ def test_fused_append_head_dim_64(drkv_lib, oracle):
                  fused=True)
 
 
-def test_fused_append_head_dim_256_takes_the_append_kernel(drkv_lib, oracle):
+def test_fused_append_head_dim_256(drkv_lib, oracle):
     _decode_case(oracle, layers=1, hq=24, hkv=4, d=256, page=256, dtype=oracle.F16, theta=1e7, lens=[1000, 300],
                  seed=6, rot=64, fused=True)
 

@@ -127,7 +127,7 @@ def test_planned_pass_matches_checker_and_per_sequence_pass(drkv_lib, oracle, ca
 def test_planned_pass_with_the_append_in_the_same_call(drkv_lib, oracle, case):
     """Every branch decodes one token: room is reserved (copy-on-write of a shared partial tail page), the plan
     counts the token, and one call per layer appends it and attends.  Pool bytes must equal the checker's append
-    bit for bit and the outputs its attention within 2e-3; head_dim 256 takes the append kernel in front."""
+    bit for bit and the outputs its attention within 2e-3."""
     import torch
     from deusridet_b200 import PagedKVEngine
 
